@@ -1,0 +1,141 @@
+/*
+ * C ABI of libmxfp6_b200.so: the W6A8 (packed MXFP6 E3M2 weights x MXFP8 E4M3
+ * activations, UE8M0 scale per 32 K values) kernel library for NVIDIA B200
+ * (sm_100a).
+ *
+ * Conventions
+ *  - every pointer named *_dev or documented as "device" is a device pointer on
+ *    the CUDA device that is current when the call is made;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *  - calls only enqueue work; they never synchronise unless stated;
+ *  - the return value is 0 on success; otherwise mxfp6_b200_last_error() returns a
+ *    thread-local message (the reference raises TORCH_CHECK errors at the same
+ *    places, e.g. csrc/torch_extension.cu:1769-1845);
+ *  - dtype codes: 0 = float16, 1 = bfloat16.
+ *
+ * Each entry point names the reference operator it stands in for
+ * (file:line inside Nekofish-L/mxfp6_sm120).
+ */
+#ifndef MXFP6_B200_H_
+#define MXFP6_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MXFP6_B200_ABI_VERSION 1
+
+#define MXFP6_DTYPE_F16 0
+#define MXFP6_DTYPE_BF16 1
+
+#define MXFP6_OK 0
+#define MXFP6_ERR_INVALID_ARGUMENT 1
+#define MXFP6_ERR_CUDA 2
+#define MXFP6_ERR_UNSUPPORTED 3
+#define MXFP6_ERR_DEVICE_TIMEOUT 4
+#define MXFP6_ERR_WORKSPACE 5
+
+int mxfp6_b200_abi_version(void);
+const char* mxfp6_b200_last_error(void);
+
+/* Synchronises the current device and reads the status word that kernels with
+ * bounded waits write when a wait expires (0 = none did).  `reset` != 0 clears it. */
+int mxfp6_b200_device_status(int* value, int reset);
+
+/* ---- layout utilities ------------------------------------------------- */
+
+/* torch.ops.mxfp6.pack_fp6 (csrc/torch_extension.cu:2121-2156, kernels
+ * csrc/packing.cu:93-160): n codes (n % 4 == 0) -> n*3/4 bytes. */
+int mxfp6_pack_fp6(const uint8_t* codes_dev, int64_t n, uint8_t* packed_dev, void* stream);
+/* torch.ops.mxfp6.unpack_fp6 (csrc/packing.cu:162-200). */
+int mxfp6_unpack_fp6(const uint8_t* packed_dev, int64_t rows, int64_t k, uint8_t* codes_dev,
+                     void* stream);
+/* torch.ops.mxfp6.pad_fp6 (csrc/packing.cu:202-218): every 12 bytes -> 16 bytes. */
+int mxfp6_pad_fp6(const uint8_t* packed_dev, int64_t bytes, uint8_t* padded_dev, void* stream);
+/* torch.ops.mxfp6.expand_fp6_to_fp8 (csrc/packing.cu:61-89,220-237). */
+int mxfp6_expand_fp6_to_fp8(const uint8_t* packed_dev, int64_t rows, int64_t k,
+                            uint8_t* e4m3_dev, void* stream);
+/* torch.ops.mxfp6.pack_scales / unpack_scales (csrc/packing.cu:239-283): logical
+ * [rows, k/32] <-> packed ceil128(rows) * ceil4(k/32) bytes, padding = 0x7f. */
+int mxfp6_pack_scales(const uint8_t* logical_dev, int64_t rows, int64_t k, uint8_t* packed_dev,
+                      void* stream);
+int mxfp6_unpack_scales(const uint8_t* packed_dev, int64_t rows, int64_t k,
+                        uint8_t* logical_dev, void* stream);
+int64_t mxfp6_packed_scale_bytes(int64_t rows, int64_t k);
+/* torch.ops.mxfp6.pack_grouped_scales (csrc/moe.cu:4206-4224,4790-4826):
+ * scale_offsets[e] = sum of ceil128(rows of experts before e). */
+int mxfp6_grouped_scale_offsets(const int64_t* expert_offsets_dev, int experts,
+                                int64_t* scale_offsets_dev, void* stream);
+int mxfp6_pack_grouped_scales(const uint8_t* logical_dev, const int64_t* expert_offsets_dev,
+                              const int64_t* scale_offsets_dev, int experts,
+                              int64_t padded_rows, int64_t k, uint8_t* packed_dev, void* stream);
+
+/* ---- quantizers --------------------------------------------------------- */
+
+/* torch.ops.mxfp6.quantize_mxfp8 / _logical / _dual / _dual_out
+ * (csrc/quantization.cu:70-191,247-404).  Either scale output may be NULL. */
+int mxfp6_quantize_mxfp8(const void* input_dev, int dtype, int64_t rows, int64_t k,
+                         uint8_t* values_dev, uint8_t* packed_scales_dev,
+                         uint8_t* logical_scales_dev, void* stream);
+/* torch.ops.mxfp6.quantize_mxfp6 (csrc/quantization.cu:193-243,406-409):
+ * values are the packed 6-bit stream (rows * k * 3/4 bytes). */
+int mxfp6_quantize_mxfp6(const void* input_dev, int dtype, int64_t rows, int64_t k,
+                         uint8_t* values_dev, uint8_t* packed_scales_dev,
+                         uint8_t* logical_scales_dev, void* stream);
+
+/* ---- dense W6A8 GEMM ------------------------------------------------------ */
+
+/* torch.ops.mxfp6.gemm_w6a8 (csrc/torch_extension.cu:1769-1845):
+ * out[m, n] = alpha * A8[m, k] x W6[n, k]^T.  m > 0, n % 8 == 0, k % 128 == 0.
+ * Split-K scratch comes from the per-device workspace arena (below). */
+int mxfp6_gemm_w6a8(const uint8_t* a_values_dev, const uint8_t* a_scales_dev,
+                    const uint8_t* w_values_dev, const uint8_t* w_scales_dev, int64_t m,
+                    int64_t n, int64_t k, float alpha, void* out_dev, int out_dtype,
+                    void* stream);
+/* Same with an explicit tile/split choice and caller-owned scratch
+ * (tile_tokens / splits = 0 selects from the built-in table; the stand-in for
+ * torch.ops.mxfp6.gemm_w6a8_config, csrc/torch_extension.cu:1847-1867).  When the
+ * chosen plan splits K, scratch_dev must hold mxfp6_gemm_w6a8_scratch_bytes()
+ * bytes whose trailing counter region was zeroed once. */
+int mxfp6_gemm_w6a8_ex(const uint8_t* a_values_dev, const uint8_t* a_scales_dev,
+                       const uint8_t* w_values_dev, const uint8_t* w_scales_dev, int64_t m,
+                       int64_t n, int64_t k, float alpha, void* out_dev, int out_dtype,
+                       int tile_tokens, int splits, void* scratch_dev, size_t scratch_bytes,
+                       void* stream);
+/* Plan query: fills tile_tokens, splits, stages, grid, partial bytes, counter bytes. */
+int mxfp6_gemm_w6a8_plan(int64_t m, int64_t n, int64_t k, int tile_tokens, int splits,
+                         int64_t out_plan[6]);
+/* torch.ops.mxfp6.gemm_from_float (csrc/torch_extension.cu:1869-1925): quantize the
+ * FP16/BF16 activation to MXFP8 into caller-provided staging buffers
+ * (m*k bytes and mxfp6_packed_scale_bytes(m, k) bytes), then run the GEMM. */
+int mxfp6_gemm_from_float(const void* a_dev, int a_dtype, const uint8_t* w_values_dev,
+                          const uint8_t* w_scales_dev, int64_t m, int64_t n, int64_t k,
+                          float alpha, void* out_dev, int out_dtype, uint8_t* a_values_stage_dev,
+                          uint8_t* a_scales_stage_dev, void* stream);
+
+/* ---- split-K workspace arena ----------------------------------------------
+ * torch.ops.mxfp6.begin_workspace_planning / finalize_workspace_planning /
+ * workspace_stats / workspace_barriers_zero (csrc/torch_extension.cu:1955-2116).
+ * While planning, launches record the scratch they need and use a transient
+ * stream-ordered allocation.  finalize freezes the capacity; afterwards each
+ * stream gets one persistent lane on its first eager launch and a launch that
+ * is being captured on a stream without a lane fails. */
+int mxfp6_workspace_begin_planning(void);
+int mxfp6_workspace_finalize_planning(void* stream, int64_t out_stats[10]);
+/* stats, in the order of the reference's dictionary
+ * (csrc/torch_extension.cu:1965-1991): [0] layouts, [1] max_reduction_bytes,
+ * [2] max_barrier_bytes, [3] arena_bytes, [4] lanes, [5] total_arena_bytes,
+ * [6] planning, [7] frozen, [8] persistent_launches, [9] fallback_launches */
+int mxfp6_workspace_stats(int64_t out_stats[10]);
+int mxfp6_workspace_barriers_zero(int* all_zero);
+/* Drops every lane and returns the arena to its initial state (test helper). */
+int mxfp6_workspace_reset(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MXFP6_B200_H_ */

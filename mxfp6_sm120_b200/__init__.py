@@ -1,0 +1,49 @@
+"""B200-native (sm_100a) W6A8 GEMM and MoE kernels with packed MXFP6 weights.
+
+Drop-in for the operator surface of Nekofish-L/mxfp6_sm120's ``mxfp6`` package:
+``import mxfp6_sm120_b200 as mxfp6``.
+"""
+
+from ._loader import load_library
+from .ops import (
+    MXFP8Tensor,
+    PackedMXFP6Tensor,
+    SCALE_VECTOR_SIZE,
+    TUNED_M,
+    TUNED_NK,
+    autotune_w6a8,
+    begin_workspace_planning,
+    device_status,
+    expand_fp6_to_fp8,
+    finalize_workspace_planning,
+    gemm,
+    gemm_from_codes,
+    gemm_from_float,
+    gemm_packed,
+    gemm_w6a8,
+    gemm_w6a8_config,
+    gemm_w6a8_plan,
+    is_available,
+    is_tuned_shape,
+    pack_fp6,
+    pack_grouped_scales,
+    pack_operand,
+    pack_scales,
+    packed_scale_numel,
+    pad_fp6,
+    quantize_activation,
+    quantize_mxfp6,
+    quantize_mxfp8,
+    quantize_mxfp8_dual,
+    quantize_mxfp8_dual_out,
+    quantize_mxfp8_logical,
+    to_mma_k64_weight,
+    unpack_fp6,
+    unpack_operand,
+    unpack_scales,
+    warmup_w6a8,
+    workspace_barriers_zero,
+    workspace_stats,
+)
+
+__version__ = "0.1.0"

@@ -1,0 +1,438 @@
+// extern "C" boundary of libmxfp6_b200.so and the split-K workspace arena.
+//
+// The arena follows the reference's contract (csrc/torch_extension.cu:103-138,
+// 247-335,1955-2116): Disabled -> Planning (record needs, transient scratch) ->
+// Frozen (one persistent lane per stream, counters zeroed once, kernels reset
+// their own counters, capture on a lane-less stream is an error).
+#include "../../include/mxfp6_b200.h"
+
+#include "gemm.cuh"
+
+#include <algorithm>
+#include <mutex>
+#include <set>
+#include <unordered_map>
+#include <vector>
+
+namespace mx {
+
+// ---- error text -------------------------------------------------------------
+namespace {
+thread_local char g_error[512] = "";
+}
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+const char* last_error() { return g_error; }
+
+// ---- kernels implemented in the other translation units ------------------------
+int quantize_mxfp8(const void*, int, int64_t, int64_t, uint8_t*, uint8_t*, uint8_t*, cudaStream_t);
+int quantize_mxfp6(const void*, int, int64_t, int64_t, uint8_t*, uint8_t*, uint8_t*, cudaStream_t);
+int pack_fp6(const uint8_t*, int64_t, uint8_t*, cudaStream_t);
+int unpack_fp6(const uint8_t*, int64_t, int64_t, uint8_t*, cudaStream_t);
+int expand_fp6_to_fp8(const uint8_t*, int64_t, int64_t, uint8_t*, cudaStream_t);
+int pad_fp6(const uint8_t*, int64_t, uint8_t*, cudaStream_t);
+int pack_scales(const uint8_t*, int64_t, int64_t, uint8_t*, cudaStream_t);
+int unpack_scales(const uint8_t*, int64_t, int64_t, uint8_t*, cudaStream_t);
+int grouped_scale_offsets(const int64_t*, int, int64_t*, cudaStream_t);
+int pack_grouped_scales(const uint8_t*, const int64_t*, const int64_t*, int, int64_t, int64_t,
+                        uint8_t*, cudaStream_t);
+
+// ---- workspace arena ------------------------------------------------------------
+namespace {
+
+enum class ArenaMode { Disabled, Planning, Frozen };
+
+struct Lane {
+  cudaStream_t stream = nullptr;
+  uint8_t* storage = nullptr;
+};
+
+struct Arena {
+  ArenaMode mode = ArenaMode::Disabled;
+  size_t max_reduction_bytes = 0;
+  size_t max_barrier_bytes = 0;
+  std::set<std::pair<size_t, size_t>> layouts;
+  std::vector<Lane> lanes;
+  int64_t persistent_launches = 0;
+  int64_t fallback_launches = 0;
+};
+
+std::mutex g_arena_mutex;
+std::unordered_map<int, Arena> g_arenas;
+
+bool stream_is_capturing(cudaStream_t stream) {
+  cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &status) != cudaSuccess) return false;
+  return status != cudaStreamCaptureStatusNone;
+}
+
+void fill_stats(const Arena& a, int64_t out[10]) {
+  const int64_t bytes = (int64_t)(a.max_reduction_bytes + a.max_barrier_bytes);
+  out[0] = (int64_t)a.layouts.size();
+  out[1] = (int64_t)a.max_reduction_bytes;
+  out[2] = (int64_t)a.max_barrier_bytes;
+  out[3] = bytes;
+  out[4] = (int64_t)a.lanes.size();
+  out[5] = bytes * (int64_t)a.lanes.size();
+  out[6] = a.mode == ArenaMode::Planning;
+  out[7] = a.mode == ArenaMode::Frozen;
+  out[8] = a.persistent_launches;
+  out[9] = a.fallback_launches;
+}
+
+int new_lane(Arena& arena, cudaStream_t stream, Lane* lane) {
+  const size_t bytes = arena.max_reduction_bytes + arena.max_barrier_bytes;
+  uint8_t* storage = nullptr;
+  MX_CUDA(cudaMalloc(&storage, bytes));
+  MX_CUDA(cudaMemsetAsync(storage + arena.max_reduction_bytes, 0, arena.max_barrier_bytes,
+                          stream));
+  lane->stream = stream;
+  lane->storage = storage;
+  return kOk;
+}
+
+struct Scratch {
+  float* partials = nullptr;
+  uint32_t* counters = nullptr;
+  uint8_t* transient = nullptr;  // freed (stream-ordered) after the launch
+};
+
+// Picks scratch for a split-K launch: a persistent lane when the arena is frozen
+// and large enough, otherwise a stream-ordered transient allocation.
+int select_scratch(int device, cudaStream_t stream, size_t reduction_bytes, size_t barrier_bytes,
+                   Scratch* out) {
+  {
+    std::lock_guard<std::mutex> lock(g_arena_mutex);
+    auto it = g_arenas.find(device);
+    if (it != g_arenas.end()) {
+      Arena& arena = it->second;
+      if (arena.mode == ArenaMode::Planning) {
+        arena.layouts.emplace(reduction_bytes, barrier_bytes);
+        arena.max_reduction_bytes = std::max(arena.max_reduction_bytes, reduction_bytes);
+        arena.max_barrier_bytes = std::max(arena.max_barrier_bytes, barrier_bytes);
+      } else if (arena.mode == ArenaMode::Frozen) {
+        if (reduction_bytes <= arena.max_reduction_bytes &&
+            barrier_bytes <= arena.max_barrier_bytes) {
+          auto lane = std::find_if(arena.lanes.begin(), arena.lanes.end(),
+                                   [stream](const Lane& l) { return l.stream == stream; });
+          if (lane == arena.lanes.end()) {
+            if (stream_is_capturing(stream)) {
+              set_error(
+                  "split-K persistent workspace has no lane for the current CUDA Graph capture "
+                  "stream; run an eager warm-up on this stream after "
+                  "finalize_workspace_planning() and before capture");
+              return kWorkspaceError;
+            }
+            Lane fresh;
+            if (int rc = new_lane(arena, stream, &fresh)) return rc;
+            arena.lanes.push_back(fresh);
+            lane = std::prev(arena.lanes.end());
+          }
+          out->partials = reinterpret_cast<float*>(lane->storage);
+          out->counters = reinterpret_cast<uint32_t*>(lane->storage + arena.max_reduction_bytes);
+          ++arena.persistent_launches;
+          return kOk;
+        }
+        ++arena.fallback_launches;
+        if (stream_is_capturing(stream)) {
+          set_error(
+              "split-K persistent workspace is unavailable during CUDA Graph capture: the "
+              "selected layout exceeds the frozen arena capacity; re-run workspace planning "
+              "with every captured shape");
+          return kWorkspaceError;
+        }
+      }
+    }
+  }
+  uint8_t* storage = nullptr;
+  const size_t reduction_padded = (reduction_bytes + 255) & ~size_t(255);
+  MX_CUDA(cudaMallocAsync(&storage, reduction_padded + barrier_bytes, stream));
+  MX_CUDA(cudaMemsetAsync(storage + reduction_padded, 0, barrier_bytes, stream));
+  out->transient = storage;
+  out->partials = reinterpret_cast<float*>(storage);
+  out->counters = reinterpret_cast<uint32_t*>(storage + reduction_padded);
+  return kOk;
+}
+
+int dense_problem(GemmProblem* p, const uint8_t* a_values, const uint8_t* a_scales,
+                  const uint8_t* w_values, const uint8_t* w_scales, int64_t m, int64_t n,
+                  int64_t k, float alpha, void* out, int out_dtype) {
+  MX_REQUIRE(m > 0, "m must be positive; got %lld", (long long)m);
+  MX_REQUIRE(n > 0 && n % 8 == 0 && n <= INT32_MAX, "n must be a positive multiple of 8; got %lld",
+             (long long)n);
+  MX_REQUIRE(k > 0 && k % 128 == 0 && k <= INT32_MAX,
+             "k must be a positive multiple of 128; got %lld", (long long)k);
+  p->a_values = a_values;
+  p->a_scales = a_scales;
+  p->w_values = w_values;
+  p->w_scales = w_scales;
+  p->m_total = m;
+  p->n = (int)n;
+  p->k = (int)k;
+  p->alpha = alpha;
+  p->out = out;
+  p->out_dtype = out_dtype;
+  p->groups = 1;
+  return kOk;
+}
+
+}  // namespace
+
+int run_gemm_with_arena(GemmProblem& p, cudaStream_t stream) {
+  GemmPlan plan;
+  if (int rc = plan_w6a8(p, &plan)) return rc;
+  Scratch scratch;
+  if (plan.splits > 1) {
+    int device = 0;
+    MX_CUDA(cudaGetDevice(&device));
+    if (int rc = select_scratch(device, stream, plan.partial_bytes, plan.counter_bytes, &scratch))
+      return rc;
+    p.partials = scratch.partials;
+    p.partial_bytes = plan.partial_bytes;
+    p.counters = scratch.counters;
+    p.counter_bytes = plan.counter_bytes;
+  }
+  const int rc = launch_w6a8(p, plan, stream);
+  if (scratch.transient != nullptr) cudaFreeAsync(scratch.transient, stream);
+  return rc;
+}
+
+}  // namespace mx
+
+using namespace mx;
+
+extern "C" {
+
+int mxfp6_b200_abi_version(void) { return MXFP6_B200_ABI_VERSION; }
+const char* mxfp6_b200_last_error(void) { return last_error(); }
+
+int mxfp6_b200_device_status(int* value, int reset) {
+  MX_REQUIRE(value != nullptr, "value must not be null");
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  return read_device_status(device, value, reset != 0);
+}
+
+int mxfp6_pack_fp6(const uint8_t* codes, int64_t n, uint8_t* packed, void* stream) {
+  return pack_fp6(codes, n, packed, static_cast<cudaStream_t>(stream));
+}
+int mxfp6_unpack_fp6(const uint8_t* packed, int64_t rows, int64_t k, uint8_t* codes,
+                     void* stream) {
+  return unpack_fp6(packed, rows, k, codes, static_cast<cudaStream_t>(stream));
+}
+int mxfp6_pad_fp6(const uint8_t* packed, int64_t bytes, uint8_t* padded, void* stream) {
+  return pad_fp6(packed, bytes, padded, static_cast<cudaStream_t>(stream));
+}
+int mxfp6_expand_fp6_to_fp8(const uint8_t* packed, int64_t rows, int64_t k, uint8_t* e4m3,
+                            void* stream) {
+  return expand_fp6_to_fp8(packed, rows, k, e4m3, static_cast<cudaStream_t>(stream));
+}
+int mxfp6_pack_scales(const uint8_t* logical, int64_t rows, int64_t k, uint8_t* packed,
+                      void* stream) {
+  return pack_scales(logical, rows, k, packed, static_cast<cudaStream_t>(stream));
+}
+int mxfp6_unpack_scales(const uint8_t* packed, int64_t rows, int64_t k, uint8_t* logical,
+                        void* stream) {
+  return unpack_scales(packed, rows, k, logical, static_cast<cudaStream_t>(stream));
+}
+int64_t mxfp6_packed_scale_bytes(int64_t rows, int64_t k) { return packed_scale_bytes(rows, k); }
+int mxfp6_grouped_scale_offsets(const int64_t* expert_offsets, int experts,
+                                int64_t* scale_offsets, void* stream) {
+  return grouped_scale_offsets(expert_offsets, experts, scale_offsets,
+                               static_cast<cudaStream_t>(stream));
+}
+int mxfp6_pack_grouped_scales(const uint8_t* logical, const int64_t* expert_offsets,
+                              const int64_t* scale_offsets, int experts, int64_t padded_rows,
+                              int64_t k, uint8_t* packed, void* stream) {
+  return pack_grouped_scales(logical, expert_offsets, scale_offsets, experts, padded_rows, k,
+                             packed, static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_quantize_mxfp8(const void* input, int dtype, int64_t rows, int64_t k, uint8_t* values,
+                         uint8_t* packed_scales, uint8_t* logical_scales, void* stream) {
+  return quantize_mxfp8(input, dtype, rows, k, values, packed_scales, logical_scales,
+                        static_cast<cudaStream_t>(stream));
+}
+int mxfp6_quantize_mxfp6(const void* input, int dtype, int64_t rows, int64_t k, uint8_t* values,
+                         uint8_t* packed_scales, uint8_t* logical_scales, void* stream) {
+  return quantize_mxfp6(input, dtype, rows, k, values, packed_scales, logical_scales,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_gemm_w6a8(const uint8_t* a_values, const uint8_t* a_scales, const uint8_t* w_values,
+                    const uint8_t* w_scales, int64_t m, int64_t n, int64_t k, float alpha,
+                    void* out, int out_dtype, void* stream) {
+  GemmProblem p;
+  if (int rc = dense_problem(&p, a_values, a_scales, w_values, w_scales, m, n, k, alpha, out,
+                             out_dtype))
+    return rc;
+  return run_gemm_with_arena(p, static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_gemm_w6a8_ex(const uint8_t* a_values, const uint8_t* a_scales, const uint8_t* w_values,
+                       const uint8_t* w_scales, int64_t m, int64_t n, int64_t k, float alpha,
+                       void* out, int out_dtype, int tile_tokens, int splits, void* scratch,
+                       size_t scratch_bytes, void* stream) {
+  GemmProblem p;
+  if (int rc = dense_problem(&p, a_values, a_scales, w_values, w_scales, m, n, k, alpha, out,
+                             out_dtype))
+    return rc;
+  p.tile_tokens = tile_tokens;
+  p.splits = splits;
+  GemmPlan plan;
+  if (int rc = plan_w6a8(p, &plan)) return rc;
+  if (plan.splits > 1) {
+    const size_t reduction_padded = (plan.partial_bytes + 255) & ~size_t(255);
+    MX_REQUIRE(scratch != nullptr && scratch_bytes >= reduction_padded + plan.counter_bytes,
+               "scratch must hold %zu bytes for this plan", reduction_padded + plan.counter_bytes);
+    p.partials = static_cast<float*>(scratch);
+    p.partial_bytes = plan.partial_bytes;
+    p.counters = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + reduction_padded);
+    p.counter_bytes = plan.counter_bytes;
+  }
+  return launch_w6a8(p, plan, static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_gemm_w6a8_plan(int64_t m, int64_t n, int64_t k, int tile_tokens, int splits,
+                         int64_t out_plan[6]) {
+  MX_REQUIRE(out_plan != nullptr, "out_plan must not be null");
+  GemmProblem p;
+  if (int rc = dense_problem(&p, nullptr, nullptr, nullptr, nullptr, m, n, k, 1.0f, nullptr,
+                             kBF16))
+    return rc;
+  p.tile_tokens = tile_tokens;
+  p.splits = splits;
+  GemmPlan plan;
+  if (int rc = plan_w6a8(p, &plan)) return rc;
+  out_plan[0] = plan.tile_tokens;
+  out_plan[1] = plan.splits;
+  out_plan[2] = plan.stages;
+  out_plan[3] = plan.grid;
+  out_plan[4] = (int64_t)((plan.partial_bytes + 255) & ~size_t(255));
+  out_plan[5] = (int64_t)plan.counter_bytes;
+  return kOk;
+}
+
+int mxfp6_gemm_from_float(const void* a, int a_dtype, const uint8_t* w_values,
+                          const uint8_t* w_scales, int64_t m, int64_t n, int64_t k, float alpha,
+                          void* out, int out_dtype, uint8_t* a_values_stage,
+                          uint8_t* a_scales_stage, void* stream) {
+  MX_REQUIRE(a_values_stage != nullptr && a_scales_stage != nullptr,
+             "staging buffers must not be null");
+  GemmProblem p;
+  if (int rc = dense_problem(&p, a_values_stage, a_scales_stage, w_values, w_scales, m, n, k,
+                             alpha, out, out_dtype))
+    return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (int rc = quantize_mxfp8(a, a_dtype, m, k, a_values_stage, a_scales_stage, nullptr, s))
+    return rc;
+  return run_gemm_with_arena(p, s);
+}
+
+int mxfp6_workspace_begin_planning(void) {
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  std::lock_guard<std::mutex> lock(g_arena_mutex);
+  Arena& arena = g_arenas[device];
+  if (arena.mode == ArenaMode::Frozen) {
+    set_error(
+        "persistent split-K workspace for CUDA device %d is already frozen; resizing it could "
+        "invalidate captured graphs",
+        device);
+    return kWorkspaceError;
+  }
+  if (arena.mode == ArenaMode::Planning) {
+    set_error("workspace planning is already active for CUDA device %d", device);
+    return kWorkspaceError;
+  }
+  arena = Arena{};
+  arena.mode = ArenaMode::Planning;
+  return kOk;
+}
+
+int mxfp6_workspace_finalize_planning(void* stream, int64_t out_stats[10]) {
+  MX_REQUIRE(out_stats != nullptr, "out_stats must not be null");
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  std::lock_guard<std::mutex> lock(g_arena_mutex);
+  auto it = g_arenas.find(device);
+  if (it == g_arenas.end() || it->second.mode != ArenaMode::Planning) {
+    set_error("workspace planning is not active for CUDA device %d", device);
+    return kWorkspaceError;
+  }
+  Arena& arena = it->second;
+  if (arena.max_reduction_bytes + arena.max_barrier_bytes > 0) {
+    arena.max_reduction_bytes = (arena.max_reduction_bytes + 255) & ~size_t(255);
+    Lane lane;
+    if (int rc = new_lane(arena, static_cast<cudaStream_t>(stream), &lane)) return rc;
+    arena.lanes.push_back(lane);
+  }
+  arena.mode = ArenaMode::Frozen;
+  fill_stats(arena, out_stats);
+  return kOk;
+}
+
+int mxfp6_workspace_stats(int64_t out_stats[10]) {
+  MX_REQUIRE(out_stats != nullptr, "out_stats must not be null");
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  std::lock_guard<std::mutex> lock(g_arena_mutex);
+  auto it = g_arenas.find(device);
+  if (it == g_arenas.end()) {
+    fill_stats(Arena{}, out_stats);
+  } else {
+    fill_stats(it->second, out_stats);
+  }
+  return kOk;
+}
+
+int mxfp6_workspace_barriers_zero(int* all_zero) {
+  MX_REQUIRE(all_zero != nullptr, "all_zero must not be null");
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  std::vector<uint8_t*> tails;
+  size_t bytes = 0;
+  {
+    std::lock_guard<std::mutex> lock(g_arena_mutex);
+    auto it = g_arenas.find(device);
+    if (it == g_arenas.end() || it->second.mode != ArenaMode::Frozen) {
+      set_error("persistent workspace is not frozen for CUDA device %d", device);
+      return kWorkspaceError;
+    }
+    bytes = it->second.max_barrier_bytes;
+    for (const Lane& lane : it->second.lanes) {
+      tails.push_back(lane.storage + it->second.max_reduction_bytes);
+    }
+  }
+  *all_zero = 1;
+  if (bytes == 0) return kOk;
+  MX_CUDA(cudaDeviceSynchronize());
+  std::vector<uint8_t> host(bytes);
+  for (uint8_t* tail : tails) {
+    MX_CUDA(cudaMemcpy(host.data(), tail, bytes, cudaMemcpyDeviceToHost));
+    if (!std::all_of(host.begin(), host.end(), [](uint8_t v) { return v == 0; })) {
+      *all_zero = 0;
+      return kOk;
+    }
+  }
+  return kOk;
+}
+
+int mxfp6_workspace_reset(void) {
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  MX_CUDA(cudaDeviceSynchronize());
+  std::lock_guard<std::mutex> lock(g_arena_mutex);
+  auto it = g_arenas.find(device);
+  if (it != g_arenas.end()) {
+    for (Lane& lane : it->second.lanes) cudaFree(lane.storage);
+    g_arenas.erase(it);
+  }
+  return kOk;
+}
+
+}  // extern "C"

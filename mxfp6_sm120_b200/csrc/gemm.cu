@@ -1,0 +1,735 @@
+// W6A8 block-scaled GEMM for sm_100a: out[m, f] = alpha * sum_k A8[m,k] * W6[f,k]
+// with one UE8M0 scale per 32 K values on both operands.
+//
+// Replaces the reference's CUTLASS SM120 instantiations
+// (csrc/include/mxfp6_gemm/kernel_normal.hpp:94-184, kernel_swapped.hpp:98-317)
+// and its grouped kernels (csrc/moe.cu:1483-1692) with ONE persistent,
+// warp-specialised tcgen05 kernel:
+//   * the weight tile (128 output features x 128 K) is MMA operand A.  TMA reads
+//     the packed 6-bit rows with the 16U6_ALIGN16B tensor-map type, which expands
+//     every 12 packed bytes to a 16-byte shared-memory segment, the form
+//     tcgen05.mma kind::mxf8f6f4 consumes;
+//   * the activation tile (TN rows x 128 K, E4M3 bytes) is operand B, so a decode
+//     batch of 1..32 rows costs one narrow MMA N instead of a padded 128-row M;
+//   * scale atoms (512 bytes = 128 rows x 4 k-groups) are bulk-copied to shared
+//     memory and moved to tensor memory with tcgen05.cp; the per-MMA k-group is
+//     selected through the scale-id fields of the instruction descriptor;
+//   * FP32 accumulators live in tensor memory, double buffered, so the epilogue
+//     of tile i overlaps the main loop of tile i+1;
+//   * split-K writes FP32 partial tiles to a caller-provided scratch arena and the
+//     last-arriving CTA of a tile reduces them in split order (deterministic) and
+//     resets the tile counter, so the arena needs zeroing only once.
+// Every wait is bounded: on expiry the CTA records a code in the device status
+// word, lets its copies drain, frees tensor memory and returns.
+#include "gemm.cuh"
+#include "ptx.cuh"
+
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+#include <cstring>
+#include <cstdlib>
+
+namespace mx {
+namespace {
+
+constexpr int kTileF = 128;         // output features per tile (MMA M)
+constexpr int kTileK = 128;         // K values per pipeline stage
+constexpr int kMmaK = 32;           // K values per tcgen05.mma
+constexpr int kThreads = 192;       // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr int kMaxGroups = 512;
+constexpr uint32_t kWTileBytes = kTileF * kTileK;  // padded 6-bit rows: 128 B per row
+constexpr uint32_t kAtomBytes = 512;
+constexpr long long kWaitCycles = 4000000000ll;    // about two seconds
+
+struct KernelArgs {
+  const uint8_t* w_scales;
+  const uint8_t* a_scales;
+  const int64_t* expert_offsets;
+  const int64_t* scale_offsets;
+  void* out;
+  float* partials;
+  uint32_t* counters;
+  int* status;
+  int64_t m_total;
+  int groups;
+  int n;
+  int k_blocks;       // k / 128
+  int n_tiles;        // ceil(n / 128)
+  int splits;
+  int out_dtype;
+  float alpha;
+  uint32_t w_tx_bytes;  // bytes one weight-tile TMA adds to the mbarrier
+  int a_scale_row_blocks;  // 128-row blocks present in the activation scale buffer
+};
+
+template <int TN>
+struct Cfg {
+  static constexpr int kAcc = (2 * TN + 12 <= 512) ? 2 : 1;  // accumulator buffers
+  static constexpr int kSfbAtoms = TN <= 128 ? 1 : 2;
+  static constexpr int kSfaCol = kAcc * TN;
+  static constexpr int kSfbCol = kSfaCol + 4;
+  static constexpr int kColsUsed = kSfbCol + 4 * kSfbAtoms;
+  static constexpr int kTmemCols =
+      kColsUsed <= 32 ? 32 : kColsUsed <= 64 ? 64 : kColsUsed <= 128 ? 128 : kColsUsed <= 256 ? 256 : 512;
+  static constexpr uint32_t kATileBytes = TN * kTileK;
+  static constexpr uint32_t kStageBytes = kWTileBytes + kATileBytes;
+  static constexpr uint32_t kSfStageBytes = kAtomBytes * (1 + kSfbAtoms);
+  static constexpr uint32_t kFixedBytes = 1024 /*align slack*/ + 4096 /*barriers + tables*/;
+  static constexpr int kStagesRaw =
+      (int)((232448u - kFixedBytes) / (kStageBytes + kSfStageBytes));
+  static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
+  static constexpr size_t kSmemBytes =
+      kFixedBytes + (size_t)kStages * (kStageBytes + kSfStageBytes);
+};
+
+struct Work {
+  int group, n_tile, m_tile, split, tile_id;
+  int64_t row0;        // first activation row of the tile
+  int rows;            // valid rows in the tile
+  int64_t scale_row0;  // packed-scale row of row0
+};
+
+// tile_prefix[g] = number of row tiles of groups < g.
+template <int TN>
+__device__ __forceinline__ bool decode_work(int w, const KernelArgs& a, const int* tile_prefix,
+                                            Work* out) {
+  const int total_row_tiles = tile_prefix[a.groups];
+  const int total = total_row_tiles * a.n_tiles * a.splits;
+  if (w >= total) return false;
+  out->split = w % a.splits;
+  const int rest = w / a.splits;
+  out->tile_id = rest;
+  // Largest g with n_tiles * tile_prefix[g] <= rest.
+  int lo = 0, hi = a.groups;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (tile_prefix[mid] * a.n_tiles <= rest) lo = mid; else hi = mid;
+  }
+  // Skip empty groups that share the same prefix value.
+  while (lo + 1 < a.groups && tile_prefix[lo + 1] * a.n_tiles <= rest) ++lo;
+  out->group = lo;
+  const int local = rest - tile_prefix[lo] * a.n_tiles;
+  const int mt = tile_prefix[lo + 1] - tile_prefix[lo];
+  out->m_tile = local % mt;
+  out->n_tile = local / mt;
+  int64_t begin = 0, end = a.m_total, sbegin = 0;
+  if (a.expert_offsets != nullptr) {
+    begin = a.expert_offsets[lo];
+    end = a.expert_offsets[lo + 1];
+    sbegin = a.scale_offsets[lo];
+  }
+  out->row0 = begin + (int64_t)out->m_tile * TN;
+  const int64_t left = end - out->row0;
+  out->rows = left < TN ? (int)left : TN;
+  out->scale_row0 = sbegin + (int64_t)out->m_tile * TN;
+  return true;
+}
+
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int* abort,
+                                             int* status, int code) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+#pragma unroll 1
+  for (uint32_t spin = 0;; ++spin) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    if ((spin & 63u) == 63u) {
+      if (*abort != 0) return false;
+      if (clock64() - start > kWaitCycles) {
+        *abort = 1;
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+template <int TN>
+__global__ void __launch_bounds__(kThreads, 1)
+w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
+                 const KernelArgs args) {
+  using C = Cfg<TN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* w_tiles = smem;
+  uint8_t* a_tiles = w_tiles + (size_t)C::kStages * kWTileBytes;
+  uint8_t* sf_tiles = a_tiles + (size_t)C::kStages * C::kATileBytes;
+  uint8_t* fixed = sf_tiles + (size_t)C::kStages * C::kSfStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(fixed);  // full[S], empty[S], tfull[2], tempty[2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fixed + 8 * (2 * C::kStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  int* tile_prefix = reinterpret_cast<int*>(fixed + 1024);  // kMaxGroups + 1 ints
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t full0 = ptx::smem_u32(bars);
+  const uint32_t empty0 = full0 + 8 * C::kStages;
+  const uint32_t tfull0 = empty0 + 8 * C::kStages;
+  const uint32_t tempty0 = tfull0 + 16;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    *last_flag = 0;
+    for (int s = 0; s < C::kStages; ++s) {
+      ptx::mbar_init(full0 + 8 * s, 1);
+      ptx::mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(tfull0 + 8 * i, 1);
+      ptx::mbar_init(tempty0 + 8 * i, 4);
+    }
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tm_w);
+    ptx::prefetch_tensormap(&tm_a);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), C::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  // Row-tile prefix table (one entry per group).
+  if (args.expert_offsets == nullptr) {
+    if (threadIdx.x == 0) {
+      tile_prefix[0] = 0;
+      tile_prefix[1] = (int)((args.m_total + TN - 1) / TN);
+    }
+  } else {
+    for (int g = threadIdx.x; g < args.groups; g += kThreads) {
+      const int64_t rows = args.expert_offsets[g + 1] - args.expert_offsets[g];
+      tile_prefix[g + 1] = (int)((rows + TN - 1) / TN);
+    }
+    __syncthreads();
+    if (warp == 0) {
+      int carry = 0;
+      for (int base = 0; base < args.groups; base += 32) {
+        const int g = base + lane;
+        const int v = g < args.groups ? tile_prefix[g + 1] : 0;
+        int incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int up = __shfl_up_sync(0xffffffffu, incl, d);
+          if (lane >= d) incl += up;
+        }
+        if (g < args.groups) tile_prefix[g + 1] = carry + incl;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) tile_prefix[0] = 0;
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int kb_total = args.k_blocks;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t tx = args.w_tx_bytes + C::kATileBytes + kAtomBytes * (1 + C::kSfbAtoms);
+      const int atoms_per_rb = kb_total;  // k/128 atoms per 128-row block
+      Work wk;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && decode_work<TN>(w, args, tile_prefix, &wk); w += gridDim.x) {
+        const int kb0 = (int)(((int64_t)wk.split * kb_total) / args.splits);
+        const int kb1 = (int)(((int64_t)(wk.split + 1) * kb_total) / args.splits);
+        const int w_row = wk.group * args.n + wk.n_tile * kTileF;
+        const uint8_t* sfa_src =
+            args.w_scales + ((int64_t)(w_row / kAtomRows) * atoms_per_rb) * kAtomBytes;
+        const int sfb_rb0 = (int)(wk.scale_row0 / kAtomRows);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!bounded_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag, args.status, 101)) {
+            ok = false;
+            break;
+          }
+          const uint32_t bar = full0 + 8 * stage;
+          ptx::mbar_arrive_expect_tx(bar, tx);
+          ptx::tma_load_2d(ptx::smem_u32(w_tiles + (size_t)stage * kWTileBytes), &tm_w,
+                           kb * kTileK, w_row, bar);
+          ptx::tma_load_2d(ptx::smem_u32(a_tiles + (size_t)stage * C::kATileBytes), &tm_a,
+                           kb * kTileK, (int)wk.row0, bar);
+          uint8_t* sf = sf_tiles + (size_t)stage * C::kSfStageBytes;
+          ptx::bulk_load(ptx::smem_u32(sf), sfa_src + (int64_t)kb * kAtomBytes, kAtomBytes, bar);
+#pragma unroll
+          for (int j = 0; j < C::kSfbAtoms; ++j) {
+            // A tile that ends inside the last row block re-reads that block
+            // for the rows it does not have; those accumulator rows are never stored.
+            int rb = sfb_rb0 + j;
+            if (rb >= args.a_scale_row_blocks) rb = args.a_scale_row_blocks - 1;
+            ptx::bulk_load(ptx::smem_u32(sf + kAtomBytes * (1 + j)),
+                           args.a_scales + ((int64_t)rb * atoms_per_rb + kb) * kAtomBytes,
+                           kAtomBytes, bar);
+          }
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      // E3M2 weights (A, format 4) x E4M3 activations (B, format 0), both K-major,
+      // UE8M0 scales, M = 128, N = TN.
+      constexpr uint32_t kIdesc = (4u << 7) | (0u << 10) | ((uint32_t)(TN >> 3) << 17) |
+                                  (1u << 23) | ((uint32_t)(kTileF >> 4) << 24);
+      const uint32_t sfa_t = tmem_base + C::kSfaCol;
+      Work wk;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && decode_work<TN>(w, args, tile_prefix, &wk); w += gridDim.x) {
+        const int kb0 = (int)(((int64_t)wk.split * kb_total) / args.splits);
+        const int kb1 = (int)(((int64_t)(wk.split + 1) * kb_total) / args.splits);
+        if (!bounded_wait(tempty0 + 8 * acc, acc_phase ^ 1u, abort_flag, args.status, 102)) break;
+        ptx::tc_fence_after();
+        const uint32_t d_t = tmem_base + acc * TN;
+        const uint32_t sfb_t =
+            tmem_base + C::kSfbCol + (uint32_t)((wk.scale_row0 % kAtomRows) / 32);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!bounded_wait(full0 + 8 * stage, phase, abort_flag, args.status, 103)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sf = ptx::smem_u32(sf_tiles + (size_t)stage * C::kSfStageBytes);
+          ptx::tc_cp_32x128b_warpx4(sfa_t, ptx::smem_desc_scale_atom(sf));
+#pragma unroll
+          for (int j = 0; j < C::kSfbAtoms; ++j) {
+            ptx::tc_cp_32x128b_warpx4(tmem_base + C::kSfbCol + 4 * j,
+                                      ptx::smem_desc_scale_atom(sf + kAtomBytes * (1 + j)));
+          }
+          const uint64_t a_desc =
+              ptx::smem_desc_sw128(ptx::smem_u32(w_tiles + (size_t)stage * kWTileBytes));
+          const uint64_t b_desc =
+              ptx::smem_desc_sw128(ptx::smem_u32(a_tiles + (size_t)stage * C::kATileBytes));
+#pragma unroll
+          for (int ks = 0; ks < kTileK / kMmaK; ++ks) {
+            const uint32_t idesc = kIdesc | ((uint32_t)ks << 4) | ((uint32_t)ks << 29);
+            // 32 K values = 32 bytes = 2 descriptor address units.
+            ptx::tc_mma_mxf8f6f4(d_t, a_desc + 2 * ks, b_desc + 2 * ks, idesc, sfa_t, sfb_t,
+                                 (kb > kb0 || ks > 0) ? 1u : 0u);
+          }
+          ptx::tc_commit(empty0 + 8 * stage);
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        ptx::tc_commit(tfull0 + 8 * acc);
+        if (++acc == C::kAcc) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int quarter = warp & 3;  // tensor-memory lane quarter this warp may read
+    const int fl = quarter * 32 + lane;
+    const int etid = threadIdx.x - 64;  // 0..127
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    Work wk;
+    for (int w = blockIdx.x; decode_work<TN>(w, args, tile_prefix, &wk); w += gridDim.x) {
+      bool ready = bounded_wait(tfull0 + 8 * acc, acc_phase, abort_flag, args.status, 104);
+      if (args.splits > 1) {
+        // The split-K path below uses a 128-thread named barrier, so the four
+        // epilogue warps must agree on whether to go on.
+        uint32_t all;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\t"
+            "setp.ne.b32 p, %1, 0;\n\t"
+            "bar.red.and.pred q, 1, 128, p;\n\t"
+            "selp.u32 %0, 1, 0, q;\n\t}"
+            : "=r"(all)
+            : "r"((uint32_t)ready)
+            : "memory");
+        ready = all != 0;
+      }
+      if (!ready) break;
+      ptx::tc_fence_after();
+      const int f = wk.n_tile * kTileF + fl;
+      const bool f_ok = f < args.n;
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * TN;
+      float* part = nullptr;
+      if (args.splits > 1) {
+        part = args.partials + ((size_t)wk.tile_id * args.splits + wk.split) * (TN * kTileF);
+      }
+#pragma unroll 1
+      for (int c0 = 0; c0 < TN; c0 += 16) {
+        uint32_t r[16];
+        ptx::tmem_ld_x16(t_addr + c0, r);
+        ptx::tmem_ld_wait();
+        if (args.splits > 1) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c0 + j < wk.rows) __stcg(part + (c0 + j) * kTileF + fl, __uint_as_float(r[j]));
+          }
+        } else if (f_ok) {
+          if (args.out_dtype == kBF16) {
+            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(args.out) + wk.row0 * args.n + f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (c0 + j < wk.rows)
+                o[(int64_t)(c0 + j) * args.n] = __float2bfloat16_rn(args.alpha * __uint_as_float(r[j]));
+            }
+          } else {
+            __half* o = static_cast<__half*>(args.out) + wk.row0 * args.n + f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (c0 + j < wk.rows)
+                o[(int64_t)(c0 + j) * args.n] = __float2half_rn(args.alpha * __uint_as_float(r[j]));
+            }
+          }
+        }
+      }
+      // Accumulator buffer is free for the next tile.
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tempty0 + 8 * acc);
+      if (++acc == C::kAcc) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+      if (args.splits > 1) {
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (etid == 0) {
+          const uint32_t old = atomicAdd(args.counters + wk.tile_id, 1u);
+          *last_flag = (old == (uint32_t)(args.splits - 1)) ? 1 : 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool last = *last_flag != 0;
+        if (last) {
+          __threadfence();
+          const float* base = args.partials + (size_t)wk.tile_id * args.splits * (TN * kTileF);
+          for (int t = 0; t < wk.rows; ++t) {
+            float sum = 0.0f;
+            for (int s = 0; s < args.splits; ++s) {
+              sum += __ldcg(base + ((size_t)s * TN + t) * kTileF + fl);
+            }
+            if (f_ok) {
+              const int64_t idx = (wk.row0 + t) * args.n + f;
+              if (args.out_dtype == kBF16) {
+                static_cast<__nv_bfloat16*>(args.out)[idx] = __float2bfloat16_rn(args.alpha * sum);
+              } else {
+                static_cast<__half*>(args.out)[idx] = __float2half_rn(args.alpha * sum);
+              }
+            }
+          }
+          if (etid == 0) args.counters[wk.tile_id] = 0u;  // self-reset for the next launch
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    // Give copies and MMAs still in flight time to land before the CTA's shared
+    // and tensor memory are handed back.
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                              const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = []() -> EncodeFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
+            cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      return nullptr;
+    }
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+int make_map(CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t inner,
+             uint64_t rows, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) {
+    set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+    return kCudaError;
+  }
+  const cuuint64_t dims[2] = {inner, rows};
+  const cuuint64_t strides[1] = {row_stride_bytes};
+  const cuuint32_t box[2] = {box_inner, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult rc = fn(map, type, 2, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (inner=%llu rows=%llu stride=%llu)",
+              (int)rc, (unsigned long long)inner, (unsigned long long)rows,
+              (unsigned long long)row_stride_bytes);
+    return kCudaError;
+  }
+  return kOk;
+}
+
+// Tensor maps are pure functions of (pointer, extents, box); encoding costs a
+// few microseconds, so a small per-process cache keeps it off the decode path.
+struct MapKey {
+  const void* base;
+  uint64_t inner, rows;
+  uint32_t box_rows;
+  int type;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && inner == o.inner && rows == o.rows && box_rows == o.box_rows &&
+           type == o.type;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    h = h * 1000003u ^ k.inner;
+    h = h * 1000003u ^ k.rows;
+    h = h * 1000003u ^ k.box_rows;
+    h = h * 1000003u ^ (size_t)k.type;
+    return h;
+  }
+};
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+int cached_map(CUtensorMap* out, CUtensorMapDataType type, const void* base, uint64_t inner,
+               uint64_t rows, uint64_t stride, uint32_t box_rows) {
+  const MapKey key{base, inner, rows, box_rows, (int)type};
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) {
+      *out = it->second;
+      return kOk;
+    }
+  }
+  CUtensorMap map;
+  if (int rc = make_map(&map, type, base, inner, rows, stride, kTileK, box_rows)) return rc;
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps.emplace(key, map);
+  }
+  *out = map;
+  return kOk;
+}
+
+template <int TN>
+int launch_tn(const CUtensorMap& tm_w, const CUtensorMap& tm_a, const KernelArgs& args,
+              const GemmPlan& plan, cudaStream_t stream) {
+  static bool configured[64] = {};
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  if (device < 64 && !configured[device]) {
+    MX_CUDA(cudaFuncSetAttribute(w6a8_gemm_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)Cfg<TN>::kSmemBytes));
+    configured[device] = true;
+  }
+  w6a8_gemm_kernel<TN><<<plan.grid, kThreads, Cfg<TN>::kSmemBytes, stream>>>(tm_w, tm_a, args);
+  MX_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+template <int TN>
+void fill_plan(GemmPlan* plan) {
+  plan->stages = Cfg<TN>::kStages;
+  plan->smem_bytes = Cfg<TN>::kSmemBytes;
+}
+
+int sm_count() {
+  static int count = []() {
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) {
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    }
+    return sms > 0 ? sms : 148;
+  }();
+  return count;
+}
+
+}  // namespace
+
+int plan_w6a8(const GemmProblem& p, GemmPlan* plan) {
+  MX_REQUIRE(p.m_total > 0, "m must be positive; got %lld", (long long)p.m_total);
+  MX_REQUIRE(p.n > 0 && p.n % 8 == 0, "n must be a positive multiple of 8; got %d", p.n);
+  MX_REQUIRE(p.k > 0 && p.k % 128 == 0, "k must be a positive multiple of 128; got %d", p.k);
+  MX_REQUIRE(p.groups >= 1 && p.groups <= kMaxGroups, "groups must be in [1, %d]", kMaxGroups);
+  MX_REQUIRE(p.groups == 1 || p.n % 128 == 0, "grouped weights need n %% 128 == 0");
+  const bool grouped = p.expert_offsets != nullptr;
+  int tn = p.tile_tokens;
+  if (tn == 0) {
+    // Rows per group that a tile should cover.
+    const int64_t rows = grouped ? (p.m_total + p.groups - 1) / p.groups : p.m_total;
+    if (!grouped && rows <= 16) tn = 16;
+    else if (rows <= 32) tn = 32;
+    else if (rows <= 64) tn = 64;
+    else if (!grouped && rows <= 96) tn = 96;
+    else if (rows <= 128) tn = 128;
+    else if (!grouped && rows % 256 == 0) tn = 256;
+    else tn = 128;
+  }
+  switch (tn) {
+    case 16: fill_plan<16>(plan); break;
+    case 32: fill_plan<32>(plan); break;
+    case 64: fill_plan<64>(plan); break;
+    case 96: fill_plan<96>(plan); break;
+    case 128: fill_plan<128>(plan); break;
+    case 192: fill_plan<192>(plan); break;
+    case 256: fill_plan<256>(plan); break;
+    default:
+      set_error("unsupported tile_tokens %d (use 16, 32, 64, 96, 128, 192 or 256)", tn);
+      return kInvalidArgument;
+  }
+  MX_REQUIRE(!(grouped && (tn == 16 || tn == 96 || tn == 192)),
+             "grouped launches need tile_tokens in {32, 64, 128, 256}");
+  MX_REQUIRE(!(tn == 16 && p.m_total > 16), "tile_tokens 16 needs m <= 16");
+  MX_REQUIRE(!(tn == 96 && p.m_total > 96), "tile_tokens 96 needs m <= 96");
+  plan->tile_tokens = tn;
+  const int n_tiles = (p.n + kTileF - 1) / kTileF;
+  const int k_blocks = p.k / kTileK;
+  // Upper bound of row tiles: every group may add one ragged tile.
+  const int64_t row_tiles =
+      grouped ? (p.m_total / tn + (p.groups < p.m_total ? p.groups : p.m_total))
+              : (p.m_total + tn - 1) / tn;
+  const int64_t tiles = row_tiles * n_tiles;
+  const int sms = sm_count();
+  int splits = p.splits;
+  if (splits == 0) {
+    splits = 1;
+    if (!grouped && tiles * 2 <= sms) {
+      splits = (int)(sms / tiles);
+      const int max_splits = k_blocks / 2 > 0 ? k_blocks / 2 : 1;
+      if (splits > max_splits) splits = max_splits;
+      if (splits > 16) splits = 16;
+    }
+  }
+  MX_REQUIRE(splits >= 1 && splits <= k_blocks, "splits must be in [1, k/128]");
+  plan->splits = splits;
+  const int64_t work = tiles * splits;
+  plan->grid = (int)(work < sms ? work : sms);
+  if (plan->grid < 1) plan->grid = 1;
+  plan->partial_bytes = splits > 1 ? (size_t)tiles * splits * tn * kTileF * sizeof(float) : 0;
+  plan->counter_bytes = splits > 1 ? (size_t)tiles * sizeof(uint32_t) : 0;
+  return kOk;
+}
+
+int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream) {
+  MX_REQUIRE(p.w_values && p.w_scales && p.a_values && p.a_scales && p.out,
+             "operand pointers must not be null");
+  MX_REQUIRE((reinterpret_cast<uintptr_t>(p.w_values) & 31) == 0,
+             "packed weight values must be 32-byte aligned");
+  MX_REQUIRE((reinterpret_cast<uintptr_t>(p.a_values) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(p.w_scales) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(p.a_scales) & 15) == 0,
+             "activation values and scale buffers must be 16-byte aligned");
+  MX_REQUIRE(p.out_dtype == kBF16 || p.out_dtype == kF16,
+             "out_dtype must be float16 or bfloat16");
+  if (plan.splits > 1) {
+    MX_REQUIRE(p.partials != nullptr && p.counters != nullptr &&
+                   p.partial_bytes >= plan.partial_bytes && p.counter_bytes >= plan.counter_bytes,
+               "split-K scratch is missing or too small (%zu + %zu bytes needed)",
+               plan.partial_bytes, plan.counter_bytes);
+  }
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  CUtensorMap tm_w, tm_a;
+  if (int rc = cached_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B, p.w_values,
+                          (uint64_t)p.k, (uint64_t)p.groups * p.n, (uint64_t)p.k * 3 / 4,
+                          kTileF))
+    return rc;
+  if (int rc = cached_map(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.a_values, (uint64_t)p.k,
+                          (uint64_t)p.m_total, (uint64_t)p.k, (uint32_t)plan.tile_tokens))
+    return rc;
+  KernelArgs args;
+  args.w_scales = p.w_scales;
+  args.a_scales = p.a_scales;
+  args.expert_offsets = p.expert_offsets;
+  args.scale_offsets = p.scale_offsets;
+  args.out = p.out;
+  args.partials = p.partials;
+  args.counters = p.counters;
+  args.status = device_status_word(device);
+  if (args.status == nullptr) return kCudaError;
+  args.m_total = p.m_total;
+  args.groups = p.groups;
+  args.n = p.n;
+  args.k_blocks = p.k / kTileK;
+  args.n_tiles = (p.n + kTileF - 1) / kTileF;
+  args.splits = plan.splits;
+  args.out_dtype = p.out_dtype;
+  args.alpha = p.alpha;
+  static const uint32_t w_tx = []() {
+    const char* env = std::getenv("MXFP6_B200_W_TX_BYTES");
+    return env != nullptr ? (uint32_t)std::atoi(env) : kWTileBytes;
+  }();
+  args.w_tx_bytes = w_tx;
+  {
+    const int64_t scale_rows = p.a_scale_rows > 0 ? p.a_scale_rows : round_up64(p.m_total, kAtomRows);
+    args.a_scale_row_blocks = (int)(scale_rows / kAtomRows);
+  }
+  switch (plan.tile_tokens) {
+    case 16: return launch_tn<16>(tm_w, tm_a, args, plan, stream);
+    case 32: return launch_tn<32>(tm_w, tm_a, args, plan, stream);
+    case 64: return launch_tn<64>(tm_w, tm_a, args, plan, stream);
+    case 96: return launch_tn<96>(tm_w, tm_a, args, plan, stream);
+    case 128: return launch_tn<128>(tm_w, tm_a, args, plan, stream);
+    case 192: return launch_tn<192>(tm_w, tm_a, args, plan, stream);
+    case 256: return launch_tn<256>(tm_w, tm_a, args, plan, stream);
+  }
+  set_error("unsupported tile_tokens %d", plan.tile_tokens);
+  return kInvalidArgument;
+}
+
+// One status word per device, allocated on first use and never freed.
+int* device_status_word(int device) {
+  static std::mutex mutex;
+  static int* words[64] = {};
+  if (device < 0 || device >= 64) {
+    set_error("device index %d out of range", device);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mutex);
+  if (words[device] == nullptr) {
+    int* ptr = nullptr;
+    if (cudaMalloc(&ptr, sizeof(int)) != cudaSuccess || cudaMemset(ptr, 0, sizeof(int)) != cudaSuccess) {
+      set_error("could not allocate the device status word");
+      return nullptr;
+    }
+    words[device] = ptr;
+  }
+  return words[device];
+}
+
+int read_device_status(int device, int* value, bool reset) {
+  int* word = device_status_word(device);
+  if (word == nullptr) return kCudaError;
+  MX_CUDA(cudaDeviceSynchronize());
+  MX_CUDA(cudaMemcpy(value, word, sizeof(int), cudaMemcpyDeviceToHost));
+  if (reset && *value != 0) MX_CUDA(cudaMemset(word, 0, sizeof(int)));
+  return kOk;
+}
+
+}  // namespace mx

@@ -1,0 +1,62 @@
+// Host-visible description of one W6A8 GEMM launch (dense or row-grouped).
+#pragma once
+
+#include "common.cuh"
+
+namespace mx {
+
+// Epilogue selector of the tcgen05 kernel.
+enum GemmEpilogue : int {
+  kEpiStore = 0,      // out[row, f] = cast(alpha * acc)
+};
+
+struct GemmProblem {
+  // Weights: `groups` matrices of [n, k] E3M2 codes, packed rows of k*3/4 bytes,
+  // stored back to back; packed scales likewise (n % 128 == 0 when groups > 1).
+  const uint8_t* w_values = nullptr;
+  const uint8_t* w_scales = nullptr;
+  // Activations: [m_total, k] E4M3 bytes with packed scales.  For grouped
+  // launches rows [expert_offsets[g], expert_offsets[g+1]) belong to matrix g and
+  // their scales start at packed row scale_offsets[g] (a multiple of 128).
+  const uint8_t* a_values = nullptr;
+  const uint8_t* a_scales = nullptr;
+  int64_t a_scale_rows = 0;  // padded row count of the activation scale buffer
+  const int64_t* expert_offsets = nullptr;  // device, groups + 1 entries, or null (dense)
+  const int64_t* scale_offsets = nullptr;   // device, groups + 1 entries, or null (dense)
+  int groups = 1;
+  int64_t m_total = 0;
+  int n = 0;
+  int k = 0;
+  float alpha = 1.0f;
+  void* out = nullptr;  // [m_total, n]
+  int out_dtype = kBF16;
+  // Split-K scratch: fp32 partial tiles and one counter per output tile.
+  float* partials = nullptr;
+  size_t partial_bytes = 0;
+  uint32_t* counters = nullptr;
+  size_t counter_bytes = 0;
+  // Optional overrides (0 = choose from the static table).
+  int tile_tokens = 0;
+  int splits = 0;
+};
+
+struct GemmPlan {
+  int tile_tokens = 0;  // activation rows per tile (MMA N)
+  int splits = 1;
+  int stages = 0;
+  int grid = 0;
+  size_t smem_bytes = 0;
+  size_t partial_bytes = 0;   // scratch the plan needs when splits > 1
+  size_t counter_bytes = 0;
+};
+
+// Chooses tile/split-K for a problem; pure host arithmetic.
+int plan_w6a8(const GemmProblem& p, GemmPlan* plan);
+// Launches the kernel on `stream`; the plan must come from plan_w6a8.
+int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream);
+
+// Device status word (0 = ok) shared by all kernels with bounded waits.
+int* device_status_word(int device);
+int read_device_status(int device, int* value, bool reset);
+
+}  // namespace mx

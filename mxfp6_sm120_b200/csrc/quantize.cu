@@ -1,0 +1,270 @@
+// BF16/FP16 -> MXFP8 (E4M3) and -> MXFP6 (E3M2) dynamic quantizers, one UE8M0
+// scale per 32 consecutive K values.
+//
+// Arithmetic follows the reference quantizer (csrc/quantization.cu:96-144):
+//   absmax over the 32 values (FP32), raw = max(absmax / T, 1e-30) with IEEE
+//   division (T = 448 for E4M3, 28 for E3M2), scale = raw rounded up to a power
+//   of two, code = exponent byte, q = cvt_rn_satfinite(x * (1 / scale)).
+// The launch shape is new: every thread moves one (MXFP8) or two (MXFP6) 16-byte
+// vectors, the group maximum is a 2- or 1-step shuffle, value stores are 8- or
+// 12-byte vectors, and the padding bytes of the packed scale buffer are written
+// by the same launch instead of a preceding memset.
+#include "common.cuh"
+
+#include <cuda_fp8.h>
+#include <cuda_fp6.h>
+
+namespace mx {
+namespace {
+
+constexpr int kQuantThreads = 256;
+
+template <class T>
+struct Vec8 {
+  uint4 raw;
+  __device__ __forceinline__ void unpack(float (&v)[8]) const;
+};
+
+template <>
+__device__ __forceinline__ void Vec8<__nv_bfloat16>::unpack(float (&v)[8]) const {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+template <>
+__device__ __forceinline__ void Vec8<__half>::unpack(float (&v)[8]) const {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+    const float2 f = __half22float2(h);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+__device__ __forceinline__ float absmax8(const float (&v)[8]) {
+  float m = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+  return m;
+}
+
+// Writes 0x7f into every byte of the packed scale buffer that belongs to a
+// padded row or a padded k-group, starting at byte `begin`.
+__device__ __forceinline__ void fill_scale_padding(uint8_t* packed, int64_t begin, int64_t total,
+                                                   int64_t rows, int groups, int64_t tid,
+                                                   int64_t nthreads) {
+  const int64_t atoms_per_rb = (groups + kAtomGroups - 1) / kAtomGroups;
+  for (int64_t idx = begin + tid; idx < total; idx += nthreads) {
+    const int64_t atom = idx / 512;
+    const int within = static_cast<int>(idx % 512);
+    const int64_t row = (atom / atoms_per_rb) * kAtomRows + ((within % 16) / 4) * 32 + within / 16;
+    const int64_t g = (atom % atoms_per_rb) * kAtomGroups + within % 4;
+    if (row >= rows || g >= groups) packed[idx] = kUe8m0One;
+  }
+}
+
+// One thread per 8 consecutive K values, four threads per scale group.
+template <class T>
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_mxfp8_kernel(const T* __restrict__ in, uint8_t* __restrict__ out,
+                      uint8_t* __restrict__ packed, uint8_t* __restrict__ logical, int64_t rows,
+                      int k, int64_t pad_begin, int64_t pad_total) {
+  const int groups = k / kScaleVec;
+  const int64_t chunks = rows * (k / 8);
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t rounds = (chunks + nthreads - 1) / nthreads;
+  for (int64_t it = 0; it < rounds; ++it) {
+    const int64_t c = it * nthreads + tid;
+    const bool valid = c < chunks;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (valid) {
+      Vec8<T> raw;
+      raw.raw = __ldg(reinterpret_cast<const uint4*>(in) + c);
+      raw.unpack(v);
+    }
+    float amax = absmax8(v);
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
+    const float inv = __fdiv_rn(1.0f, __uint_as_float(sbits));
+    if (valid) {
+      uint32_t w[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+            make_float2(v[4 * i] * inv, v[4 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+            make_float2(v[4 * i + 2] * inv, v[4 * i + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+        w[i] = lo | (hi << 16);
+      }
+      reinterpret_cast<uint2*>(out)[c] = make_uint2(w[0], w[1]);
+      if ((c & 3) == 0) {
+        const int64_t group = c >> 2;
+        const uint8_t code = static_cast<uint8_t>(sbits >> 23);
+        if (logical != nullptr) logical[group] = code;
+        if (packed != nullptr) {
+          const int64_t row = group / groups;
+          const int g = static_cast<int>(group - row * groups);
+          packed[packed_scale_offset(row, g, groups)] = code;
+        }
+      }
+    }
+  }
+  if (packed != nullptr && pad_begin < pad_total) {
+    fill_scale_padding(packed, pad_begin, pad_total, rows, groups, tid, nthreads);
+  }
+}
+
+// One thread per 16 consecutive K values (two per scale group); the sixteen
+// E3M2 codes leave as three 32-bit words (code i at bits 6i..6i+5).
+template <class T>
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_mxfp6_kernel(const T* __restrict__ in, uint8_t* __restrict__ out,
+                      uint8_t* __restrict__ packed, uint8_t* __restrict__ logical, int64_t rows,
+                      int k, int64_t pad_begin, int64_t pad_total) {
+  const int groups = k / kScaleVec;
+  const int64_t chunks = rows * (k / 16);
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t rounds = (chunks + nthreads - 1) / nthreads;
+  for (int64_t it = 0; it < rounds; ++it) {
+    const int64_t c = it * nthreads + tid;
+    const bool valid = c < chunks;
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = 0.0f;
+    if (valid) {
+      Vec8<T> a, b;
+      a.raw = __ldg(reinterpret_cast<const uint4*>(in) + 2 * c);
+      b.raw = __ldg(reinterpret_cast<const uint4*>(in) + 2 * c + 1);
+      float lo[8], hi[8];
+      a.unpack(lo);
+      b.unpack(hi);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[i] = lo[i];
+        v[8 + i] = hi[i];
+      }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    const uint32_t sbits = ue8m0_scale_bits(amax, 28.0f);
+    const float inv = __fdiv_rn(1.0f, __uint_as_float(sbits));
+    if (valid) {
+      uint32_t unit[4];  // four codes -> 24 bits, code i at bits 6i..6i+5
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t p0 = __nv_cvt_float2_to_fp6x2(
+            make_float2(v[4 * u] * inv, v[4 * u + 1] * inv), __NV_E3M2, cudaRoundNearest);
+        const uint32_t p1 = __nv_cvt_float2_to_fp6x2(
+            make_float2(v[4 * u + 2] * inv, v[4 * u + 3] * inv), __NV_E3M2, cudaRoundNearest);
+        unit[u] = (p0 & 0x3fu) | (((p0 >> 8) & 0x3fu) << 6) | ((p1 & 0x3fu) << 12) |
+                  (((p1 >> 8) & 0x3fu) << 18);
+      }
+      uint32_t* dst = reinterpret_cast<uint32_t*>(out + c * 12);
+      dst[0] = unit[0] | (unit[1] << 24);
+      dst[1] = (unit[1] >> 8) | (unit[2] << 16);
+      dst[2] = (unit[2] >> 16) | (unit[3] << 8);
+      if ((c & 1) == 0) {
+        const int64_t group = c >> 1;
+        const uint8_t code = static_cast<uint8_t>(sbits >> 23);
+        if (logical != nullptr) logical[group] = code;
+        if (packed != nullptr) {
+          const int64_t row = group / groups;
+          const int g = static_cast<int>(group - row * groups);
+          packed[packed_scale_offset(row, g, groups)] = code;
+        }
+      }
+    }
+  }
+  if (packed != nullptr && pad_begin < pad_total) {
+    fill_scale_padding(packed, pad_begin, pad_total, rows, groups, tid, nthreads);
+  }
+}
+
+int check_args(const void* in, int dtype, int64_t rows, int64_t k, const void* values) {
+  MX_REQUIRE(in != nullptr && values != nullptr, "input and output pointers must not be null");
+  MX_REQUIRE(dtype == kF16 || dtype == kBF16, "input must be float16 or bfloat16");
+  MX_REQUIRE(rows > 0, "M must be positive; got %lld", (long long)rows);
+  MX_REQUIRE(k > 0 && k % kScaleVec == 0, "K must be a positive multiple of 32; got %lld",
+             (long long)k);
+  MX_REQUIRE(rows <= INT32_MAX && k <= INT32_MAX, "M and K must fit in a 32-bit integer");
+  MX_REQUIRE((reinterpret_cast<uintptr_t>(in) & 15) == 0, "input must be 16-byte aligned");
+  return kOk;
+}
+
+void padding_range(int64_t rows, int64_t k, int64_t* begin, int64_t* total) {
+  const int64_t groups = k / kScaleVec;
+  *total = packed_scale_bytes(rows, k);
+  if (groups % kAtomGroups != 0) {
+    *begin = 0;
+  } else if (rows % kAtomRows != 0) {
+    *begin = (rows / kAtomRows) * (groups / kAtomGroups) * 512;
+  } else {
+    *begin = *total;
+  }
+}
+
+int grid_for(int64_t chunks) {
+  // Enough CTAs to fill 148 SMs at 8 resident CTAs each; grid-stride beyond that.
+  const int64_t want = (chunks + kQuantThreads - 1) / kQuantThreads;
+  const int64_t cap = 148 * 16;
+  return static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
+}
+
+}  // namespace
+
+int quantize_mxfp8(const void* in, int dtype, int64_t rows, int64_t k, uint8_t* values,
+                   uint8_t* packed, uint8_t* logical, cudaStream_t stream) {
+  if (int rc = check_args(in, dtype, rows, k, values)) return rc;
+  MX_REQUIRE(packed != nullptr || logical != nullptr, "at least one scale output is required");
+  MX_REQUIRE((reinterpret_cast<uintptr_t>(values) & 7) == 0, "values must be 8-byte aligned");
+  int64_t pad_begin = 0, pad_total = 0;
+  if (packed != nullptr) padding_range(rows, k, &pad_begin, &pad_total);
+  const int64_t chunks = rows * (k / 8);
+  const int grid = grid_for(chunks);
+  if (dtype == kBF16) {
+    quantize_mxfp8_kernel<__nv_bfloat16><<<grid, kQuantThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(in), values, packed, logical, rows,
+        static_cast<int>(k), pad_begin, pad_total);
+  } else {
+    quantize_mxfp8_kernel<__half><<<grid, kQuantThreads, 0, stream>>>(
+        static_cast<const __half*>(in), values, packed, logical, rows, static_cast<int>(k),
+        pad_begin, pad_total);
+  }
+  MX_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int quantize_mxfp6(const void* in, int dtype, int64_t rows, int64_t k, uint8_t* values,
+                   uint8_t* packed, uint8_t* logical, cudaStream_t stream) {
+  if (int rc = check_args(in, dtype, rows, k, values)) return rc;
+  MX_REQUIRE(packed != nullptr || logical != nullptr, "at least one scale output is required");
+  MX_REQUIRE((reinterpret_cast<uintptr_t>(values) & 3) == 0, "values must be 4-byte aligned");
+  int64_t pad_begin = 0, pad_total = 0;
+  if (packed != nullptr) padding_range(rows, k, &pad_begin, &pad_total);
+  const int64_t chunks = rows * (k / 16);
+  const int grid = grid_for(chunks);
+  if (dtype == kBF16) {
+    quantize_mxfp6_kernel<__nv_bfloat16><<<grid, kQuantThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(in), values, packed, logical, rows,
+        static_cast<int>(k), pad_begin, pad_total);
+  } else {
+    quantize_mxfp6_kernel<__half><<<grid, kQuantThreads, 0, stream>>>(
+        static_cast<const __half*>(in), values, packed, logical, rows, static_cast<int>(k),
+        pad_begin, pad_total);
+  }
+  MX_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+}  // namespace mx

@@ -1,0 +1,832 @@
+"""Python operator surface of the B200 W6A8 library.
+
+Names, argument meaning and error behaviour follow the reference's
+``python/mxfp6/ops.py`` so that callers can switch libraries; every function
+forwards raw device pointers to the C ABI in ``libmxfp6_b200.so``.  There is no
+fallback: a missing library raises ``ImportError`` and a non-sm_100 GPU raises
+``RuntimeError``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from ._loader import check, library, load_library
+
+SCALE_VECTOR_SIZE = 32
+# (N, K) pairs the static tile/split-K table was measured on: the dense
+# projections of a 27B-class decoder (hidden 5120, intermediate 17408).
+TUNED_NK = frozenset(
+    {
+        (7168, 5120),
+        (5120, 6144),
+        (34816, 5120),
+        (5120, 17408),
+        (2048, 5120),
+    }
+)
+TUNED_M = frozenset((1, 2, 4, 8, 16, 24, 32, 64, 96, 512, 1024, 2048, 4096, 8192))
+
+_DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1}
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _ptr(tensor: torch.Tensor | None) -> int | None:
+    return None if tensor is None else tensor.data_ptr()
+
+
+def _require_cuda_uint8_contiguous(tensor: torch.Tensor, name: str) -> None:
+    if tensor.device.type != "cuda":
+        raise ValueError(f"{name} must be a CUDA tensor; got {tensor.device}")
+    if tensor.dtype != torch.uint8:
+        raise TypeError(f"{name} must have dtype torch.uint8; got {tensor.dtype}")
+    if not tensor.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def _require_sm100(device: torch.device) -> None:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    capability = torch.cuda.get_device_capability(index)
+    if capability != (10, 0):
+        raise RuntimeError(
+            f"MXFP6 native GEMM requires SM100 (B200); device {index} is "
+            f"SM{capability[0]}{capability[1]}"
+        )
+
+
+def _resolve_device(device: torch.device | str | int | None) -> torch.device:
+    if device is None:
+        resolved = torch.device("cuda", torch.cuda.current_device())
+    elif isinstance(device, int) and not isinstance(device, bool):
+        resolved = torch.device("cuda", device)
+    else:
+        resolved = torch.device(device)
+    if resolved.type != "cuda":
+        raise ValueError(f"workspace device must be CUDA; got {resolved}")
+    if resolved.index is None:
+        resolved = torch.device("cuda", torch.cuda.current_device())
+    _require_sm100(resolved)
+    load_library()
+    return resolved
+
+
+_STAT_KEYS = (
+    "layouts",
+    "max_reduction_bytes",
+    "max_barrier_bytes",
+    "arena_bytes",
+    "lanes",
+    "total_arena_bytes",
+    "planning",
+    "frozen",
+    "persistent_launches",
+    "fallback_launches",
+)
+
+
+def begin_workspace_planning(device: torch.device | str | int | None = None) -> None:
+    """Collect split-K workspace layouts selected during subsequent warm-up."""
+    resolved = _resolve_device(device)
+    with torch.cuda.device(resolved):
+        check(library().mxfp6_workspace_begin_planning())
+
+
+def finalize_workspace_planning(
+    device: torch.device | str | int | None = None,
+) -> dict[str, int]:
+    """Freeze the arena capacity and allocate its current-stream lane."""
+    resolved = _resolve_device(device)
+    stats = (ctypes.c_int64 * 10)()
+    with torch.cuda.device(resolved):
+        check(library().mxfp6_workspace_finalize_planning(_stream(resolved), stats))
+    return dict(zip(_STAT_KEYS, (int(v) for v in stats)))
+
+
+def workspace_stats(device: torch.device | str | int | None = None) -> dict[str, int]:
+    """Return planner capacity and launch counters for ``device``."""
+    resolved = _resolve_device(device)
+    stats = (ctypes.c_int64 * 10)()
+    with torch.cuda.device(resolved):
+        check(library().mxfp6_workspace_stats(stats))
+    return dict(zip(_STAT_KEYS, (int(v) for v in stats)))
+
+
+def workspace_barriers_zero(device: torch.device | str | int | None = None) -> bool:
+    """Synchronize and verify every frozen lane's counter tail is zero."""
+    resolved = _resolve_device(device)
+    flag = ctypes.c_int(0)
+    with torch.cuda.device(resolved):
+        check(library().mxfp6_workspace_barriers_zero(ctypes.byref(flag)))
+    return bool(flag.value)
+
+
+def device_status(device: torch.device | str | int | None = None, reset: bool = True) -> int:
+    """Synchronize and return the bounded-wait status word (0 = no wait expired)."""
+    resolved = _resolve_device(device)
+    value = ctypes.c_int(0)
+    with torch.cuda.device(resolved):
+        check(library().mxfp6_b200_device_status(ctypes.byref(value), int(reset)))
+    return int(value.value)
+
+
+def _validate_problem(m: int, n: int, k: int) -> None:
+    if m <= 0:
+        raise ValueError(f"m must be positive; got {m}")
+    if n <= 0 or n % 8:
+        raise ValueError(f"n must be a positive multiple of 8; got {n}")
+    if k <= 0 or k % 128:
+        raise ValueError(f"k must be a positive multiple of 128; got {k}")
+
+
+def _validate_output_dtype(out_dtype: torch.dtype) -> torch.dtype:
+    if out_dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError(f"out_dtype must be torch.float16 or torch.bfloat16; got {out_dtype}")
+    return out_dtype
+
+
+@dataclass(frozen=True)
+class PackedMXFP6Tensor:
+    """An E3M2 matrix and its UE8M0/32 scales in the packed physical layout."""
+
+    values: torch.Tensor
+    scales: torch.Tensor
+    rows: int
+    k: int
+    logical_scales: torch.Tensor | None = None
+
+    @property
+    def device(self) -> torch.device:
+        return self.values.device
+
+    @property
+    def shape(self) -> tuple[int, int]:
+        return (self.rows, self.k)
+
+
+@dataclass(frozen=True)
+class MXFP8Tensor:
+    """A byte-aligned E4M3 matrix and UE8M0/32 scales for native W6A8."""
+
+    values: torch.Tensor
+    scales: torch.Tensor
+    rows: int
+    k: int
+
+    @property
+    def device(self) -> torch.device:
+        return self.values.device
+
+    @property
+    def shape(self) -> tuple[int, int]:
+        return (self.rows, self.k)
+
+    def dequantized_values(self) -> torch.Tensor:
+        """Return the E4M3 payload viewed as a float8 matrix (without scales)."""
+        return self.values.view(self.rows, self.k).view(torch.float8_e4m3fn)
+
+
+def _validate_float_activation(input: torch.Tensor) -> tuple[int, int]:
+    if input.device.type != "cuda":
+        raise ValueError(f"input must be a CUDA tensor; got {input.device}")
+    if input.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError(
+            f"input must have dtype torch.float16 or torch.bfloat16; got {input.dtype}"
+        )
+    if input.ndim != 2:
+        raise ValueError(f"input must have shape [M,K]; got {tuple(input.shape)}")
+    if not input.is_contiguous():
+        raise ValueError("input must be contiguous")
+    rows, k = (int(value) for value in input.shape)
+    if rows <= 0 or k <= 0 or k % SCALE_VECTOR_SIZE:
+        raise ValueError("M must be positive and K a positive multiple of 32")
+    return rows, k
+
+
+def packed_scale_numel(rows: int, k: int) -> int:
+    """Bytes of a packed scale buffer: ceil128(rows) * ceil4(k / 32)."""
+    groups = (k // SCALE_VECTOR_SIZE + 3) // 4 * 4
+    return (rows + 127) // 128 * 128 * groups
+
+
+# --------------------------------------------------------------------------- layout
+
+
+def pack_fp6(codes: torch.Tensor) -> torch.Tensor:
+    """Pack CUDA uint8 E3M2 codes, four 6-bit values into three bytes.
+
+    ``codes`` may have any shape, must be contiguous, and must contain a number
+    of elements divisible by four.  Only each byte's low six bits are used.  The
+    returned packed representation is one-dimensional.
+    """
+    _require_cuda_uint8_contiguous(codes, "codes")
+    if codes.numel() % 4:
+        raise ValueError("codes.numel() must be divisible by four")
+    n = codes.numel()
+    out = torch.empty(n // 4 * 3, dtype=torch.uint8, device=codes.device)
+    with torch.cuda.device(codes.device):
+        check(library().mxfp6_pack_fp6(codes.data_ptr(), n, out.data_ptr(), _stream(codes.device)))
+    return out
+
+
+def unpack_fp6(packed: torch.Tensor, rows: int, k: int) -> torch.Tensor:
+    """Unpack a physical E3M2 bitstream to CUDA uint8 codes ``[rows, k]``."""
+    _require_cuda_uint8_contiguous(packed, "packed")
+    if rows <= 0 or k <= 0 or k % 4:
+        raise ValueError("rows must be positive and k must be divisible by four")
+    if packed.numel() < rows * k // 4 * 3:
+        raise ValueError("packed is too small for rows * k codes")
+    out = torch.empty((rows, k), dtype=torch.uint8, device=packed.device)
+    with torch.cuda.device(packed.device):
+        check(
+            library().mxfp6_unpack_fp6(
+                packed.data_ptr(), rows, k, out.data_ptr(), _stream(packed.device)
+            )
+        )
+    return out
+
+
+def pad_fp6(packed: torch.Tensor) -> torch.Tensor:
+    """Pad packed FP6 12-byte segments to aligned 16-byte MMA segments."""
+    _require_cuda_uint8_contiguous(packed, "packed")
+    if packed.ndim < 1 or packed.shape[-1] <= 0 or packed.shape[-1] % 12:
+        raise ValueError("packed last dimension must be a positive multiple of 12")
+    shape = (*packed.shape[:-1], packed.shape[-1] // 12 * 16)
+    out = torch.empty(shape, dtype=torch.uint8, device=packed.device)
+    with torch.cuda.device(packed.device):
+        check(
+            library().mxfp6_pad_fp6(
+                packed.data_ptr(), packed.numel(), out.data_ptr(), _stream(packed.device)
+            )
+        )
+    return out
+
+
+def to_mma_k64_weight(weight: torch.Tensor) -> torch.Tensor:
+    """Transpose packed ``[E,N,64]`` weights (kept for API compatibility)."""
+    _require_cuda_uint8_contiguous(weight, "weight")
+    if weight.ndim != 3 or weight.shape[2] != 48:
+        raise ValueError("weight must contain packed [E,N,64] FP6 values")
+    experts, rows, _ = weight.shape
+    codes = unpack_fp6(weight, experts * rows, 64)
+    transposed = codes.view(experts, rows, 64).transpose(1, 2).contiguous()
+    return pack_fp6(transposed.flatten(0, 1)).view_as(weight)
+
+
+def expand_fp6_to_fp8(packed: torch.Tensor, rows: int, k: int) -> torch.Tensor:
+    """Losslessly expand packed E3M2 to a ``torch.float8_e4m3fn`` matrix."""
+    _require_cuda_uint8_contiguous(packed, "packed")
+    if rows <= 0 or k <= 0 or k % 16:
+        raise ValueError("rows must be positive and k must be divisible by 16")
+    if packed.numel() < rows * k // 4 * 3:
+        raise ValueError("packed is too small for rows * k codes")
+    out = torch.empty((rows, k), dtype=torch.uint8, device=packed.device)
+    with torch.cuda.device(packed.device):
+        check(
+            library().mxfp6_expand_fp6_to_fp8(
+                packed.data_ptr(), rows, k, out.data_ptr(), _stream(packed.device)
+            )
+        )
+    return out.view(torch.float8_e4m3fn)
+
+
+def pack_scales(logical: torch.Tensor) -> torch.Tensor:
+    """Reorder logical UE8M0 scales to the packed 128x4-atom physical layout.
+
+    ``logical`` is a contiguous CUDA uint8 tensor of shape ``[rows, k / 32]``.
+    Byte values are encoded UE8M0 exponents (``0x7f`` represents 1.0).
+    """
+    _require_cuda_uint8_contiguous(logical, "logical scales")
+    if logical.ndim != 2 or logical.shape[0] <= 0 or logical.shape[1] <= 0:
+        raise ValueError("logical scales must have shape [rows, k / 32]")
+    rows, k_blocks = (int(v) for v in logical.shape)
+    k = k_blocks * SCALE_VECTOR_SIZE
+    out = torch.empty(packed_scale_numel(rows, k), dtype=torch.uint8, device=logical.device)
+    with torch.cuda.device(logical.device):
+        check(
+            library().mxfp6_pack_scales(
+                logical.data_ptr(), rows, k, out.data_ptr(), _stream(logical.device)
+            )
+        )
+    return out
+
+
+def unpack_scales(packed: torch.Tensor, rows: int, k: int) -> torch.Tensor:
+    """Convert packed scales back to logical ``[rows, k / 32]``."""
+    _require_cuda_uint8_contiguous(packed, "packed scales")
+    if rows <= 0 or k <= 0 or k % SCALE_VECTOR_SIZE:
+        raise ValueError("rows must be positive and k must be divisible by 32")
+    if packed.numel() < packed_scale_numel(rows, k):
+        raise ValueError("packed scales are too small for rows x k")
+    out = torch.empty((rows, k // SCALE_VECTOR_SIZE), dtype=torch.uint8, device=packed.device)
+    with torch.cuda.device(packed.device):
+        check(
+            library().mxfp6_unpack_scales(
+                packed.data_ptr(), rows, k, out.data_ptr(), _stream(packed.device)
+            )
+        )
+    return out
+
+
+def pack_grouped_scales(
+    logical: torch.Tensor,
+    expert_offsets: torch.Tensor,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Pack logical scales independently for each contiguous expert group.
+
+    ``logical`` has shape ``[M, K / 32]`` after MoE routing and
+    ``expert_offsets`` contains ``E + 1`` int64 row offsets.  The returned
+    scale offsets keep every expert on a 128-row scale-atom boundary.
+    """
+    _require_cuda_uint8_contiguous(logical, "logical scales")
+    if logical.ndim != 2 or logical.shape[0] <= 0 or logical.shape[1] <= 0:
+        raise ValueError("logical scales must have shape [M, K / 32]")
+    if (
+        expert_offsets.device != logical.device
+        or expert_offsets.dtype != torch.int64
+        or expert_offsets.ndim != 1
+        or expert_offsets.numel() < 2
+        or not expert_offsets.is_contiguous()
+    ):
+        raise ValueError(
+            "expert_offsets must be a contiguous CUDA int64 tensor with E+1 entries"
+        )
+    rows, groups = (int(v) for v in logical.shape)
+    experts = expert_offsets.numel() - 1
+    # Upper bound of padded rows: every expert may add up to 127 rows of padding.
+    padded_rows = (rows + 127) // 128 * 128 + 128 * min(experts, rows)
+    k = groups * SCALE_VECTOR_SIZE
+    scale_offsets = torch.empty(experts + 1, dtype=torch.int64, device=logical.device)
+    packed = torch.empty(
+        padded_rows * ((groups + 3) // 4 * 4), dtype=torch.uint8, device=logical.device
+    )
+    stream = _stream(logical.device)
+    with torch.cuda.device(logical.device):
+        check(
+            library().mxfp6_grouped_scale_offsets(
+                expert_offsets.data_ptr(), experts, scale_offsets.data_ptr(), stream
+            )
+        )
+        check(
+            library().mxfp6_pack_grouped_scales(
+                logical.data_ptr(),
+                expert_offsets.data_ptr(),
+                scale_offsets.data_ptr(),
+                experts,
+                padded_rows,
+                k,
+                packed.data_ptr(),
+                stream,
+            )
+        )
+    return packed, scale_offsets
+
+
+def pack_operand(codes: torch.Tensor, logical_scales: torch.Tensor) -> PackedMXFP6Tensor:
+    """Pack a logical ``[rows, k]`` E3M2 operand and its UE8M0 scales."""
+    _require_cuda_uint8_contiguous(codes, "codes")
+    _require_cuda_uint8_contiguous(logical_scales, "logical_scales")
+    if codes.ndim != 2:
+        raise ValueError("codes must have shape [rows, k]")
+    rows, k = (int(value) for value in codes.shape)
+    expected_scale_shape = (rows, k // SCALE_VECTOR_SIZE)
+    if k % SCALE_VECTOR_SIZE or tuple(logical_scales.shape) != expected_scale_shape:
+        raise ValueError(
+            f"logical_scales must have shape {expected_scale_shape}; "
+            f"got {tuple(logical_scales.shape)}"
+        )
+    if codes.device != logical_scales.device:
+        raise ValueError("codes and logical_scales must be on the same device")
+    return PackedMXFP6Tensor(
+        pack_fp6(codes),
+        pack_scales(logical_scales),
+        rows,
+        k,
+        logical_scales,
+    )
+
+
+def unpack_operand(operand: PackedMXFP6Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Return logical E3M2 codes and logical UE8M0 scales for an operand."""
+    logical_scales = operand.logical_scales
+    if logical_scales is None:
+        logical_scales = unpack_scales(operand.scales, operand.rows, operand.k)
+    return (
+        unpack_fp6(operand.values, operand.rows, operand.k),
+        logical_scales,
+    )
+
+
+# ----------------------------------------------------------------------- quantizers
+
+
+def _quantize_mxfp8_raw(
+    input: torch.Tensor,
+    values: torch.Tensor,
+    packed: torch.Tensor | None,
+    logical: torch.Tensor | None,
+) -> None:
+    rows, k = (int(v) for v in input.shape)
+    with torch.cuda.device(input.device):
+        check(
+            library().mxfp6_quantize_mxfp8(
+                input.data_ptr(),
+                _DTYPE_CODE[input.dtype],
+                rows,
+                k,
+                values.data_ptr(),
+                _ptr(packed),
+                _ptr(logical),
+                _stream(input.device),
+            )
+        )
+
+
+def quantize_mxfp8(input: torch.Tensor) -> MXFP8Tensor:
+    """Dynamically map a contiguous FP16/BF16 ``[M,K]`` activation to MXFP8.
+
+    Quantization uses one power-of-two UE8M0 scale per 32 consecutive K
+    values.  The returned value bytes and scales are already in the layouts
+    consumed by the native W6A8 kernels.
+    """
+    rows, k = _validate_float_activation(input)
+    _require_sm100(input.device)
+    load_library()
+    values = torch.empty(rows * k, dtype=torch.uint8, device=input.device)
+    scales = torch.empty(packed_scale_numel(rows, k), dtype=torch.uint8, device=input.device)
+    _quantize_mxfp8_raw(input, values, scales, None)
+    return MXFP8Tensor(values, scales, rows, k)
+
+
+def quantize_mxfp8_logical(input: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Quantize to MXFP8 with row-major ``[M,K/32]`` UE8M0 scales."""
+    rows, k = _validate_float_activation(input)
+    _require_sm100(input.device)
+    load_library()
+    values = torch.empty((rows, k), dtype=torch.uint8, device=input.device)
+    scales = torch.empty((rows, k // SCALE_VECTOR_SIZE), dtype=torch.uint8, device=input.device)
+    _quantize_mxfp8_raw(input, values, None, scales)
+    return values.view(torch.float8_e4m3fn), scales
+
+
+def quantize_mxfp8_dual(
+    input: torch.Tensor,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Quantize once and emit both the logical and the packed scale layouts."""
+    rows, k = _validate_float_activation(input)
+    _require_sm100(input.device)
+    load_library()
+    values = torch.empty((rows, k), dtype=torch.uint8, device=input.device)
+    logical = torch.empty((rows, k // SCALE_VECTOR_SIZE), dtype=torch.uint8, device=input.device)
+    packed = torch.empty(packed_scale_numel(rows, k), dtype=torch.uint8, device=input.device)
+    _quantize_mxfp8_raw(input, values, packed, logical)
+    return values.view(torch.float8_e4m3fn), logical, packed
+
+
+def quantize_mxfp8_dual_out(
+    output: torch.Tensor,
+    logical_scales: torch.Tensor,
+    packed_scales: torch.Tensor,
+    input: torch.Tensor,
+) -> None:
+    """Write one MXFP8 value tensor and both scale layouts in one kernel."""
+    rows, k = _validate_float_activation(input)
+    _require_sm100(input.device)
+    expected = (
+        (output, torch.uint8, (rows, k), "output"),
+        (logical_scales, torch.uint8, (rows, k // SCALE_VECTOR_SIZE), "logical_scales"),
+    )
+    for tensor, dtype, shape, name in expected:
+        if (
+            tensor.device != input.device
+            or tensor.dtype != dtype
+            or tensor.shape != shape
+            or not tensor.is_contiguous()
+        ):
+            raise ValueError(f"{name} must be contiguous CUDA {dtype} {shape}")
+    packed_size = packed_scale_numel(rows, k)
+    if (
+        packed_scales.device != input.device
+        or packed_scales.dtype != torch.uint8
+        or packed_scales.numel() < packed_size
+        or not packed_scales.is_contiguous()
+    ):
+        raise ValueError(
+            "packed_scales must be contiguous CUDA uint8 with at least "
+            f"{packed_size} values"
+        )
+    load_library()
+    _quantize_mxfp8_raw(input, output, packed_scales, logical_scales)
+
+
+def quantize_activation(input: torch.Tensor) -> MXFP8Tensor:
+    """Alias of :func:`quantize_mxfp8` (the 16-to-8 activation mapping)."""
+    return quantize_mxfp8(input)
+
+
+def quantize_mxfp6(input: torch.Tensor) -> PackedMXFP6Tensor:
+    """Dynamically map a contiguous FP16/BF16 ``[rows,K]`` matrix to packed MXFP6."""
+    rows, k = _validate_float_activation(input)
+    _require_sm100(input.device)
+    load_library()
+    values = torch.empty(rows * k // 4 * 3, dtype=torch.uint8, device=input.device)
+    scales = torch.empty(packed_scale_numel(rows, k), dtype=torch.uint8, device=input.device)
+    with torch.cuda.device(input.device):
+        check(
+            library().mxfp6_quantize_mxfp6(
+                input.data_ptr(),
+                _DTYPE_CODE[input.dtype],
+                rows,
+                k,
+                values.data_ptr(),
+                scales.data_ptr(),
+                None,
+                _stream(input.device),
+            )
+        )
+    return PackedMXFP6Tensor(values, scales, rows, k)
+
+
+# --------------------------------------------------------------------------- dense GEMM
+
+
+def gemm_w6a8_plan(m: int, n: int, k: int, tile_tokens: int = 0, splits: int = 0) -> dict[str, int]:
+    """Tile/split-K choice the library makes for a dense problem (host arithmetic)."""
+    _validate_problem(m, n, k)
+    plan = (ctypes.c_int64 * 6)()
+    check(library().mxfp6_gemm_w6a8_plan(m, n, k, tile_tokens, splits, plan))
+    keys = ("tile_tokens", "splits", "stages", "grid", "partial_bytes", "counter_bytes")
+    return dict(zip(keys, (int(v) for v in plan)))
+
+
+def gemm_w6a8(
+    a: MXFP8Tensor,
+    b: PackedMXFP6Tensor,
+    alpha: float = 1.0,
+    *,
+    out_dtype: torch.dtype = torch.float16,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Compute native ``MXFP8(A) @ MXFP6(B).T`` on SM100."""
+    out_dtype = _validate_output_dtype(out_dtype)
+    if not isinstance(a, MXFP8Tensor):
+        raise TypeError("a must be an MXFP8Tensor instance")
+    if not isinstance(b, PackedMXFP6Tensor):
+        raise TypeError("b must be a PackedMXFP6Tensor instance")
+    if a.k != b.k:
+        raise ValueError(f"a.k and b.k must match; got {a.k} and {b.k}")
+    if a.device != b.device:
+        raise ValueError("a and b must be on the same CUDA device")
+    _validate_problem(a.rows, b.rows, a.k)
+    for tensor, name in (
+        (a.values, "a.values"),
+        (a.scales, "a.scales"),
+        (b.values, "b.values"),
+        (b.scales, "b.scales"),
+    ):
+        _require_cuda_uint8_contiguous(tensor, name)
+    _require_sm100(a.device)
+    load_library()
+    if out is None:
+        out = torch.empty((a.rows, b.rows), dtype=out_dtype, device=a.device)
+    elif out.shape != (a.rows, b.rows) or out.dtype != out_dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [M,N] tensor of out_dtype")
+    with torch.cuda.device(a.device):
+        check(
+            library().mxfp6_gemm_w6a8(
+                a.values.data_ptr(),
+                a.scales.data_ptr(),
+                b.values.data_ptr(),
+                b.scales.data_ptr(),
+                a.rows,
+                b.rows,
+                a.k,
+                float(alpha),
+                out.data_ptr(),
+                _DTYPE_CODE[out_dtype],
+                _stream(a.device),
+            )
+        )
+    return out
+
+
+def gemm_w6a8_config(
+    a: MXFP8Tensor,
+    b: PackedMXFP6Tensor,
+    alpha: float = 1.0,
+    *,
+    out_dtype: torch.dtype = torch.float16,
+    tile_tokens: int = 0,
+    splits: int = 0,
+    scratch: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Run one explicit tile/split-K configuration with caller-owned scratch."""
+    out_dtype = _validate_output_dtype(out_dtype)
+    _validate_problem(a.rows, b.rows, a.k)
+    _require_sm100(a.device)
+    load_library()
+    plan = gemm_w6a8_plan(a.rows, b.rows, a.k, tile_tokens, splits)
+    need = plan["partial_bytes"] + plan["counter_bytes"]
+    if need and (scratch is None or scratch.numel() * scratch.element_size() < need):
+        scratch = torch.zeros(need, dtype=torch.uint8, device=a.device)
+    out = torch.empty((a.rows, b.rows), dtype=out_dtype, device=a.device)
+    with torch.cuda.device(a.device):
+        check(
+            library().mxfp6_gemm_w6a8_ex(
+                a.values.data_ptr(),
+                a.scales.data_ptr(),
+                b.values.data_ptr(),
+                b.scales.data_ptr(),
+                a.rows,
+                b.rows,
+                a.k,
+                float(alpha),
+                out.data_ptr(),
+                _DTYPE_CODE[out_dtype],
+                tile_tokens,
+                splits,
+                _ptr(scratch),
+                0 if scratch is None else scratch.numel() * scratch.element_size(),
+                _stream(a.device),
+            )
+        )
+    return out
+
+
+def gemm_from_float(
+    a: torch.Tensor,
+    b: PackedMXFP6Tensor,
+    alpha: float = 1.0,
+    *,
+    out_dtype: torch.dtype = torch.float16,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Quantize FP16/BF16 A to MXFP8 and run the native W6A8 GEMM.
+
+    Weight B remains packed at six bits.  Quantization and GEMM are launched
+    back to back on the current CUDA stream.
+    """
+    out_dtype = _validate_output_dtype(out_dtype)
+    rows, k = _validate_float_activation(a)
+    if not isinstance(b, PackedMXFP6Tensor):
+        raise TypeError("b must be a PackedMXFP6Tensor instance")
+    if k != b.k:
+        raise ValueError(f"a.shape[1] and b.k must match; got {k} and {b.k}")
+    if a.device != b.device:
+        raise ValueError("a and b must be on the same CUDA device")
+    _validate_problem(rows, b.rows, k)
+    _require_sm100(a.device)
+    load_library()
+    stage_values = torch.empty(rows * k, dtype=torch.uint8, device=a.device)
+    stage_scales = torch.empty(packed_scale_numel(rows, k), dtype=torch.uint8, device=a.device)
+    if out is None:
+        out = torch.empty((rows, b.rows), dtype=out_dtype, device=a.device)
+    elif out.shape != (rows, b.rows) or out.dtype != out_dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [M,N] tensor of out_dtype")
+    with torch.cuda.device(a.device):
+        check(
+            library().mxfp6_gemm_from_float(
+                a.data_ptr(),
+                _DTYPE_CODE[a.dtype],
+                b.values.data_ptr(),
+                b.scales.data_ptr(),
+                rows,
+                b.rows,
+                k,
+                float(alpha),
+                out.data_ptr(),
+                _DTYPE_CODE[out_dtype],
+                stage_values.data_ptr(),
+                stage_scales.data_ptr(),
+                _stream(a.device),
+            )
+        )
+    return out
+
+
+def gemm_packed(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    sfa: torch.Tensor,
+    sfb: torch.Tensor,
+    m: int,
+    n: int,
+    k: int,
+    alpha: float = 1.0,
+    *,
+    out_dtype: torch.dtype = torch.float16,
+) -> torch.Tensor:
+    """Low-level ``A @ B.T`` for already packed MXFP6 values and scales (W6A6).
+
+    The activation operand is expanded losslessly from E3M2 to E4M3
+    (:func:`expand_fp6_to_fp8`) and then takes the W6A8 kernel, which computes
+    the same products exactly.
+    """
+    out_dtype = _validate_output_dtype(out_dtype)
+    _validate_problem(m, n, k)
+    for tensor, name in ((a, "a"), (b, "b"), (sfa, "sfa"), (sfb, "sfb")):
+        _require_cuda_uint8_contiguous(tensor, name)
+    devices = {a.device, b.device, sfa.device, sfb.device}
+    if len(devices) != 1:
+        raise ValueError("a, b, sfa, and sfb must be on the same CUDA device")
+    _require_sm100(a.device)
+    load_library()
+    expanded = expand_fp6_to_fp8(a, m, k).view(torch.uint8).reshape(-1)
+    return gemm_w6a8(
+        MXFP8Tensor(expanded, sfa, m, k),
+        PackedMXFP6Tensor(b, sfb, n, k),
+        alpha,
+        out_dtype=out_dtype,
+    )
+
+
+def warmup_w6a8(
+    b: PackedMXFP6Tensor,
+    m_values: tuple[int, ...] | list[int],
+    *,
+    out_dtype: torch.dtype = torch.float16,
+) -> None:
+    """Run every listed batch size once (tensor maps, lanes and kernels get set up)."""
+    for m in m_values:
+        a = torch.zeros((int(m), b.k), dtype=torch.bfloat16, device=b.device)
+        gemm_from_float(a, b, out_dtype=out_dtype)
+    torch.cuda.synchronize(b.device)
+
+
+def autotune_w6a8(*args, **kwargs):
+    """Candidate search is replaced by a static per-M table; returns ``None``."""
+    return None
+
+
+def gemm(
+    a: torch.Tensor | MXFP8Tensor | PackedMXFP6Tensor,
+    b: PackedMXFP6Tensor,
+    alpha: float = 1.0,
+    *,
+    out_dtype: torch.dtype = torch.float16,
+) -> torch.Tensor:
+    """Compute ``A @ B.T`` using the native kernels.
+
+    FP16/BF16 activation tensors are dynamically mapped 16-to-8 and use W6A8
+    for every batch size.  :class:`MXFP8Tensor` skips that conversion.  Packed
+    MXFP6 activation inputs keep the W6A6-compatible API.
+    """
+    out_dtype = _validate_output_dtype(out_dtype)
+    if isinstance(a, torch.Tensor):
+        if not isinstance(b, PackedMXFP6Tensor):
+            raise TypeError("FP16/BF16 activation input requires a PackedMXFP6Tensor weight")
+        return gemm_from_float(a, b, alpha, out_dtype=out_dtype)
+    if isinstance(a, MXFP8Tensor):
+        if not isinstance(b, PackedMXFP6Tensor):
+            raise TypeError("MXFP8 activation requires a PackedMXFP6Tensor weight")
+        return gemm_w6a8(a, b, alpha, out_dtype=out_dtype)
+    if not isinstance(a, PackedMXFP6Tensor):
+        raise TypeError("a must be an FP16/BF16 Tensor, MXFP8Tensor, or PackedMXFP6Tensor")
+    if not isinstance(b, PackedMXFP6Tensor):
+        raise TypeError("b must be a PackedMXFP6Tensor instance")
+    if a.k != b.k:
+        raise ValueError(f"a.k and b.k must match; got {a.k} and {b.k}")
+    if a.device != b.device:
+        raise ValueError("a and b must be on the same CUDA device")
+    return gemm_packed(
+        a.values, b.values, a.scales, b.scales, a.rows, b.rows, a.k, alpha, out_dtype=out_dtype
+    )
+
+
+def gemm_from_codes(
+    a_codes: torch.Tensor,
+    b_codes: torch.Tensor,
+    sfa_logical: torch.Tensor,
+    sfb_logical: torch.Tensor,
+    alpha: float = 1.0,
+    *,
+    out_dtype: torch.dtype = torch.float16,
+) -> torch.Tensor:
+    """Convenience path that packs both operands before ``A @ B.T``."""
+    return gemm(
+        pack_operand(a_codes, sfa_logical),
+        pack_operand(b_codes, sfb_logical),
+        alpha,
+        out_dtype=out_dtype,
+    )
+
+
+def is_tuned_shape(m: int, n: int, k: int) -> bool:
+    """Return whether a problem is one the static table was measured on."""
+    return m in TUNED_M and (n, k) in TUNED_NK
+
+
+def is_available() -> bool:
+    """Return whether the library can load and the current GPU is SM100."""
+    if not torch.cuda.is_available():
+        return False
+    try:
+        load_library()
+        return torch.cuda.get_device_capability() == (10, 0)
+    except (ImportError, OSError, RuntimeError):
+        return False
