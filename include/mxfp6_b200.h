@@ -45,6 +45,11 @@ const char* mxfp6_b200_last_error(void);
  * bounded waits write when a wait expires (0 = none did).  `reset` != 0 clears it. */
 int mxfp6_b200_device_status(int* value, int reset);
 
+/* Diagnostics: CTA 0 of every later GEMM launch writes 3 x 256 int64 cycle stamps
+ * (stage issued by the TMA warp, stage seen ready by the MMA warp, stage committed)
+ * into trace_dev; NULL switches tracing off. */
+int mxfp6_b200_set_trace_buffer(void* trace_dev);
+
 /* ---- layout utilities ------------------------------------------------- */
 
 /* torch.ops.mxfp6.pack_fp6 (csrc/torch_extension.cu:2121-2156, kernels

@@ -25,6 +25,7 @@ SIGNATURES: dict[str, tuple] = {
     "mxfp6_b200_abi_version": (c_int, []),
     "mxfp6_b200_last_error": (c_char_p, []),
     "mxfp6_b200_device_status": (c_int, [_IP, c_int]),
+    "mxfp6_b200_set_trace_buffer": (c_int, [c_void_p]),
     "mxfp6_pack_fp6": (c_int, [c_void_p, c_int64, c_void_p, c_void_p]),
     "mxfp6_unpack_fp6": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "mxfp6_pad_fp6": (c_int, [c_void_p, c_int64, c_void_p, c_void_p]),

@@ -217,6 +217,11 @@ int mxfp6_b200_device_status(int* value, int reset) {
   return read_device_status(device, value, reset != 0);
 }
 
+int mxfp6_b200_set_trace_buffer(void* trace_dev) {
+  set_trace_buffer(static_cast<long long*>(trace_dev));
+  return kOk;
+}
+
 int mxfp6_pack_fp6(const uint8_t* codes, int64_t n, uint8_t* packed, void* stream) {
   return pack_fp6(codes, n, packed, static_cast<cudaStream_t>(stream));
 }

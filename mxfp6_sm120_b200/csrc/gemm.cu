@@ -39,6 +39,9 @@ constexpr int kMmaK = 32;           // K values per tcgen05.mma
 constexpr int kThreads = 192;       // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 constexpr int kMaxGroups = 512;
 constexpr uint32_t kWTileBytes = kTileF * kTileK;  // padded 6-bit rows: 128 B per row
+// The mbarrier transaction count of a 16U6_ALIGN16B load is the PACKED byte count
+// read from global memory (12 of every 16 shared-memory bytes), measured on B200.
+constexpr uint32_t kWTileTxBytes = kWTileBytes / 4 * 3;
 constexpr uint32_t kAtomBytes = 512;
 constexpr long long kWaitCycles = 4000000000ll;    // about two seconds
 
@@ -61,20 +64,28 @@ struct KernelArgs {
   float alpha;
   uint32_t w_tx_bytes;  // bytes one weight-tile TMA adds to the mbarrier
   int a_scale_row_blocks;  // 128-row blocks present in the activation scale buffer
+  long long* trace;        // optional [3][256] cycle stamps of CTA 0 (diagnostics), or null
 };
 
 template <int TN>
 struct Cfg {
-  static constexpr int kAcc = (2 * TN + 12 <= 512) ? 2 : 1;  // accumulator buffers
   static constexpr int kSfbAtoms = TN <= 128 ? 1 : 2;
+  // 128-K blocks per pipeline stage.  Narrow tiles are bound by the per-stage cost
+  // of the issuing warps (barrier wait, fence, commit), so they take more K per stage.
+  static constexpr int kSubs = TN <= 32 ? 4 : (TN <= 96 ? 2 : 1);
+  // Scale columns rotate through several sets so that the tcgen05.cp of a block
+  // never overwrites scales an earlier, still running MMA reads.
+  static constexpr int kSfSets = 4;
+  static constexpr int kSfSetCols = 4 + 4 * kSfbAtoms;
+  static constexpr int kAcc = (2 * TN + kSfSets * kSfSetCols <= 512) ? 2 : 1;  // accumulator buffers
   static constexpr int kSfaCol = kAcc * TN;
   static constexpr int kSfbCol = kSfaCol + 4;
-  static constexpr int kColsUsed = kSfbCol + 4 * kSfbAtoms;
+  static constexpr int kColsUsed = kSfaCol + kSfSets * kSfSetCols;
   static constexpr int kTmemCols =
       kColsUsed <= 32 ? 32 : kColsUsed <= 64 ? 64 : kColsUsed <= 128 ? 128 : kColsUsed <= 256 ? 256 : 512;
   static constexpr uint32_t kATileBytes = TN * kTileK;
-  static constexpr uint32_t kStageBytes = kWTileBytes + kATileBytes;
-  static constexpr uint32_t kSfStageBytes = kAtomBytes * (1 + kSfbAtoms);
+  static constexpr uint32_t kStageBytes = kSubs * (kWTileBytes + kATileBytes);
+  static constexpr uint32_t kSfStageBytes = kSubs * kAtomBytes * (1 + kSfbAtoms);
   static constexpr uint32_t kFixedBytes = 1024 /*align slack*/ + 4096 /*barriers + tables*/;
   static constexpr int kStagesRaw =
       (int)((232448u - kFixedBytes) / (kStageBytes + kSfStageBytes));
@@ -153,8 +164,8 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* w_tiles = smem;
-  uint8_t* a_tiles = w_tiles + (size_t)C::kStages * kWTileBytes;
-  uint8_t* sf_tiles = a_tiles + (size_t)C::kStages * C::kATileBytes;
+  uint8_t* a_tiles = w_tiles + (size_t)C::kStages * C::kSubs * kWTileBytes;
+  uint8_t* sf_tiles = a_tiles + (size_t)C::kStages * C::kSubs * C::kATileBytes;
   uint8_t* fixed = sf_tiles + (size_t)C::kStages * C::kSfStageBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(fixed);  // full[S], empty[S], tfull[2], tempty[2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fixed + 8 * (2 * C::kStages + 4));
@@ -226,11 +237,14 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-    if (lane == 0) {
+    // The whole warp runs the loop (so that addresses stay warp-uniform) and one
+    // elected lane issues the copies.
+    {
       int stage = 0;
       uint32_t phase = 0;
-      const uint32_t tx = args.w_tx_bytes + C::kATileBytes + kAtomBytes * (1 + C::kSfbAtoms);
+      const uint32_t tx_sub = args.w_tx_bytes + C::kATileBytes + kAtomBytes * (1 + C::kSfbAtoms);
       const int atoms_per_rb = kb_total;  // k/128 atoms per 128-row block
+      int trace_i = 0;
       Work wk;
       bool ok = true;
       for (int w = blockIdx.x; ok && decode_work<TN>(w, args, tile_prefix, &wk); w += gridDim.x) {
@@ -240,29 +254,43 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         const uint8_t* sfa_src =
             args.w_scales + ((int64_t)(w_row / kAtomRows) * atoms_per_rb) * kAtomBytes;
         const int sfb_rb0 = (int)(wk.scale_row0 / kAtomRows);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!bounded_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag, args.status, 101)) {
-            ok = false;
-            break;
-          }
+        for (int kb = kb0; kb < kb1; kb += C::kSubs) {
+          const int nsub = (kb1 - kb) < C::kSubs ? (kb1 - kb) : C::kSubs;
+          ok = __all_sync(0xffffffffu, bounded_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag,
+                                                    args.status, 101));
+          if (!ok) break;
           const uint32_t bar = full0 + 8 * stage;
-          ptx::mbar_arrive_expect_tx(bar, tx);
-          ptx::tma_load_2d(ptx::smem_u32(w_tiles + (size_t)stage * kWTileBytes), &tm_w,
-                           kb * kTileK, w_row, bar);
-          ptx::tma_load_2d(ptx::smem_u32(a_tiles + (size_t)stage * C::kATileBytes), &tm_a,
-                           kb * kTileK, (int)wk.row0, bar);
-          uint8_t* sf = sf_tiles + (size_t)stage * C::kSfStageBytes;
-          ptx::bulk_load(ptx::smem_u32(sf), sfa_src + (int64_t)kb * kAtomBytes, kAtomBytes, bar);
-#pragma unroll
-          for (int j = 0; j < C::kSfbAtoms; ++j) {
-            // A tile that ends inside the last row block re-reads that block
-            // for the rows it does not have; those accumulator rows are never stored.
-            int rb = sfb_rb0 + j;
-            if (rb >= args.a_scale_row_blocks) rb = args.a_scale_row_blocks - 1;
-            ptx::bulk_load(ptx::smem_u32(sf + kAtomBytes * (1 + j)),
-                           args.a_scales + ((int64_t)rb * atoms_per_rb + kb) * kAtomBytes,
-                           kAtomBytes, bar);
+          if (args.trace != nullptr && blockIdx.x == 0 && trace_i < 256) {
+            if (lane == 0) args.trace[trace_i] = clock64();
+            ++trace_i;
           }
+          if (ptx::elect_one()) {
+            ptx::mbar_arrive_expect_tx(bar, tx_sub * nsub);
+            for (int sub = 0; sub < nsub; ++sub) {
+              ptx::tma_load_2d(
+                  ptx::smem_u32(w_tiles + (size_t)(stage * C::kSubs + sub) * kWTileBytes), &tm_w,
+                  (kb + sub) * kTileK, w_row, bar);
+              ptx::tma_load_2d(
+                  ptx::smem_u32(a_tiles + (size_t)(stage * C::kSubs + sub) * C::kATileBytes),
+                  &tm_a, (kb + sub) * kTileK, (int)wk.row0, bar);
+            }
+            // Scale atoms of consecutive K blocks are adjacent in memory: one bulk
+            // copy per operand row block covers the whole stage.
+            uint8_t* sf = sf_tiles + (size_t)stage * C::kSfStageBytes;
+            ptx::bulk_load(ptx::smem_u32(sf), sfa_src + (int64_t)kb * kAtomBytes,
+                           kAtomBytes * nsub, bar);
+#pragma unroll
+            for (int j = 0; j < C::kSfbAtoms; ++j) {
+              // A tile that ends inside the last row block re-reads that block for
+              // the rows it does not have; those accumulator rows are never stored.
+              int rb = sfb_rb0 + j;
+              if (rb >= args.a_scale_row_blocks) rb = args.a_scale_row_blocks - 1;
+              ptx::bulk_load(ptx::smem_u32(sf + kAtomBytes * C::kSubs * (1 + j)),
+                             args.a_scales + ((int64_t)rb * atoms_per_rb + kb) * kAtomBytes,
+                             kAtomBytes * nsub, bar);
+            }
+          }
+          __syncwarp();
           if (++stage == C::kStages) {
             stage = 0;
             phase ^= 1u;
@@ -272,7 +300,7 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -281,49 +309,68 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       // UE8M0 scales, M = 128, N = TN.
       constexpr uint32_t kIdesc = (4u << 7) | (0u << 10) | ((uint32_t)(TN >> 3) << 17) |
                                   (1u << 23) | ((uint32_t)(kTileF >> 4) << 24);
-      const uint32_t sfa_t = tmem_base + C::kSfaCol;
+      uint32_t sf_set = 0;
+      int trace_i = 0;
       Work wk;
       bool ok = true;
       for (int w = blockIdx.x; ok && decode_work<TN>(w, args, tile_prefix, &wk); w += gridDim.x) {
         const int kb0 = (int)(((int64_t)wk.split * kb_total) / args.splits);
         const int kb1 = (int)(((int64_t)(wk.split + 1) * kb_total) / args.splits);
-        if (!bounded_wait(tempty0 + 8 * acc, acc_phase ^ 1u, abort_flag, args.status, 102)) break;
+        if (!__all_sync(0xffffffffu, bounded_wait(tempty0 + 8 * acc, acc_phase ^ 1u, abort_flag,
+                                                  args.status, 102)))
+          break;
         ptx::tc_fence_after();
         const uint32_t d_t = tmem_base + acc * TN;
-        const uint32_t sfb_t =
-            tmem_base + C::kSfbCol + (uint32_t)((wk.scale_row0 % kAtomRows) / 32);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!bounded_wait(full0 + 8 * stage, phase, abort_flag, args.status, 103)) {
-            ok = false;
-            break;
-          }
+        const uint32_t sfb_sub = (uint32_t)((wk.scale_row0 % kAtomRows) / 32);
+        for (int kb = kb0; kb < kb1; kb += C::kSubs) {
+          const int nsub = (kb1 - kb) < C::kSubs ? (kb1 - kb) : C::kSubs;
+          ok = __all_sync(0xffffffffu,
+                          bounded_wait(full0 + 8 * stage, phase, abort_flag, args.status, 103));
+          if (!ok) break;
           ptx::tc_fence_after();
-          const uint32_t sf = ptx::smem_u32(sf_tiles + (size_t)stage * C::kSfStageBytes);
-          ptx::tc_cp_32x128b_warpx4(sfa_t, ptx::smem_desc_scale_atom(sf));
+          if (args.trace != nullptr && blockIdx.x == 0 && trace_i < 256 && lane == 0)
+            args.trace[256 + trace_i] = clock64();
+          if (ptx::elect_one()) {
+            const uint32_t sf = ptx::smem_u32(sf_tiles + (size_t)stage * C::kSfStageBytes);
+            for (int sub = 0; sub < nsub; ++sub) {
+              const uint32_t sfa_t = tmem_base + C::kSfaCol + sf_set * C::kSfSetCols;
+              const uint32_t sfb_base = tmem_base + C::kSfbCol + sf_set * C::kSfSetCols;
+              const uint32_t sfb_t = sfb_base + sfb_sub;
+              sf_set = (sf_set + 1u) % C::kSfSets;
+              ptx::tc_cp_32x128b_warpx4(sfa_t, ptx::smem_desc_scale_atom(sf + kAtomBytes * sub));
 #pragma unroll
-          for (int j = 0; j < C::kSfbAtoms; ++j) {
-            ptx::tc_cp_32x128b_warpx4(tmem_base + C::kSfbCol + 4 * j,
-                                      ptx::smem_desc_scale_atom(sf + kAtomBytes * (1 + j)));
-          }
-          const uint64_t a_desc =
-              ptx::smem_desc_sw128(ptx::smem_u32(w_tiles + (size_t)stage * kWTileBytes));
-          const uint64_t b_desc =
-              ptx::smem_desc_sw128(ptx::smem_u32(a_tiles + (size_t)stage * C::kATileBytes));
+              for (int j = 0; j < C::kSfbAtoms; ++j) {
+                ptx::tc_cp_32x128b_warpx4(
+                    sfb_base + 4 * j,
+                    ptx::smem_desc_scale_atom(sf + kAtomBytes * (C::kSubs * (1 + j) + sub)));
+              }
+              const uint64_t a_desc = ptx::smem_desc_sw128(
+                  ptx::smem_u32(w_tiles + (size_t)(stage * C::kSubs + sub) * kWTileBytes));
+              const uint64_t b_desc = ptx::smem_desc_sw128(
+                  ptx::smem_u32(a_tiles + (size_t)(stage * C::kSubs + sub) * C::kATileBytes));
 #pragma unroll
-          for (int ks = 0; ks < kTileK / kMmaK; ++ks) {
-            const uint32_t idesc = kIdesc | ((uint32_t)ks << 4) | ((uint32_t)ks << 29);
-            // 32 K values = 32 bytes = 2 descriptor address units.
-            ptx::tc_mma_mxf8f6f4(d_t, a_desc + 2 * ks, b_desc + 2 * ks, idesc, sfa_t, sfb_t,
-                                 (kb > kb0 || ks > 0) ? 1u : 0u);
+              for (int ks = 0; ks < kTileK / kMmaK; ++ks) {
+                const uint32_t idesc = kIdesc | ((uint32_t)ks << 4) | ((uint32_t)ks << 29);
+                // 32 K values = 32 bytes = 2 descriptor address units.
+                ptx::tc_mma_mxf8f6f4(d_t, a_desc + 2 * ks, b_desc + 2 * ks, idesc, sfa_t, sfb_t,
+                                     (kb + sub > kb0 || ks > 0) ? 1u : 0u);
+              }
+            }
+            ptx::tc_commit(empty0 + 8 * stage);
           }
-          ptx::tc_commit(empty0 + 8 * stage);
+          __syncwarp();
+          if (args.trace != nullptr && blockIdx.x == 0 && trace_i < 256) {
+            if (lane == 0) args.trace[512 + trace_i] = clock64();
+            ++trace_i;
+          }
           if (++stage == C::kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        ptx::tc_commit(tfull0 + 8 * acc);
+        if (ptx::elect_one()) ptx::tc_commit(tfull0 + 8 * acc);
+        __syncwarp();
         if (++acc == C::kAcc) {
           acc = 0;
           acc_phase ^= 1u;
@@ -411,17 +458,32 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         if (last) {
           __threadfence();
           const float* base = args.partials + (size_t)wk.tile_id * args.splits * (TN * kTileF);
-          for (int t = 0; t < wk.rows; ++t) {
-            float sum = 0.0f;
+          // Eight rows at a time so that 8 x splits independent loads are in
+          // flight per thread; the sum over splits stays in split order.
+          for (int t0 = 0; t0 < wk.rows; t0 += 8) {
+            float sum[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum[j] = 0.0f;
             for (int s = 0; s < args.splits; ++s) {
-              sum += __ldcg(base + ((size_t)s * TN + t) * kTileF + fl);
+              const float* src = base + ((size_t)s * TN + t0) * kTileF + fl;
+              float v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = (t0 + j < wk.rows) ? __ldcg(src + j * kTileF) : 0.0f;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) sum[j] += v[j];
             }
             if (f_ok) {
-              const int64_t idx = (wk.row0 + t) * args.n + f;
-              if (args.out_dtype == kBF16) {
-                static_cast<__nv_bfloat16*>(args.out)[idx] = __float2bfloat16_rn(args.alpha * sum);
-              } else {
-                static_cast<__half*>(args.out)[idx] = __float2half_rn(args.alpha * sum);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (t0 + j < wk.rows) {
+                  const int64_t idx = (wk.row0 + t0 + j) * args.n + f;
+                  if (args.out_dtype == kBF16) {
+                    static_cast<__nv_bfloat16*>(args.out)[idx] =
+                        __float2bfloat16_rn(args.alpha * sum[j]);
+                  } else {
+                    static_cast<__half*>(args.out)[idx] = __float2half_rn(args.alpha * sum[j]);
+                  }
+                }
               }
             }
           }
@@ -537,6 +599,8 @@ int cached_map(CUtensorMap* out, CUtensorMapDataType type, const void* base, uin
   return kOk;
 }
 
+long long* g_trace = nullptr;
+
 template <int TN>
 int launch_tn(const CUtensorMap& tm_w, const CUtensorMap& tm_a, const KernelArgs& args,
               const GemmPlan& plan, cudaStream_t stream) {
@@ -584,11 +648,12 @@ int plan_w6a8(const GemmProblem& p, GemmPlan* plan) {
     // Rows per group that a tile should cover.
     const int64_t rows = grouped ? (p.m_total + p.groups - 1) / p.groups : p.m_total;
     if (!grouped && rows <= 16) tn = 16;
-    else if (rows <= 32) tn = 32;
+    else if (!grouped && rows <= 32) tn = 32;
     else if (rows <= 64) tn = 64;
     else if (!grouped && rows <= 96) tn = 96;
     else if (rows <= 128) tn = 128;
-    else if (!grouped && rows % 256 == 0) tn = 256;
+    else if (!grouped && rows % 256 == 0 && p.k >= 12288) tn = 256;
+    else if (!grouped) tn = 192;
     else tn = 128;
   }
   switch (tn) {
@@ -603,10 +668,12 @@ int plan_w6a8(const GemmProblem& p, GemmPlan* plan) {
       set_error("unsupported tile_tokens %d (use 16, 32, 64, 96, 128, 192 or 256)", tn);
       return kInvalidArgument;
   }
-  MX_REQUIRE(!(grouped && (tn == 16 || tn == 96 || tn == 192)),
-             "grouped launches need tile_tokens in {32, 64, 128, 256}");
-  MX_REQUIRE(!(tn == 16 && p.m_total > 16), "tile_tokens 16 needs m <= 16");
-  MX_REQUIRE(!(tn == 96 && p.m_total > 96), "tile_tokens 96 needs m <= 96");
+  // The tensor-memory address of the activation scales must sit on an even
+  // column, so tiles that start inside a 128-row scale atom need 64-row steps.
+  MX_REQUIRE(!(grouped && (tn == 16 || tn == 32 || tn == 96)),
+             "grouped launches need tile_tokens in {64, 128, 192, 256}");
+  MX_REQUIRE(!((tn == 16 || tn == 32 || tn == 96) && p.m_total > tn),
+             "tile_tokens %d needs m <= %d", tn, tn);
   plan->tile_tokens = tn;
   const int n_tiles = (p.n + kTileF - 1) / kTileF;
   const int k_blocks = p.k / kTileK;
@@ -619,7 +686,7 @@ int plan_w6a8(const GemmProblem& p, GemmPlan* plan) {
   int splits = p.splits;
   if (splits == 0) {
     splits = 1;
-    if (!grouped && tiles * 2 <= sms) {
+    if (!grouped && tn <= 96 && tiles * 2 <= sms) {
       splits = (int)(sms / tiles);
       const int max_splits = k_blocks / 2 > 0 ? k_blocks / 2 : 1;
       if (splits > max_splits) splits = max_splits;
@@ -683,9 +750,10 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
   args.alpha = p.alpha;
   static const uint32_t w_tx = []() {
     const char* env = std::getenv("MXFP6_B200_W_TX_BYTES");
-    return env != nullptr ? (uint32_t)std::atoi(env) : kWTileBytes;
+    return env != nullptr ? (uint32_t)std::atoi(env) : kWTileTxBytes;
   }();
   args.w_tx_bytes = w_tx;
+  args.trace = g_trace;
   {
     const int64_t scale_rows = p.a_scale_rows > 0 ? p.a_scale_rows : round_up64(p.m_total, kAtomRows);
     args.a_scale_row_blocks = (int)(scale_rows / kAtomRows);
@@ -702,6 +770,8 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
   set_error("unsupported tile_tokens %d", plan.tile_tokens);
   return kInvalidArgument;
 }
+
+void set_trace_buffer(long long* ptr) { g_trace = ptr; }
 
 // One status word per device, allocated on first use and never freed.
 int* device_status_word(int device) {

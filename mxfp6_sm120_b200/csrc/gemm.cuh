@@ -55,6 +55,10 @@ int plan_w6a8(const GemmProblem& p, GemmPlan* plan);
 // Launches the kernel on `stream`; the plan must come from plan_w6a8.
 int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream);
 
+// Diagnostics: CTA 0 of later launches writes [3][256] clock64 stamps (producer
+// issue, stage ready at the MMA warp, stage committed) to this device buffer.
+void set_trace_buffer(long long* ptr);
+
 // Device status word (0 = ok) shared by all kernels with bounded waits.
 int* device_status_word(int device);
 int read_device_status(int device, int* value, bool reset);
