@@ -1,0 +1,426 @@
+"""Headline benchmark: the dense W6A8 projection sweep of a 27B-class decoder.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass over the 70 shapes of the sweep - five (N, K) projections x
+fourteen batch sizes M - each as the call a user makes (BF16 activation ->
+MXFP8 quantization -> tcgen05 W6A8 GEMM against packed MXFP6 weights), captured in
+one CUDA graph and replayed.  Shapes run M-major so that the 270 MB of packed
+weights cycle through the 126 MB L2 between two uses of the same matrix.
+Rank 0 prints one JSON line; the value is whole-job TFLOP/s (2*M*N*K summed over
+the sweep / step time, max over ranks).
+
+With N > 1 the projections are sharded the way a tensor-parallel decoder shards
+them: K = 5120 inputs are column-parallel (split N, no collective), the two
+projections that reduce over a wide K (5120x6144, 5120x17408) are row-parallel
+(split K) followed by an NCCL all-reduce of the BF16 partials.
+
+``--impl reference`` times the reference's CPU path for the same metric (MXFP6
+decode + MXFP8 quantize + FP32 matmul, restated in ``oracle/``) on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+NK_SHAPES = [(7168, 5120), (5120, 6144), (34816, 5120), (5120, 17408), (2048, 5120)]
+M_VALUES = [1, 2, 4, 8, 16, 24, 32, 64, 96, 512, 1024, 2048, 4096, 8192]
+ROW_PARALLEL = {(5120, 6144), (5120, 17408)}
+WORKLOAD = "dense W6A8 projection sweep: 5 (N,K) x 14 M, BF16 in -> MXFP8 quant -> GEMM vs packed MXFP6"
+
+
+def sweep_flops() -> float:
+    return float(sum(2 * m * n * k for m in M_VALUES for n, k in NK_SHAPES))
+
+
+def gemm_bytes(m: int, n: int, k: int) -> int:
+    """Algorithmic bytes of one pre-quantized GEMM call."""
+    return n * k * 3 // 4 + n * k // 32 + m * k + m * k // 32 + m * n * 2
+
+
+def load_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        data["source"] = "measured"
+        return data
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------ clocks
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[list[str]] = []
+        self._proc: subprocess.Popen | None = None
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self) -> None:
+        assert self._proc is not None and self._proc.stdout is not None
+        for line in self._proc.stdout:
+            fields = [field.strip() for field in line.split(",")]
+            if len(fields) >= 6:
+                self.samples.append(fields)
+
+    def __enter__(self):
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self._thread.start()
+            time.sleep(0.3)  # first samples arrive before the timed region starts
+            self.samples.clear()
+        except OSError:
+            self._proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self._proc is not None:
+            self._proc.terminate()
+            try:
+                self._proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self._proc.kill()
+            self._thread.join(timeout=5)
+
+    def summary(self) -> dict:
+        mhz = sorted(int(s[0]) for s in self.samples if s and s[0].isdigit())
+        max_mhz = max((int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()), default=0)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for s in self.samples if len(s) >= 6
+                          for i in range(4) if s[2 + i].lower().startswith("active")})
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max_mhz or None,
+                "reasons": reasons, "samples": len(mhz)}
+
+
+# ------------------------------------------------------------------------------ CPU arm
+
+
+def cpu_reference_sample(threads: int) -> dict:
+    """Times the CPU restatement of the path on a bounded sample of the sweep.
+
+    Sample: the (2048, 5120) projection at M in {1, 32, 512}: quantize the BF16
+    activation to MXFP8, decode both operands, FP32 matmul, cast to BF16.  The
+    weight decode happens once per projection and is reported separately.
+    """
+    from oracle import mx_oracle as o
+
+    torch.set_num_threads(threads)
+    n, k = 2048, 5120
+    gen = torch.Generator(device="cpu").manual_seed(1004)
+    w = (torch.randn((n, k), generator=gen) * 0.02).to(torch.bfloat16)
+    w_codes, w_scales = o.quantize_mxfp6(w)
+    t0 = time.perf_counter()
+    w_deq = o.dequant_mxfp6(w_codes, w_scales)
+    decode_s = time.perf_counter() - t0
+    flops = 0.0
+    seconds = 0.0
+    for m in (1, 32, 512):
+        a = torch.randn((m, k), generator=torch.Generator(device="cpu").manual_seed(2000 + m)).to(
+            torch.bfloat16)
+        best = None
+        for _ in range(3):
+            t0 = time.perf_counter()
+            a_codes, a_scales = o.quantize_mxfp8_torch(a)
+            out = (o.dequant_mxfp8(a_codes, a_scales) @ w_deq.t()).to(torch.bfloat16)
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        del out
+        flops += 2.0 * m * n * k
+        seconds += best
+    return {"value": flops / seconds / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": "N=2048,K=5120 at M in {1,32,512}: MXFP8 quantize + decode + FP32 matmul "
+                      f"(best of 3 each; weight decode {decode_s:.2f} s excluded)",
+            "seconds": seconds}
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    for _ in range(max(0, min(args.warmup, 1))):
+        cpu_reference_sample(threads)
+    t0 = time.perf_counter()
+    results = [cpu_reference_sample(threads) for _ in range(max(1, min(args.steps, 3)))]
+    wall = time.perf_counter() - t0
+    value = sum(r["value"] for r in results) / len(results)
+    base = results[-1]
+    line = {
+        "impl": "reference", "metric": "W6A8 GEMM TFLOP/s over the dense M sweep", "value": value,
+        "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": len(results), "warmup": min(args.warmup, 1),
+        "ms_per_step": wall / len(results) * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "mxfp6 x mxfp8 -> f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": base["sample"]},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": base["cores"],
+                         "kind": base["kind"], "sample": base["sample"]},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------ GPU arm
+
+
+def build_sweep(mx, device, rank: int, world: int):
+    """Weights (random packed bytes; every 6-bit pattern is a valid E3M2 code) and
+    BF16 activations for every shape, sharded for this rank."""
+    from mxfp6_sm120_b200 import tp
+
+    gen = torch.Generator(device=device).manual_seed(1000 + rank)
+    layers = {}
+    for index, (n, k) in enumerate(NK_SHAPES):
+        if world == 1:
+            n_loc, k_loc, mode = n, k, "full"
+        elif (n, k) in ROW_PARALLEL:
+            b, e = tp.shard_bounds(k, world, rank)
+            n_loc, k_loc, mode = n, e - b, "row"
+        else:
+            b, e = tp.shard_bounds(n, world, rank)
+            n_loc, k_loc, mode = e - b, k, "column"
+        values = torch.randint(0, 256, (n_loc * k_loc * 3 // 4,), generator=gen, dtype=torch.uint8,
+                               device=device)
+        scales = torch.randint(118, 124, (mx.packed_scale_numel(n_loc, k_loc),), generator=gen,
+                               dtype=torch.uint8, device=device)
+        layers[(n, k)] = (mx.PackedMXFP6Tensor(values, scales, n_loc, k_loc), mode)
+    acts = {}
+    for m in M_VALUES:
+        for (n, k), (weight, _) in layers.items():
+            acts[(m, n, k)] = torch.randn((m, weight.k), generator=gen, device=device,
+                                          dtype=torch.float32).to(torch.bfloat16)
+    return layers, acts
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=100)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-e2e", action="store_true")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch.distributed as dist
+
+    import mxfp6_sm120_b200 as mx
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    warmup = max(3, args.warmup)
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    mx.load_library()  # ImportError if the CUDA library is missing: there is no fallback
+    if not mx.is_available():
+        raise RuntimeError("bench.py needs an sm_100 GPU and libmxfp6_b200.so")
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    peaks = load_peaks()
+
+    layers, acts = build_sweep(mx, device, rank, world)
+    outs = {key: torch.empty((key[0], layers[key[1:]][0].rows), dtype=torch.bfloat16, device=device)
+            for key in acts}
+    order = [(m, n, k) for m in M_VALUES for (n, k) in NK_SHAPES]
+
+    def run_shape(key, a=None):
+        weight, mode = layers[key[1:]]
+        out = mx.gemm_from_float(acts[key] if a is None else a, weight, out_dtype=torch.bfloat16,
+                                 out=outs[key])
+        if mode == "row" and world > 1:
+            dist.all_reduce(out)
+        return out
+
+    def run_sweep():
+        for key in order:
+            run_shape(key)
+
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        # plan the split-K arena on the capture stream, then freeze it
+        mx.begin_workspace_planning(device)
+        run_sweep()
+        mx.finalize_workspace_planning(device)
+        run_sweep()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            run_sweep()
+        launches_per_step = 2 * len(order) + (0 if world == 1 else 2 * len(M_VALUES))
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize(device)
+
+        for _ in range(warmup):
+            graph.replay()
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clocks:
+            start.record(stream)
+            for _ in range(args.steps):
+                graph.replay()
+            stop.record(stream)
+            barrier()
+        ms_total = start.elapsed_time(stop)
+        if world > 1:
+            t = torch.tensor([ms_total], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_total = float(t.item())
+        ms_per_step = ms_total / args.steps
+        value = sweep_flops() / (ms_per_step * 1e-3) / 1e12
+
+        # ---- GEMM kernel alone (pre-quantized activations), per shape, for the roofline
+        per_shape = []
+        gemm_ms = 0.0
+        small_bytes = small_ms = 0.0
+        big_flops = big_ms = 0.0
+        if rank == 0 or world > 1:
+            quantized = {key: mx.quantize_mxfp8(acts[key]) for key in order}
+            reps = 5
+            for key in order:
+                weight, _ = layers[key[1:]]
+                g = torch.cuda.CUDAGraph()
+                mx.gemm_w6a8(quantized[key], weight, out_dtype=torch.bfloat16, out=outs[key])
+                stream.synchronize()
+                with torch.cuda.graph(g, stream=stream):
+                    for _ in range(reps):
+                        mx.gemm_w6a8(quantized[key], weight, out_dtype=torch.bfloat16, out=outs[key])
+                shape_start = torch.cuda.Event(enable_timing=True)
+                shape_stop = torch.cuda.Event(enable_timing=True)
+                g.replay()
+                shape_start.record(stream)
+                g.replay()
+                shape_stop.record(stream)
+                stream.synchronize()
+                us = shape_start.elapsed_time(shape_stop) * 1e3 / reps
+                m = key[0]
+                flops = 2.0 * m * weight.rows * weight.k
+                byts = gemm_bytes(m, weight.rows, weight.k)
+                per_shape.append({"m": m, "n": key[1], "k": key[2], "us": round(us, 2),
+                                  "tflops": round(flops / us / 1e6, 1),
+                                  "gbs": round(byts / us / 1e3, 0)})
+                gemm_ms += us / 1e3
+                if m <= 32:
+                    small_bytes += byts
+                    small_ms += us / 1e3
+                if m >= 4096:
+                    big_flops += flops
+                    big_ms += us / 1e3
+
+        # ---- end to end through the public API with host buffers
+        e2e = None
+        if not args.no_e2e and world == 1:
+            host_in = {key: torch.empty(acts[key].shape, dtype=torch.bfloat16).pin_memory()
+                       for key in order}
+            host_out = {key: torch.empty(outs[key].shape, dtype=torch.bfloat16).pin_memory()
+                        for key in order}
+            for key in order:
+                host_in[key].copy_(acts[key])
+            h2d = sum(t.numel() * 2 for t in host_in.values())
+            d2h = sum(t.numel() * 2 for t in host_out.values())
+
+            def e2e_step():
+                for key in order:
+                    acts[key].copy_(host_in[key], non_blocking=True)
+                    out = run_shape(key)
+                    host_out[key].copy_(out, non_blocking=True)
+
+            e2e_step()
+            stream.synchronize()
+            e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            steps = max(1, min(args.steps, 3))
+            e_start.record(stream)
+            for _ in range(steps):
+                e2e_step()
+            e_stop.record(stream)
+            stream.synchronize()
+            e_ms = e_start.elapsed_time(e_stop) / steps
+            e2e = {"value": sweep_flops() / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                   "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e_ms}
+
+    status = mx.device_status(device)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    fp8_peak = 2.0 * float(peaks["bf16_tflops_sustained"])
+    line = {
+        "metric": "W6A8 GEMM TFLOP/s over the dense M sweep", "value": value, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "mxfp6(e3m2) x mxfp8(e4m3) -> f32 accumulate -> bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "shapes": NK_SHAPES, "m_values": M_VALUES,
+                   "parallelism": "single GPU" if world == 1 else
+                   f"tp{world}: K=5120 projections column-parallel, 5120x6144 and 5120x17408 "
+                   "row-parallel + NCCL all-reduce",
+                   "l2": "inputs larger than L2: shapes run M-major, 270 MB of packed weights "
+                         "cycle through the 126 MB L2 between reuses",
+                   "graph": "one CUDA graph per step"},
+        "clocks": clocks.summary(),
+        "gpu_launches": launches_per_step * args.steps,
+        "device_status": status,
+    }
+    if big_ms > 0:
+        achieved = big_flops / (big_ms * 1e-3) / 1e12
+        line["roofline"] = {
+            "bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
+            "frac": achieved / fp8_peak, "traffic": None,
+            "kernel": "w6a8_gemm_kernel, M >= 4096 launches of the sweep",
+            "peak_note": f"2 x bf16_tflops_sustained ({peaks['source']}): kind::mxf8f6f4 runs at "
+                         "the FP8 rate, twice the BF16 rate the peak file measures",
+            "frac_of_nominal_4500": achieved / 4500.0,
+        }
+    if small_ms > 0:
+        achieved = small_bytes / (small_ms * 1e-3) / 1e9
+        line["roofline_small_m"] = {
+            "bound": "hbm", "achieved": achieved, "peak": float(peaks["hbm_gbs"]), "unit": "GB/s",
+            "frac": achieved / float(peaks["hbm_gbs"]), "traffic": None,
+            "kernel": "w6a8_gemm_kernel, M <= 32 launches of the sweep",
+            "peak_note": f"hbm_gbs ({peaks['source']})",
+        }
+    if per_shape:
+        line["gemm_only_ms_per_step"] = gemm_ms
+        line["sweep"] = per_shape
+    if e2e is not None:
+        line["e2e"] = e2e
+    if not args.no_cpu_baseline and world == 1:
+        base = cpu_reference_sample(os.cpu_count() or 1)
+        line["cpu_baseline"] = {key: base[key] for key in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
