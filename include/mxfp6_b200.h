@@ -121,6 +121,72 @@ int mxfp6_gemm_from_float(const void* a_dev, int a_dtype, const uint8_t* w_value
                           float alpha, void* out_dev, int out_dtype, uint8_t* a_values_stage_dev,
                           uint8_t* a_scales_stage_dev, void* stream);
 
+/* ---- routed MoE -----------------------------------------------------------------
+ * All calls are allocation-free and capturable in a CUDA graph. */
+
+/* torch.ops.mxfp6.qwen35_topk_quant_out (csrc/moe.cu:620-962, host :9716-10008):
+ * per token, MXFP8-quantize the BF16 hidden row (values, logical scales [T, H/32]
+ * and/or dense packed scales; all three optional together with `quantized` NULL)
+ * and take the softmax top-k of its BF16 router logits (FP32 weights, INT32 ids;
+ * ties go to the smaller id; renormalize divides by the sum of the k weights).
+ * Generic in H (multiple of 32), experts (<= 1024) and k (<= 16). */
+int mxfp6_moe_topk_quant(const void* hidden_dev, const void* logits_dev, int64_t tokens,
+                         int hidden_size, int experts, int topk, int renormalize,
+                         uint8_t* quantized_dev, uint8_t* logical_scales_dev,
+                         uint8_t* dense_scales_dev, float* topk_weights_dev,
+                         int32_t* topk_ids_dev, void* stream);
+/* torch.ops.mxfp6.route_mxfp8_out / qwen35_route_mxfp8_out (csrc/moe.cu:4263-4446):
+ * expert_offsets[E+1] (exclusive prefix of counts), scale_offsets[E+1] (prefix of
+ * 128-padded counts), cursors[E] (scratch), inverse_permutation[T*k] (route -> row,
+ * -1 for routes whose expert is not local), optional source_tokens[row], optional
+ * copy of the MXFP8 rows into permuted[T*k, H], and the rows' scales in the grouped
+ * packed layout.  expert_map (global id -> local id or -1) may be NULL. */
+int mxfp6_moe_route(const uint8_t* activation_dev, const uint8_t* logical_scales_dev,
+                    const void* topk_ids_dev, int ids_are_int64, int64_t tokens, int topk,
+                    int hidden_size, const int32_t* expert_map_dev, int expert_map_size,
+                    int local_experts, int64_t* expert_offsets_dev, int64_t* scale_offsets_dev,
+                    int32_t* cursors_dev, uint8_t* permuted_dev, uint8_t* grouped_scales_dev,
+                    int32_t* inverse_permutation_dev, int32_t* source_tokens_dev, void* stream);
+/* torch.ops.mxfp6.grouped_gemm_w6a8_out (csrc/moe.cu:7551-7676): rows
+ * [expert_offsets[e], expert_offsets[e+1]) of the activation times weight e
+ * ([E, n, k*3/4] bytes, scales [E, n*k/32]); n % 128 == 0, k % 128 == 0.
+ * m_total is the row capacity of the activation / output buffers. */
+int mxfp6_grouped_gemm_w6a8(void* out_dev, int out_dtype, const uint8_t* activation_dev,
+                            const uint8_t* activation_scales_dev, int64_t activation_scale_rows,
+                            const uint8_t* weight_dev, const uint8_t* weight_scales_dev,
+                            const int64_t* expert_offsets_dev, const int64_t* scale_offsets_dev,
+                            int experts, int64_t m_total, int64_t n, int64_t k, int tile_tokens,
+                            void* stream);
+/* torch.ops.mxfp6.qwen35_grouped_w1_silu_mxfp8_out (csrc/moe.cu:2288-2687, host
+ * :4106-4204): W1 = [E, 2*inter, k] (gate rows, then up rows); output E4M3
+ * [m_total, inter] = MXFP8(bf16(silu(bf16 gate)) * bf16 up) with scales in the grouped
+ * packed layout (same scale_offsets) and/or logical [m_total, inter/32].  With
+ * expert_offsets == NULL and experts == 1 it is the dense form used for the shared
+ * expert (activation scales and output scales in the dense packed layout). */
+int mxfp6_w1_swiglu_mxfp8(uint8_t* output_dev, uint8_t* out_packed_scales_dev,
+                          uint8_t* out_logical_scales_dev, const uint8_t* activation_dev,
+                          const uint8_t* activation_scales_dev, int64_t activation_scale_rows,
+                          const uint8_t* weight_dev, const uint8_t* weight_scales_dev,
+                          const int64_t* expert_offsets_dev, const int64_t* scale_offsets_dev,
+                          int experts, int64_t m_total, int64_t inter, int64_t k, int tile_tokens,
+                          void* stream);
+/* torch.ops.mxfp6.silu_and_mul_mxfp8_{grouped,grouped_out,logical,packed_out}
+ * (csrc/moe.cu:5135-5282): input FP16/BF16 [rows, 2*inter]; output E4M3 [rows, inter];
+ * scales logical and/or packed (grouped when the offset arrays are given). */
+int mxfp6_silu_and_mul_mxfp8(const void* input_dev, int dtype, int64_t rows, int64_t inter,
+                             uint8_t* output_dev, uint8_t* logical_scales_dev,
+                             uint8_t* packed_scales_dev, const int64_t* expert_offsets_dev,
+                             const int64_t* scale_offsets_dev, int experts, void* stream);
+/* torch.ops.mxfp6.moe_reduce_out (csrc/moe.cu:7927-8082, host :8377-8531):
+ * out[t] = cast(sigmoid(gate[t]) * shared[t] + sum_r w[t,r] * routed[inv[t,r]]), FP32.
+ * shared / shared_gate may be NULL; gate dtype 0/1/2 = f16/bf16/f32; gate_stride is
+ * the row length of the gate tensor (its last column is used). */
+int mxfp6_moe_reduce(void* out_dev, const void* routed_dev, int dtype,
+                     const float* topk_weights_dev, const int32_t* inverse_permutation_dev,
+                     const void* shared_dev, const void* shared_gate_dev, int gate_dtype,
+                     int gate_stride, int64_t tokens, int hidden_size, int topk,
+                     int64_t routed_rows, void* stream);
+
 /* ---- split-K workspace arena ----------------------------------------------
  * torch.ops.mxfp6.begin_workspace_planning / finalize_workspace_planning /
  * workspace_stats / workspace_barriers_zero (csrc/torch_extension.cu:1955-2116).

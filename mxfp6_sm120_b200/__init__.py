@@ -46,4 +46,36 @@ from .ops import (
     workspace_stats,
 )
 
+from .moe_ops import (
+    dense_w1_silu_mxfp8_out,
+    grouped_gemm_w6a8,
+    grouped_gemm_w6a8_out,
+    grouped_scale_rows,
+    moe_reduce_out,
+    moe_reduce_tp2_out,
+    qwen35_grouped_w1_silu_mxfp8_out,
+    qwen35_route_mxfp8_out,
+    qwen35_topk_quant_out,
+    qwen35_topk_quant_route_out,
+    route_mxfp8_out,
+    silu_and_mul_mxfp8_grouped,
+    silu_and_mul_mxfp8_grouped_out,
+    silu_and_mul_mxfp8_logical,
+    silu_and_mul_mxfp8_packed_out,
+)
+from .qwen35 import (
+    MoeShape,
+    Qwen35GroupedWorkspace,
+    Qwen35MoeB1Workspace,
+    SharedExpertWorkspace,
+    qwen35_grouped_gemm_out,
+    qwen35_grouped_moe_logits_out,
+    qwen35_grouped_moe_out,
+    qwen35_grouped_reduce_out,
+    qwen35_grouped_workspace_bytes,
+    qwen35_grouped_workspace_shapes,
+    qwen35_moe_b1_out,
+    shared_expert_out,
+)
+
 __version__ = "0.1.0"

@@ -62,6 +62,36 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p, c_int,
          c_void_p, c_void_p, c_void_p],
     ),
+    "mxfp6_moe_topk_quant": (
+        c_int,
+        [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_void_p],
+    ),
+    "mxfp6_moe_route": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_int, c_int,
+         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    ),
+    "mxfp6_grouped_gemm_w6a8": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
+    ),
+    "mxfp6_w1_swiglu_mxfp8": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
+    ),
+    "mxfp6_silu_and_mul_mxfp8": (
+        c_int,
+        [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_int, c_void_p],
+    ),
+    "mxfp6_moe_reduce": (
+        c_int,
+        [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,
+         c_int, c_int, c_int64, c_void_p],
+    ),
     "mxfp6_workspace_begin_planning": (c_int, []),
     "mxfp6_workspace_finalize_planning": (c_int, [c_void_p, _I64P]),
     "mxfp6_workspace_stats": (c_int, [_I64P]),

@@ -41,6 +41,16 @@ int grouped_scale_offsets(const int64_t*, int, int64_t*, cudaStream_t);
 int pack_grouped_scales(const uint8_t*, const int64_t*, const int64_t*, int, int64_t, int64_t,
                         uint8_t*, cudaStream_t);
 
+int moe_topk_quant(const void*, const void*, int64_t, int, int, int, int, uint8_t*, uint8_t*,
+                   uint8_t*, float*, int32_t*, cudaStream_t);
+int moe_route(const uint8_t*, const uint8_t*, const void*, int, int64_t, int, int, const int32_t*,
+              int, int, int64_t*, int64_t*, int32_t*, uint8_t*, uint8_t*, int32_t*, int32_t*,
+              cudaStream_t);
+int silu_mul_quant(const void*, int, int64_t, int, uint8_t*, uint8_t*, uint8_t*, const int64_t*,
+                   const int64_t*, int, cudaStream_t);
+int moe_reduce(void*, const void*, int, const float*, const int32_t*, const void*, const void*, int,
+               int, int64_t, int, int, int64_t, cudaStream_t);
+
 // ---- workspace arena ------------------------------------------------------------
 namespace {
 
@@ -336,6 +346,97 @@ int mxfp6_gemm_from_float(const void* a, int a_dtype, const uint8_t* w_values,
   if (int rc = quantize_mxfp8(a, a_dtype, m, k, a_values_stage, a_scales_stage, nullptr, s))
     return rc;
   return run_gemm_with_arena(p, s);
+}
+
+int mxfp6_grouped_gemm_w6a8(void* out, int out_dtype, const uint8_t* activation,
+                            const uint8_t* activation_scales, int64_t activation_scale_rows,
+                            const uint8_t* weight, const uint8_t* weight_scales,
+                            const int64_t* expert_offsets, const int64_t* scale_offsets,
+                            int experts, int64_t m_total, int64_t n, int64_t k, int tile_tokens,
+                            void* stream) {
+  MX_REQUIRE(expert_offsets != nullptr && scale_offsets != nullptr,
+             "expert_offsets and scale_offsets must not be null");
+  GemmProblem p;
+  if (int rc = dense_problem(&p, activation, activation_scales, weight, weight_scales, m_total, n,
+                             k, 1.0f, out, out_dtype))
+    return rc;
+  p.groups = experts;
+  p.expert_offsets = expert_offsets;
+  p.scale_offsets = scale_offsets;
+  p.a_scale_rows = activation_scale_rows;
+  p.tile_tokens = tile_tokens;
+  p.splits = 1;
+  GemmPlan plan;
+  if (int rc = plan_w6a8(p, &plan)) return rc;
+  return launch_w6a8(p, plan, static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_w1_swiglu_mxfp8(uint8_t* output, uint8_t* out_packed_scales,
+                          uint8_t* out_logical_scales, const uint8_t* activation,
+                          const uint8_t* activation_scales, int64_t activation_scale_rows,
+                          const uint8_t* weight, const uint8_t* weight_scales,
+                          const int64_t* expert_offsets, const int64_t* scale_offsets,
+                          int experts, int64_t m_total, int64_t inter, int64_t k, int tile_tokens,
+                          void* stream) {
+  MX_REQUIRE((expert_offsets == nullptr) == (scale_offsets == nullptr),
+             "expert_offsets and scale_offsets go together");
+  MX_REQUIRE(expert_offsets != nullptr || experts == 1, "a dense launch has exactly one weight");
+  GemmProblem p;
+  if (int rc = dense_problem(&p, activation, activation_scales, weight, weight_scales, m_total,
+                             inter, k, 1.0f, output, kBF16))
+    return rc;
+  p.mode = kGemmSwigluMxfp8;
+  p.groups = experts;
+  p.expert_offsets = expert_offsets;
+  p.scale_offsets = scale_offsets;
+  p.out_scale_offsets = scale_offsets;
+  p.out_packed_scales = out_packed_scales;
+  p.out_logical_scales = out_logical_scales;
+  p.a_scale_rows = activation_scale_rows;
+  p.tile_tokens = tile_tokens;
+  p.splits = 1;
+  GemmPlan plan;
+  if (int rc = plan_w6a8(p, &plan)) return rc;
+  return launch_w6a8(p, plan, static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_moe_topk_quant(const void* hidden, const void* logits, int64_t tokens, int hidden_size,
+                         int experts, int topk, int renormalize, uint8_t* quantized,
+                         uint8_t* logical_scales, uint8_t* dense_scales, float* topk_weights,
+                         int32_t* topk_ids, void* stream) {
+  return moe_topk_quant(hidden, logits, tokens, hidden_size, experts, topk, renormalize, quantized,
+                        logical_scales, dense_scales, topk_weights, topk_ids,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_moe_route(const uint8_t* activation, const uint8_t* logical_scales, const void* topk_ids,
+                    int ids_are_int64, int64_t tokens, int topk, int hidden_size,
+                    const int32_t* expert_map, int expert_map_size, int local_experts,
+                    int64_t* expert_offsets, int64_t* scale_offsets, int32_t* cursors,
+                    uint8_t* permuted, uint8_t* grouped_scales, int32_t* inverse_permutation,
+                    int32_t* source_tokens, void* stream) {
+  return moe_route(activation, logical_scales, topk_ids, ids_are_int64, tokens, topk, hidden_size,
+                   expert_map, expert_map_size, local_experts, expert_offsets, scale_offsets,
+                   cursors, permuted, grouped_scales, inverse_permutation, source_tokens,
+                   static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_silu_and_mul_mxfp8(const void* input, int dtype, int64_t rows, int64_t inter,
+                             uint8_t* output, uint8_t* logical_scales, uint8_t* packed_scales,
+                             const int64_t* expert_offsets, const int64_t* scale_offsets,
+                             int experts, void* stream) {
+  MX_REQUIRE(inter > 0 && inter <= INT32_MAX, "intermediate size out of range");
+  return silu_mul_quant(input, dtype, rows, (int)inter, output, logical_scales, packed_scales,
+                        expert_offsets, scale_offsets, experts, static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_moe_reduce(void* out, const void* routed, int dtype, const float* topk_weights,
+                     const int32_t* inverse_permutation, const void* shared,
+                     const void* shared_gate, int gate_dtype, int gate_stride, int64_t tokens,
+                     int hidden_size, int topk, int64_t routed_rows, void* stream) {
+  return moe_reduce(out, routed, dtype, topk_weights, inverse_permutation, shared, shared_gate,
+                    gate_dtype, gate_stride, tokens, hidden_size, topk, routed_rows,
+                    static_cast<cudaStream_t>(stream));
 }
 
 int mxfp6_workspace_begin_planning(void) {

@@ -24,6 +24,8 @@
 #include "gemm.cuh"
 #include "ptx.cuh"
 
+#include <cuda_fp8.h>
+
 #include <cuda.h>
 #include <mutex>
 #include <unordered_map>
@@ -64,28 +66,43 @@ struct KernelArgs {
   float alpha;
   uint32_t w_tx_bytes;  // bytes one weight-tile TMA adds to the mbarrier
   int a_scale_row_blocks;  // 128-row blocks present in the activation scale buffer
+  // SwiGLU mode: weight matrices hold 2 * n rows (gate rows first, then up rows);
+  // the output is E4M3 [m_total, n] with UE8M0 scales per 32 features, logical
+  // [m_total, n / 32] and/or packed (row r of group g -> packed row
+  // out_scale_offsets[g] + r - expert_offsets[g]; identity when null).
+  int w_rows_per_group;
+  uint8_t* out_packed_scales;
+  uint8_t* out_logical_scales;
+  const int64_t* out_scale_offsets;
   long long* trace;        // optional [3][256] cycle stamps of CTA 0 (diagnostics), or null
 };
 
-template <int TN>
+constexpr int kModeStore = 0;   // out = cast(alpha * acc)
+constexpr int kModeSwiglu = 1;  // out = MXFP8(bf16(silu(bf16 gate)) * bf16 up)
+
+template <int TN, int MODE>
 struct Cfg {
+  static constexpr int kWTiles = MODE == kModeSwiglu ? 2 : 1;  // weight tiles per K block
   static constexpr int kSfbAtoms = TN <= 128 ? 1 : 2;
   // 128-K blocks per pipeline stage.  Narrow tiles are bound by the per-stage cost
   // of the issuing warps (barrier wait, fence, commit), so they take more K per stage.
-  static constexpr int kSubs = TN <= 32 ? 4 : (TN <= 96 ? 2 : 1);
+  static constexpr int kSubs =
+      MODE == kModeSwiglu ? (TN <= 32 ? 2 : 1) : (TN <= 32 ? 4 : (TN <= 96 ? 2 : 1));
   // Scale columns rotate through several sets so that the tcgen05.cp of a block
   // never overwrites scales an earlier, still running MMA reads.
   static constexpr int kSfSets = 4;
-  static constexpr int kSfSetCols = 4 + 4 * kSfbAtoms;
-  static constexpr int kAcc = (2 * TN + kSfSets * kSfSetCols <= 512) ? 2 : 1;  // accumulator buffers
-  static constexpr int kSfaCol = kAcc * TN;
-  static constexpr int kSfbCol = kSfaCol + 4;
+  static constexpr int kSfSetCols = 4 * kWTiles + 4 * kSfbAtoms;
+  static constexpr int kAccCols = kWTiles * TN;  // accumulator columns per buffer
+  static constexpr int kAcc = (2 * kAccCols + kSfSets * kSfSetCols <= 512) ? 2 : 1;
+  static constexpr int kSfaCol = kAcc * kAccCols;
+  static constexpr int kSfbCol = kSfaCol + 4 * kWTiles;
   static constexpr int kColsUsed = kSfaCol + kSfSets * kSfSetCols;
+  static_assert(kColsUsed <= 512, "tile does not fit tensor memory");
   static constexpr int kTmemCols =
       kColsUsed <= 32 ? 32 : kColsUsed <= 64 ? 64 : kColsUsed <= 128 ? 128 : kColsUsed <= 256 ? 256 : 512;
   static constexpr uint32_t kATileBytes = TN * kTileK;
-  static constexpr uint32_t kStageBytes = kSubs * (kWTileBytes + kATileBytes);
-  static constexpr uint32_t kSfStageBytes = kSubs * kAtomBytes * (1 + kSfbAtoms);
+  static constexpr uint32_t kStageBytes = kSubs * (kWTiles * kWTileBytes + kATileBytes);
+  static constexpr uint32_t kSfStageBytes = kSubs * kAtomBytes * (kWTiles + kSfbAtoms);
   static constexpr uint32_t kFixedBytes = 1024 /*align slack*/ + 4096 /*barriers + tables*/;
   static constexpr int kStagesRaw =
       (int)((232448u - kFixedBytes) / (kStageBytes + kSfStageBytes));
@@ -155,16 +172,16 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
   }
 }
 
-template <int TN>
+template <int TN, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
                  const KernelArgs args) {
-  using C = Cfg<TN>;
+  using C = Cfg<TN, MODE>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* w_tiles = smem;
-  uint8_t* a_tiles = w_tiles + (size_t)C::kStages * C::kSubs * kWTileBytes;
+  uint8_t* a_tiles = w_tiles + (size_t)C::kStages * C::kSubs * C::kWTiles * kWTileBytes;
   uint8_t* sf_tiles = a_tiles + (size_t)C::kStages * C::kSubs * C::kATileBytes;
   uint8_t* fixed = sf_tiles + (size_t)C::kStages * C::kSfStageBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(fixed);  // full[S], empty[S], tfull[2], tempty[2]
@@ -242,7 +259,8 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     {
       int stage = 0;
       uint32_t phase = 0;
-      const uint32_t tx_sub = args.w_tx_bytes + C::kATileBytes + kAtomBytes * (1 + C::kSfbAtoms);
+      const uint32_t tx_sub = C::kWTiles * args.w_tx_bytes + C::kATileBytes +
+                              kAtomBytes * (C::kWTiles + C::kSfbAtoms);
       const int atoms_per_rb = kb_total;  // k/128 atoms per 128-row block
       int trace_i = 0;
       Work wk;
@@ -250,9 +268,7 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       for (int w = blockIdx.x; ok && decode_work<TN>(w, args, tile_prefix, &wk); w += gridDim.x) {
         const int kb0 = (int)(((int64_t)wk.split * kb_total) / args.splits);
         const int kb1 = (int)(((int64_t)(wk.split + 1) * kb_total) / args.splits);
-        const int w_row = wk.group * args.n + wk.n_tile * kTileF;
-        const uint8_t* sfa_src =
-            args.w_scales + ((int64_t)(w_row / kAtomRows) * atoms_per_rb) * kAtomBytes;
+        const int w_row = wk.group * args.w_rows_per_group + wk.n_tile * kTileF;
         const int sfb_rb0 = (int)(wk.scale_row0 / kAtomRows);
         for (int kb = kb0; kb < kb1; kb += C::kSubs) {
           const int nsub = (kb1 - kb) < C::kSubs ? (kb1 - kb) : C::kSubs;
@@ -267,9 +283,14 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           if (ptx::elect_one()) {
             ptx::mbar_arrive_expect_tx(bar, tx_sub * nsub);
             for (int sub = 0; sub < nsub; ++sub) {
-              ptx::tma_load_2d(
-                  ptx::smem_u32(w_tiles + (size_t)(stage * C::kSubs + sub) * kWTileBytes), &tm_w,
-                  (kb + sub) * kTileK, w_row, bar);
+#pragma unroll
+              for (int t = 0; t < C::kWTiles; ++t) {
+                // tile 0: gate rows (or the only tile); tile 1: up rows, n rows further down
+                ptx::tma_load_2d(
+                    ptx::smem_u32(w_tiles + (size_t)((stage * C::kSubs + sub) * C::kWTiles + t) *
+                                                kWTileBytes),
+                    &tm_w, (kb + sub) * kTileK, w_row + t * args.n, bar);
+              }
               ptx::tma_load_2d(
                   ptx::smem_u32(a_tiles + (size_t)(stage * C::kSubs + sub) * C::kATileBytes),
                   &tm_a, (kb + sub) * kTileK, (int)wk.row0, bar);
@@ -277,15 +298,21 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             // Scale atoms of consecutive K blocks are adjacent in memory: one bulk
             // copy per operand row block covers the whole stage.
             uint8_t* sf = sf_tiles + (size_t)stage * C::kSfStageBytes;
-            ptx::bulk_load(ptx::smem_u32(sf), sfa_src + (int64_t)kb * kAtomBytes,
-                           kAtomBytes * nsub, bar);
+#pragma unroll
+            for (int t = 0; t < C::kWTiles; ++t) {
+              const uint8_t* sfa_src =
+                  args.w_scales +
+                  ((int64_t)((w_row + t * args.n) / kAtomRows) * atoms_per_rb + kb) * kAtomBytes;
+              ptx::bulk_load(ptx::smem_u32(sf + kAtomBytes * C::kSubs * t), sfa_src,
+                             kAtomBytes * nsub, bar);
+            }
 #pragma unroll
             for (int j = 0; j < C::kSfbAtoms; ++j) {
               // A tile that ends inside the last row block re-reads that block for
               // the rows it does not have; those accumulator rows are never stored.
               int rb = sfb_rb0 + j;
               if (rb >= args.a_scale_row_blocks) rb = args.a_scale_row_blocks - 1;
-              ptx::bulk_load(ptx::smem_u32(sf + kAtomBytes * C::kSubs * (1 + j)),
+              ptx::bulk_load(ptx::smem_u32(sf + kAtomBytes * C::kSubs * (C::kWTiles + j)),
                              args.a_scales + ((int64_t)rb * atoms_per_rb + kb) * kAtomBytes,
                              kAtomBytes * nsub, bar);
             }
@@ -320,7 +347,7 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                                                   args.status, 102)))
           break;
         ptx::tc_fence_after();
-        const uint32_t d_t = tmem_base + acc * TN;
+        const uint32_t d_t = tmem_base + acc * C::kAccCols;
         const uint32_t sfb_sub = (uint32_t)((wk.scale_row0 % kAtomRows) / 32);
         for (int kb = kb0; kb < kb1; kb += C::kSubs) {
           const int nsub = (kb1 - kb) < C::kSubs ? (kb1 - kb) : C::kSubs;
@@ -337,23 +364,30 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
               const uint32_t sfb_base = tmem_base + C::kSfbCol + sf_set * C::kSfSetCols;
               const uint32_t sfb_t = sfb_base + sfb_sub;
               sf_set = (sf_set + 1u) % C::kSfSets;
-              ptx::tc_cp_32x128b_warpx4(sfa_t, ptx::smem_desc_scale_atom(sf + kAtomBytes * sub));
+#pragma unroll
+              for (int t = 0; t < C::kWTiles; ++t) {
+                ptx::tc_cp_32x128b_warpx4(
+                    sfa_t + 4 * t, ptx::smem_desc_scale_atom(sf + kAtomBytes * (C::kSubs * t + sub)));
+              }
 #pragma unroll
               for (int j = 0; j < C::kSfbAtoms; ++j) {
                 ptx::tc_cp_32x128b_warpx4(
                     sfb_base + 4 * j,
-                    ptx::smem_desc_scale_atom(sf + kAtomBytes * (C::kSubs * (1 + j) + sub)));
+                    ptx::smem_desc_scale_atom(sf + kAtomBytes * (C::kSubs * (C::kWTiles + j) + sub)));
               }
-              const uint64_t a_desc = ptx::smem_desc_sw128(
-                  ptx::smem_u32(w_tiles + (size_t)(stage * C::kSubs + sub) * kWTileBytes));
               const uint64_t b_desc = ptx::smem_desc_sw128(
                   ptx::smem_u32(a_tiles + (size_t)(stage * C::kSubs + sub) * C::kATileBytes));
 #pragma unroll
-              for (int ks = 0; ks < kTileK / kMmaK; ++ks) {
-                const uint32_t idesc = kIdesc | ((uint32_t)ks << 4) | ((uint32_t)ks << 29);
-                // 32 K values = 32 bytes = 2 descriptor address units.
-                ptx::tc_mma_mxf8f6f4(d_t, a_desc + 2 * ks, b_desc + 2 * ks, idesc, sfa_t, sfb_t,
-                                     (kb + sub > kb0 || ks > 0) ? 1u : 0u);
+              for (int t = 0; t < C::kWTiles; ++t) {
+                const uint64_t a_desc = ptx::smem_desc_sw128(ptx::smem_u32(
+                    w_tiles + (size_t)((stage * C::kSubs + sub) * C::kWTiles + t) * kWTileBytes));
+#pragma unroll
+                for (int ks = 0; ks < kTileK / kMmaK; ++ks) {
+                  const uint32_t idesc = kIdesc | ((uint32_t)ks << 4) | ((uint32_t)ks << 29);
+                  // 32 K values = 32 bytes = 2 descriptor address units.
+                  ptx::tc_mma_mxf8f6f4(d_t + t * TN, a_desc + 2 * ks, b_desc + 2 * ks, idesc,
+                                       sfa_t + 4 * t, sfb_t, (kb + sub > kb0 || ks > 0) ? 1u : 0u);
+                }
               }
             }
             ptx::tc_commit(empty0 + 8 * stage);
@@ -405,11 +439,53 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       ptx::tc_fence_after();
       const int f = wk.n_tile * kTileF + fl;
       const bool f_ok = f < args.n;
-      const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * TN;
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * C::kAccCols;
       float* part = nullptr;
       if (args.splits > 1) {
         part = args.partials + ((size_t)wk.tile_id * args.splits + wk.split) * (TN * kTileF);
       }
+      if constexpr (MODE == kModeSwiglu) {
+        // Lane = intermediate feature, column = token.  The 32 lanes of this warp
+        // are exactly one 32-feature scale group of every token row.
+        const int groups = args.n / kScaleVec;
+        const int g_index = f / kScaleVec;
+        int64_t srow0 = wk.row0;
+        if (args.out_scale_offsets != nullptr) {
+          srow0 = args.out_scale_offsets[wk.group] + (int64_t)wk.m_tile * TN;
+        }
+#pragma unroll 1
+        for (int c0 = 0; c0 < TN; c0 += 16) {
+          uint32_t rg[16], ru[16];
+          ptx::tmem_ld_x16(t_addr + c0, rg);
+          ptx::tmem_ld_x16(t_addr + TN + c0, ru);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float g = round_bf16(__uint_as_float(rg[j]));
+            const float u = round_bf16(__uint_as_float(ru[j]));
+            const float sv = round_bf16(__fdiv_rn(g, 1.0f + expf(-g)));
+            const float v = round_bf16(sv * u);
+            float amax = fabsf(v);
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+            const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
+            const float inv = __fdiv_rn(1.0f, __uint_as_float(sbits));
+            const uint32_t code =
+                __nv_cvt_float2_to_fp8x2(make_float2(v * inv, 0.0f), __NV_SATFINITE, __NV_E4M3) & 0xffu;
+            if (c0 + j < wk.rows && f_ok) {
+              const int64_t row = wk.row0 + c0 + j;
+              static_cast<uint8_t*>(args.out)[row * args.n + f] = (uint8_t)code;
+              if (lane == 0) {
+                const uint8_t sc = (uint8_t)(sbits >> 23);
+                if (args.out_logical_scales != nullptr)
+                  args.out_logical_scales[row * groups + g_index] = sc;
+                if (args.out_packed_scales != nullptr)
+                  args.out_packed_scales[packed_scale_offset(srow0 + c0 + j, g_index, groups)] = sc;
+              }
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < TN; c0 += 16) {
         uint32_t r[16];
@@ -437,6 +513,7 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             }
           }
         }
+      }
       }
       // Accumulator buffer is free for the next tile.
       ptx::tc_fence_before();
@@ -601,26 +678,28 @@ int cached_map(CUtensorMap* out, CUtensorMapDataType type, const void* base, uin
 
 long long* g_trace = nullptr;
 
-template <int TN>
+template <int TN, int MODE>
 int launch_tn(const CUtensorMap& tm_w, const CUtensorMap& tm_a, const KernelArgs& args,
               const GemmPlan& plan, cudaStream_t stream) {
   static bool configured[64] = {};
   int device = 0;
   MX_CUDA(cudaGetDevice(&device));
   if (device < 64 && !configured[device]) {
-    MX_CUDA(cudaFuncSetAttribute(w6a8_gemm_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)Cfg<TN>::kSmemBytes));
+    MX_CUDA(cudaFuncSetAttribute(w6a8_gemm_kernel<TN, MODE>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)Cfg<TN, MODE>::kSmemBytes));
     configured[device] = true;
   }
-  w6a8_gemm_kernel<TN><<<plan.grid, kThreads, Cfg<TN>::kSmemBytes, stream>>>(tm_w, tm_a, args);
+  w6a8_gemm_kernel<TN, MODE>
+      <<<plan.grid, kThreads, Cfg<TN, MODE>::kSmemBytes, stream>>>(tm_w, tm_a, args);
   MX_CUDA(cudaGetLastError());
   return kOk;
 }
 
-template <int TN>
+template <int TN, int MODE>
 void fill_plan(GemmPlan* plan) {
-  plan->stages = Cfg<TN>::kStages;
-  plan->smem_bytes = Cfg<TN>::kSmemBytes;
+  plan->stages = Cfg<TN, MODE>::kStages;
+  plan->smem_bytes = Cfg<TN, MODE>::kSmemBytes;
 }
 
 int sm_count() {
@@ -656,17 +735,34 @@ int plan_w6a8(const GemmProblem& p, GemmPlan* plan) {
     else if (!grouped) tn = 192;
     else tn = 128;
   }
-  switch (tn) {
-    case 16: fill_plan<16>(plan); break;
-    case 32: fill_plan<32>(plan); break;
-    case 64: fill_plan<64>(plan); break;
-    case 96: fill_plan<96>(plan); break;
-    case 128: fill_plan<128>(plan); break;
-    case 192: fill_plan<192>(plan); break;
-    case 256: fill_plan<256>(plan); break;
-    default:
-      set_error("unsupported tile_tokens %d (use 16, 32, 64, 96, 128, 192 or 256)", tn);
-      return kInvalidArgument;
+  const bool swiglu = p.mode == kGemmSwigluMxfp8;
+  if (swiglu) {
+    MX_REQUIRE(p.n % 128 == 0, "SwiGLU mode needs the intermediate size to be a multiple of 128");
+    MX_REQUIRE(p.splits <= 1, "SwiGLU mode does not split K");
+    if (tn > 128) tn = 128;
+    if (tn == 96) tn = 128;
+    switch (tn) {
+      case 16: fill_plan<16, kModeSwiglu>(plan); break;
+      case 32: fill_plan<32, kModeSwiglu>(plan); break;
+      case 64: fill_plan<64, kModeSwiglu>(plan); break;
+      case 128: fill_plan<128, kModeSwiglu>(plan); break;
+      default:
+        set_error("unsupported tile_tokens %d for SwiGLU mode (use 16, 32, 64 or 128)", tn);
+        return kInvalidArgument;
+    }
+  } else {
+    switch (tn) {
+      case 16: fill_plan<16, kModeStore>(plan); break;
+      case 32: fill_plan<32, kModeStore>(plan); break;
+      case 64: fill_plan<64, kModeStore>(plan); break;
+      case 96: fill_plan<96, kModeStore>(plan); break;
+      case 128: fill_plan<128, kModeStore>(plan); break;
+      case 192: fill_plan<192, kModeStore>(plan); break;
+      case 256: fill_plan<256, kModeStore>(plan); break;
+      default:
+        set_error("unsupported tile_tokens %d (use 16, 32, 64, 96, 128, 192 or 256)", tn);
+        return kInvalidArgument;
+    }
   }
   // The tensor-memory address of the activation scales must sit on an even
   // column, so tiles that start inside a 128-row scale atom need 64-row steps.
@@ -686,7 +782,7 @@ int plan_w6a8(const GemmProblem& p, GemmPlan* plan) {
   int splits = p.splits;
   if (splits == 0) {
     splits = 1;
-    if (!grouped && tn <= 96 && tiles * 2 <= sms) {
+    if (!grouped && !swiglu && tn <= 96 && tiles * 2 <= sms) {
       splits = (int)(sms / tiles);
       const int max_splits = k_blocks / 2 > 0 ? k_blocks / 2 : 1;
       if (splits > max_splits) splits = max_splits;
@@ -712,8 +808,11 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
                  (reinterpret_cast<uintptr_t>(p.w_scales) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(p.a_scales) & 15) == 0,
              "activation values and scale buffers must be 16-byte aligned");
-  MX_REQUIRE(p.out_dtype == kBF16 || p.out_dtype == kF16,
+  const bool swiglu = p.mode == kGemmSwigluMxfp8;
+  MX_REQUIRE(swiglu || p.out_dtype == kBF16 || p.out_dtype == kF16,
              "out_dtype must be float16 or bfloat16");
+  MX_REQUIRE(!swiglu || p.out_packed_scales != nullptr || p.out_logical_scales != nullptr,
+             "SwiGLU mode needs a scale output");
   if (plan.splits > 1) {
     MX_REQUIRE(p.partials != nullptr && p.counters != nullptr &&
                    p.partial_bytes >= plan.partial_bytes && p.counter_bytes >= plan.counter_bytes,
@@ -724,8 +823,8 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
   MX_CUDA(cudaGetDevice(&device));
   CUtensorMap tm_w, tm_a;
   if (int rc = cached_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B, p.w_values,
-                          (uint64_t)p.k, (uint64_t)p.groups * p.n, (uint64_t)p.k * 3 / 4,
-                          kTileF))
+                          (uint64_t)p.k, (uint64_t)p.groups * p.n * (swiglu ? 2 : 1),
+                          (uint64_t)p.k * 3 / 4, kTileF))
     return rc;
   if (int rc = cached_map(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.a_values, (uint64_t)p.k,
                           (uint64_t)p.m_total, (uint64_t)p.k, (uint32_t)plan.tile_tokens))
@@ -743,6 +842,10 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
   args.m_total = p.m_total;
   args.groups = p.groups;
   args.n = p.n;
+  args.w_rows_per_group = p.n * (swiglu ? 2 : 1);
+  args.out_packed_scales = p.out_packed_scales;
+  args.out_logical_scales = p.out_logical_scales;
+  args.out_scale_offsets = p.out_scale_offsets;
   args.k_blocks = p.k / kTileK;
   args.n_tiles = (p.n + kTileF - 1) / kTileF;
   args.splits = plan.splits;
@@ -758,14 +861,23 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
     const int64_t scale_rows = p.a_scale_rows > 0 ? p.a_scale_rows : round_up64(p.m_total, kAtomRows);
     args.a_scale_row_blocks = (int)(scale_rows / kAtomRows);
   }
-  switch (plan.tile_tokens) {
-    case 16: return launch_tn<16>(tm_w, tm_a, args, plan, stream);
-    case 32: return launch_tn<32>(tm_w, tm_a, args, plan, stream);
-    case 64: return launch_tn<64>(tm_w, tm_a, args, plan, stream);
-    case 96: return launch_tn<96>(tm_w, tm_a, args, plan, stream);
-    case 128: return launch_tn<128>(tm_w, tm_a, args, plan, stream);
-    case 192: return launch_tn<192>(tm_w, tm_a, args, plan, stream);
-    case 256: return launch_tn<256>(tm_w, tm_a, args, plan, stream);
+  if (swiglu) {
+    switch (plan.tile_tokens) {
+      case 16: return launch_tn<16, kModeSwiglu>(tm_w, tm_a, args, plan, stream);
+      case 32: return launch_tn<32, kModeSwiglu>(tm_w, tm_a, args, plan, stream);
+      case 64: return launch_tn<64, kModeSwiglu>(tm_w, tm_a, args, plan, stream);
+      case 128: return launch_tn<128, kModeSwiglu>(tm_w, tm_a, args, plan, stream);
+    }
+  } else {
+    switch (plan.tile_tokens) {
+      case 16: return launch_tn<16, kModeStore>(tm_w, tm_a, args, plan, stream);
+      case 32: return launch_tn<32, kModeStore>(tm_w, tm_a, args, plan, stream);
+      case 64: return launch_tn<64, kModeStore>(tm_w, tm_a, args, plan, stream);
+      case 96: return launch_tn<96, kModeStore>(tm_w, tm_a, args, plan, stream);
+      case 128: return launch_tn<128, kModeStore>(tm_w, tm_a, args, plan, stream);
+      case 192: return launch_tn<192, kModeStore>(tm_w, tm_a, args, plan, stream);
+      case 256: return launch_tn<256, kModeStore>(tm_w, tm_a, args, plan, stream);
+    }
   }
   set_error("unsupported tile_tokens %d", plan.tile_tokens);
   return kInvalidArgument;

@@ -6,8 +6,12 @@
 namespace mx {
 
 // Epilogue selector of the tcgen05 kernel.
-enum GemmEpilogue : int {
-  kEpiStore = 0,      // out[row, f] = cast(alpha * acc)
+enum GemmMode : int {
+  kGemmStore = 0,        // out[row, f] = cast(alpha * acc), FP16/BF16
+  // Weights hold 2 * n rows per group (gate rows, then up rows).  out[row, f] =
+  // MXFP8 of bf16(silu(bf16(gate)) ) * bf16(up) with one UE8M0 scale per 32 features
+  // (the reference's fused W1 epilogue, csrc/moe.cu:2226-2235).
+  kGemmSwigluMxfp8 = 1,
 };
 
 struct GemmProblem {
@@ -35,6 +39,12 @@ struct GemmProblem {
   size_t partial_bytes = 0;
   uint32_t* counters = nullptr;
   size_t counter_bytes = 0;
+  int mode = kGemmStore;
+  // SwiGLU mode outputs: scales of the E4M3 result, logical [m_total, n/32] and/or
+  // packed; out_scale_offsets (device, groups + 1) maps group rows to packed rows.
+  uint8_t* out_packed_scales = nullptr;
+  uint8_t* out_logical_scales = nullptr;
+  const int64_t* out_scale_offsets = nullptr;
   // Optional overrides (0 = choose from the static table).
   int tile_tokens = 0;
   int splits = 0;

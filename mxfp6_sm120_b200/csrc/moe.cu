@@ -1,0 +1,543 @@
+// Routed-MoE support kernels: softmax top-k + MXFP8 quantization of the token rows,
+// expert histogram / offsets, row permutation with grouped-packed scales, the
+// unfused SiLU*mul + MXFP8 requantization, and the weighted reduce with the gated
+// shared expert.
+//
+// Arithmetic follows the reference:
+//   * top-k: FP32 softmax of BF16 logits (expf, max-subtracted, multiply by 1/sum,
+//     non-finite -> 0), k rounds of arg-max with ties to the smaller expert id,
+//     optional renormalisation w / sum(w)            (csrc/moe.cu:412-510);
+//   * routing: counts -> exclusive prefix = expert_offsets, prefix of 128-padded
+//     counts = scale_offsets, row order inside an expert is arrival order
+//                                                     (csrc/moe.cu:4263-4446);
+//   * SiLU path: g = bf16(a_g); u = bf16(a_u); s = bf16(g / (1 + expf(-g)));
+//     v = bf16(s * u); MXFP8 quantization of v per 32   (csrc/moe.cu:5199-5205);
+//   * reduce: out[t] = cast(sigmoid(gate_t) * shared[t] + sum_r w[t,r] * routed[inv[t,r]])
+//     in FP32, shared term first, routes in order       (csrc/moe.cu:7972-7988).
+// The launch shapes are new and generic in hidden size, expert count and k.
+#include "common.cuh"
+
+#include <cuda_fp8.h>
+
+namespace mx {
+namespace {
+
+constexpr int kMaxTopk = 16;
+constexpr int kMaxExperts = 1024;
+
+__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+// ---------------------------------------------------------------- top-k + quantize
+// One CTA per token.  All threads quantize the hidden row; warp 0 then does the
+// softmax top-k of that token's logits.
+__global__ void __launch_bounds__(256)
+topk_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16* __restrict__ logits,
+                  uint8_t* __restrict__ quantized, uint8_t* __restrict__ logical_scales,
+                  uint8_t* __restrict__ dense_scales, float* __restrict__ topk_weights,
+                  int32_t* __restrict__ topk_ids, int hidden_size, int experts, int topk,
+                  int renormalize) {
+  const int token = blockIdx.x;
+  const int groups = hidden_size / kScaleVec;
+  if (quantized != nullptr) {
+    const int chunks = hidden_size / 8;
+    const int rounds = (chunks + blockDim.x - 1) / blockDim.x;
+    for (int it = 0; it < rounds; ++it) {
+      const int c = it * blockDim.x + threadIdx.x;
+      const bool valid = c < chunks;
+      float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (valid) {
+        const uint4 raw =
+            __ldg(reinterpret_cast<const uint4*>(hidden + (int64_t)token * hidden_size) + c);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          v[2 * i] = __uint_as_float(w[i] << 16);
+          v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+      }
+      float amax = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
+      const float inv = __fdiv_rn(1.0f, __uint_as_float(sbits));
+      if (valid) {
+        const uint2 packed = make_uint2(e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
+                                        e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
+        reinterpret_cast<uint2*>(quantized + (int64_t)token * hidden_size)[c] = packed;
+        if ((c & 3) == 0) {
+          const int g = c >> 2;
+          const uint8_t code = static_cast<uint8_t>(sbits >> 23);
+          if (logical_scales != nullptr) logical_scales[(int64_t)token * groups + g] = code;
+          if (dense_scales != nullptr) dense_scales[packed_scale_offset(token, g, groups)] = code;
+        }
+      }
+    }
+  }
+  if (topk_ids == nullptr || threadIdx.x >= 32) return;
+  // ---- softmax top-k by warp 0; lane l owns experts l, l + 32, ...
+  const int lane = threadIdx.x;
+  constexpr int kPerLane = kMaxExperts / 32;
+  float p[kPerLane];
+  float vmax = -INFINITY;
+  const int per_lane = (experts + 31) / 32;
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    p[i] = -INFINITY;
+    const int e = lane + 32 * i;
+    if (i < per_lane && e < experts) {
+      p[i] = __bfloat162float(logits[(int64_t)token * experts + e]);
+      vmax = fmaxf(vmax, p[i]);
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, d));
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    const int e = lane + 32 * i;
+    if (i < per_lane && e < experts) {
+      p[i] = expf(p[i] - vmax);
+      sum += p[i];
+    } else {
+      p[i] = -1.0f;  // never selected
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+  const float inv_sum = 1.0f / sum;
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    if (p[i] >= 0.0f) {
+      float q = p[i] * inv_sum;
+      if (!isfinite(q)) q = 0.0f;
+      p[i] = q;
+    }
+  }
+  float weight_sum = 0.0f;
+  float my_weight = 0.0f;  // lane r keeps the r-th selected weight
+  int my_id = 0;
+  for (int r = 0; r < topk; ++r) {
+    float best = -2.0f;
+    int best_id = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int e = lane + 32 * i;
+      if (p[i] > best) {  // ascending ids inside a lane: first maximum is the smallest id
+        best = p[i];
+        best_id = e;
+      }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, d);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_id, d);
+      if (ov > best || (ov == best && oi < best_id)) {
+        best = ov;
+        best_id = oi;
+      }
+    }
+    if (lane == (best_id & 31)) {
+#pragma unroll
+      for (int i = 0; i < kPerLane; ++i) {
+        if (lane + 32 * i == best_id) p[i] = -10000.0f;
+      }
+    }
+    if (lane == r) {
+      my_weight = best;
+      my_id = best_id;
+    }
+    weight_sum += best;
+  }
+  if (lane < topk) {
+    float w = my_weight;
+    if (renormalize) w = weight_sum > 0.0f ? w / weight_sum : 0.0f;
+    topk_weights[(int64_t)token * topk + lane] = w;
+    topk_ids[(int64_t)token * topk + lane] = my_id;
+  }
+}
+
+// ---------------------------------------------------------------- counts and offsets
+__device__ __forceinline__ int local_expert(int64_t global, const int32_t* expert_map,
+                                            int map_size, int local_experts) {
+  if (global < 0) return -1;
+  int local = static_cast<int>(global);
+  if (expert_map != nullptr) {
+    if (global >= map_size) return -1;
+    local = expert_map[global];
+  }
+  return (local >= 0 && local < local_experts) ? local : -1;
+}
+
+// Single CTA: histogram of the routed expert ids, exclusive prefix sums.
+template <class Id>
+__global__ void __launch_bounds__(1024)
+route_count_kernel(const Id* __restrict__ topk_ids, int64_t routes,
+                   const int32_t* __restrict__ expert_map, int map_size, int local_experts,
+                   int64_t* __restrict__ expert_offsets, int64_t* __restrict__ scale_offsets,
+                   int32_t* __restrict__ cursors) {
+  __shared__ int counts[kMaxExperts];
+  __shared__ int warp_sums[2][32];
+  const int tid = threadIdx.x;
+  for (int e = tid; e < kMaxExperts; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int64_t i = tid; i < routes; i += blockDim.x) {
+    const int e = local_expert(static_cast<int64_t>(topk_ids[i]), expert_map, map_size,
+                               local_experts);
+    if (e >= 0) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  // Block-wide inclusive scans (one expert per thread) of counts and padded counts.
+  const int c = tid < local_experts ? counts[tid] : 0;
+  const int pc = (c + kAtomRows - 1) / kAtomRows * kAtomRows;
+  int incl = c, pincl = pc;
+  const int lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, incl, d);
+    const int b = __shfl_up_sync(0xffffffffu, pincl, d);
+    if (lane >= d) {
+      incl += a;
+      pincl += b;
+    }
+  }
+  if (lane == 31) {
+    warp_sums[0][warp] = incl;
+    warp_sums[1][warp] = pincl;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int a = warp_sums[0][lane], b = warp_sums[1][lane];
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int ua = __shfl_up_sync(0xffffffffu, a, d);
+      const int ub = __shfl_up_sync(0xffffffffu, b, d);
+      if (lane >= d) {
+        a += ua;
+        b += ub;
+      }
+    }
+    warp_sums[0][lane] = a;
+    warp_sums[1][lane] = b;
+  }
+  __syncthreads();
+  const int base = warp > 0 ? warp_sums[0][warp - 1] : 0;
+  const int pbase = warp > 0 ? warp_sums[1][warp - 1] : 0;
+  if (tid < local_experts) {
+    expert_offsets[tid] = base + incl - c;
+    scale_offsets[tid] = pbase + pincl - pc;
+    if (cursors != nullptr) cursors[tid] = 0;
+    if (tid == local_experts - 1) {
+      expert_offsets[local_experts] = base + incl;
+      scale_offsets[local_experts] = pbase + pincl;
+    }
+  }
+}
+
+// One warp per route: claim a row of its expert, copy the MXFP8 row and its scales.
+template <class Id>
+__global__ void __launch_bounds__(256)
+route_scatter_kernel(const uint8_t* __restrict__ activation,
+                     const uint8_t* __restrict__ logical_scales, const Id* __restrict__ topk_ids,
+                     int64_t routes, int topk, int hidden_size,
+                     const int32_t* __restrict__ expert_map, int map_size, int local_experts,
+                     const int64_t* __restrict__ expert_offsets,
+                     const int64_t* __restrict__ scale_offsets, int32_t* __restrict__ cursors,
+                     uint8_t* __restrict__ permuted, uint8_t* __restrict__ grouped_scales,
+                     int32_t* __restrict__ inverse_permutation,
+                     int32_t* __restrict__ source_tokens) {
+  const int lane = threadIdx.x & 31;
+  const int64_t route = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (route >= routes) return;
+  const int e = local_expert(static_cast<int64_t>(topk_ids[route]), expert_map, map_size,
+                             local_experts);
+  if (e < 0) {
+    if (lane == 0) inverse_permutation[route] = -1;  // dropped: the reducer skips it
+    return;
+  }
+  int local = 0;
+  if (lane == 0) local = atomicAdd(&cursors[e], 1);
+  local = __shfl_sync(0xffffffffu, local, 0);
+  const int64_t row = expert_offsets[e] + local;
+  const int64_t token = route / topk;
+  if (permuted != nullptr) {
+    const uint4* src = reinterpret_cast<const uint4*>(activation + token * hidden_size);
+    uint4* dst = reinterpret_cast<uint4*>(permuted + row * hidden_size);
+    for (int i = lane; i < hidden_size / 16; i += 32) dst[i] = __ldg(src + i);
+  }
+  const int groups = hidden_size / kScaleVec;
+  const int64_t srow = scale_offsets[e] + local;
+  for (int g = lane; g < groups; g += 32) {
+    grouped_scales[packed_scale_offset(srow, g, groups)] = __ldg(logical_scales + token * groups + g);
+  }
+  if (lane == 0) {
+    inverse_permutation[route] = static_cast<int32_t>(row);
+    if (source_tokens != nullptr) source_tokens[row] = static_cast<int32_t>(token);
+  }
+}
+
+// ---------------------------------------------------------------- SiLU * mul + MXFP8
+// input [rows, 2I] (gate columns first), output [rows, I] E4M3 + scales.  Scale
+// placement: logical [rows, I/32]; or packed with row -> scale row through
+// expert/scale offsets (grouped) or identity (dense).
+template <class T>
+__global__ void __launch_bounds__(256)
+silu_mul_quant_kernel(const T* __restrict__ input, uint8_t* __restrict__ output,
+                      uint8_t* __restrict__ logical, uint8_t* __restrict__ packed, int64_t rows,
+                      int inter, const int64_t* __restrict__ expert_offsets,
+                      const int64_t* __restrict__ scale_offsets, int experts) {
+  const int groups = inter / kScaleVec;
+  const int64_t chunks = rows * (inter / 8);
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t rounds = (chunks + nthreads - 1) / nthreads;
+  for (int64_t it = 0; it < rounds; ++it) {
+    const int64_t c = it * nthreads + tid;
+    const bool valid = c < chunks;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    int64_t row = 0;
+    int col = 0;
+    if (valid) {
+      row = c / (inter / 8);
+      col = static_cast<int>(c - row * (inter / 8)) * 8;
+      const T* g_ptr = input + row * 2 * inter + col;
+      const uint4 graw = __ldg(reinterpret_cast<const uint4*>(g_ptr));
+      const uint4 uraw = __ldg(reinterpret_cast<const uint4*>(g_ptr + inter));
+      const T* gv = reinterpret_cast<const T*>(&graw);
+      const T* uv = reinterpret_cast<const T*>(&uraw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float g = round_bf16(to_float(gv[i]));
+        const float u = round_bf16(to_float(uv[i]));
+        const float s = round_bf16(__fdiv_rn(g, 1.0f + expf(-g)));
+        v[i] = round_bf16(s * u);
+      }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
+    const float inv = __fdiv_rn(1.0f, __uint_as_float(sbits));
+    if (valid) {
+      reinterpret_cast<uint2*>(output)[c] =
+          make_uint2(e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
+                     e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
+      if ((c & 3) == 0) {
+        const int g = col / kScaleVec;
+        const uint8_t code = static_cast<uint8_t>(sbits >> 23);
+        if (logical != nullptr) logical[row * groups + g] = code;
+        if (packed != nullptr) {
+          int64_t srow = row;
+          if (expert_offsets != nullptr) {
+            int lo = 0, hi = experts;  // largest e with expert_offsets[e] <= row
+            while (hi - lo > 1) {
+              const int mid = (lo + hi) >> 1;
+              if (expert_offsets[mid] <= row) lo = mid; else hi = mid;
+            }
+            srow = scale_offsets[lo] + (row - expert_offsets[lo]);
+          }
+          packed[packed_scale_offset(srow, g, groups)] = code;
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------- weighted reduce
+template <class T>
+struct Pack8 {
+  uint4 raw;
+};
+
+template <class T>
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
+  const T* p = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = to_float(p[i]);
+}
+
+template <class T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ __half from_float<__half>(float v) {
+  return __float2half_rn(v);
+}
+
+// grid = (tokens, ceil(H / (8 * blockDim.x))); every thread owns 8 consecutive columns.
+template <class T>
+__global__ void __launch_bounds__(256)
+moe_reduce_kernel(T* __restrict__ out, const T* __restrict__ routed,
+                  const float* __restrict__ topk_weights,
+                  const int32_t* __restrict__ inverse_permutation, const T* __restrict__ shared,
+                  const void* __restrict__ shared_gate, int gate_dtype, int gate_stride,
+                  int hidden_size, int topk, int64_t routed_rows) {
+  const int token = blockIdx.x;
+  const int col = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (col >= hidden_size) return;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (shared != nullptr) {
+    float gate = 1.0f;
+    if (shared_gate != nullptr) {
+      const int64_t gi = (int64_t)token * gate_stride + (gate_stride - 1);
+      float x;
+      if (gate_dtype == kF32) x = static_cast<const float*>(shared_gate)[gi];
+      else if (gate_dtype == kBF16) x = __bfloat162float(static_cast<const __nv_bfloat16*>(shared_gate)[gi]);
+      else x = __half2float(static_cast<const __half*>(shared_gate)[gi]);
+      gate = __fdiv_rn(1.0f, 1.0f + expf(-x));
+    }
+    float s[8];
+    unpack8<T>(__ldg(reinterpret_cast<const uint4*>(shared + (int64_t)token * hidden_size + col)), s);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = gate * s[i];
+  }
+  for (int r = 0; r < topk; ++r) {
+    const int32_t row = inverse_permutation[(int64_t)token * topk + r];
+    if (row < 0 || row >= routed_rows) continue;
+    const float w = topk_weights[(int64_t)token * topk + r];
+    float v[8];
+    unpack8<T>(__ldg(reinterpret_cast<const uint4*>(routed + (int64_t)row * hidden_size + col)), v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(w, v[i]));
+  }
+  uint4 packed;
+  T* o = reinterpret_cast<T*>(&packed);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = from_float<T>(acc[i]);
+  *reinterpret_cast<uint4*>(out + (int64_t)token * hidden_size + col) = packed;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+int moe_topk_quant(const void* hidden, const void* logits, int64_t tokens, int hidden_size,
+                   int experts, int topk, int renormalize, uint8_t* quantized,
+                   uint8_t* logical_scales, uint8_t* dense_scales, float* topk_weights,
+                   int32_t* topk_ids, cudaStream_t stream) {
+  MX_REQUIRE(tokens > 0 && tokens <= INT32_MAX, "tokens must be positive");
+  MX_REQUIRE(hidden_size > 0 && hidden_size % kScaleVec == 0, "hidden size must be a multiple of 32");
+  MX_REQUIRE(quantized == nullptr || (hidden != nullptr && aligned16(hidden)),
+             "hidden must be a 16-byte aligned device pointer");
+  if (topk_ids != nullptr) {
+    MX_REQUIRE(logits != nullptr && topk_weights != nullptr, "logits/topk_weights must not be null");
+    MX_REQUIRE(experts > 0 && experts <= kMaxExperts, "experts must be in [1, %d]", kMaxExperts);
+    MX_REQUIRE(topk > 0 && topk <= kMaxTopk && topk <= experts, "topk must be in [1, %d]", kMaxTopk);
+  }
+  topk_quant_kernel<<<(unsigned)tokens, 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(hidden), static_cast<const __nv_bfloat16*>(logits),
+      quantized, logical_scales, dense_scales, topk_weights, topk_ids, hidden_size, experts, topk,
+      renormalize);
+  MX_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int moe_route(const uint8_t* activation, const uint8_t* logical_scales, const void* topk_ids,
+              int ids_are_int64, int64_t tokens, int topk, int hidden_size,
+              const int32_t* expert_map, int map_size, int local_experts,
+              int64_t* expert_offsets, int64_t* scale_offsets, int32_t* cursors,
+              uint8_t* permuted, uint8_t* grouped_scales, int32_t* inverse_permutation,
+              int32_t* source_tokens, cudaStream_t stream) {
+  MX_REQUIRE(tokens > 0 && topk > 0, "tokens and topk must be positive");
+  MX_REQUIRE(local_experts > 0 && local_experts <= kMaxExperts, "local_experts must be in [1, %d]",
+             kMaxExperts);
+  MX_REQUIRE(hidden_size > 0 && hidden_size % kScaleVec == 0 && hidden_size % 16 == 0,
+             "hidden size must be a multiple of 32");
+  MX_REQUIRE(topk_ids && expert_offsets && scale_offsets && cursors && grouped_scales &&
+                 inverse_permutation && logical_scales,
+             "routing buffers must not be null");
+  MX_REQUIRE(permuted == nullptr || (activation != nullptr && aligned16(activation) && aligned16(permuted)),
+             "activation / permuted rows must be 16-byte aligned");
+  const int64_t routes = tokens * topk;
+  const unsigned scatter_grid = (unsigned)((routes + 7) / 8);
+  if (ids_are_int64) {
+    const int64_t* ids = static_cast<const int64_t*>(topk_ids);
+    route_count_kernel<int64_t><<<1, 1024, 0, stream>>>(ids, routes, expert_map, map_size,
+                                                        local_experts, expert_offsets,
+                                                        scale_offsets, cursors);
+    route_scatter_kernel<int64_t><<<scatter_grid, 256, 0, stream>>>(
+        activation, logical_scales, ids, routes, topk, hidden_size, expert_map, map_size,
+        local_experts, expert_offsets, scale_offsets, cursors, permuted, grouped_scales,
+        inverse_permutation, source_tokens);
+  } else {
+    const int32_t* ids = static_cast<const int32_t*>(topk_ids);
+    route_count_kernel<int32_t><<<1, 1024, 0, stream>>>(ids, routes, expert_map, map_size,
+                                                        local_experts, expert_offsets,
+                                                        scale_offsets, cursors);
+    route_scatter_kernel<int32_t><<<scatter_grid, 256, 0, stream>>>(
+        activation, logical_scales, ids, routes, topk, hidden_size, expert_map, map_size,
+        local_experts, expert_offsets, scale_offsets, cursors, permuted, grouped_scales,
+        inverse_permutation, source_tokens);
+  }
+  MX_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int silu_mul_quant(const void* input, int dtype, int64_t rows, int inter, uint8_t* output,
+                   uint8_t* logical, uint8_t* packed, const int64_t* expert_offsets,
+                   const int64_t* scale_offsets, int experts, cudaStream_t stream) {
+  MX_REQUIRE(input != nullptr && output != nullptr, "pointers must not be null");
+  MX_REQUIRE(dtype == kF16 || dtype == kBF16, "input must be float16 or bfloat16");
+  MX_REQUIRE(rows > 0 && inter > 0 && inter % kScaleVec == 0,
+             "input must be [M, 2K] with K divisible by 32");
+  MX_REQUIRE(aligned16(input) && (reinterpret_cast<uintptr_t>(output) & 7) == 0,
+             "input/output must be 16/8-byte aligned");
+  MX_REQUIRE(logical != nullptr || packed != nullptr, "one scale output is required");
+  MX_REQUIRE((expert_offsets == nullptr) == (scale_offsets == nullptr),
+             "expert_offsets and scale_offsets go together");
+  const int64_t chunks = rows * (inter / 8);
+  int64_t blocks = (chunks + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == kBF16) {
+    silu_mul_quant_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(input), output, logical, packed, rows, inter,
+        expert_offsets, scale_offsets, experts);
+  } else {
+    silu_mul_quant_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>(
+        static_cast<const __half*>(input), output, logical, packed, rows, inter, expert_offsets,
+        scale_offsets, experts);
+  }
+  MX_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int moe_reduce(void* out, const void* routed, int dtype, const float* topk_weights,
+               const int32_t* inverse_permutation, const void* shared, const void* shared_gate,
+               int gate_dtype, int gate_stride, int64_t tokens, int hidden_size, int topk,
+               int64_t routed_rows, cudaStream_t stream) {
+  MX_REQUIRE(out && routed && topk_weights && inverse_permutation, "pointers must not be null");
+  MX_REQUIRE(dtype == kF16 || dtype == kBF16, "routed_output must be float16 or bfloat16");
+  MX_REQUIRE(tokens > 0 && topk > 0 && hidden_size > 0 && hidden_size % 8 == 0,
+             "hidden size must be a multiple of 8");
+  MX_REQUIRE(aligned16(out) && aligned16(routed) && (shared == nullptr || aligned16(shared)),
+             "row buffers must be 16-byte aligned");
+  MX_REQUIRE(shared_gate == nullptr || shared != nullptr, "shared_gate requires shared_output");
+  MX_REQUIRE(gate_stride >= 1, "gate stride must be positive");
+  const int threads = hidden_size / 8 < 256 ? ((hidden_size / 8 + 31) / 32 * 32) : 256;
+  const dim3 grid((unsigned)tokens, (unsigned)((hidden_size / 8 + threads - 1) / threads));
+  if (dtype == kBF16) {
+    moe_reduce_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+        static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(routed), topk_weights,
+        inverse_permutation, static_cast<const __nv_bfloat16*>(shared), shared_gate, gate_dtype,
+        gate_stride, hidden_size, topk, routed_rows);
+  } else {
+    moe_reduce_kernel<__half><<<grid, threads, 0, stream>>>(
+        static_cast<__half*>(out), static_cast<const __half*>(routed), topk_weights,
+        inverse_permutation, static_cast<const __half*>(shared), shared_gate, gate_dtype,
+        gate_stride, hidden_size, topk, routed_rows);
+  }
+  MX_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+}  // namespace mx

@@ -1,0 +1,689 @@
+"""Routed-MoE operators (top-k routing, permutation, grouped W6A8 GEMMs, fused
+SwiGLU requantization, reduce) with the names and argument meaning of the
+reference's ``python/mxfp6/ops.py``.  All ``*_out`` functions write into
+caller-owned tensors and allocate nothing, so a whole layer captures into one
+CUDA graph.  Shapes are generic (hidden size, intermediate size, expert count
+and k are read from the tensors) instead of the reference's hard-coded
+2048 / 256 / 256 / 8.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ._loader import check, library, load_library
+from .ops import (
+    SCALE_VECTOR_SIZE,
+    _DTYPE_CODE,
+    _ptr,
+    _require_cuda_uint8_contiguous,
+    _require_sm100,
+    _stream,
+    _validate_output_dtype,
+    packed_scale_numel,
+)
+
+_GATE_CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+
+
+def _as_u8(tensor: torch.Tensor) -> torch.Tensor:
+    return tensor.view(torch.uint8) if tensor.dtype == torch.float8_e4m3fn else tensor
+
+
+def _check_offsets(tensor: torch.Tensor, device: torch.device, name: str) -> None:
+    if (
+        tensor.device != device
+        or tensor.dtype != torch.int64
+        or tensor.ndim != 1
+        or tensor.numel() < 2
+        or not tensor.is_contiguous()
+    ):
+        raise ValueError(f"{name} must be a contiguous CUDA int64 tensor with E+1 entries")
+
+
+def grouped_scale_rows(rows: int, experts: int) -> int:
+    """Row capacity of a grouped packed scale buffer: every active expert may add
+    up to 127 rows of padding (the reference's sizing, python/mxfp6/ops.py:1494)."""
+    return rows + min(rows, experts) * 127
+
+
+# ------------------------------------------------------------------- SiLU * mul + MXFP8
+
+
+def _check_silu_input(input: torch.Tensor) -> tuple[int, int]:
+    if (
+        input.device.type != "cuda"
+        or input.dtype not in (torch.float16, torch.bfloat16)
+        or input.ndim != 2
+        or not input.is_contiguous()
+        or input.shape[1] % 64
+    ):
+        raise ValueError(
+            "input must be contiguous CUDA float16/bfloat16 [M,2K] with K divisible by 32"
+        )
+    return int(input.shape[0]), int(input.shape[1]) // 2
+
+
+def _silu_raw(input, output, logical, packed, expert_offsets, scale_offsets) -> None:
+    rows, inter = _check_silu_input(input)
+    experts = 0 if expert_offsets is None else expert_offsets.numel() - 1
+    with torch.cuda.device(input.device):
+        check(
+            library().mxfp6_silu_and_mul_mxfp8(
+                input.data_ptr(), _DTYPE_CODE[input.dtype], rows, inter, output.data_ptr(),
+                _ptr(logical), _ptr(packed), _ptr(expert_offsets), _ptr(scale_offsets), experts,
+                _stream(input.device),
+            )
+        )
+
+
+def silu_and_mul_mxfp8_logical(input: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Fuse SiLU-and-mul with row-major logical MXFP8 quantization."""
+    rows, inter = _check_silu_input(input)
+    _require_sm100(input.device)
+    load_library()
+    values = torch.empty((rows, inter), dtype=torch.uint8, device=input.device)
+    scales = torch.empty((rows, inter // SCALE_VECTOR_SIZE), dtype=torch.uint8, device=input.device)
+    _silu_raw(input, values, scales, None, None, None)
+    return values.view(torch.float8_e4m3fn), scales
+
+
+def silu_and_mul_mxfp8_packed_out(
+    output: torch.Tensor, packed_scales: torch.Tensor, input: torch.Tensor
+) -> None:
+    """Fuse SiLU-and-mul with MXFP8 quantization into dense packed scales."""
+    rows, inter = _check_silu_input(input)
+    if _as_u8(output).shape != (rows, inter) or not output.is_contiguous():
+        raise ValueError(f"output must be contiguous CUDA MXFP8 {(rows, inter)}")
+    _require_cuda_uint8_contiguous(packed_scales, "packed_scales")
+    if packed_scales.numel() < packed_scale_numel(rows, inter):
+        raise ValueError("packed_scales is too small")
+    _require_sm100(input.device)
+    load_library()
+    _silu_raw(input, _as_u8(output), None, packed_scales, None, None)
+
+
+def silu_and_mul_mxfp8_grouped(
+    input: torch.Tensor,
+    expert_offsets: torch.Tensor,
+    scale_offsets: torch.Tensor | None = None,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Fuse SiLU-and-mul with routed MXFP8 quantization and scale packing."""
+    rows, inter = _check_silu_input(input)
+    _check_offsets(expert_offsets, input.device, "expert_offsets")
+    if scale_offsets is not None:
+        _check_offsets(scale_offsets, input.device, "scale_offsets")
+        if scale_offsets.shape != expert_offsets.shape:
+            raise ValueError("scale_offsets must have E+1 entries")
+    _require_sm100(input.device)
+    load_library()
+    experts = expert_offsets.numel() - 1
+    if scale_offsets is None:
+        scale_offsets = torch.empty_like(expert_offsets)
+        with torch.cuda.device(input.device):
+            check(
+                library().mxfp6_grouped_scale_offsets(
+                    expert_offsets.data_ptr(), experts, scale_offsets.data_ptr(),
+                    _stream(input.device),
+                )
+            )
+    values = torch.empty((rows, inter), dtype=torch.uint8, device=input.device)
+    groups = (inter // SCALE_VECTOR_SIZE + 3) // 4 * 4
+    scales = torch.full(
+        (grouped_scale_rows(rows, experts) * groups,), 0x7F, dtype=torch.uint8, device=input.device
+    )
+    _silu_raw(input, values, None, scales, expert_offsets, scale_offsets)
+    return values.view(torch.float8_e4m3fn), scales, scale_offsets
+
+
+def silu_and_mul_mxfp8_grouped_out(
+    output: torch.Tensor,
+    scales: torch.Tensor,
+    input: torch.Tensor,
+    expert_offsets: torch.Tensor,
+    scale_offsets: torch.Tensor,
+    use_pdl: bool = False,
+    grouped_output: torch.Tensor | None = None,
+    weight: torch.Tensor | None = None,
+    weight_scales: torch.Tensor | None = None,
+) -> None:
+    """Write grouped activation, optionally launching its W2 GEMM."""
+    rows, inter = _check_silu_input(input)
+    _check_offsets(expert_offsets, input.device, "expert_offsets")
+    _check_offsets(scale_offsets, input.device, "scale_offsets")
+    if _as_u8(output).shape != (rows, inter) or not output.is_contiguous():
+        raise ValueError(f"output must be contiguous CUDA MXFP8 {(rows, inter)}")
+    _require_cuda_uint8_contiguous(scales, "scales")
+    fused = grouped_output is not None
+    if fused != (weight is not None) or fused != (weight_scales is not None):
+        raise ValueError("grouped_output, weight, and weight_scales must be provided together")
+    _require_sm100(input.device)
+    load_library()
+    _silu_raw(input, _as_u8(output), None, scales, expert_offsets, scale_offsets)
+    if fused:
+        grouped_gemm_w6a8_out(
+            grouped_output, output, scales, weight, weight_scales, expert_offsets, scale_offsets
+        )
+
+
+# ------------------------------------------------------------------------------ routing
+
+
+def _route_raw(activation, logical_scales, topk_ids, expert_map, local_experts, permuted,
+               grouped_scales, cursors, expert_offsets, scale_offsets, inverse, source_tokens):
+    tokens, hidden = (int(v) for v in activation.shape)
+    with torch.cuda.device(activation.device):
+        check(
+            library().mxfp6_moe_route(
+                _as_u8(activation).data_ptr(), logical_scales.data_ptr(), topk_ids.data_ptr(),
+                int(topk_ids.dtype == torch.int64), tokens, int(topk_ids.shape[1]), hidden,
+                _ptr(expert_map), 0 if expert_map is None else expert_map.numel(), local_experts,
+                expert_offsets.data_ptr(), scale_offsets.data_ptr(), cursors.data_ptr(),
+                None if permuted is None else _as_u8(permuted).data_ptr(),
+                grouped_scales.data_ptr(), inverse.data_ptr(), _ptr(source_tokens),
+                _stream(activation.device),
+            )
+        )
+
+
+def _check_route_inputs(activation, logical_scales, topk_ids) -> None:
+    if (
+        activation.device.type != "cuda"
+        or activation.dtype not in (torch.float8_e4m3fn, torch.uint8)
+        or activation.ndim != 2
+        or not activation.is_contiguous()
+        or activation.shape[1] % SCALE_VECTOR_SIZE
+    ):
+        raise ValueError(
+            "activation must be contiguous CUDA float8_e4m3fn/uint8 [M,K] with K divisible by 32"
+        )
+    expected = (activation.shape[0], activation.shape[1] // SCALE_VECTOR_SIZE)
+    if (
+        logical_scales.device != activation.device
+        or logical_scales.dtype != torch.uint8
+        or tuple(logical_scales.shape) != expected
+        or not logical_scales.is_contiguous()
+    ):
+        raise ValueError(f"logical_scales must be contiguous CUDA uint8 {expected}")
+    if (
+        topk_ids.device != activation.device
+        or topk_ids.dtype not in (torch.int32, torch.int64)
+        or topk_ids.ndim != 2
+        or topk_ids.shape[0] != activation.shape[0]
+        or not topk_ids.is_contiguous()
+    ):
+        raise ValueError("topk_ids must be contiguous CUDA int32/int64 [M,topk]")
+
+
+def route_mxfp8_out(
+    activation: torch.Tensor,
+    logical_scales: torch.Tensor,
+    topk_ids: torch.Tensor,
+    expert_map: torch.Tensor | None,
+    local_experts: int,
+    permuted_activation: torch.Tensor,
+    include_shared: bool = False,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Route MXFP8 rows into ``permuted_activation``.
+
+    Returns ``(grouped_scales, expert_offsets, scale_offsets, inverse_permutation)``.
+    ``expert_map`` (global id -> local id or -1) drops routes of experts that live
+    on other ranks; their ``inverse_permutation`` entries are -1.
+    """
+    _check_route_inputs(activation, logical_scales, topk_ids)
+    if include_shared:
+        raise ValueError("include_shared is not supported: run the shared expert as a dense GEMM")
+    routes = activation.shape[0] * topk_ids.shape[1]
+    if (
+        permuted_activation.device != activation.device
+        or permuted_activation.dtype != activation.dtype
+        or tuple(permuted_activation.shape) != (routes, activation.shape[1])
+        or not permuted_activation.is_contiguous()
+    ):
+        raise ValueError(
+            f"permuted_activation must be contiguous {(routes, activation.shape[1])} "
+            "with the activation dtype and device"
+        )
+    if not 1 <= local_experts <= 1024:
+        raise ValueError("local_experts must be in [1, 1024]")
+    if expert_map is not None and (
+        expert_map.device != activation.device
+        or expert_map.dtype != torch.int32
+        or expert_map.ndim != 1
+        or not expert_map.is_contiguous()
+    ):
+        raise ValueError("expert_map must be a contiguous CUDA int32 vector")
+    _require_sm100(activation.device)
+    load_library()
+    device = activation.device
+    groups = (activation.shape[1] // SCALE_VECTOR_SIZE + 3) // 4 * 4
+    grouped_scales = torch.full(
+        (grouped_scale_rows(routes, local_experts) * groups,), 0x7F, dtype=torch.uint8, device=device
+    )
+    expert_offsets = torch.empty(local_experts + 1, dtype=torch.int64, device=device)
+    scale_offsets = torch.empty(local_experts + 1, dtype=torch.int64, device=device)
+    cursors = torch.empty(local_experts, dtype=torch.int32, device=device)
+    inverse = torch.empty(routes, dtype=torch.int32, device=device)
+    _route_raw(activation, logical_scales, topk_ids, expert_map, local_experts,
+               permuted_activation, grouped_scales, cursors, expert_offsets, scale_offsets,
+               inverse, None)
+    return grouped_scales, expert_offsets, scale_offsets, inverse
+
+
+def qwen35_route_mxfp8_out(
+    activation: torch.Tensor,
+    logical_scales: torch.Tensor,
+    topk_ids: torch.Tensor,
+    permuted_activation: torch.Tensor,
+    packed_scales: torch.Tensor,
+    expert_cursors: torch.Tensor,
+    expert_offsets: torch.Tensor,
+    scale_offsets: torch.Tensor,
+    inverse_permutation: torch.Tensor,
+    include_shared: bool = False,
+    source_tokens: torch.Tensor | None = None,
+    expert_map: torch.Tensor | None = None,
+) -> None:
+    """Route MXFP8 rows into preallocated grouped buffers (allocation-free)."""
+    _check_route_inputs(activation, logical_scales, topk_ids)
+    if include_shared:
+        raise ValueError("include_shared is not supported: run the shared expert as a dense GEMM")
+    _require_sm100(activation.device)
+    load_library()
+    local_experts = expert_offsets.numel() - 1
+    _route_raw(activation, logical_scales, topk_ids, expert_map, local_experts,
+               permuted_activation, packed_scales, expert_cursors, expert_offsets, scale_offsets,
+               inverse_permutation, source_tokens)
+
+
+def qwen35_topk_quant_out(
+    quantized: torch.Tensor,
+    logical_scales: torch.Tensor,
+    packed_scales: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    hidden: torch.Tensor,
+    routed_logits: torch.Tensor,
+    renormalize: bool = False,
+) -> None:
+    """Fuse softmax top-k routing with dual-layout MXFP8 quantization of ``hidden``."""
+    if (
+        hidden.device.type != "cuda"
+        or hidden.dtype != torch.bfloat16
+        or hidden.ndim != 2
+        or hidden.shape[0] < 1
+        or hidden.shape[1] % SCALE_VECTOR_SIZE
+        or not hidden.is_contiguous()
+    ):
+        raise ValueError("hidden must be contiguous CUDA bfloat16 [B,H] with H divisible by 32")
+    batch, width = (int(v) for v in hidden.shape)
+    if (
+        routed_logits.device != hidden.device
+        or routed_logits.dtype != torch.bfloat16
+        or routed_logits.ndim != 2
+        or routed_logits.shape[0] != batch
+        or not routed_logits.is_contiguous()
+    ):
+        raise ValueError("routed_logits must be contiguous CUDA bfloat16 [B,E]")
+    experts = int(routed_logits.shape[1])
+    topk = int(topk_ids.shape[1]) if topk_ids.ndim == 2 else 0
+    expected = (
+        (quantized, torch.uint8, (batch, width), "quantized"),
+        (logical_scales, torch.uint8, (batch, width // SCALE_VECTOR_SIZE), "logical_scales"),
+        (topk_weights, torch.float32, (batch, topk), "topk_weights"),
+        (topk_ids, torch.int32, (batch, topk), "topk_ids"),
+    )
+    for tensor, dtype, shape, name in expected:
+        if (
+            tensor.device != hidden.device
+            or _as_u8(tensor).dtype != dtype
+            or tuple(tensor.shape) != shape
+            or not tensor.is_contiguous()
+        ):
+            raise ValueError(f"{name} must be contiguous CUDA {dtype} {tuple(shape)}")
+    if (
+        packed_scales.device != hidden.device
+        or packed_scales.dtype != torch.uint8
+        or packed_scales.numel() < packed_scale_numel(batch, width)
+        or not packed_scales.is_contiguous()
+    ):
+        raise ValueError("packed_scales must be contiguous CUDA uint8 of the dense packed size")
+    if not isinstance(renormalize, bool):
+        raise TypeError("renormalize must be a bool")
+    if not 1 <= topk <= 16 or not topk <= experts <= 1024:
+        raise ValueError("need 1 <= topk <= 16 and topk <= experts <= 1024")
+    _require_sm100(hidden.device)
+    load_library()
+    with torch.cuda.device(hidden.device):
+        check(
+            library().mxfp6_moe_topk_quant(
+                hidden.data_ptr(), routed_logits.data_ptr(), batch, width, experts, topk,
+                int(renormalize), _as_u8(quantized).data_ptr(), logical_scales.data_ptr(),
+                packed_scales.data_ptr(), topk_weights.data_ptr(), topk_ids.data_ptr(),
+                _stream(hidden.device),
+            )
+        )
+
+
+def qwen35_topk_quant_route_out(
+    quantized: torch.Tensor,
+    logical_scales: torch.Tensor,
+    dense_scales: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    permuted_activation: torch.Tensor,
+    grouped_scales: torch.Tensor,
+    expert_cursors: torch.Tensor,
+    expert_offsets: torch.Tensor,
+    scale_offsets: torch.Tensor,
+    inverse_permutation: torch.Tensor,
+    hidden: torch.Tensor,
+    routed_logits: torch.Tensor,
+    grouped_output: torch.Tensor | None = None,
+    weight: torch.Tensor | None = None,
+    weight_scales: torch.Tensor | None = None,
+    source_tokens: torch.Tensor | None = None,
+    renormalize: bool = False,
+    expert_map: torch.Tensor | None = None,
+) -> None:
+    """Top-k routing + quantization + row permutation, optionally followed by the
+    grouped W1 GEMM (``grouped_output``/``weight``/``weight_scales`` together).
+
+    Rows are always materialised in ``permuted_activation``; ``source_tokens``,
+    when given, additionally receives the token index of every routed row.
+    """
+    fused = grouped_output is not None
+    if fused != (weight is not None) or fused != (weight_scales is not None):
+        raise ValueError("grouped_output, weight, and weight_scales must be provided together")
+    qwen35_topk_quant_out(quantized, logical_scales, dense_scales, topk_weights, topk_ids, hidden,
+                          routed_logits, renormalize)
+    qwen35_route_mxfp8_out(quantized, logical_scales, topk_ids, permuted_activation,
+                           grouped_scales, expert_cursors, expert_offsets, scale_offsets,
+                           inverse_permutation, source_tokens=source_tokens,
+                           expert_map=expert_map)
+    if fused:
+        grouped_gemm_w6a8_out(grouped_output, permuted_activation, grouped_scales, weight,
+                              weight_scales, expert_offsets, scale_offsets)
+
+
+# ------------------------------------------------------------------------ grouped GEMMs
+
+
+def _check_grouped_operands(activation, activation_scales, weight, weight_scales, expert_offsets,
+                            scale_offsets) -> tuple[int, int, int, int]:
+    if (
+        activation.device.type != "cuda"
+        or activation.dtype not in (torch.float8_e4m3fn, torch.uint8)
+        or activation.ndim != 2
+        or not activation.is_contiguous()
+    ):
+        raise ValueError("activation must be contiguous CUDA float8_e4m3fn/uint8 [M,K]")
+    _require_sm100(activation.device)
+    for tensor, name in (
+        (activation_scales, "activation_scales"),
+        (weight, "weight"),
+        (weight_scales, "weight_scales"),
+    ):
+        _require_cuda_uint8_contiguous(tensor, name)
+        if tensor.device != activation.device:
+            raise ValueError(f"{name} must be on {activation.device}")
+    if weight.ndim != 3:
+        raise ValueError("weight must have shape [E,N,packed_K]")
+    for tensor, name in ((expert_offsets, "expert_offsets"), (scale_offsets, "scale_offsets")):
+        if (
+            tensor.device != activation.device
+            or tensor.dtype != torch.int64
+            or tensor.ndim != 1
+            or not tensor.is_contiguous()
+        ):
+            raise ValueError(f"{name} must be a contiguous CUDA int64 tensor")
+    experts, rows_per_expert, packed_k = (int(v) for v in weight.shape)
+    k = packed_k * 4 // 3
+    if int(activation.shape[1]) != k:
+        raise ValueError(f"activation K {activation.shape[1]} does not match weight K {k}")
+    if expert_offsets.numel() != experts + 1 or scale_offsets.numel() != experts + 1:
+        raise ValueError("expert_offsets and scale_offsets must have E+1 entries")
+    groups = (k // SCALE_VECTOR_SIZE + 3) // 4 * 4
+    scale_rows = activation_scales.numel() // groups // 128 * 128
+    return experts, rows_per_expert, k, scale_rows
+
+
+def grouped_gemm_w6a8_out(
+    output: torch.Tensor,
+    activation: torch.Tensor,
+    activation_scales: torch.Tensor,
+    weight: torch.Tensor,
+    weight_scales: torch.Tensor,
+    expert_offsets: torch.Tensor,
+    scale_offsets: torch.Tensor,
+    tile_n: int = 0,
+    use_pdl: bool = False,
+) -> None:
+    """Run native grouped ``A8 @ W6.T`` into a preallocated output.
+
+    ``tile_n`` (the reference's tile selector) is accepted and ignored unless it is
+    one of the token-tile sizes 64, 128, 192, 256 of the tcgen05 kernel.
+    """
+    experts, n, k, scale_rows = _check_grouped_operands(
+        activation, activation_scales, weight, weight_scales, expert_offsets, scale_offsets
+    )
+    if (
+        output.device != activation.device
+        or output.dtype not in (torch.float16, torch.bfloat16)
+        or output.ndim != 2
+        or tuple(output.shape) != (activation.shape[0], n)
+        or not output.is_contiguous()
+    ):
+        raise ValueError("output must be contiguous CUDA float16/bfloat16 [M,N]")
+    load_library()
+    tile = tile_n if tile_n in (64, 128, 192, 256) else 0
+    with torch.cuda.device(activation.device):
+        check(
+            library().mxfp6_grouped_gemm_w6a8(
+                output.data_ptr(), _DTYPE_CODE[output.dtype], _as_u8(activation).data_ptr(),
+                activation_scales.data_ptr(), scale_rows, weight.data_ptr(),
+                weight_scales.data_ptr(), expert_offsets.data_ptr(), scale_offsets.data_ptr(),
+                experts, int(activation.shape[0]), n, k, tile, _stream(activation.device),
+            )
+        )
+
+
+def grouped_gemm_w6a8(
+    activation: torch.Tensor,
+    activation_scales: torch.Tensor,
+    weight: torch.Tensor,
+    weight_scales: torch.Tensor,
+    expert_offsets: torch.Tensor,
+    scale_offsets: torch.Tensor,
+    *,
+    out_dtype: torch.dtype = torch.bfloat16,
+) -> torch.Tensor:
+    """Return native grouped ``A8 @ W6.T`` for routed MoE rows."""
+    out_dtype = _validate_output_dtype(out_dtype)
+    if weight.ndim != 3:
+        raise ValueError("weight must have shape [E,N,packed_K]")
+    output = torch.empty(
+        (activation.shape[0], weight.shape[1]), device=activation.device, dtype=out_dtype
+    )
+    grouped_gemm_w6a8_out(
+        output, activation, activation_scales, weight, weight_scales, expert_offsets, scale_offsets
+    )
+    return output
+
+
+def qwen35_grouped_w1_silu_mxfp8_out(
+    output: torch.Tensor,
+    output_scales: torch.Tensor,
+    activation: torch.Tensor,
+    activation_scales: torch.Tensor,
+    weight: torch.Tensor,
+    weight_scales: torch.Tensor,
+    expert_offsets: torch.Tensor,
+    scale_offsets: torch.Tensor,
+    use_pdl: bool = False,
+    source_tokens: torch.Tensor | None = None,
+    tile_tokens: int = 0,
+) -> None:
+    """Grouped W1 (gate rows, then up rows) with the fused SiLU*mul + MXFP8 epilogue.
+
+    ``activation`` holds the permuted rows and ``activation_scales`` their grouped
+    packed scales; ``output`` is E4M3 ``[rows, I]`` and ``output_scales`` the grouped
+    packed scales of the result (same ``scale_offsets``).
+    """
+    if source_tokens is not None and activation.shape[0] != output.shape[0]:
+        raise ValueError(
+            "indirect rows are not supported: pass the permuted activation rows "
+            "(qwen35_route_mxfp8_out writes them)"
+        )
+    experts, two_inter, k, scale_rows = _check_grouped_operands(
+        activation, activation_scales, weight, weight_scales, expert_offsets, scale_offsets
+    )
+    inter = two_inter // 2
+    if _as_u8(output).shape != (activation.shape[0], inter) or not output.is_contiguous():
+        raise ValueError(f"output must be contiguous CUDA MXFP8 {(activation.shape[0], inter)}")
+    _require_cuda_uint8_contiguous(output_scales, "output_scales")
+    load_library()
+    with torch.cuda.device(activation.device):
+        check(
+            library().mxfp6_w1_swiglu_mxfp8(
+                _as_u8(output).data_ptr(), output_scales.data_ptr(), None,
+                _as_u8(activation).data_ptr(), activation_scales.data_ptr(), scale_rows,
+                weight.data_ptr(), weight_scales.data_ptr(), expert_offsets.data_ptr(),
+                scale_offsets.data_ptr(), experts, int(activation.shape[0]), inter, k, tile_tokens,
+                _stream(activation.device),
+            )
+        )
+
+
+def dense_w1_silu_mxfp8_out(
+    output: torch.Tensor,
+    output_scales: torch.Tensor,
+    activation: torch.Tensor,
+    activation_scales: torch.Tensor,
+    weight: torch.Tensor,
+    weight_scales: torch.Tensor,
+) -> None:
+    """Dense W1 + fused SiLU*mul + MXFP8 (the shared expert's first projection).
+
+    ``weight`` is packed ``[2I, K*3/4]`` (gate rows, then up rows); activation and
+    output scales use the dense packed layout.
+    """
+    rows, k = (int(v) for v in activation.shape)
+    inter = int(weight.numel()) // (k * 3 // 4) // 2
+    _require_sm100(activation.device)
+    load_library()
+    groups = (k // SCALE_VECTOR_SIZE + 3) // 4 * 4
+    with torch.cuda.device(activation.device):
+        check(
+            library().mxfp6_w1_swiglu_mxfp8(
+                _as_u8(output).data_ptr(), output_scales.data_ptr(), None,
+                _as_u8(activation).data_ptr(), activation_scales.data_ptr(),
+                activation_scales.numel() // groups // 128 * 128, weight.data_ptr(),
+                weight_scales.data_ptr(), None, None, 1, rows, inter, k, 0,
+                _stream(activation.device),
+            )
+        )
+
+
+# ------------------------------------------------------------------------------- reduce
+
+
+def moe_reduce_out(
+    output: torch.Tensor,
+    routed_output: torch.Tensor,
+    topk_weights: torch.Tensor,
+    inverse_permutation: torch.Tensor,
+    shared_output: torch.Tensor | None = None,
+    shared_gate: torch.Tensor | None = None,
+    use_pdl: bool = False,
+) -> None:
+    """Reduce routed rows and optionally gate/add a shared-expert output."""
+    if (
+        routed_output.device.type != "cuda"
+        or routed_output.dtype not in (torch.float16, torch.bfloat16)
+        or routed_output.ndim != 2
+        or not routed_output.is_contiguous()
+    ):
+        raise ValueError("routed_output must be contiguous CUDA float16/bfloat16 [routes,H]")
+    if (
+        output.device != routed_output.device
+        or output.dtype != routed_output.dtype
+        or output.ndim != 2
+        or not output.is_contiguous()
+    ):
+        raise ValueError("output must be contiguous CUDA [tokens,H] with routed_output's dtype")
+    if (
+        topk_weights.device != routed_output.device
+        or topk_weights.dtype != torch.float32
+        or topk_weights.ndim != 2
+        or not topk_weights.is_contiguous()
+    ):
+        raise ValueError("topk_weights must be contiguous CUDA float32 [tokens,topk]")
+    if (
+        inverse_permutation.device != routed_output.device
+        or inverse_permutation.dtype != torch.int32
+        or inverse_permutation.ndim != 1
+        or not inverse_permutation.is_contiguous()
+    ):
+        raise ValueError("inverse_permutation must be a contiguous CUDA int32 vector")
+    if shared_output is not None and (
+        shared_output.device != routed_output.device
+        or shared_output.dtype != routed_output.dtype
+        or shared_output.shape != output.shape
+        or not shared_output.is_contiguous()
+    ):
+        raise ValueError(
+            "shared_output must be contiguous and match output's device, dtype, and shape"
+        )
+    gate_stride = 1
+    if shared_gate is not None:
+        if (
+            shared_output is None
+            or shared_gate.device != routed_output.device
+            or shared_gate.dtype not in _GATE_CODE
+            or not shared_gate.is_contiguous()
+            or (
+                shared_gate.numel() != output.shape[0]
+                and (shared_gate.ndim != 2 or shared_gate.shape[0] != output.shape[0])
+            )
+        ):
+            raise ValueError(
+                "shared_gate requires shared_output and one contiguous floating "
+                "value or row per token"
+            )
+        gate_stride = shared_gate.numel() // output.shape[0]
+    load_library()
+    tokens, hidden = (int(v) for v in output.shape)
+    with torch.cuda.device(output.device):
+        check(
+            library().mxfp6_moe_reduce(
+                output.data_ptr(), routed_output.data_ptr(), _DTYPE_CODE[output.dtype],
+                topk_weights.data_ptr(), inverse_permutation.data_ptr(), _ptr(shared_output),
+                _ptr(shared_gate), 0 if shared_gate is None else _GATE_CODE[shared_gate.dtype],
+                gate_stride, tokens, hidden, int(topk_weights.shape[1]),
+                int(routed_output.shape[0]), _stream(output.device),
+            )
+        )
+
+
+def moe_reduce_tp2_out(
+    output: torch.Tensor,
+    routed_output: torch.Tensor,
+    topk_weights: torch.Tensor,
+    inverse_permutation: torch.Tensor,
+    shared_output: torch.Tensor | None = None,
+    shared_gate: torch.Tensor | None = None,
+    group=None,
+) -> None:
+    """Reduce, then sum the result over the tensor-parallel ranks.
+
+    The reference fuses a 2-rank peer-pointer all-reduce with unbounded spins into
+    its reducer (csrc/moe.cu:7698-7925); here the reduce kernel is followed by an
+    NCCL all-reduce on the same stream for any world size.
+    """
+    import torch.distributed as dist
+
+    moe_reduce_out(output, routed_output, topk_weights, inverse_permutation, shared_output,
+                   shared_gate)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(output, group=group)

@@ -1,0 +1,402 @@
+"""Allocation-free routed-MoE schedules and their scratch workspaces.
+
+Follows the reference's ``python/mxfp6/qwen35.py`` (workspace carved out of
+caller-owned storage, one call per layer, capturable in one CUDA graph) with two
+differences: the sizes (hidden, intermediate, experts, k) are parameters with the
+reference model's values as defaults instead of module constants, and one
+persistent grouped tcgen05 kernel family serves every batch size, so the
+single-token schedule is the grouped schedule.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .moe_ops import (
+    dense_w1_silu_mxfp8_out,
+    grouped_gemm_w6a8_out,
+    grouped_scale_rows,
+    moe_reduce_out,
+    qwen35_grouped_w1_silu_mxfp8_out,
+    qwen35_route_mxfp8_out,
+    qwen35_topk_quant_out,
+    qwen35_topk_quant_route_out,
+)
+from .ops import MXFP8Tensor, PackedMXFP6Tensor, gemm_w6a8, packed_scale_numel, quantize_mxfp8_logical
+
+_HIDDEN_SIZE = 2048
+_INTERMEDIATE_SIZE = 512
+_NUM_EXPERTS = 256
+_TOPK = 8
+_SCALE_ROWS_PER_ATOM = 128
+
+
+def _align_up(value: int, alignment: int) -> int:
+    return (value + alignment - 1) // alignment * alignment
+
+
+def _groups4(width: int) -> int:
+    return (width // 32 + 3) // 4 * 4
+
+
+@dataclass(frozen=True)
+class MoeShape:
+    """Sizes of one routed-MoE layer."""
+
+    hidden: int = _HIDDEN_SIZE
+    intermediate: int = _INTERMEDIATE_SIZE
+    experts: int = _NUM_EXPERTS
+    topk: int = _TOPK
+
+
+def _layout(batch_size: int, shape: MoeShape) -> list[tuple[str, tuple[int, ...], torch.dtype, int]]:
+    routes = batch_size * shape.topk
+    padded_rows = grouped_scale_rows(routes, shape.experts)
+    return [
+        ("quantized", (batch_size, shape.hidden), torch.uint8, 16),
+        ("input_scales", (batch_size, shape.hidden // 32), torch.uint8, 16),
+        ("packed_input_scales", (packed_scale_numel(batch_size, shape.hidden),), torch.uint8, 16),
+        ("topk_weights", (batch_size, shape.topk), torch.float32, 16),
+        ("topk_ids", (batch_size, shape.topk), torch.int32, 16),
+        ("source_tokens", (routes,), torch.int32, 16),
+        ("permuted", (routes, shape.hidden), torch.uint8, 128),
+        ("grouped_input_scales", (padded_rows * _groups4(shape.hidden),), torch.uint8, 128),
+        ("activated", (routes, shape.intermediate), torch.uint8, 128),
+        ("activated_scales", (padded_rows * _groups4(shape.intermediate),), torch.uint8, 128),
+        ("expert_cursors", (shape.experts,), torch.int32, 16),
+        ("expert_offsets", (shape.experts + 1,), torch.int64, 16),
+        ("scale_offsets", (shape.experts + 1,), torch.int64, 16),
+        ("inverse_permutation", (routes,), torch.int32, 16),
+        ("routed_output", (routes, shape.hidden), torch.bfloat16, 128),
+    ]
+
+
+def qwen35_grouped_workspace_bytes(batch_size: int, shape: MoeShape = MoeShape()) -> int:
+    """Bytes of scratch one layer call needs for ``batch_size`` tokens."""
+    if batch_size < 1:
+        raise ValueError("batch_size must be positive")
+    offset = 0
+    for _, dims, dtype, alignment in _layout(batch_size, shape):
+        elements = 1
+        for d in dims:
+            elements *= d
+        offset = _align_up(offset, alignment) + elements * torch.empty((), dtype=dtype).element_size()
+    return _align_up(offset, 256)
+
+
+def qwen35_grouped_workspace_shapes(
+    batch_size: int, shape: MoeShape = MoeShape()
+) -> tuple[tuple[int, int], tuple[int, int]]:
+    """Return two BF16 workspace shapes that together hold the grouped schedule's
+    scratch (the reference splits its scratch over two tensors the same way)."""
+    total = qwen35_grouped_workspace_bytes(batch_size, shape)
+    routes = batch_size * shape.topk
+    half = _align_up((total + 1) // 2, 256)
+    width = (half // 2 + routes - 1) // routes
+    return (routes, width), (routes, width)
+
+
+class _ByteArena:
+    def __init__(self, storage: torch.Tensor, offset: int = 0) -> None:
+        if not storage.is_contiguous():
+            raise ValueError("workspace storage must be contiguous")
+        self.storage = storage.view(torch.uint8).flatten()
+        self.offset = offset
+
+    def take(self, shape: tuple[int, ...], dtype: torch.dtype, alignment: int) -> torch.Tensor:
+        elements = 1
+        for dimension in shape:
+            elements *= dimension
+        size = elements * torch.empty((), dtype=dtype).element_size()
+        base = self.storage.data_ptr()
+        self.offset = _align_up(base + self.offset, alignment) - base
+        end = self.offset + size
+        if end > self.storage.numel():
+            raise ValueError("grouped MoE workspace is too small")
+        result = self.storage[self.offset : end].view(dtype).view(shape)
+        self.offset = end
+        return result
+
+
+@dataclass(frozen=True)
+class Qwen35GroupedWorkspace:
+    """Views over graph-stable scratch storage for the grouped schedule."""
+
+    quantized: torch.Tensor
+    input_scales: torch.Tensor
+    packed_input_scales: torch.Tensor
+    topk_weights: torch.Tensor
+    topk_ids: torch.Tensor
+    source_tokens: torch.Tensor
+    permuted: torch.Tensor
+    grouped_input_scales: torch.Tensor
+    activated: torch.Tensor
+    activated_scales: torch.Tensor
+    expert_cursors: torch.Tensor
+    expert_offsets: torch.Tensor
+    scale_offsets: torch.Tensor
+    inverse_permutation: torch.Tensor
+    routed_output: torch.Tensor
+    shape: MoeShape = MoeShape()
+
+    @classmethod
+    def from_storage(
+        cls,
+        output: torch.Tensor,
+        first: torch.Tensor,
+        second: torch.Tensor | None = None,
+        shape: MoeShape = MoeShape(),
+    ) -> "Qwen35GroupedWorkspace":
+        """Partition caller-owned scratch tensors without allocating CUDA memory.
+
+        ``first`` (and ``second`` when the scratch is split in two, as the reference
+        does) must together hold :func:`qwen35_grouped_workspace_bytes` bytes.
+        """
+        if (
+            output.dtype != torch.bfloat16
+            or output.ndim != 2
+            or output.shape[1] != shape.hidden
+            or not output.is_contiguous()
+        ):
+            raise ValueError(f"output must be contiguous BF16 [B,{shape.hidden}]")
+        batch_size = int(output.shape[0])
+        arenas = [_ByteArena(first)] + ([] if second is None else [_ByteArena(second)])
+        views = {}
+        index = 0
+        for name, dims, dtype, alignment in _layout(batch_size, shape):
+            while True:
+                try:
+                    views[name] = arenas[index].take(dims, dtype, alignment)
+                    break
+                except ValueError:
+                    index += 1
+                    if index >= len(arenas):
+                        raise ValueError("grouped MoE workspace is too small") from None
+        return cls(shape=shape, **views)
+
+    @classmethod
+    def allocate(cls, batch_size: int, device, shape: MoeShape = MoeShape()):
+        """Convenience constructor that owns its storage."""
+        storage = torch.empty(
+            qwen35_grouped_workspace_bytes(batch_size, shape) + 256, dtype=torch.uint8, device=device
+        )
+        output = torch.empty((batch_size, shape.hidden), dtype=torch.bfloat16, device=device)
+        return cls.from_storage(output, storage, None, shape)
+
+
+def qwen35_grouped_gemm_out(
+    workspace: Qwen35GroupedWorkspace,
+    hidden: torch.Tensor,
+    router_logits: torch.Tensor,
+    w1: torch.Tensor,
+    w1_scales: torch.Tensor,
+    w2: torch.Tensor,
+    w2_scales: torch.Tensor,
+    renormalize: bool = True,
+    expert_map: torch.Tensor | None = None,
+) -> None:
+    """Queue routing and the two grouped GEMMs into ``workspace``.
+
+    top-k + MXFP8 quantization + row permutation, then the grouped W1 with the
+    fused SiLU*mul + MXFP8 epilogue, then the grouped W2 into
+    ``workspace.routed_output``.
+    """
+    qwen35_topk_quant_route_out(
+        workspace.quantized,
+        workspace.input_scales,
+        workspace.packed_input_scales,
+        workspace.topk_weights,
+        workspace.topk_ids,
+        workspace.permuted,
+        workspace.grouped_input_scales,
+        workspace.expert_cursors,
+        workspace.expert_offsets,
+        workspace.scale_offsets,
+        workspace.inverse_permutation,
+        hidden,
+        router_logits,
+        source_tokens=workspace.source_tokens,
+        renormalize=renormalize,
+        expert_map=expert_map,
+    )
+    _grouped_experts_out(workspace, w1, w1_scales, w2, w2_scales)
+
+
+def _grouped_experts_out(workspace, w1, w1_scales, w2, w2_scales) -> None:
+    qwen35_grouped_w1_silu_mxfp8_out(
+        workspace.activated,
+        workspace.activated_scales,
+        workspace.permuted,
+        workspace.grouped_input_scales,
+        w1,
+        w1_scales,
+        workspace.expert_offsets,
+        workspace.scale_offsets,
+    )
+    grouped_gemm_w6a8_out(
+        workspace.routed_output,
+        workspace.activated,
+        workspace.activated_scales,
+        w2,
+        w2_scales,
+        workspace.expert_offsets,
+        workspace.scale_offsets,
+    )
+
+
+def qwen35_grouped_reduce_out(
+    workspace: Qwen35GroupedWorkspace,
+    output: torch.Tensor,
+    shared_output: torch.Tensor | None = None,
+    shared_gate: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Reduce routed rows and optionally add the (gated) shared expert."""
+    moe_reduce_out(
+        output,
+        workspace.routed_output,
+        workspace.topk_weights,
+        workspace.inverse_permutation,
+        shared_output=shared_output,
+        shared_gate=shared_gate,
+    )
+    return output
+
+
+def qwen35_grouped_moe_logits_out(
+    workspace: Qwen35GroupedWorkspace,
+    output: torch.Tensor,
+    hidden: torch.Tensor,
+    router_logits: torch.Tensor,
+    w1: torch.Tensor,
+    w1_scales: torch.Tensor,
+    w2: torch.Tensor,
+    w2_scales: torch.Tensor,
+    shared_output: torch.Tensor | None = None,
+    renormalize: bool = True,
+    shared_gate: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Run the allocation-free fused-router grouped schedule."""
+    qwen35_grouped_gemm_out(
+        workspace, hidden, router_logits, w1, w1_scales, w2, w2_scales, renormalize=renormalize
+    )
+    return qwen35_grouped_reduce_out(workspace, output, shared_output, shared_gate)
+
+
+def qwen35_grouped_moe_out(
+    workspace: Qwen35GroupedWorkspace,
+    output: torch.Tensor,
+    hidden: torch.Tensor,
+    w1: torch.Tensor,
+    w1_scales: torch.Tensor,
+    w2: torch.Tensor,
+    w2_scales: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+) -> torch.Tensor:
+    """Run the routed schedule with caller-provided top-k weights and ids."""
+    qwen35_topk_quant_out_rows(workspace, hidden)
+    qwen35_route_mxfp8_out(
+        workspace.quantized,
+        workspace.input_scales,
+        topk_ids,
+        workspace.permuted,
+        workspace.grouped_input_scales,
+        workspace.expert_cursors,
+        workspace.expert_offsets,
+        workspace.scale_offsets,
+        workspace.inverse_permutation,
+        source_tokens=workspace.source_tokens,
+    )
+    _grouped_experts_out(workspace, w1, w1_scales, w2, w2_scales)
+    moe_reduce_out(output, workspace.routed_output, topk_weights, workspace.inverse_permutation)
+    return output
+
+
+def qwen35_topk_quant_out_rows(workspace: Qwen35GroupedWorkspace, hidden: torch.Tensor) -> None:
+    """Quantize ``hidden`` into the workspace (values, logical and dense packed scales)."""
+    from ._loader import check, library
+    from .ops import _stream
+
+    batch, width = (int(v) for v in hidden.shape)
+    with torch.cuda.device(hidden.device):
+        check(
+            library().mxfp6_moe_topk_quant(
+                hidden.data_ptr(), None, batch, width, 0, 0, 0, workspace.quantized.data_ptr(),
+                workspace.input_scales.data_ptr(), workspace.packed_input_scales.data_ptr(), None,
+                None, _stream(hidden.device),
+            )
+        )
+
+
+@dataclass(frozen=True)
+class SharedExpertWorkspace:
+    """Scratch of the always-on shared expert: its MXFP8 intermediate and output."""
+
+    activated: torch.Tensor
+    activated_scales: torch.Tensor
+    output: torch.Tensor
+
+    @classmethod
+    def allocate(cls, batch_size: int, device, shape: MoeShape = MoeShape()):
+        return cls(
+            torch.empty((batch_size, shape.intermediate), dtype=torch.uint8, device=device),
+            torch.full((packed_scale_numel(batch_size, shape.intermediate),), 0x7F,
+                       dtype=torch.uint8, device=device),
+            torch.empty((batch_size, shape.hidden), dtype=torch.bfloat16, device=device),
+        )
+
+
+def shared_expert_out(
+    shared: SharedExpertWorkspace,
+    workspace: Qwen35GroupedWorkspace,
+    w1: PackedMXFP6Tensor,
+    w2: PackedMXFP6Tensor,
+) -> torch.Tensor:
+    """Shared expert on the rows already quantized in ``workspace``: dense W1 with the
+    fused SiLU*mul + MXFP8 epilogue, then the dense W2 GEMM (BF16 out).
+
+    The reference's callers compute the same thing with two dense GEMMs and
+    ``silu_and_mul_mxfp8_packed_out`` (benchmarks/benchmark_qwen35_moe_layer.py:1102-1127).
+    """
+    batch, hidden = (int(v) for v in workspace.quantized.shape)
+    dense_w1_silu_mxfp8_out(shared.activated, shared.activated_scales, workspace.quantized,
+                            workspace.packed_input_scales, w1.values, w1.scales)
+    act = MXFP8Tensor(shared.activated.view(-1), shared.activated_scales, batch,
+                      int(shared.activated.shape[1]))
+    return gemm_w6a8(act, w2, out_dtype=torch.bfloat16, out=shared.output)
+
+
+# ---- single-token schedule: same kernels, kept for API compatibility -----------------
+
+
+@dataclass(frozen=True)
+class Qwen35MoeB1Workspace:
+    """Workspace of the one-token decode schedule (a batch-1 grouped workspace)."""
+
+    grouped: Qwen35GroupedWorkspace
+
+    @classmethod
+    def allocate(cls, device, shape: MoeShape = MoeShape()):
+        return cls(Qwen35GroupedWorkspace.allocate(1, device, shape))
+
+
+def qwen35_moe_b1_out(
+    workspace: Qwen35MoeB1Workspace,
+    output: torch.Tensor,
+    hidden: torch.Tensor,
+    router_logits: torch.Tensor,
+    w1: torch.Tensor,
+    w1_scales: torch.Tensor,
+    w2: torch.Tensor,
+    w2_scales: torch.Tensor,
+    shared_output: torch.Tensor | None = None,
+    shared_gate: torch.Tensor | None = None,
+    renormalize: bool = True,
+) -> torch.Tensor:
+    """One-token decode: the grouped schedule at batch 1."""
+    return qwen35_grouped_moe_logits_out(
+        workspace.grouped, output, hidden, router_logits, w1, w1_scales, w2, w2_scales,
+        shared_output=shared_output, renormalize=renormalize, shared_gate=shared_gate,
+    )

@@ -1,0 +1,298 @@
+"""GPU parity tests of the routed-MoE path against the CPU oracle.
+
+Expert ids must be identical, byte outputs bit-exact, grouped GEMMs within
+rel-Frobenius 1e-3 and the whole layer within cosine >= 0.999 of the decoded CPU
+path (the tolerances named by the hot-path contract).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import mx_oracle as o
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _cpu_gen(seed):
+    return torch.Generator(device="cpu").manual_seed(seed)
+
+
+def _rel_fro(got, want) -> float:
+    got, want = got.float().cpu(), want.float().cpu()
+    return float((got - want).norm() / want.norm().clamp_min(1e-30))
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _status_clean(mx):
+    yield
+    assert mx.device_status() == 0, "a bounded device wait expired during the tests"
+
+
+@pytest.mark.parametrize("tokens,experts,topk", [(1, 256, 8), (7, 256, 8), (96, 256, 8), (33, 64, 4), (5, 40, 6)])
+def test_topk_ids_and_weights(mx, tokens, experts, topk):
+    gen = _cpu_gen(4100 + tokens)
+    hidden = torch.randn((tokens, 2048), generator=gen).to(torch.bfloat16)
+    logits = torch.randn((tokens, experts), generator=gen).to(torch.bfloat16)
+    logits[0, 3] = logits[0, 17]  # a tie: the smaller id must win
+    for renorm in (False, True):
+        q = torch.empty((tokens, 2048), dtype=torch.uint8, device=DEV)
+        ls = torch.empty((tokens, 64), dtype=torch.uint8, device=DEV)
+        ps = torch.empty(mx.packed_scale_numel(tokens, 2048), dtype=torch.uint8, device=DEV)
+        w = torch.empty((tokens, topk), dtype=torch.float32, device=DEV)
+        ids = torch.empty((tokens, topk), dtype=torch.int32, device=DEV)
+        mx.qwen35_topk_quant_out(q, ls, ps, w, ids, hidden.to(DEV), logits.to(DEV), renormalize=renorm)
+        want_w, want_ids = o.softmax_topk(logits, topk, renorm)
+        assert torch.equal(ids.cpu(), want_ids)
+        torch.testing.assert_close(w.cpu(), want_w, rtol=1e-6, atol=1e-8)
+        codes, scales = o.quantize_mxfp8_torch(hidden)
+        assert np.array_equal(q.cpu().numpy(), codes)
+        assert np.array_equal(ls.cpu().numpy(), scales)
+        assert np.array_equal(mx.unpack_scales(ps, tokens, 2048).cpu().numpy(), scales)
+
+
+def test_routing_invariants_and_expert_map(mx):
+    tokens, experts, topk, hidden = 50, 32, 4, 256
+    gen = _cpu_gen(3)
+    act = torch.randint(0, 0x78, (tokens, hidden), generator=gen, dtype=torch.uint8)
+    scales = torch.randint(120, 130, (tokens, hidden // 32), generator=gen, dtype=torch.uint8)
+    ids = torch.stack([torch.randperm(experts, generator=gen)[:topk] for _ in range(tokens)]).to(torch.int32)
+    permuted = torch.zeros((tokens * topk, hidden), dtype=torch.uint8, device=DEV)
+    grouped, offsets, soff, inverse = mx.route_mxfp8_out(
+        act.to(DEV), scales.to(DEV), ids.to(DEV), None, experts, permuted)
+    counts = torch.bincount(ids.flatten().long(), minlength=experts)
+    assert offsets.cpu().tolist() == [0, *torch.cumsum(counts, 0).tolist()]
+    assert soff.cpu().tolist() == o.grouped_scale_offsets(offsets.cpu().numpy()).tolist()
+    inv = inverse.cpu().long()
+    assert sorted(inv.tolist()) == list(range(tokens * topk))  # a permutation
+    flat = ids.flatten().long()
+    rows = permuted.cpu()
+    for route in range(tokens * topk):
+        e, row = int(flat[route]), int(inv[route])
+        assert int(offsets[e]) <= row < int(offsets[e + 1])
+        assert torch.equal(rows[row], act[route // topk])
+    # scales follow their rows into the grouped packed layout
+    logical_permuted = torch.empty((tokens * topk, hidden // 32), dtype=torch.uint8)
+    logical_permuted[inv] = scales.repeat_interleave(topk, dim=0)
+    want, _ = o.pack_grouped_scales(logical_permuted.numpy(), offsets.cpu().numpy())
+    got = grouped.cpu().numpy()[: want.size]
+    written = want != 0x7F
+    assert np.array_equal(got[written], want[written])
+    # expert parallel: only experts 8..15 are local, everything else is dropped
+    expert_map = torch.full((experts,), -1, dtype=torch.int32)
+    expert_map[8:16] = torch.arange(8, dtype=torch.int32)
+    _, loc_off, _, loc_inv = mx.route_mxfp8_out(
+        act.to(DEV), scales.to(DEV), ids.to(DEV), expert_map.to(DEV), 8, permuted)
+    local_counts = counts[8:16]
+    assert loc_off.cpu().tolist() == [0, *torch.cumsum(local_counts, 0).tolist()]
+    dropped = (flat < 8) | (flat >= 16)
+    assert bool((loc_inv.cpu()[dropped] == -1).all())
+    assert bool((loc_inv.cpu()[~dropped] >= 0).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_silu_and_mul_variants_bit_exact(mx, dtype):
+    rows, inter = 37, 256
+    x = (torch.randn((rows, 2 * inter), generator=_cpu_gen(8)) * 3).to(dtype)
+    want_codes, want_scales = o.silu_and_mul_mxfp8(x)
+    values, logical = mx.silu_and_mul_mxfp8_logical(x.to(DEV))
+    assert np.array_equal(values.view(torch.uint8).cpu().numpy(), want_codes)
+    assert np.array_equal(logical.cpu().numpy(), want_scales)
+    out = torch.empty((rows, inter), dtype=torch.uint8, device=DEV)
+    packed = torch.full((mx.packed_scale_numel(rows, inter),), 0x7F, dtype=torch.uint8, device=DEV)
+    mx.silu_and_mul_mxfp8_packed_out(out, packed, x.to(DEV))
+    assert np.array_equal(out.cpu().numpy(), want_codes)
+    assert np.array_equal(packed.cpu().numpy(), o.pack_scales(want_scales))
+    offsets = torch.tensor([0, 5, 5, 30, 37], dtype=torch.int64)
+    v2, gs, soff = mx.silu_and_mul_mxfp8_grouped(x.to(DEV), offsets.to(DEV))
+    want_grouped, want_soff = o.pack_grouped_scales(want_scales, offsets.numpy())
+    assert soff.cpu().tolist() == want_soff.tolist()
+    assert np.array_equal(gs.cpu().numpy()[: want_grouped.size], want_grouped)
+    assert np.array_equal(v2.view(torch.uint8).cpu().numpy(), want_codes)
+
+
+def _grouped_case(mx, counts, n, k, seed):
+    gen = _cpu_gen(seed)
+    experts = len(counts)
+    m = sum(counts)
+    offsets = torch.tensor((0, *np.cumsum(counts).tolist()), dtype=torch.int64)
+    a = torch.randn((m, k), generator=gen).to(torch.bfloat16)
+    w = (torch.randn((experts * n, k), generator=gen) * 0.02).to(torch.bfloat16)
+    a_q, a_s = o.quantize_mxfp8_torch(a)
+    weight = mx.quantize_mxfp6(w.to(DEV))
+    w_codes, w_scales = mx.unpack_operand(weight)
+    grouped, soff = mx.pack_grouped_scales(torch.from_numpy(a_s).to(DEV), offsets.to(DEV))
+    return (offsets, torch.from_numpy(a_q).to(DEV), grouped, soff, weight,
+            (a_q, a_s, w_codes.cpu().numpy(), w_scales.cpu().numpy()))
+
+
+@pytest.mark.parametrize("counts,n,k", [((1, 0, 3, 129, 2), 128, 128), ((5, 70, 0, 200, 1, 64), 256, 512),
+                                        ((300, 17), 128, 1024)])
+def test_grouped_gemm_matches_oracle(mx, counts, n, k):
+    offsets, a_dev, grouped, soff, weight, (a_q, a_s, w_q, w_s) = _grouped_case(mx, counts, n, k, 12035)
+    experts = len(counts)
+    w3 = weight.values.view(experts, n, k * 3 // 4)
+    for tile in (0, 64, 128, 192, 256):
+        out = torch.full((sum(counts), n), float("nan"), dtype=torch.bfloat16, device=DEV)
+        mx.grouped_gemm_w6a8_out(out, a_dev, grouped, w3, weight.scales, offsets.to(DEV), soff, tile_n=tile)
+        for e, rows in enumerate(counts):
+            if rows == 0:
+                continue
+            lo = int(offsets[e])
+            want = o.gemm_w6a8(a_q[lo : lo + rows], a_s[lo : lo + rows], w_q[e * n : (e + 1) * n],
+                               w_s[e * n : (e + 1) * n], out_dtype=torch.bfloat16)
+            assert _rel_fro(out[lo : lo + rows], want) <= 1e-3
+
+
+@pytest.mark.parametrize("counts,inter,k", [((1, 0, 3, 129, 2), 128, 256), ((40, 9, 0, 77), 256, 512)])
+def test_fused_w1_epilogue_equals_unfused_path(mx, counts, inter, k):
+    """Grouped W1 + SiLU*mul + MXFP8 in one kernel must equal grouped GEMM (BF16)
+    followed by the stand-alone SiLU kernel, byte for byte (the reference checks its
+    fused kernels the same way, tests/test_ops.py:453-459)."""
+    n = 2 * inter
+    offsets, a_dev, grouped, soff, weight, _ = _grouped_case(mx, counts, n, k, 77)
+    experts = len(counts)
+    w3 = weight.values.view(experts, n, k * 3 // 4)
+    rows = sum(counts)
+    h1 = mx.grouped_gemm_w6a8(a_dev, grouped, w3, weight.scales, offsets.to(DEV), soff)
+    want_v, want_s, _ = mx.silu_and_mul_mxfp8_grouped(h1, offsets.to(DEV), soff)
+    for tile in (0, 64, 128):
+        out = torch.zeros((rows, inter), dtype=torch.uint8, device=DEV)
+        out_scales = torch.full_like(want_s, 0x7F)
+        mx.qwen35_grouped_w1_silu_mxfp8_out(out, out_scales, a_dev, grouped, w3, weight.scales,
+                                            offsets.to(DEV), soff, tile_tokens=tile)
+        assert torch.equal(out, want_v.view(torch.uint8))
+        assert torch.equal(out_scales, want_s)
+
+
+def test_reduce_matches_oracle_and_gate_identity(mx):
+    tokens, topk, hidden = 13, 8, 2048
+    gen = _cpu_gen(31)
+    routed = torch.randn((tokens * topk, hidden), generator=gen).to(torch.bfloat16)
+    shared = torch.randn((tokens, hidden), generator=gen).to(torch.bfloat16)
+    weights = torch.rand((tokens, topk), generator=gen)
+    weights = weights / weights.sum(dim=1, keepdim=True)
+    inverse = torch.randperm(tokens * topk, generator=gen).to(torch.int32)
+    gate = torch.randn((tokens, 1), generator=gen).to(torch.bfloat16)
+    out = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=DEV)
+    mx.moe_reduce_out(out, routed.to(DEV), weights.to(DEV), inverse.to(DEV), shared.to(DEV), gate.to(DEV))
+    want = o.moe_reduce(routed, weights, inverse, shared, gate)
+    assert _rel_fro(out, want) <= 1e-3
+    assert float((out.float().cpu() - want.float()).abs().max()) <= 2.0**-7 * float(want.float().abs().max())
+    # gate logit 20 passes the shared row, gate 0 halves it
+    zeros = torch.zeros((tokens, topk), device=DEV)
+    ones = torch.ones((tokens, hidden), dtype=torch.bfloat16, device=DEV)
+    for logit, expect in ((20.0, 1.0), (0.0, 0.5)):
+        g = torch.full((tokens,), logit, dtype=torch.float32, device=DEV)
+        mx.moe_reduce_out(out, routed.to(DEV), zeros, inverse.to(DEV), ones, g)
+        assert bool((out.float() == expect).all())
+    # dropped routes (-1) are skipped
+    inverse2 = inverse.clone()
+    inverse2[::3] = -1
+    mx.moe_reduce_out(out, routed.to(DEV), weights.to(DEV), inverse2.to(DEV))
+    w2 = weights.clone().flatten()
+    w2[::3] = 0
+    want2 = o.moe_reduce(routed, w2.view(tokens, topk), inverse.clamp_min(0), None, None)
+    assert _rel_fro(out, want2) <= 1e-3
+
+
+def _layer_case(mx, tokens, shape, seed=4000):
+    """Random layer: weights are quantized on the GPU (bit-exact with the oracle by
+    the dense tests) and only the experts a batch hits are decoded on the CPU."""
+    gen = torch.Generator(device=DEV).manual_seed(seed)
+    h, i, e = shape.hidden, shape.intermediate, shape.experts
+    w1 = mx.quantize_mxfp6((torch.randn((e * 2 * i, h), generator=gen, device=DEV) * 0.02).to(torch.bfloat16))
+    w2 = mx.quantize_mxfp6((torch.randn((e * h, i), generator=gen, device=DEV) * 0.02).to(torch.bfloat16))
+    sw1 = mx.quantize_mxfp6((torch.randn((2 * i, h), generator=gen, device=DEV) * 0.02).to(torch.bfloat16))
+    sw2 = mx.quantize_mxfp6((torch.randn((h, i), generator=gen, device=DEV) * 0.02).to(torch.bfloat16))
+    cgen = _cpu_gen(4100 + tokens)
+    hidden = torch.randn((tokens, h), generator=cgen).to(torch.bfloat16)
+    logits = torch.randn((tokens, e), generator=cgen).to(torch.bfloat16)
+    gate = torch.randn((tokens,), generator=cgen).to(torch.bfloat16)
+    return w1, w2, sw1, sw2, hidden, logits, gate
+
+
+def _run_layer(mx, shape, w1, w2, sw1, sw2, hidden, logits, gate):
+    tokens = hidden.shape[0]
+    ws = mx.Qwen35GroupedWorkspace.allocate(tokens, DEV, shape)
+    shared = mx.SharedExpertWorkspace.allocate(tokens, DEV, shape)
+    out = torch.empty((tokens, shape.hidden), dtype=torch.bfloat16, device=DEV)
+    e, i, h = shape.experts, shape.intermediate, shape.hidden
+    w1v, w2v = w1.values.view(e, 2 * i, h * 3 // 4), w2.values.view(e, h, i * 3 // 4)
+
+    hidden_d, logits_d, gate_d = hidden.to(DEV), logits.to(DEV), gate.to(DEV)
+
+    def step():
+        mx.qwen35_grouped_gemm_out(ws, hidden_d, logits_d, w1v, w1.scales, w2v, w2.scales)
+        mx.shared_expert_out(shared, ws, sw1, sw2)
+        mx.qwen35_grouped_reduce_out(ws, out, shared.output, gate_d)
+
+    step()
+    return out, ws, step
+
+
+def _oracle_layer(mx, shape, w1, w2, sw1, sw2, hidden, logits, gate, ids):
+    e, i, h = shape.experts, shape.intermediate, shape.hidden
+    used = sorted(set(ids.flatten().tolist()))
+    w1c = {}
+    w1v = w1.values.view(e, -1)
+    w2v = w2.values.view(e, -1)
+    w1s_all = mx.unpack_scales(w1.scales, e * 2 * i, h).view(e, 2 * i, h // 32)
+    w2s_all = mx.unpack_scales(w2.scales, e * h, i).view(e, h, i // 32)
+
+    class Lazy(dict):
+        def __missing__(self, key):
+            raise KeyError(key)
+
+    w1_codes, w1_scales, w2_codes, w2_scales = Lazy(), Lazy(), Lazy(), Lazy()
+    for x in used:
+        w1_codes[x] = mx.unpack_fp6(w1v[x], 2 * i, h).cpu().numpy()
+        w2_codes[x] = mx.unpack_fp6(w2v[x], h, i).cpu().numpy()
+        w1_scales[x] = w1s_all[x].cpu().numpy()
+        w2_scales[x] = w2s_all[x].cpu().numpy()
+    sc = mx.unpack_operand(sw1)
+    sd = mx.unpack_operand(sw2)
+    shared = (sc[0].cpu().numpy(), sc[1].cpu().numpy(), sd[0].cpu().numpy(), sd[1].cpu().numpy())
+    return o.moe_layer(hidden, logits, w1_codes, w1_scales, w2_codes, w2_scales, shared, gate,
+                       shape.topk, True)
+
+
+@pytest.mark.parametrize("tokens", [1, 4, 24, 96, 700])
+def test_moe_layer_small_shape(mx, tokens):
+    shape = mx.MoeShape(hidden=512, intermediate=256, experts=32, topk=4)
+    case = _layer_case(mx, tokens, shape)
+    out, ws, _ = _run_layer(mx, shape, *case)
+    want, want_ids = _oracle_layer(mx, shape, *case, ids=ws.topk_ids.cpu())
+    assert torch.equal(ws.topk_ids.cpu(), want_ids)
+    cos = torch.nn.functional.cosine_similarity(out.float().cpu().flatten(), want.float().flatten(), dim=0)
+    assert float(cos) >= 0.999
+    assert _rel_fro(out, want) <= 2e-2
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 32])
+def test_moe_layer_named_config_and_graph_replay(mx, tokens):
+    """Hidden 2048, 256 experts, top-8, intermediate 512, shared expert with sigmoid gate."""
+    shape = mx.MoeShape()
+    case = _layer_case(mx, tokens, shape)
+    out, ws, step = _run_layer(mx, shape, *case)
+    want, want_ids = _oracle_layer(mx, shape, *case, ids=ws.topk_ids.cpu())
+    assert torch.equal(ws.topk_ids.cpu(), want_ids)
+    cos = torch.nn.functional.cosine_similarity(out.float().cpu().flatten(), want.float().flatten(), dim=0)
+    assert float(cos) >= 0.999
+    # the whole layer replays from one CUDA graph with identical results
+    first = out.clone()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        step()
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step()
+        for _ in range(20):
+            graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, first)
