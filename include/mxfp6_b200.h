@@ -110,6 +110,22 @@ int mxfp6_gemm_w6a8_ex(const uint8_t* a_values_dev, const uint8_t* a_scales_dev,
                        int64_t n, int64_t k, float alpha, void* out_dev, int out_dtype,
                        int tile_tokens, int splits, void* scratch_dev, size_t scratch_bytes,
                        void* stream);
+/* No counterpart in the reference.  The same GEMM for callers that cannot allocate
+ * device memory: code running inside somebody else's CUDA-graph capture, servers
+ * whose memory pool is fixed at start-up, plugins that may not touch their host's
+ * allocator.  The split-K scratch and the status word live in a fixed array inside
+ * the library image (4 MiB of partial tiles + 4 KiB of tile counters, held by every
+ * GPU that loads the library until the process exits), and the call performs no
+ * cudaMalloc / cudaFree / stream-ordered allocation.  A problem whose plan needs
+ * more scratch than that is rejected with MXFP6_ERR_INVALID_ARGUMENT and a message
+ * that gives both sizes.  The first call on each device looks up the array's device
+ * address; make that call outside any stream capture.  All calls share the one
+ * array: the counters are cleared on the stream at every call, and two calls whose
+ * kernels overlap on the GPU (different streams) race on it. */
+int mxfp6_gemm_w6a8_static_scratch(const uint8_t* a_values_dev, const uint8_t* a_scales_dev,
+                                   const uint8_t* w_values_dev, const uint8_t* w_scales_dev,
+                                   int64_t m, int64_t n, int64_t k, float alpha, void* out_dev,
+                                   int out_dtype, void* stream);
 /* Plan query: fills tile_tokens, splits, stages, grid, partial bytes, counter bytes. */
 int mxfp6_gemm_w6a8_plan(int64_t m, int64_t n, int64_t k, int tile_tokens, int splits,
                          int64_t out_plan[6]);

@@ -51,6 +51,11 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p,
          c_int, c_void_p],
     ),
+    "mxfp6_gemm_w6a8_static_scratch": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p,
+         c_int, c_void_p],
+    ),
     "mxfp6_gemm_w6a8_ex": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p,

@@ -312,6 +312,17 @@ int mxfp6_gemm_w6a8_ex(const uint8_t* a_values, const uint8_t* a_scales, const u
   return launch_w6a8(p, plan, static_cast<cudaStream_t>(stream));
 }
 
+int mxfp6_gemm_w6a8_static_scratch(const uint8_t* a_values, const uint8_t* a_scales,
+                                   const uint8_t* w_values, const uint8_t* w_scales, int64_t m,
+                                   int64_t n, int64_t k, float alpha, void* out, int out_dtype,
+                                   void* stream) {
+  GemmProblem p;
+  if (int rc = dense_problem(&p, a_values, a_scales, w_values, w_scales, m, n, k, alpha, out,
+                             out_dtype))
+    return rc;
+  return launch_w6a8_static_scratch(p, static_cast<cudaStream_t>(stream));
+}
+
 int mxfp6_gemm_w6a8_plan(int64_t m, int64_t n, int64_t k, int tile_tokens, int splits,
                          int64_t out_plan[6]) {
   MX_REQUIRE(out_plan != nullptr, "out_plan must not be null");

@@ -837,7 +837,7 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
   args.out = p.out;
   args.partials = p.partials;
   args.counters = p.counters;
-  args.status = device_status_word(device);
+  args.status = p.status_word != nullptr ? p.status_word : device_status_word(device);
   if (args.status == nullptr) return kCudaError;
   args.m_total = p.m_total;
   args.groups = p.groups;
@@ -905,12 +905,86 @@ int* device_status_word(int device) {
   return words[device];
 }
 
+// ---- GEMM without allocations ------------------------------------------------------
+// Some callers may not allocate device memory at all: code that runs while a CUDA
+// graph is being captured by an outer framework, a serving process whose memory
+// pool was sized and frozen at start-up, or a plugin that is forbidden to touch
+// the allocator of its host.  For them the split-K scratch (FP32 partial tiles,
+// tile counters) and the status word of one GEMM live in this fixed array, which
+// every GPU that loads the library holds until the process exits.
+constexpr size_t kStaticPartialBytes = size_t(4) << 20;  // FP32 partial tiles
+constexpr size_t kStaticCounterBytes = 4096;             // one counter per output tile
+constexpr size_t kStaticStatusBytes = 256;
+static __device__ __align__(256) unsigned char
+    g_static_scratch[kStaticPartialBytes + kStaticCounterBytes + kStaticStatusBytes];
+
+namespace {
+std::mutex g_static_mutex;
+unsigned char* g_static_base[64] = {};  // device address of g_static_scratch, per device
+
+// In host code `g_static_scratch` only names the symbol; its device address has to
+// be asked for, once per device, with that device current.
+int static_scratch_base(int device, unsigned char** base) {
+  if (device < 0 || device >= 64) {
+    set_error("device index %d out of range", device);
+    return kInvalidArgument;
+  }
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_base[device] == nullptr) {
+    unsigned char* ptr = nullptr;
+    MX_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch));
+    g_static_base[device] = ptr;
+  }
+  *base = g_static_base[device];
+  return kOk;
+}
+}  // namespace
+
+int launch_w6a8_static_scratch(GemmProblem& p, cudaStream_t stream) {
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  unsigned char* base = nullptr;
+  if (int rc = static_scratch_base(device, &base)) return rc;
+  GemmPlan plan;
+  if (int rc = plan_w6a8(p, &plan)) return rc;
+  if (plan.splits > 1) {
+    if (plan.partial_bytes > kStaticPartialBytes || plan.counter_bytes > kStaticCounterBytes) {
+      set_error(
+          "this problem needs %zu + %zu bytes of split-K scratch; the built-in array holds "
+          "%zu + %zu. Use mxfp6_gemm_w6a8 or mxfp6_gemm_w6a8_ex with caller-owned scratch",
+          plan.partial_bytes, plan.counter_bytes, kStaticPartialBytes, kStaticCounterBytes);
+      return kInvalidArgument;
+    }
+    p.partials = reinterpret_cast<float*>(base);
+    p.partial_bytes = kStaticPartialBytes;
+    p.counters = reinterpret_cast<uint32_t*>(base + kStaticPartialBytes);
+    p.counter_bytes = kStaticCounterBytes;
+    // The array keeps whatever the previous call left; the tile counters must start at zero.
+    MX_CUDA(cudaMemsetAsync(p.counters, 0, plan.counter_bytes, stream));
+  }
+  p.status_word = reinterpret_cast<int*>(base + kStaticPartialBytes + kStaticCounterBytes);
+  return launch_w6a8(p, plan, stream);
+}
+
 int read_device_status(int device, int* value, bool reset) {
   int* word = device_status_word(device);
   if (word == nullptr) return kCudaError;
   MX_CUDA(cudaDeviceSynchronize());
   MX_CUDA(cudaMemcpy(value, word, sizeof(int), cudaMemcpyDeviceToHost));
   if (reset && *value != 0) MX_CUDA(cudaMemset(word, 0, sizeof(int)));
+  // Fold in the status word of the allocation-free entry point, if it was used here.
+  unsigned char* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (device >= 0 && device < 64) base = g_static_base[device];
+  }
+  if (base != nullptr) {
+    int extra = 0;
+    int* extra_word = reinterpret_cast<int*>(base + kStaticPartialBytes + kStaticCounterBytes);
+    MX_CUDA(cudaMemcpy(&extra, extra_word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (reset && extra != 0) MX_CUDA(cudaMemset(extra_word, 0, sizeof(int)));
+    if (*value == 0) *value = extra;
+  }
   return kOk;
 }
 

@@ -45,6 +45,8 @@ struct GemmProblem {
   uint8_t* out_packed_scales = nullptr;
   uint8_t* out_logical_scales = nullptr;
   const int64_t* out_scale_offsets = nullptr;
+  // Status word the kernel reports an expired wait to; null = the per-device word.
+  int* status_word = nullptr;
   // Optional overrides (0 = choose from the static table).
   int tile_tokens = 0;
   int splits = 0;
@@ -68,6 +70,10 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
 // Diagnostics: CTA 0 of later launches writes [3][256] clock64 stamps (producer
 // issue, stage ready at the MMA warp, stage committed) to this device buffer.
 void set_trace_buffer(long long* ptr);
+
+// GEMM whose split-K scratch and status word live in a fixed array inside the
+// library image, for callers that must not allocate device memory.
+int launch_w6a8_static_scratch(GemmProblem& p, cudaStream_t stream);
 
 // Device status word (0 = ok) shared by all kernels with bounded waits.
 int* device_status_word(int device);
