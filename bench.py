@@ -215,6 +215,62 @@ def build_sweep(mx, device, rank: int, world: int):
     return layers, acts
 
 
+MOE_BATCHES = [1, 2, 4, 8, 16, 24, 32, 64, 96, 4096]
+
+
+def moe_layer_latency(mx, device, stream, peaks) -> dict:
+    """Latency of one routed-MoE layer (hidden 2048, 256 experts, top-8, intermediate 512,
+    gated shared expert), one CUDA graph per token batch.  ``us_warm`` = back-to-back
+    replays (the reference's method); ``us_cold`` = L2 flushed between replays."""
+    from mxfp6_sm120_b200.moe_layer import MoeLayer
+
+    shape = mx.MoeShape()
+    layer = MoeLayer.random(device, shape, seed=4000)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    rows = []
+    for batch in MOE_BATCHES:
+        gen = torch.Generator(device=device).manual_seed(4100 + batch)
+        hidden = torch.randn((batch, shape.hidden), generator=gen, device=device).to(torch.bfloat16)
+        logits = torch.randn((batch, shape.experts), generator=gen, device=device).to(torch.bfloat16)
+        gate = torch.randn((batch,), generator=gen, device=device).to(torch.bfloat16)
+        state = layer.workspace(batch)
+        layer.forward(state, hidden, logits, gate)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            layer.forward(state, hidden, logits, gate)
+        for _ in range(3):
+            graph.replay()
+        reps = 50 if batch <= 96 else 10
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for _ in range(reps):
+            graph.replay()
+        stop.record(stream)
+        stream.synchronize()
+        warm = start.elapsed_time(stop) * 1e3 / reps
+        cold = []
+        for _ in range(10):
+            flush.fill_(1)
+            start.record(stream)
+            graph.replay()
+            stop.record(stream)
+            stream.synchronize()
+            cold.append(start.elapsed_time(stop) * 1e3)
+        cold.sort()
+        used = int(torch.unique(state.workspace.topk_ids).numel())
+        byts = (used + 1) * 2457600 + batch * shape.hidden * 4 + batch * shape.experts * 2
+        flops = 9.0 * batch * 6291456
+        cold_us = cold[len(cold) // 2]
+        rows.append({"tokens": batch, "us_warm": round(warm, 1), "us_cold": round(cold_us, 1),
+                     "experts_hit": used, "gbs_cold": round(byts / cold_us / 1e3, 0),
+                     "hbm_frac_cold": round(byts / cold_us / 1e3 / float(peaks["hbm_gbs"]), 3),
+                     "tflops_warm": round(flops / warm / 1e6, 1)})
+    return {"config": "hidden 2048, 256 experts, top-8 softmax renormalised, intermediate 512, "
+                      "shared expert with sigmoid gate; router logits are inputs",
+            "kernels_per_layer": 9, "rows": rows}
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -223,6 +279,9 @@ def main() -> None:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--no-moe", action="store_true")
+    parser.add_argument("--no-per-shape", action="store_true",
+                        help="skip the per-shape GEMM-only timing (used for profiler launch lists)")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -304,7 +363,7 @@ def main() -> None:
         gemm_ms = 0.0
         small_bytes = small_ms = 0.0
         big_flops = big_ms = 0.0
-        if rank == 0 or world > 1:
+        if (rank == 0 or world > 1) and not args.no_per_shape:
             quantized = {key: mx.quantize_mxfp8(acts[key]) for key in order}
             reps = 5
             for key in order:
@@ -368,6 +427,10 @@ def main() -> None:
             e2e = {"value": sweep_flops() / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e_ms}
 
+        moe = None
+        if not args.no_moe and world == 1:
+            moe = moe_layer_latency(mx, device, stream, peaks)
+
     status = mx.device_status(device)
     if rank != 0:
         if world > 1:
@@ -414,6 +477,8 @@ def main() -> None:
         line["sweep"] = per_shape
     if e2e is not None:
         line["e2e"] = e2e
+    if moe is not None:
+        line["moe_layer"] = moe
     if not args.no_cpu_baseline and world == 1:
         base = cpu_reference_sample(os.cpu_count() or 1)
         line["cpu_baseline"] = {key: base[key] for key in ("value", "unit", "cores", "kind", "sample")}

@@ -1,0 +1,90 @@
+"""One routed-MoE layer (routed experts + always-on shared expert) as a single object.
+
+The caller side of the grouped schedule: weights, workspaces and one ``forward`` that
+queues the whole layer on the current stream without allocating, so it captures into
+one CUDA graph.  The reference leaves this composition to its benchmark
+(benchmarks/benchmark_qwen35_moe_layer.py:1102-1127,1401-1403,1524-1549).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .ops import PackedMXFP6Tensor, quantize_mxfp6
+from .qwen35 import (
+    MoeShape,
+    Qwen35GroupedWorkspace,
+    SharedExpertWorkspace,
+    qwen35_grouped_gemm_out,
+    qwen35_grouped_reduce_out,
+    shared_expert_out,
+)
+
+
+@dataclass
+class MoeLayerState:
+    workspace: Qwen35GroupedWorkspace
+    shared: SharedExpertWorkspace
+    output: torch.Tensor
+
+
+@dataclass
+class MoeLayer:
+    shape: MoeShape
+    w1: PackedMXFP6Tensor          # [E * 2I, H]: per expert gate rows then up rows
+    w2: PackedMXFP6Tensor          # [E * H, I]
+    shared_w1: PackedMXFP6Tensor   # [2I, H]
+    shared_w2: PackedMXFP6Tensor   # [H, I]
+    expert_map: torch.Tensor | None = None  # global expert id -> local id or -1 (expert parallel)
+
+    @classmethod
+    def random(cls, device, shape: MoeShape = MoeShape(), seed: int = 4000, experts: int | None = None):
+        """Weights ~ N(0, 0.02) quantized to packed MXFP6 on the device."""
+        gen = torch.Generator(device=device).manual_seed(seed)
+        h, i = shape.hidden, shape.intermediate
+        e = shape.experts if experts is None else experts
+
+        def make(rows, cols):
+            chunks = []
+            step = max(1, (1 << 26) // cols)  # quantize in slabs to bound the BF16 staging memory
+            for lo in range(0, rows, step):
+                n = min(step, rows - lo)
+                w = (torch.randn((n, cols), generator=gen, device=device) * 0.02).to(torch.bfloat16)
+                chunks.append(quantize_mxfp6(w))
+            if len(chunks) == 1:
+                return chunks[0]
+            assert step % 128 == 0
+            return PackedMXFP6Tensor(torch.cat([c.values for c in chunks]),
+                                     torch.cat([c.scales for c in chunks]), rows, cols)
+
+        return cls(shape, make(e * 2 * i, h), make(e * h, i), make(2 * i, h), make(h, i))
+
+    @property
+    def local_experts(self) -> int:
+        return self.w1.rows // (2 * self.shape.intermediate)
+
+    def workspace(self, tokens: int) -> MoeLayerState:
+        device = self.w1.values.device
+        local = MoeShape(self.shape.hidden, self.shape.intermediate, self.local_experts, self.shape.topk)
+        return MoeLayerState(
+            Qwen35GroupedWorkspace.allocate(tokens, device, local),
+            SharedExpertWorkspace.allocate(tokens, device, self.shape),
+            torch.empty((tokens, self.shape.hidden), dtype=torch.bfloat16, device=device),
+        )
+
+    def forward(self, state: MoeLayerState, hidden: torch.Tensor, router_logits: torch.Tensor,
+                shared_gate: torch.Tensor | None, with_shared: bool = True) -> torch.Tensor:
+        e, i, h = self.local_experts, self.shape.intermediate, self.shape.hidden
+        qwen35_grouped_gemm_out(
+            state.workspace, hidden, router_logits,
+            self.w1.values.view(e, 2 * i, h * 3 // 4), self.w1.scales,
+            self.w2.values.view(e, h, i * 3 // 4), self.w2.scales,
+            renormalize=True, expert_map=self.expert_map,
+        )
+        shared_out = None
+        if with_shared:
+            shared_out = shared_expert_out(state.shared, state.workspace, self.shared_w1, self.shared_w2)
+        return qwen35_grouped_reduce_out(state.workspace, state.output, shared_out,
+                                         shared_gate if with_shared else None)
