@@ -126,9 +126,16 @@ int mxfp6_gemm_w6a8_static_scratch(const uint8_t* a_values_dev, const uint8_t* a
                                    const uint8_t* w_values_dev, const uint8_t* w_scales_dev,
                                    int64_t m, int64_t n, int64_t k, float alpha, void* out_dev,
                                    int out_dtype, void* stream);
-/* Plan query: fills tile_tokens, splits, stages, grid, partial bytes, counter bytes. */
+/* Plan query: fills tile_tokens, scratch splits, stages, grid, partial bytes, counter
+ * bytes, cluster split factor. */
 int mxfp6_gemm_w6a8_plan(int64_t m, int64_t n, int64_t k, int tile_tokens, int splits,
-                         int64_t out_plan[6]);
+                         int64_t out_plan[7]);
+/* How launches with too few tiles split K (the stand-in for the reference's
+ * MXFP6_STREAM_K switch, csrc/torch_extension.cu:35-57): 1 = thread-block clusters
+ * that reduce through distributed shared memory (default, no scratch), 2 = FP32
+ * partial tiles in the scratch arena, 3 = never split. */
+int mxfp6_set_split_k_mode(int mode);
+int mxfp6_get_split_k_mode(void);
 /* torch.ops.mxfp6.gemm_from_float (csrc/torch_extension.cu:1869-1925): quantize the
  * FP16/BF16 activation to MXFP8 into caller-provided staging buffers
  * (m*k bytes and mxfp6_packed_scale_bytes(m, k) bytes), then run the GEMM. */

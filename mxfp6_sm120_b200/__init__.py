@@ -24,6 +24,8 @@ from .ops import (
     gemm_w6a8_config,
     gemm_w6a8_plan,
     is_available,
+    is_stream_k_enabled,
+    set_split_k_mode,
     is_tuned_shape,
     pack_fp6,
     pack_grouped_scales,

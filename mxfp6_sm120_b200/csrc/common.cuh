@@ -93,10 +93,30 @@ __device__ __forceinline__ float round_bf16(float v) {
 }
 
 // UE8M0 scale selection of the reference quantizer (csrc/quantization.cu:118-131):
-// smallest power of two >= absmax / target_max, with a 1e-30 floor.
+// smallest power of two >= absmax / target_max, with a 1e-30 floor, returned as the
+// FP32 bit pattern of that power of two.
+//
+// The reference divides (IEEE) and rounds the quotient's bits up to a power of two.
+// Both targets are 1.75 * 2^s (448 = 1.75 * 2^8, 28 = 1.75 * 2^4), so with
+// absmax = 1.m * 2^e the result is 2^(e - s) when 1.m <= 1.75 and 2^(e - s + 1)
+// otherwise: integer work on the exponent and mantissa fields, no division.  This
+// is exact for FP16/BF16 inputs: their absmax has at most 11 significant bits, so
+// the quotient is never within one FP32 rounding of a power of two unless it IS
+// one.  The floor ceil_pow2(1e-30) = 2^-99 is exponent field 28.
+template <int kTargetShift>  // 8 for E4M3 (448), 4 for E3M2 (28)
+__device__ __forceinline__ uint32_t ue8m0_scale_bits_shift(float absmax) {
+  const uint32_t b = __float_as_uint(absmax);
+  int code = static_cast<int>(b >> 23) - kTargetShift + ((b & 0x7fffffu) > 0x600000u ? 1 : 0);
+  code = code < 28 ? 28 : code;
+  return static_cast<uint32_t>(code) << 23;
+}
 __device__ __forceinline__ uint32_t ue8m0_scale_bits(float absmax, float target_max) {
-  const float raw = fmaxf(__fdiv_rn(absmax, target_max), 1.0e-30f);
-  return (__float_as_uint(raw) + 0x007fffffu) & 0x7f800000u;
+  return target_max == 448.0f ? ue8m0_scale_bits_shift<8>(absmax)
+                              : ue8m0_scale_bits_shift<4>(absmax);
+}
+// Exact reciprocal of the power of two whose bits are `scale_bits`.
+__device__ __forceinline__ float ue8m0_inverse(uint32_t scale_bits) {
+  return __uint_as_float((254u << 23) - scale_bits);
 }
 #endif
 

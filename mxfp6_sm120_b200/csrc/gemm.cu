@@ -71,6 +71,9 @@ struct KernelArgs {
   // [m_total, n / 32] and/or packed (row r of group g -> packed row
   // out_scale_offsets[g] + r - expert_offsets[g]; identity when null).
   int w_rows_per_group;
+  // > 1: the CTAs of a thread-block cluster split K among themselves and reduce
+  // their FP32 partial tiles through distributed shared memory (args.splits == cluster_k).
+  int cluster_k;
   uint8_t* out_packed_scales;
   uint8_t* out_logical_scales;
   const int64_t* out_scale_offsets;
@@ -87,7 +90,7 @@ struct Cfg {
   // 128-K blocks per pipeline stage.  Narrow tiles are bound by the per-stage cost
   // of the issuing warps (barrier wait, fence, commit), so they take more K per stage.
   static constexpr int kSubs =
-      MODE == kModeSwiglu ? (TN <= 32 ? 2 : 1) : (TN <= 32 ? 4 : (TN <= 96 ? 2 : 1));
+      MODE == kModeSwiglu ? (TN <= 32 ? 2 : 1) : (TN <= 96 ? 2 : 1);
   // Scale columns rotate through several sets so that the tcgen05.cp of a block
   // never overwrites scales an earlier, still running MMA reads.
   static constexpr int kSfSets = 4;
@@ -104,11 +107,14 @@ struct Cfg {
   static constexpr uint32_t kStageBytes = kSubs * (kWTiles * kWTileBytes + kATileBytes);
   static constexpr uint32_t kSfStageBytes = kSubs * kAtomBytes * (kWTiles + kSfbAtoms);
   static constexpr uint32_t kFixedBytes = 1024 /*align slack*/ + 4096 /*barriers + tables*/;
+  // Cluster split-K: every CTA parks its FP32 partial tile here for its peers.
+  static constexpr bool kClusterOk = TN <= 96;
+  static constexpr uint32_t kRedBytes = kClusterOk ? kAccCols * kTileF * 4 : 0;
   static constexpr int kStagesRaw =
-      (int)((232448u - kFixedBytes) / (kStageBytes + kSfStageBytes));
+      (int)((232448u - kFixedBytes - kRedBytes) / (kStageBytes + kSfStageBytes));
   static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
   static constexpr size_t kSmemBytes =
-      kFixedBytes + (size_t)kStages * (kStageBytes + kSfStageBytes);
+      kFixedBytes + kRedBytes + (size_t)kStages * (kStageBytes + kSfStageBytes);
 };
 
 struct Work {
@@ -154,6 +160,19 @@ __device__ __forceinline__ bool decode_work(int w, const KernelArgs& a, const in
   return true;
 }
 
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Launch timeline of CTA 0 (diagnostics): trace[768] counts launches, slot s of
+// launch l is trace[776 + 8 * (l % 60) + s] in nanoseconds of the global timer.
+#define MX_STAMP(slot_index)                                                         \
+  do {                                                                               \
+    if (args.trace != nullptr && blockIdx.x == 0)                                    \
+      args.trace[776 + 8 * (*launch_slot) + (slot_index)] = global_ns();             \
+  } while (0)
+
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int* abort,
                                              int* status, int code) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
@@ -172,6 +191,65 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
   }
 }
 
+__device__ __forceinline__ bool bounded_wait_cluster(uint32_t bar, uint32_t parity,
+                                                     volatile int* abort, int* status, int code) {
+  if (ptx::mbar_try_wait_cluster(bar, parity)) return true;
+  const long long start = clock64();
+#pragma unroll 1
+  for (uint32_t spin = 0;; ++spin) {
+    if (ptx::mbar_try_wait_cluster(bar, parity)) return true;
+    if ((spin & 63u) == 63u) {
+      if (*abort != 0) return false;
+      if (clock64() - start > kWaitCycles) {
+        *abort = 1;
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+// Final value(s) of one (token row, feature) element -> global memory.  In SwiGLU
+// mode all 32 lanes of the warp must call together (the scale group is the warp).
+template <int MODE>
+__device__ __forceinline__ void emit_element(const KernelArgs& args, int64_t row, int f, bool ok,
+                                             int lane, float main_acc, float up_acc,
+                                             int64_t scale_row) {
+  if constexpr (MODE == kModeSwiglu) {
+    const int groups = args.n / kScaleVec;
+    const float g = round_bf16(main_acc);
+    const float u = round_bf16(up_acc);
+    const float sv = round_bf16(__fdiv_rn(g, 1.0f + expf(-g)));
+    const float v = round_bf16(sv * u);
+    float amax = fabsf(v);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
+    const float inv = ue8m0_inverse(sbits);
+    const uint32_t code =
+        __nv_cvt_float2_to_fp8x2(make_float2(v * inv, 0.0f), __NV_SATFINITE, __NV_E4M3) & 0xffu;
+    if (ok) {
+      static_cast<uint8_t*>(args.out)[row * args.n + f] = (uint8_t)code;
+      if (lane == 0) {
+        const uint8_t sc = (uint8_t)(sbits >> 23);
+        const int g_index = f / kScaleVec;
+        if (args.out_logical_scales != nullptr) args.out_logical_scales[row * groups + g_index] = sc;
+        if (args.out_packed_scales != nullptr)
+          args.out_packed_scales[packed_scale_offset(scale_row, g_index, groups)] = sc;
+      }
+    }
+  } else {
+    if (ok) {
+      if (args.out_dtype == kBF16) {
+        static_cast<__nv_bfloat16*>(args.out)[row * args.n + f] =
+            __float2bfloat16_rn(args.alpha * main_acc);
+      } else {
+        static_cast<__half*>(args.out)[row * args.n + f] = __float2half_rn(args.alpha * main_acc);
+      }
+    }
+  }
+}
+
 template <int TN, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
@@ -185,10 +263,12 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   uint8_t* sf_tiles = a_tiles + (size_t)C::kStages * C::kSubs * C::kATileBytes;
   uint8_t* fixed = sf_tiles + (size_t)C::kStages * C::kSfStageBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(fixed);  // full[S], empty[S], tfull[2], tempty[2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fixed + 8 * (2 * C::kStages + 4));
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fixed + 8 * (2 * C::kStages + 6));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  volatile int* launch_slot = reinterpret_cast<volatile int*>(tmem_slot + 3);
   int* tile_prefix = reinterpret_cast<int*>(fixed + 1024);  // kMaxGroups + 1 ints
+  float* red = reinterpret_cast<float*>(fixed + 4096);      // cluster split-K partial tile
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -196,10 +276,17 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   const uint32_t empty0 = full0 + 8 * C::kStages;
   const uint32_t tfull0 = empty0 + 8 * C::kStages;
   const uint32_t tempty0 = tfull0 + 16;
+  const uint32_t red_full = tempty0 + 16;   // all partial tiles of the cluster are written
+  const uint32_t red_empty = red_full + 8;  // all peers have read this CTA's partial tile
+  const int cluster_k = args.cluster_k;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     *last_flag = 0;
+    if (args.trace != nullptr && blockIdx.x == 0) {
+      *launch_slot = (int)(atomicAdd((unsigned long long*)(args.trace + 768), 1ull) % 60ull);
+      args.trace[776 + 8 * (*launch_slot)] = global_ns();
+    }
     for (int s = 0; s < C::kStages; ++s) {
       ptx::mbar_init(full0 + 8 * s, 1);
       ptx::mbar_init(empty0 + 8 * s, 1);
@@ -208,6 +295,8 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       ptx::mbar_init(tfull0 + 8 * i, 1);
       ptx::mbar_init(tempty0 + 8 * i, 4);
     }
+    ptx::mbar_init(red_full, 4 * (cluster_k > 1 ? cluster_k : 1));
+    ptx::mbar_init(red_empty, 4 * (cluster_k > 1 ? cluster_k : 1));
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tm_w);
     ptx::prefetch_tensormap(&tm_a);
@@ -216,6 +305,10 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     ptx::tmem_alloc(ptx::smem_u32(tmem_slot), C::kTmemCols);
     ptx::tmem_relinquish();
   }
+  // Everything above is independent of earlier kernels; from here on global memory
+  // written by them is read, so wait for them, then let the next kernel's prologue start.
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
   // Row-tile prefix table (one entry per group).
   if (args.expert_offsets == nullptr) {
     if (threadIdx.x == 0) {
@@ -249,6 +342,9 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Peers must see this CTA's barriers initialised before they arrive on them.
+  if (cluster_k > 1) ptx::cluster_sync_all();
+  if (threadIdx.x == 0) MX_STAMP(1);
 
   const int kb_total = args.k_blocks;
 
@@ -277,6 +373,7 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           if (!ok) break;
           const uint32_t bar = full0 + 8 * stage;
           if (args.trace != nullptr && blockIdx.x == 0 && trace_i < 256) {
+            if (lane == 0 && trace_i == 0) MX_STAMP(2);
             if (lane == 0) args.trace[trace_i] = clock64();
             ++trace_i;
           }
@@ -355,8 +452,10 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                           bounded_wait(full0 + 8 * stage, phase, abort_flag, args.status, 103));
           if (!ok) break;
           ptx::tc_fence_after();
-          if (args.trace != nullptr && blockIdx.x == 0 && trace_i < 256 && lane == 0)
+          if (args.trace != nullptr && blockIdx.x == 0 && trace_i < 256 && lane == 0) {
+            if (trace_i == 0) MX_STAMP(3);
             args.trace[256 + trace_i] = clock64();
+          }
           if (ptx::elect_one()) {
             const uint32_t sf = ptx::smem_u32(sf_tiles + (size_t)stage * C::kSfStageBytes);
             for (int sub = 0; sub < nsub; ++sub) {
@@ -405,6 +504,7 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         if (!ok) break;
         if (ptx::elect_one()) ptx::tc_commit(tfull0 + 8 * acc);
         __syncwarp();
+        if (lane == 0) MX_STAMP(4);
         if (++acc == C::kAcc) {
           acc = 0;
           acc_phase ^= 1u;
@@ -418,9 +518,94 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     const int etid = threadIdx.x - 64;  // 0..127
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t red_phase = 0;
+    bool red_used = false;
+    const uint32_t my_rank = cluster_k > 1 ? ptx::cluster_ctarank() : 0u;
     Work wk;
     for (int w = blockIdx.x; decode_work<TN>(w, args, tile_prefix, &wk); w += gridDim.x) {
       bool ready = bounded_wait(tfull0 + 8 * acc, acc_phase, abort_flag, args.status, 104);
+      if (etid == 0) MX_STAMP(5);
+      if constexpr (C::kClusterOk) {
+        if (cluster_k > 1) {
+          // ---- cluster split-K: partial tile -> own shared memory -> peers reduce ----
+          if (!ready) break;
+          ptx::tc_fence_after();
+          const uint32_t t_addr0 =
+              tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * C::kAccCols;
+          // Peers must have finished reading the partial tile of the previous round.
+          if (!bounded_wait_cluster(red_empty, red_phase ^ 1u, abort_flag, args.status, 105)) break;
+#pragma unroll 1
+          for (int c0 = 0; c0 < wk.rows; c0 += 16) {
+#pragma unroll
+            for (int t = 0; t < C::kWTiles; ++t) {
+              uint32_t r[16];
+              ptx::tmem_ld_x16(t_addr0 + t * TN + c0, r);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (c0 + j < wk.rows) red[(t * TN + c0 + j) * kTileF + fl] = __uint_as_float(r[j]);
+              }
+            }
+          }
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(tempty0 + 8 * acc);
+          if (++acc == C::kAcc) {
+            acc = 0;
+            acc_phase ^= 1u;
+          }
+          // One arrival per epilogue warp on every CTA of the cluster (release).
+          if (lane < cluster_k) ptx::mbar_arrive_remote(ptx::mapa(red_full, (uint32_t)lane));
+          red_used = true;
+          if (!bounded_wait_cluster(red_full, red_phase, abort_flag, args.status, 106)) break;
+          const int f = wk.n_tile * kTileF + fl;
+          const bool f_ok = f < args.n;
+          int64_t srow0 = wk.row0;
+          if (MODE == kModeSwiglu && args.out_scale_offsets != nullptr) {
+            srow0 = args.out_scale_offsets[wk.group] + (int64_t)wk.m_tile * TN;
+          }
+          // Token rows are dealt round-robin to the CTAs; the sum runs over the ranks
+          // in order, so the result does not depend on timing.
+          // Four rows per round: all their remote loads are issued before any is used.
+          for (int t0 = (int)my_rank; t0 < wk.rows; t0 += 4 * cluster_k) {
+            float vm[4][8], vu[4][8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int t = t0 + j * cluster_k;
+              const uint32_t local = ptx::smem_u32(red + t * kTileF + fl);
+#pragma unroll
+              for (int r = 0; r < 8; ++r) {
+                vm[j][r] = 0.0f;
+                vu[j][r] = 0.0f;
+                if (t < wk.rows && r < cluster_k) {
+                  const uint32_t remote = ptx::mapa(local, (uint32_t)r);
+                  vm[j][r] = ptx::ld_dsmem_f32(remote);
+                  if (MODE == kModeSwiglu) vu[j][r] = ptx::ld_dsmem_f32(remote + TN * kTileF * 4);
+                }
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int t = t0 + j * cluster_k;
+              float main_acc = 0.0f, up_acc = 0.0f;
+#pragma unroll
+              for (int r = 0; r < 8; ++r) {
+                if (r < cluster_k) {
+                  main_acc += vm[j][r];
+                  up_acc += vu[j][r];
+                }
+              }
+              if (t < wk.rows) {  // warp-uniform: every lane of the warp has the same t
+                emit_element<MODE>(args, wk.row0 + t, f, f_ok, lane, main_acc, up_acc, srow0 + t);
+              }
+            }
+          }
+          __syncwarp();
+          if (lane < cluster_k) ptx::mbar_arrive_remote(ptx::mapa(red_empty, (uint32_t)lane));
+          red_phase ^= 1u;
+          continue;
+        }
+      }
       if (args.splits > 1) {
         // The split-K path below uses a 128-thread named barrier, so the four
         // epilogue warps must agree on whether to go on.
@@ -469,7 +654,7 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
             const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
-            const float inv = __fdiv_rn(1.0f, __uint_as_float(sbits));
+            const float inv = ue8m0_inverse(sbits);
             const uint32_t code =
                 __nv_cvt_float2_to_fp8x2(make_float2(v * inv, 0.0f), __NV_SATFINITE, __NV_E4M3) & 0xffu;
             if (c0 + j < wk.rows && f_ok) {
@@ -569,9 +754,14 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
     }
+    // A CTA of a cluster must not exit while peers may still read its partial tile.
+    if (cluster_k > 1 && red_used) {
+      bounded_wait_cluster(red_empty, red_phase ^ 1u, abort_flag, args.status, 107);
+    }
   }
 
   // ---------------- teardown ----------------
+  if (threadIdx.x == 64) MX_STAMP(6);
   ptx::tc_fence_before();
   __syncthreads();
   if (*abort_flag != 0) {
@@ -583,6 +773,7 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, C::kTmemCols);
   }
+  if (threadIdx.x == 32) MX_STAMP(7);
 }
 
 // ------------------------------------------------------------------ host side
@@ -677,6 +868,15 @@ int cached_map(CUtensorMap* out, CUtensorMapDataType type, const void* base, uin
 }
 
 long long* g_trace = nullptr;
+int g_split_mode = 1;
+
+bool use_pdl() {
+  static const bool enabled = []() {
+    const char* env = std::getenv("MXFP6_B200_PDL");
+    return env == nullptr || env[0] != '0';
+  }();
+  return enabled;
+}
 
 template <int TN, int MODE>
 int launch_tn(const CUtensorMap& tm_w, const CUtensorMap& tm_a, const KernelArgs& args,
@@ -690,9 +890,58 @@ int launch_tn(const CUtensorMap& tm_w, const CUtensorMap& tm_a, const KernelArgs
                                  (int)Cfg<TN, MODE>::kSmemBytes));
     configured[device] = true;
   }
-  w6a8_gemm_kernel<TN, MODE>
-      <<<plan.grid, kThreads, Cfg<TN, MODE>::kSmemBytes, stream>>>(tm_w, tm_a, args);
-  MX_CUDA(cudaGetLastError());
+  if (plan.cluster_k > 1) {
+    if constexpr (Cfg<TN, MODE>::kClusterOk) {
+      cudaLaunchConfig_t config = {};
+      config.gridDim = dim3((unsigned)plan.grid);
+      config.blockDim = dim3(kThreads);
+      config.dynamicSmemBytes = Cfg<TN, MODE>::kSmemBytes;
+      config.stream = stream;
+      cudaLaunchAttribute attribute[2];
+      attribute[0].id = cudaLaunchAttributeClusterDimension;
+      attribute[0].val.clusterDim.x = (unsigned)plan.cluster_k;
+      attribute[0].val.clusterDim.y = 1;
+      attribute[0].val.clusterDim.z = 1;
+      attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attribute[1].val.programmaticStreamSerializationAllowed = 1;
+      config.attrs = attribute;
+      config.numAttrs = use_pdl() ? 2 : 1;
+      // Never launch more clusters than can be resident: the persistent loop covers the rest.
+      static int max_clusters[64][9] = {};
+      if (device < 64 && max_clusters[device][plan.cluster_k] == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, w6a8_gemm_kernel<TN, MODE>, &config) != cudaSuccess ||
+            n < 1) {
+          (void)cudaGetLastError();
+          n = 1;
+        }
+        max_clusters[device][plan.cluster_k] = n;
+      }
+      const int resident = device < 64 ? max_clusters[device][plan.cluster_k] : 1;
+      if (plan.grid / plan.cluster_k > resident) config.gridDim = dim3((unsigned)(resident * plan.cluster_k));
+      MX_CUDA(cudaLaunchKernelEx(&config, w6a8_gemm_kernel<TN, MODE>, tm_w, tm_a, args));
+      return kOk;
+    } else {
+      set_error("tile_tokens %d cannot use cluster split-K", TN);
+      return kInvalidArgument;
+    }
+  }
+  {
+    // Programmatic dependent launch: the prologue (barriers, tensor memory, tensor-map
+    // prefetch) may run while the previous kernel on the stream drains; the kernel
+    // itself waits (griddepcontrol.wait) before it touches global memory.
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)plan.grid);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = Cfg<TN, MODE>::kSmemBytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = use_pdl() ? 1 : 0;
+    MX_CUDA(cudaLaunchKernelEx(&config, w6a8_gemm_kernel<TN, MODE>, tm_w, tm_a, args));
+  }
   return kOk;
 }
 
@@ -780,20 +1029,43 @@ int plan_w6a8(const GemmProblem& p, GemmPlan* plan) {
   const int64_t tiles = row_tiles * n_tiles;
   const int sms = sm_count();
   int splits = p.splits;
-  if (splits == 0) {
+  int cluster_k = 1;
+  const int mode = p.split_mode != 0 ? p.split_mode : default_split_mode();
+  if (p.cluster_k > 1) {
+    MX_REQUIRE(tn <= 96 && p.cluster_k <= 8 && p.cluster_k <= k_blocks && splits <= 1,
+               "cluster_k needs tile_tokens <= 96, cluster_k <= min(8, k/128) and no scratch split");
+    cluster_k = p.cluster_k;
     splits = 1;
-    if (!grouped && !swiglu && tn <= 96 && tiles * 2 <= sms) {
-      splits = (int)(sms / tiles);
-      const int max_splits = k_blocks / 2 > 0 ? k_blocks / 2 : 1;
-      if (splits > max_splits) splits = max_splits;
-      if (splits > 16) splits = 16;
+  } else if (splits == 0) {
+    splits = 1;
+    if (tn <= 96 && tiles * 2 <= sms) {
+      if (mode == 1) {
+        // Leave a few SMs of slack: clusters need all their CTAs inside one GPC.
+        int64_t ck = (sms - 16) / tiles;
+        if (ck > 8) ck = 8;
+        if (ck > k_blocks) ck = k_blocks;
+        if (ck >= 2) cluster_k = (int)ck;
+      } else if (mode == 2 && !grouped && !swiglu) {
+        splits = (int)(sms / tiles);
+        const int max_splits = k_blocks / 2 > 0 ? k_blocks / 2 : 1;
+        if (splits > max_splits) splits = max_splits;
+        if (splits > 16) splits = 16;
+      }
     }
   }
   MX_REQUIRE(splits >= 1 && splits <= k_blocks, "splits must be in [1, k/128]");
+  MX_REQUIRE(!(splits > 1 && (grouped || swiglu)),
+             "scratch split-K is available for dense store-mode launches only");
   plan->splits = splits;
-  const int64_t work = tiles * splits;
-  plan->grid = (int)(work < sms ? work : sms);
-  if (plan->grid < 1) plan->grid = 1;
+  plan->cluster_k = cluster_k;
+  if (cluster_k > 1) {
+    const int64_t clusters = tiles < sms / cluster_k ? tiles : sms / cluster_k;
+    plan->grid = (int)(clusters < 1 ? 1 : clusters) * cluster_k;
+  } else {
+    const int64_t work = tiles * splits;
+    plan->grid = (int)(work < sms ? work : sms);
+    if (plan->grid < 1) plan->grid = 1;
+  }
   plan->partial_bytes = splits > 1 ? (size_t)tiles * splits * tn * kTileF * sizeof(float) : 0;
   plan->counter_bytes = splits > 1 ? (size_t)tiles * sizeof(uint32_t) : 0;
   return kOk;
@@ -848,7 +1120,8 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
   args.out_scale_offsets = p.out_scale_offsets;
   args.k_blocks = p.k / kTileK;
   args.n_tiles = (p.n + kTileF - 1) / kTileF;
-  args.splits = plan.splits;
+  args.splits = plan.cluster_k > 1 ? plan.cluster_k : plan.splits;
+  args.cluster_k = plan.cluster_k;
   args.out_dtype = p.out_dtype;
   args.alpha = p.alpha;
   static const uint32_t w_tx = []() {
@@ -884,6 +1157,8 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
 }
 
 void set_trace_buffer(long long* ptr) { g_trace = ptr; }
+void set_default_split_mode(int mode) { g_split_mode = (mode >= 1 && mode <= 3) ? mode : 1; }
+int default_split_mode() { return g_split_mode; }
 
 // One status word per device, allocated on first use and never freed.
 int* device_status_word(int device) {
@@ -945,6 +1220,7 @@ int launch_w6a8_static_scratch(GemmProblem& p, cudaStream_t stream) {
   MX_CUDA(cudaGetDevice(&device));
   unsigned char* base = nullptr;
   if (int rc = static_scratch_base(device, &base)) return rc;
+  p.split_mode = 2;  // this entry point exists for the scratch-based split
   GemmPlan plan;
   if (int rc = plan_w6a8(p, &plan)) return rc;
   if (plan.splits > 1) {

@@ -47,6 +47,11 @@ struct GemmProblem {
   const int64_t* out_scale_offsets = nullptr;
   // Status word the kernel reports an expired wait to; null = the per-device word.
   int* status_word = nullptr;
+  // How K is split when a launch has too few tiles for the GPU: 0 = library default,
+  // 1 = thread-block clusters reducing through distributed shared memory,
+  // 2 = FP32 partial tiles in the scratch arena, 3 = never split.
+  int split_mode = 0;
+  int cluster_k = 0;  // explicit cluster size along K (0 = choose)
   // Optional overrides (0 = choose from the static table).
   int tile_tokens = 0;
   int splits = 0;
@@ -54,7 +59,8 @@ struct GemmProblem {
 
 struct GemmPlan {
   int tile_tokens = 0;  // activation rows per tile (MMA N)
-  int splits = 1;
+  int splits = 1;      // scratch-arena split-K factor
+  int cluster_k = 1;   // cluster split-K factor (CTAs per cluster)
   int stages = 0;
   int grid = 0;
   size_t smem_bytes = 0;
@@ -66,6 +72,10 @@ struct GemmPlan {
 int plan_w6a8(const GemmProblem& p, GemmPlan* plan);
 // Launches the kernel on `stream`; the plan must come from plan_w6a8.
 int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream);
+
+// Process-wide default of GemmProblem::split_mode (1 = cluster, 2 = scratch arena, 3 = off).
+void set_default_split_mode(int mode);
+int default_split_mode();
 
 // Diagnostics: CTA 0 of later launches writes [3][256] clock64 stamps (producer
 // issue, stage ready at the MMA warp, stage committed) to this device buffer.

@@ -65,7 +65,7 @@ topk_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16*
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
       const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
-      const float inv = __fdiv_rn(1.0f, __uint_as_float(sbits));
+      const float inv = ue8m0_inverse(sbits);
       if (valid) {
         const uint2 packed = make_uint2(e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
                                         e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
@@ -324,7 +324,7 @@ silu_mul_quant_kernel(const T* __restrict__ input, uint8_t* __restrict__ output,
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
-    const float inv = __fdiv_rn(1.0f, __uint_as_float(sbits));
+    const float inv = ue8m0_inverse(sbits);
     if (valid) {
       reinterpret_cast<uint2*>(output)[c] =
           make_uint2(e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),

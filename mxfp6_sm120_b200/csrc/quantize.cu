@@ -75,44 +75,56 @@ __global__ void __launch_bounds__(kQuantThreads)
 quantize_mxfp8_kernel(const T* __restrict__ in, uint8_t* __restrict__ out,
                       uint8_t* __restrict__ packed, uint8_t* __restrict__ logical, int64_t rows,
                       int k, int64_t pad_begin, int64_t pad_total) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int groups = k / kScaleVec;
   const int64_t chunks = rows * (k / 8);
   const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t rounds = (chunks + nthreads - 1) / nthreads;
+  // Four independent 16-byte loads per thread are issued before any of them is
+  // used, so that enough bytes are in flight to cover HBM latency.
+  constexpr int kUnroll = 4;
+  const int64_t per_round = nthreads * kUnroll;
+  const int64_t rounds = (chunks + per_round - 1) / per_round;
   for (int64_t it = 0; it < rounds; ++it) {
-    const int64_t c = it * nthreads + tid;
-    const bool valid = c < chunks;
-    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (valid) {
-      Vec8<T> raw;
-      raw.raw = __ldg(reinterpret_cast<const uint4*>(in) + c);
-      raw.unpack(v);
-    }
-    float amax = absmax8(v);
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
-    const float inv = __fdiv_rn(1.0f, __uint_as_float(sbits));
-    if (valid) {
-      uint32_t w[2];
+    Vec8<T> raw[kUnroll];
+    int64_t cs[kUnroll];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const uint32_t lo = __nv_cvt_float2_to_fp8x2(
-            make_float2(v[4 * i] * inv, v[4 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
-        const uint32_t hi = __nv_cvt_float2_to_fp8x2(
-            make_float2(v[4 * i + 2] * inv, v[4 * i + 3] * inv), __NV_SATFINITE, __NV_E4M3);
-        w[i] = lo | (hi << 16);
-      }
-      reinterpret_cast<uint2*>(out)[c] = make_uint2(w[0], w[1]);
-      if ((c & 3) == 0) {
-        const int64_t group = c >> 2;
-        const uint8_t code = static_cast<uint8_t>(sbits >> 23);
-        if (logical != nullptr) logical[group] = code;
-        if (packed != nullptr) {
-          const int64_t row = group / groups;
-          const int g = static_cast<int>(group - row * groups);
-          packed[packed_scale_offset(row, g, groups)] = code;
+    for (int u = 0; u < kUnroll; ++u) {
+      cs[u] = it * per_round + u * nthreads + tid;
+      raw[u].raw = make_uint4(0u, 0u, 0u, 0u);
+      if (cs[u] < chunks) raw[u].raw = __ldg(reinterpret_cast<const uint4*>(in) + cs[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t c = cs[u];
+      const bool valid = c < chunks;
+      float v[8];
+      raw[u].unpack(v);
+      float amax = absmax8(v);
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
+      const float inv = ue8m0_inverse(sbits);
+      if (valid) {
+        uint32_t w[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+              make_float2(v[4 * i] * inv, v[4 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+          const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+              make_float2(v[4 * i + 2] * inv, v[4 * i + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+          w[i] = lo | (hi << 16);
+        }
+        reinterpret_cast<uint2*>(out)[c] = make_uint2(w[0], w[1]);
+        if ((c & 3) == 0) {
+          const int64_t group = c >> 2;
+          const uint8_t code = static_cast<uint8_t>(sbits >> 23);
+          if (logical != nullptr) logical[group] = code;
+          if (packed != nullptr) {
+            const int64_t row = group / groups;
+            const int g = static_cast<int>(group - row * groups);
+            packed[packed_scale_offset(row, g, groups)] = code;
+          }
         }
       }
     }
@@ -129,6 +141,7 @@ __global__ void __launch_bounds__(kQuantThreads)
 quantize_mxfp6_kernel(const T* __restrict__ in, uint8_t* __restrict__ out,
                       uint8_t* __restrict__ packed, uint8_t* __restrict__ logical, int64_t rows,
                       int k, int64_t pad_begin, int64_t pad_total) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int groups = k / kScaleVec;
   const int64_t chunks = rows * (k / 16);
   const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -158,7 +171,7 @@ quantize_mxfp6_kernel(const T* __restrict__ in, uint8_t* __restrict__ out,
     for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     const uint32_t sbits = ue8m0_scale_bits(amax, 28.0f);
-    const float inv = __fdiv_rn(1.0f, __uint_as_float(sbits));
+    const float inv = ue8m0_inverse(sbits);
     if (valid) {
       uint32_t unit[4];  // four codes -> 24 bits, code i at bits 6i..6i+5
 #pragma unroll
@@ -216,7 +229,8 @@ void padding_range(int64_t rows, int64_t k, int64_t* begin, int64_t* total) {
 
 int grid_for(int64_t chunks) {
   // Enough CTAs to fill 148 SMs at 8 resident CTAs each; grid-stride beyond that.
-  const int64_t want = (chunks + kQuantThreads - 1) / kQuantThreads;
+  // Every thread takes four chunks per round.
+  const int64_t want = (chunks + 4 * kQuantThreads - 1) / (4 * kQuantThreads);
   const int64_t cap = 148 * 16;
   return static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
 }

@@ -13,11 +13,12 @@ from dataclasses import dataclass
 import torch
 
 from .ops import PackedMXFP6Tensor, quantize_mxfp6
+from .moe_ops import qwen35_route_mxfp8_out, qwen35_topk_quant_out
 from .qwen35 import (
     MoeShape,
     Qwen35GroupedWorkspace,
     SharedExpertWorkspace,
-    qwen35_grouped_gemm_out,
+    _grouped_experts_out,
     qwen35_grouped_reduce_out,
     shared_expert_out,
 )
@@ -28,6 +29,9 @@ class MoeLayerState:
     workspace: Qwen35GroupedWorkspace
     shared: SharedExpertWorkspace
     output: torch.Tensor
+    side_stream: torch.cuda.Stream | None = None
+    fork: torch.cuda.Event | None = None
+    join: torch.cuda.Event | None = None
 
 
 @dataclass
@@ -72,19 +76,39 @@ class MoeLayer:
             Qwen35GroupedWorkspace.allocate(tokens, device, local),
             SharedExpertWorkspace.allocate(tokens, device, self.shape),
             torch.empty((tokens, self.shape.hidden), dtype=torch.bfloat16, device=device),
+            torch.cuda.Stream(device) if device.type == "cuda" else None,
+            torch.cuda.Event() if device.type == "cuda" else None,
+            torch.cuda.Event() if device.type == "cuda" else None,
         )
 
     def forward(self, state: MoeLayerState, hidden: torch.Tensor, router_logits: torch.Tensor,
                 shared_gate: torch.Tensor | None, with_shared: bool = True) -> torch.Tensor:
+        """Queue the layer on the current stream.  The shared expert runs on a side
+        stream between the quantization and the final reduce (the reference's
+        benchmark overlaps it the same way); under capture both branches land in
+        the one graph."""
         e, i, h = self.local_experts, self.shape.intermediate, self.shape.hidden
-        qwen35_grouped_gemm_out(
-            state.workspace, hidden, router_logits,
-            self.w1.values.view(e, 2 * i, h * 3 // 4), self.w1.scales,
-            self.w2.values.view(e, h, i * 3 // 4), self.w2.scales,
-            renormalize=True, expert_map=self.expert_map,
-        )
+        ws = state.workspace
+        qwen35_topk_quant_out(ws.quantized, ws.input_scales, ws.packed_input_scales, ws.topk_weights,
+                              ws.topk_ids, hidden, router_logits, renormalize=True)
         shared_out = None
-        if with_shared:
-            shared_out = shared_expert_out(state.shared, state.workspace, self.shared_w1, self.shared_w2)
-        return qwen35_grouped_reduce_out(state.workspace, state.output, shared_out,
+        overlap = with_shared and state.side_stream is not None
+        if overlap:
+            current = torch.cuda.current_stream(hidden.device)
+            state.fork.record(current)
+            state.side_stream.wait_event(state.fork)
+            with torch.cuda.stream(state.side_stream):
+                shared_out = shared_expert_out(state.shared, ws, self.shared_w1, self.shared_w2)
+                state.join.record(state.side_stream)
+        qwen35_route_mxfp8_out(ws.quantized, ws.input_scales, ws.topk_ids, ws.permuted,
+                               ws.grouped_input_scales, ws.expert_cursors, ws.expert_offsets,
+                               ws.scale_offsets, ws.inverse_permutation,
+                               source_tokens=ws.source_tokens, expert_map=self.expert_map)
+        _grouped_experts_out(ws, self.w1.values.view(e, 2 * i, h * 3 // 4), self.w1.scales,
+                             self.w2.values.view(e, h, i * 3 // 4), self.w2.scales)
+        if overlap:
+            torch.cuda.current_stream(hidden.device).wait_event(state.join)
+        elif with_shared:
+            shared_out = shared_expert_out(state.shared, ws, self.shared_w1, self.shared_w2)
+        return qwen35_grouped_reduce_out(ws, state.output, shared_out,
                                          shared_gate if with_shared else None)

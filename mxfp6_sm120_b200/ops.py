@@ -135,6 +135,26 @@ def device_status(device: torch.device | str | int | None = None, reset: bool = 
     return int(value.value)
 
 
+_SPLIT_MODES = {"cluster": 1, "workspace": 2, "off": 3}
+
+
+def set_split_k_mode(mode: str) -> None:
+    """Choose how launches with too few tiles split K.
+
+    ``"cluster"`` (default): thread-block clusters reduce through distributed shared
+    memory, no scratch.  ``"workspace"``: FP32 partial tiles in the split-K arena
+    (the reference's Stream-K workspace model).  ``"off"``: never split.
+    """
+    if mode not in _SPLIT_MODES:
+        raise ValueError(f"mode must be one of {sorted(_SPLIT_MODES)}")
+    check(library().mxfp6_set_split_k_mode(_SPLIT_MODES[mode]))
+
+
+def is_stream_k_enabled() -> bool:
+    """Whether split-K uses the workspace arena (the reference's MXFP6_STREAM_K switch)."""
+    return library().mxfp6_get_split_k_mode() == 2
+
+
 def _validate_problem(m: int, n: int, k: int) -> None:
     if m <= 0:
         raise ValueError(f"m must be positive; got {m}")
@@ -558,9 +578,10 @@ def quantize_mxfp6(input: torch.Tensor) -> PackedMXFP6Tensor:
 def gemm_w6a8_plan(m: int, n: int, k: int, tile_tokens: int = 0, splits: int = 0) -> dict[str, int]:
     """Tile/split-K choice the library makes for a dense problem (host arithmetic)."""
     _validate_problem(m, n, k)
-    plan = (ctypes.c_int64 * 6)()
+    plan = (ctypes.c_int64 * 7)()
     check(library().mxfp6_gemm_w6a8_plan(m, n, k, tile_tokens, splits, plan))
-    keys = ("tile_tokens", "splits", "stages", "grid", "partial_bytes", "counter_bytes")
+    keys = ("tile_tokens", "splits", "stages", "grid", "partial_bytes", "counter_bytes",
+            "cluster_k")
     return dict(zip(keys, (int(v) for v in plan)))
 
 

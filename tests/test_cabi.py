@@ -59,8 +59,25 @@ def test_plan_is_host_arithmetic_and_validates():
     assert small["tile_tokens"] == 16 and small["splits"] >= 1 and small["stages"] >= 2
     big = mx.gemm_w6a8_plan(8192, 34816, 5120)
     assert big["tile_tokens"] in (192, 256) and big["splits"] == 1 and big["grid"] <= 148
-    split = mx.gemm_w6a8_plan(32, 2048, 5120)
-    assert split["splits"] > 1 and split["partial_bytes"] > 0 and split["counter_bytes"] > 0
+    clustered = mx.gemm_w6a8_plan(32, 2048, 5120)
+    assert clustered["cluster_k"] == 8 and clustered["splits"] == 1 and clustered["partial_bytes"] == 0
+    assert clustered["grid"] % clustered["cluster_k"] == 0
+    mx.set_split_k_mode("workspace")
+    try:
+        assert mx.is_stream_k_enabled()
+        split = mx.gemm_w6a8_plan(32, 2048, 5120)
+        assert split["splits"] > 1 and split["partial_bytes"] > 0 and split["counter_bytes"] > 0
+        assert split["cluster_k"] == 1
+    finally:
+        mx.set_split_k_mode("cluster")
+    mx.set_split_k_mode("off")
+    try:
+        off = mx.gemm_w6a8_plan(32, 2048, 5120)
+        assert off["splits"] == 1 and off["cluster_k"] == 1
+    finally:
+        mx.set_split_k_mode("cluster")
+    with pytest.raises(ValueError):
+        mx.set_split_k_mode("bogus")
     with pytest.raises(ValueError, match="multiple of 128"):
         mx.gemm_w6a8_plan(16, 1024, 2000)
     with pytest.raises(ValueError, match="multiple of 8"):

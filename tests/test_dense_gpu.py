@@ -250,6 +250,16 @@ def test_workspace_arena_planning_and_graph_replay(mx):
     from mxfp6_sm120_b200._loader import check, library
 
     check(library().mxfp6_workspace_reset())
+    mx.set_split_k_mode("workspace")  # the arena serves the scratch-based split
+    try:
+        _arena_body(mx, check, library)
+    finally:
+        mx.set_split_k_mode("cluster")
+        torch.cuda.synchronize()
+        check(library().mxfp6_workspace_reset())
+
+
+def _arena_body(mx, check, library):
     gen = _cpu_gen(21)
     w = mx.quantize_mxfp6((torch.randn((2048, 5120), generator=gen) * 0.02).to(torch.bfloat16).to(DEV))
     acts = {m: torch.randn((m, 5120), generator=gen).to(torch.bfloat16).to(DEV) for m in (1, 16, 32)}
@@ -291,5 +301,25 @@ def test_workspace_arena_planning_and_graph_replay(mx):
     except RuntimeError as error:
         refused = "no lane" in str(error)
     assert refused
-    torch.cuda.synchronize()
-    check(library().mxfp6_workspace_reset())
+
+
+def test_cluster_split_k_matches_scratch_split_and_single_pass(mx):
+    """The three ways of covering K agree within the GEMM tolerance and each is
+    deterministic run to run."""
+    gen = _cpu_gen(14)
+    a = torch.randn((24, 6144), generator=gen).to(torch.bfloat16)
+    w = (torch.randn((5120, 6144), generator=gen) * 0.02).to(torch.bfloat16)
+    act, wgt, (a_q, a_s, w_q, w_s) = _packed_operands(mx, a, w)
+    want = o.gemm_w6a8(a_q, a_s, w_q, w_s, out_dtype=torch.bfloat16)
+    outs = {}
+    for mode in ("cluster", "workspace", "off"):
+        mx.set_split_k_mode(mode)
+        try:
+            plan = mx.gemm_w6a8_plan(24, 5120, 6144)
+            outs[mode] = mx.gemm_w6a8(act, wgt, out_dtype=torch.bfloat16)
+            for _ in range(3):
+                assert torch.equal(mx.gemm_w6a8(act, wgt, out_dtype=torch.bfloat16), outs[mode])
+        finally:
+            mx.set_split_k_mode("cluster")
+        assert _rel_fro(outs[mode], want) <= GEMM_REL_FRO, (mode, plan)
+    assert mx.gemm_w6a8_plan(24, 5120, 6144)["cluster_k"] == 3

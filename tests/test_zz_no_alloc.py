@@ -40,12 +40,16 @@ def test_static_scratch_gemm_matches_regular_entry_point(mx):
     lib = library()
     # 2048 x 5120 at M = 8 splits K nine ways, so the scratch array is really used.
     act, wgt = _operands(mx, 8, 2048, 5120, seed=5)
-    plan = mx.gemm_w6a8_plan(8, 2048, 5120)
-    assert plan["splits"] > 1
-    scratch = torch.zeros(plan["partial_bytes"] + plan["counter_bytes"], dtype=torch.uint8, device=DEV)
-    want = torch.empty((8, 2048), dtype=torch.bfloat16, device=DEV)
-    assert _call(lib, "mxfp6_gemm_w6a8_ex", act, wgt, want,
-                 (0, 0, scratch.data_ptr(), scratch.numel())) == 0
+    mx.set_split_k_mode("workspace")  # the entry point under test always splits through scratch
+    try:
+        plan = mx.gemm_w6a8_plan(8, 2048, 5120)
+        assert plan["splits"] > 1
+        scratch = torch.zeros(plan["partial_bytes"] + plan["counter_bytes"], dtype=torch.uint8, device=DEV)
+        want = torch.empty((8, 2048), dtype=torch.bfloat16, device=DEV)
+        assert _call(lib, "mxfp6_gemm_w6a8_ex", act, wgt, want,
+                     (0, 0, scratch.data_ptr(), scratch.numel())) == 0
+    finally:
+        mx.set_split_k_mode("cluster")
     for _ in range(2):  # two calls in a row share the array; the second must not see stale counters
         got = torch.full((8, 2048), float("nan"), dtype=torch.bfloat16, device=DEV)
         assert _call(lib, "mxfp6_gemm_w6a8_static_scratch", act, wgt, got) == 0
@@ -65,7 +69,11 @@ def test_static_scratch_rejects_oversized_problems(mx):
     from mxfp6_sm120_b200._loader import library
 
     lib = library()
-    plan = mx.gemm_w6a8_plan(96, 7168, 5120)
+    mx.set_split_k_mode("workspace")
+    try:
+        plan = mx.gemm_w6a8_plan(96, 7168, 5120)
+    finally:
+        mx.set_split_k_mode("cluster")
     assert plan["partial_bytes"] > 4 << 20  # needs more than the 4 MiB built in
     act, wgt = _operands(mx, 96, 7168, 5120, seed=7)
     out = torch.empty((96, 7168), dtype=torch.bfloat16, device=DEV)
