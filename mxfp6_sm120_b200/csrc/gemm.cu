@@ -83,7 +83,7 @@ struct KernelArgs {
 constexpr int kModeStore = 0;   // out = cast(alpha * acc)
 constexpr int kModeSwiglu = 1;  // out = MXFP8(bf16(silu(bf16 gate)) * bf16 up)
 
-template <int TN, int MODE>
+template <int TN, int MODE, int CL>
 struct Cfg {
   static constexpr int kWTiles = MODE == kModeSwiglu ? 2 : 1;  // weight tiles per K block
   static constexpr int kSfbAtoms = TN <= 128 ? 1 : 2;
@@ -106,9 +106,13 @@ struct Cfg {
   static constexpr uint32_t kATileBytes = TN * kTileK;
   static constexpr uint32_t kStageBytes = kSubs * (kWTiles * kWTileBytes + kATileBytes);
   static constexpr uint32_t kSfStageBytes = kSubs * kAtomBytes * (kWTiles + kSfbAtoms);
-  static constexpr uint32_t kFixedBytes = 1024 /*align slack*/ + 4096 /*barriers + tables*/;
+  // Per-warp staging of the epilogue: 32 rows x 33 floats (SwiGLU) or 32 x 32 halves.
+  static constexpr uint32_t kEpiWarpBytes = MODE == kModeSwiglu ? 32 * 33 * 4 + 128 : 2048;
+  static constexpr uint32_t kFixedBytes =
+      1024 /*align slack*/ + 4096 /*barriers + tables*/ + 4 * kEpiWarpBytes;
   // Cluster split-K: every CTA parks its FP32 partial tile here for its peers.
-  static constexpr bool kClusterOk = TN <= 96;
+  static constexpr bool kClusterOk = CL != 0;
+  static_assert(!kClusterOk || TN <= 96, "cluster split-K is for narrow tiles");
   static constexpr uint32_t kRedBytes = kClusterOk ? kAccCols * kTileF * 4 : 0;
   static constexpr int kStagesRaw =
       (int)((232448u - kFixedBytes - kRedBytes) / (kStageBytes + kSfStageBytes));
@@ -250,11 +254,11 @@ __device__ __forceinline__ void emit_element(const KernelArgs& args, int64_t row
   }
 }
 
-template <int TN, int MODE>
+template <int TN, int MODE, int CL>
 __global__ void __launch_bounds__(kThreads, 1)
 w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
                  const KernelArgs args) {
-  using C = Cfg<TN, MODE>;
+  using C = Cfg<TN, MODE, CL>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -268,7 +272,8 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
   volatile int* launch_slot = reinterpret_cast<volatile int*>(tmem_slot + 3);
   int* tile_prefix = reinterpret_cast<int*>(fixed + 1024);  // kMaxGroups + 1 ints
-  float* red = reinterpret_cast<float*>(fixed + 4096);      // cluster split-K partial tile
+  uint8_t* epi_stage = fixed + 4096;                          // 4 x kEpiWarpBytes
+  float* red = reinterpret_cast<float*>(fixed + 4096 + 4 * C::kEpiWarpBytes);  // cluster partial tile
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -278,7 +283,7 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   const uint32_t tempty0 = tfull0 + 16;
   const uint32_t red_full = tempty0 + 16;   // all partial tiles of the cluster are written
   const uint32_t red_empty = red_full + 8;  // all peers have read this CTA's partial tile
-  const int cluster_k = args.cluster_k;
+  const int cluster_k = CL != 0 ? args.cluster_k : 1;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -629,76 +634,111 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       if (args.splits > 1) {
         part = args.partials + ((size_t)wk.tile_id * args.splits + wk.split) * (TN * kTileF);
       }
+      // Lane = feature, column = token row in tensor memory; global memory wants
+      // the features of a row next to each other.  Each warp turns 32 columns at a
+      // time through its own slice of shared memory and then writes whole row
+      // segments with 16-byte stores.  Columns at or beyond wk.rows are skipped.
+      constexpr int kChunk = TN >= 32 ? 32 : 16;
+      uint8_t* stage_bytes = epi_stage + quarter * C::kEpiWarpBytes;
+      const int f0 = wk.n_tile * kTileF + quarter * 32;  // first feature of this warp
       if constexpr (MODE == kModeSwiglu) {
-        // Lane = intermediate feature, column = token.  The 32 lanes of this warp
-        // are exactly one 32-feature scale group of every token row.
+        float* stage = reinterpret_cast<float*>(stage_bytes);  // [kChunk][33]
         const int groups = args.n / kScaleVec;
-        const int g_index = f / kScaleVec;
+        const int g_index = f0 / kScaleVec;
         int64_t srow0 = wk.row0;
         if (args.out_scale_offsets != nullptr) {
           srow0 = args.out_scale_offsets[wk.group] + (int64_t)wk.m_tile * TN;
         }
 #pragma unroll 1
-        for (int c0 = 0; c0 < TN; c0 += 16) {
-          uint32_t rg[16], ru[16];
-          ptx::tmem_ld_x16(t_addr + c0, rg);
-          ptx::tmem_ld_x16(t_addr + TN + c0, ru);
+        for (int c0 = 0; c0 < wk.rows; c0 += kChunk) {
+          uint32_t rg[kChunk], ru[kChunk];
+          ptx::tmem_ld_chunk<kChunk>(t_addr + c0, rg);
+          ptx::tmem_ld_chunk<kChunk>(t_addr + TN + c0, ru);
           ptx::tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
+          for (int j = 0; j < kChunk; ++j) {
             const float g = round_bf16(__uint_as_float(rg[j]));
             const float u = round_bf16(__uint_as_float(ru[j]));
             const float sv = round_bf16(__fdiv_rn(g, 1.0f + expf(-g)));
-            const float v = round_bf16(sv * u);
-            float amax = fabsf(v);
+            stage[j * 33 + lane] = round_bf16(sv * u);
+          }
+          __syncwarp();
+          // Now lane = token row: its 32 features are one scale group.
+          if (lane < kChunk) {
+            float v[32];
+            float amax = 0.0f;
 #pragma unroll
-            for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+            for (int i = 0; i < 32; ++i) {
+              v[i] = stage[lane * 33 + i];
+              amax = fmaxf(amax, fabsf(v[i]));
+            }
             const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
             const float inv = ue8m0_inverse(sbits);
-            const uint32_t code =
-                __nv_cvt_float2_to_fp8x2(make_float2(v * inv, 0.0f), __NV_SATFINITE, __NV_E4M3) & 0xffu;
-            if (c0 + j < wk.rows && f_ok) {
-              const int64_t row = wk.row0 + c0 + j;
-              static_cast<uint8_t*>(args.out)[row * args.n + f] = (uint8_t)code;
-              if (lane == 0) {
-                const uint8_t sc = (uint8_t)(sbits >> 23);
-                if (args.out_logical_scales != nullptr)
-                  args.out_logical_scales[row * groups + g_index] = sc;
-                if (args.out_packed_scales != nullptr)
-                  args.out_packed_scales[packed_scale_offset(srow0 + c0 + j, g_index, groups)] = sc;
-              }
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+                  make_float2(v[4 * i] * inv, v[4 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+              const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+                  make_float2(v[4 * i + 2] * inv, v[4 * i + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+              w[i] = lo | (hi << 16);
+            }
+            const int t = c0 + lane;
+            if (t < wk.rows && f0 < args.n) {
+              const int64_t row = wk.row0 + t;
+              uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(args.out) + row * args.n + f0);
+              dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+              const uint8_t sc = (uint8_t)(sbits >> 23);
+              if (args.out_logical_scales != nullptr)
+                args.out_logical_scales[row * groups + g_index] = sc;
+              if (args.out_packed_scales != nullptr)
+                args.out_packed_scales[packed_scale_offset(srow0 + t, g_index, groups)] = sc;
             }
           }
+          __syncwarp();
         }
-      } else {
+      } else if (args.splits > 1) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < TN; c0 += 16) {
-        uint32_t r[16];
-        ptx::tmem_ld_x16(t_addr + c0, r);
-        ptx::tmem_ld_wait();
-        if (args.splits > 1) {
+        for (int c0 = 0; c0 < wk.rows; c0 += 16) {
+          uint32_t r[16];
+          ptx::tmem_ld_x16(t_addr + c0, r);
+          ptx::tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (c0 + j < wk.rows) __stcg(part + (c0 + j) * kTileF + fl, __uint_as_float(r[j]));
           }
-        } else if (f_ok) {
-          if (args.out_dtype == kBF16) {
-            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(args.out) + wk.row0 * args.n + f;
+        }
+      } else {
+        uint16_t* stage = reinterpret_cast<uint16_t*>(stage_bytes);  // [kChunk][32] halves
+        const bool bf16_out = args.out_dtype == kBF16;
+#pragma unroll 1
+        for (int c0 = 0; c0 < wk.rows; c0 += kChunk) {
+          uint32_t r[kChunk];
+          ptx::tmem_ld_chunk<kChunk>(t_addr + c0, r);
+          ptx::tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (c0 + j < wk.rows)
-                o[(int64_t)(c0 + j) * args.n] = __float2bfloat16_rn(args.alpha * __uint_as_float(r[j]));
-            }
-          } else {
-            __half* o = static_cast<__half*>(args.out) + wk.row0 * args.n + f;
+          for (int j = 0; j < kChunk; ++j) {
+            const float v = args.alpha * __uint_as_float(r[j]);
+            stage[j * 32 + lane] = bf16_out ? __bfloat16_as_ushort(__float2bfloat16_rn(v))
+                                            : __half_as_ushort(__float2half_rn(v));
+          }
+          __syncwarp();
+          // 4 lanes cover one 64-byte row segment; a warp writes 8 rows per pass.
+          const int seg = lane & 3;
+          const int fseg = f0 + seg * 8;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (c0 + j < wk.rows)
-                o[(int64_t)(c0 + j) * args.n] = __float2half_rn(args.alpha * __uint_as_float(r[j]));
+          for (int pass = 0; pass < kChunk / 8; ++pass) {
+            const int rr = (lane >> 2) + 8 * pass;
+            const int t = c0 + rr;
+            if (t < wk.rows && fseg < args.n) {
+              const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * 32 + seg * 8);
+              *reinterpret_cast<uint4*>(static_cast<uint16_t*>(args.out) +
+                                        (wk.row0 + t) * args.n + fseg) = v;
             }
           }
+          __syncwarp();
         }
-      }
       }
       // Accumulator buffer is free for the next tile.
       ptx::tc_fence_before();
@@ -878,77 +918,83 @@ bool use_pdl() {
   return enabled;
 }
 
-template <int TN, int MODE>
-int launch_tn(const CUtensorMap& tm_w, const CUtensorMap& tm_a, const KernelArgs& args,
-              const GemmPlan& plan, cudaStream_t stream) {
+template <int TN, int MODE, int CL>
+int launch_variant(const CUtensorMap& tm_w, const CUtensorMap& tm_a, const KernelArgs& args,
+                   const GemmPlan& plan, cudaStream_t stream) {
+  using C = Cfg<TN, MODE, CL>;
   static bool configured[64] = {};
   int device = 0;
   MX_CUDA(cudaGetDevice(&device));
   if (device < 64 && !configured[device]) {
-    MX_CUDA(cudaFuncSetAttribute(w6a8_gemm_kernel<TN, MODE>,
+    MX_CUDA(cudaFuncSetAttribute(w6a8_gemm_kernel<TN, MODE, CL>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)Cfg<TN, MODE>::kSmemBytes));
+                                 (int)C::kSmemBytes));
     configured[device] = true;
   }
-  if (plan.cluster_k > 1) {
-    if constexpr (Cfg<TN, MODE>::kClusterOk) {
-      cudaLaunchConfig_t config = {};
-      config.gridDim = dim3((unsigned)plan.grid);
-      config.blockDim = dim3(kThreads);
-      config.dynamicSmemBytes = Cfg<TN, MODE>::kSmemBytes;
-      config.stream = stream;
-      cudaLaunchAttribute attribute[2];
-      attribute[0].id = cudaLaunchAttributeClusterDimension;
-      attribute[0].val.clusterDim.x = (unsigned)plan.cluster_k;
-      attribute[0].val.clusterDim.y = 1;
-      attribute[0].val.clusterDim.z = 1;
-      attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-      attribute[1].val.programmaticStreamSerializationAllowed = 1;
-      config.attrs = attribute;
-      config.numAttrs = use_pdl() ? 2 : 1;
-      // Never launch more clusters than can be resident: the persistent loop covers the rest.
-      static int max_clusters[64][9] = {};
-      if (device < 64 && max_clusters[device][plan.cluster_k] == 0) {
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, w6a8_gemm_kernel<TN, MODE>, &config) != cudaSuccess ||
-            n < 1) {
-          (void)cudaGetLastError();
-          n = 1;
-        }
-        max_clusters[device][plan.cluster_k] = n;
+  // Programmatic dependent launch: the prologue (barriers, tensor memory, tensor-map
+  // prefetch) may run while the previous kernel on the stream drains; the kernel
+  // itself waits (griddepcontrol.wait) before it touches global memory.
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((unsigned)plan.grid);
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = C::kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  int count = 0;
+  if (CL != 0) {
+    attribute[count].id = cudaLaunchAttributeClusterDimension;
+    attribute[count].val.clusterDim.x = (unsigned)plan.cluster_k;
+    attribute[count].val.clusterDim.y = 1;
+    attribute[count].val.clusterDim.z = 1;
+    ++count;
+  }
+  if (use_pdl()) {
+    attribute[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  config.attrs = attribute;
+  config.numAttrs = count;
+  if (CL != 0) {
+    // Never launch more clusters than can be resident: the persistent loop covers the rest.
+    static int max_clusters[64][9] = {};
+    if (device < 64 && max_clusters[device][plan.cluster_k] == 0) {
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, w6a8_gemm_kernel<TN, MODE, CL>, &config) !=
+              cudaSuccess ||
+          n < 1) {
+        (void)cudaGetLastError();
+        n = 1;
       }
-      const int resident = device < 64 ? max_clusters[device][plan.cluster_k] : 1;
-      if (plan.grid / plan.cluster_k > resident) config.gridDim = dim3((unsigned)(resident * plan.cluster_k));
-      MX_CUDA(cudaLaunchKernelEx(&config, w6a8_gemm_kernel<TN, MODE>, tm_w, tm_a, args));
-      return kOk;
+      max_clusters[device][plan.cluster_k] = n;
+    }
+    const int resident = device < 64 ? max_clusters[device][plan.cluster_k] : 1;
+    if (plan.grid / plan.cluster_k > resident) {
+      config.gridDim = dim3((unsigned)(resident * plan.cluster_k));
+    }
+  }
+  MX_CUDA(cudaLaunchKernelEx(&config, w6a8_gemm_kernel<TN, MODE, CL>, tm_w, tm_a, args));
+  return kOk;
+}
+
+template <int TN, int MODE>
+int launch_tn(const CUtensorMap& tm_w, const CUtensorMap& tm_a, const KernelArgs& args,
+              const GemmPlan& plan, cudaStream_t stream) {
+  if (plan.cluster_k > 1) {
+    if constexpr (TN <= 96) {
+      return launch_variant<TN, MODE, 1>(tm_w, tm_a, args, plan, stream);
     } else {
       set_error("tile_tokens %d cannot use cluster split-K", TN);
       return kInvalidArgument;
     }
   }
-  {
-    // Programmatic dependent launch: the prologue (barriers, tensor memory, tensor-map
-    // prefetch) may run while the previous kernel on the stream drains; the kernel
-    // itself waits (griddepcontrol.wait) before it touches global memory.
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3((unsigned)plan.grid);
-    config.blockDim = dim3(kThreads);
-    config.dynamicSmemBytes = Cfg<TN, MODE>::kSmemBytes;
-    config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = attribute;
-    config.numAttrs = use_pdl() ? 1 : 0;
-    MX_CUDA(cudaLaunchKernelEx(&config, w6a8_gemm_kernel<TN, MODE>, tm_w, tm_a, args));
-  }
-  return kOk;
+  return launch_variant<TN, MODE, 0>(tm_w, tm_a, args, plan, stream);
 }
 
 template <int TN, int MODE>
 void fill_plan(GemmPlan* plan) {
-  plan->stages = Cfg<TN, MODE>::kStages;
-  plan->smem_bytes = Cfg<TN, MODE>::kSmemBytes;
+  plan->stages = Cfg<TN, MODE, 0>::kStages;
+  plan->smem_bytes = Cfg<TN, MODE, 0>::kSmemBytes;
 }
 
 int sm_count() {
@@ -1083,6 +1129,7 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
   const bool swiglu = p.mode == kGemmSwigluMxfp8;
   MX_REQUIRE(swiglu || p.out_dtype == kBF16 || p.out_dtype == kF16,
              "out_dtype must be float16 or bfloat16");
+  MX_REQUIRE((reinterpret_cast<uintptr_t>(p.out) & 15) == 0, "the output must be 16-byte aligned");
   MX_REQUIRE(!swiglu || p.out_packed_scales != nullptr || p.out_logical_scales != nullptr,
              "SwiGLU mode needs a scale output");
   if (plan.splits > 1) {
