@@ -433,8 +433,7 @@ def main() -> None:
 
     status = mx.device_status(device)
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        finish(world)
         return
 
     fp8_peak = 2.0 * float(peaks["bf16_tflops_sustained"])
@@ -483,8 +482,17 @@ def main() -> None:
         base = cpu_reference_sample(os.cpu_count() or 1)
         line["cpu_baseline"] = {key: base[key] for key in ("value", "unit", "cores", "kind", "sample")}
     print(json.dumps(line), flush=True)
+    finish(world)
+
+
+def finish(world: int) -> None:
+    """Leave a multi-rank run without tearing NCCL down: communicators that were
+    captured into CUDA graphs can block in destroy_process_group, and every rank has
+    already synchronised and reported by the time this is called."""
     if world > 1:
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
