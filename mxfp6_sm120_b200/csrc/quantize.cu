@@ -74,7 +74,7 @@ template <class T>
 __global__ void __launch_bounds__(kQuantThreads)
 quantize_mxfp8_kernel(const T* __restrict__ in, uint8_t* __restrict__ out,
                       uint8_t* __restrict__ packed, uint8_t* __restrict__ logical, int64_t rows,
-                      int k, int64_t pad_begin, int64_t pad_total) {
+                      int k, int64_t pad_begin, int64_t pad_total, bool quad_scales) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int groups = k / kScaleVec;
   const int64_t chunks = rows * (k / 8);
@@ -116,15 +116,32 @@ quantize_mxfp8_kernel(const T* __restrict__ in, uint8_t* __restrict__ out,
           w[i] = lo | (hi << 16);
         }
         reinterpret_cast<uint2*>(out)[c] = make_uint2(w[0], w[1]);
-        if ((c & 3) == 0) {
-          const int64_t group = c >> 2;
-          const uint8_t code = static_cast<uint8_t>(sbits >> 23);
-          if (logical != nullptr) logical[group] = code;
+      }
+      // Scale bytes.  Four consecutive groups of a row are four consecutive bytes in
+      // both layouts when the row holds a multiple of four groups, so lanes 0 and 16
+      // collect the codes of lanes +4, +8, +12 and store one 32-bit word each.
+      const uint32_t code = sbits >> 23;
+      if (quad_scales) {
+        uint32_t word = code;
+        word |= __shfl_down_sync(0xffffffffu, code, 4) << 8;
+        word |= __shfl_down_sync(0xffffffffu, code, 8) << 16;
+        word |= __shfl_down_sync(0xffffffffu, code, 12) << 24;
+        if (valid && (threadIdx.x & 15) == 0) {
+          const uint32_t group = static_cast<uint32_t>(c >> 2);  // fits: checked on the host
+          if (logical != nullptr) *reinterpret_cast<uint32_t*>(logical + group) = word;
           if (packed != nullptr) {
-            const int64_t row = group / groups;
-            const int g = static_cast<int>(group - row * groups);
-            packed[packed_scale_offset(row, g, groups)] = code;
+            const uint32_t row = group / static_cast<uint32_t>(groups);
+            const int g = static_cast<int>(group - row * static_cast<uint32_t>(groups));
+            *reinterpret_cast<uint32_t*>(packed + packed_scale_offset(row, g, groups)) = word;
           }
+        }
+      } else if (valid && (c & 3) == 0) {
+        const int64_t group = c >> 2;
+        if (logical != nullptr) logical[group] = static_cast<uint8_t>(code);
+        if (packed != nullptr) {
+          const int64_t row = group / groups;
+          const int g = static_cast<int>(group - row * groups);
+          packed[packed_scale_offset(row, g, groups)] = static_cast<uint8_t>(code);
         }
       }
     }
@@ -231,7 +248,8 @@ int grid_for(int64_t chunks) {
   // Enough CTAs to fill 148 SMs at 8 resident CTAs each; grid-stride beyond that.
   // Every thread takes four chunks per round.
   const int64_t want = (chunks + 4 * kQuantThreads - 1) / (4 * kQuantThreads);
-  const int64_t cap = 148 * 16;
+  // One round per thread up to a million CTAs: no ragged last round.
+  const int64_t cap = 1 << 20;
   return static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
 }
 
@@ -246,14 +264,19 @@ int quantize_mxfp8(const void* in, int dtype, int64_t rows, int64_t k, uint8_t* 
   if (packed != nullptr) padding_range(rows, k, &pad_begin, &pad_total);
   const int64_t chunks = rows * (k / 8);
   const int grid = grid_for(chunks);
+  // Word-wide scale stores need whole quads of groups per row, 4-byte aligned
+  // scale buffers and 32-bit group indices.
+  const bool quad = (k / kScaleVec) % 4 == 0 && chunks < (int64_t(1) << 33) &&
+                    (reinterpret_cast<uintptr_t>(packed) & 3) == 0 &&
+                    (reinterpret_cast<uintptr_t>(logical) & 3) == 0;
   if (dtype == kBF16) {
     quantize_mxfp8_kernel<__nv_bfloat16><<<grid, kQuantThreads, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(in), values, packed, logical, rows,
-        static_cast<int>(k), pad_begin, pad_total);
+        static_cast<int>(k), pad_begin, pad_total, quad);
   } else {
     quantize_mxfp8_kernel<__half><<<grid, kQuantThreads, 0, stream>>>(
         static_cast<const __half*>(in), values, packed, logical, rows, static_cast<int>(k),
-        pad_begin, pad_total);
+        pad_begin, pad_total, quad);
   }
   MX_CUDA(cudaGetLastError());
   return kOk;

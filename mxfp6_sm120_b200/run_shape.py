@@ -4,7 +4,8 @@
     python -m mxfp6_sm120_b200.run_shape --op quantize --m 8192 --k 5120
     python -m mxfp6_sm120_b200.run_shape --op moe --m 32
 
-Prints the mean device time per call measured with CUDA events.
+Prints the mean device time per call: ``--iters`` calls are captured in one CUDA graph
+and the replay is timed with CUDA events.
 """
 
 from __future__ import annotations
@@ -55,14 +56,21 @@ def main() -> None:
         def call():
             return layer.forward(state, hidden, logits, gate)
 
-    call()
-    torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(args.iters):
+    # Time graph replays so that host launch overhead does not hide short kernels.
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
         call()
-    stop.record()
-    torch.cuda.synchronize()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(args.iters):
+                call()
+        graph.replay()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        graph.replay()
+        stop.record(stream)
+        stream.synchronize()
     print(f"{args.op} m={args.m} n={args.n} k={args.k}: {start.elapsed_time(stop) * 1e3 / args.iters:.1f} us per call")
     print("device status", mx.device_status())
 
