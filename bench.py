@@ -271,6 +271,54 @@ def moe_layer_latency(mx, device, stream, peaks) -> dict:
             "kernels_per_layer": 9, "rows": rows}
 
 
+def moe_layer_latency_ep(mx, device, stream, world: int, rank: int) -> dict:
+    """The same layer with the 256 routed experts sharded over the ranks: all-gather
+    dispatch of the MXFP8 rows, local grouped GEMMs, all-to-all combine.  Token batches
+    are global; each rank brings batch / world tokens (batches smaller than the world
+    size are skipped).  Latency = max over ranks of the graph replay time."""
+    import torch.distributed as dist
+
+    from mxfp6_sm120_b200.ep import ExpertParallelMoe
+    from mxfp6_sm120_b200.moe_layer import MoeLayer
+
+    shape = mx.MoeShape()
+    layer = MoeLayer.random(device, shape, seed=4000)
+    moe = ExpertParallelMoe(layer)
+    del layer
+    rows = []
+    for batch in MOE_BATCHES:
+        if batch % world:
+            continue
+        local = batch // world
+        gen = torch.Generator(device=device).manual_seed(4100 + batch + rank)
+        hidden = torch.randn((local, shape.hidden), generator=gen, device=device).to(torch.bfloat16)
+        logits = torch.randn((local, shape.experts), generator=gen, device=device).to(torch.bfloat16)
+        gate = torch.randn((local,), generator=gen, device=device).to(torch.bfloat16)
+        state = moe.state(local)
+        moe.forward(state, hidden, logits, gate)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            moe.forward(state, hidden, logits, gate)
+        for _ in range(3):
+            graph.replay()
+        reps = 30 if batch <= 96 else 10
+        dist.barrier()
+        torch.cuda.synchronize(device)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for _ in range(reps):
+            graph.replay()
+        stop.record(stream)
+        stream.synchronize()
+        t = torch.tensor([start.elapsed_time(stop) * 1e3 / reps], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        rows.append({"tokens": batch, "tokens_per_rank": local, "us_warm": round(float(t.item()), 1)})
+    return {"config": f"expert parallel over {world} ranks ({shape.experts // world} experts each): "
+                      "all-gather dispatch, all-to-all combine, shared expert replicated",
+            "rows": rows}
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -430,6 +478,8 @@ def main() -> None:
         moe = None
         if not args.no_moe and world == 1:
             moe = moe_layer_latency(mx, device, stream, peaks)
+        elif not args.no_moe:
+            moe = moe_layer_latency_ep(mx, device, stream, world, rank)
 
     status = mx.device_status(device)
     if rank != 0:

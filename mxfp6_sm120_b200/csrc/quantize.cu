@@ -248,8 +248,10 @@ int grid_for(int64_t chunks) {
   // Enough CTAs to fill 148 SMs at 8 resident CTAs each; grid-stride beyond that.
   // Every thread takes four chunks per round.
   const int64_t want = (chunks + 4 * kQuantThreads - 1) / (4 * kQuantThreads);
-  // One round per thread up to a million CTAs: no ragged last round.
-  const int64_t cap = 1 << 20;
+  // Persistent once the GPU is full (4 CTAs of 256 threads fit an SM at 59 registers):
+  // CTAs then loop over rounds instead of being relaunched, and only the last of
+  // several rounds is ragged.
+  const int64_t cap = 148 * 4;
   return static_cast<int>(want < 1 ? 1 : (want > cap ? cap : want));
 }
 

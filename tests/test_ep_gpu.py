@@ -1,0 +1,69 @@
+"""Expert-parallel MoE on 2 GPUs against the single-GPU layer (skipped below 2 GPUs).
+
+Each rank is a child process (one process per GPU, NCCL).  With NVLS off and no
+rank leaving mid-step, as the pool's rules for multi-rank tests ask.
+"""
+
+from __future__ import annotations
+
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, results) -> None:
+    import torch.distributed as dist
+
+    import mxfp6_sm120_b200 as mx
+    from mxfp6_sm120_b200.ep import ExpertParallelMoe
+    from mxfp6_sm120_b200.moe_layer import MoeLayer
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    device = torch.device("cuda", rank)
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    shape = mx.MoeShape(hidden=512, intermediate=256, experts=32, topk=4)
+    layer = MoeLayer.random(device, shape, seed=7)  # same seed: identical weights on every rank
+    local_tokens = 5
+    gen = torch.Generator(device="cpu").manual_seed(11)
+    hidden = torch.randn((world * local_tokens, shape.hidden), generator=gen).to(torch.bfloat16).to(device)
+    logits = torch.randn((world * local_tokens, shape.experts), generator=gen).to(torch.bfloat16).to(device)
+    gate = torch.randn((world * local_tokens,), generator=gen).to(torch.bfloat16).to(device)
+    # single-GPU result over all tokens
+    state = layer.workspace(world * local_tokens)
+    want = layer.forward(state, hidden, logits, gate).clone()
+    # expert parallel over the two ranks
+    mine = slice(rank * local_tokens, (rank + 1) * local_tokens)
+    moe = ExpertParallelMoe(layer)
+    ep_state = moe.state(local_tokens)
+    got = moe.forward(ep_state, hidden[mine].contiguous(), logits[mine].contiguous(), gate[mine].contiguous())
+    torch.cuda.synchronize()
+    cos = torch.nn.functional.cosine_similarity(got.float().flatten(), want[mine].float().flatten(), dim=0)
+    same_ids = torch.equal(ep_state.local.topk_ids, state.workspace.topk_ids[mine])
+    results[rank] = (bool(same_ids), float(cos), mx.device_status())
+    dist.barrier()
+    torch.cuda.synchronize()
+    os._exit(0)  # no NCCL teardown: every rank has reported and is between steps
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_matches_single_gpu_layer():
+    import torch.multiprocessing as mp
+
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    for rank in range(world):
+        same_ids, cos, status = results[rank]
+        assert same_ids and cos >= 0.999 and status == 0
