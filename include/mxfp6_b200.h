@@ -170,6 +170,19 @@ int mxfp6_moe_route(const uint8_t* activation_dev, const uint8_t* logical_scales
                     int local_experts, int64_t* expert_offsets_dev, int64_t* scale_offsets_dev,
                     int32_t* cursors_dev, uint8_t* permuted_dev, uint8_t* grouped_scales_dev,
                     int32_t* inverse_permutation_dev, int32_t* source_tokens_dev, void* stream);
+/* torch.ops.mxfp6.qwen35_topk_quant_route_out (csrc/moe.cu:620-962, host :9716-10008):
+ * mxfp6_moe_topk_quant followed by mxfp6_moe_route.  Batches of at most 8 tokens
+ * (and tokens * topk <= 1024) run as ONE single-CTA kernel; larger ones as three. */
+int mxfp6_moe_topk_quant_route(const void* hidden_dev, const void* logits_dev, int64_t tokens,
+                               int hidden_size, int experts, int topk, int renormalize,
+                               uint8_t* quantized_dev, uint8_t* logical_scales_dev,
+                               uint8_t* dense_scales_dev, float* topk_weights_dev,
+                               int32_t* topk_ids_dev, const int32_t* expert_map_dev,
+                               int expert_map_size, int local_experts,
+                               int64_t* expert_offsets_dev, int64_t* scale_offsets_dev,
+                               int32_t* cursors_dev, uint8_t* permuted_dev,
+                               uint8_t* grouped_scales_dev, int32_t* inverse_permutation_dev,
+                               int32_t* source_tokens_dev, void* stream);
 /* torch.ops.mxfp6.grouped_gemm_w6a8_out (csrc/moe.cu:7551-7676): rows
  * [expert_offsets[e], expert_offsets[e+1]) of the activation times weight e
  * ([E, n, k*3/4] bytes, scales [E, n*k/32]); n % 128 == 0, k % 128 == 0.

@@ -5,6 +5,12 @@ Drop-in for the operator surface of Nekofish-L/mxfp6_sm120's ``mxfp6`` package:
 """
 
 from ._loader import load_library
+from .autotune import (
+    W6A8Config,
+    cache_directory as autotune_cache_directory,
+    is_autotune_cache_only,
+    is_autotune_enabled,
+)
 from .ops import (
     MXFP8Tensor,
     PackedMXFP6Tensor,

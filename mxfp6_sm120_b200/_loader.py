@@ -74,6 +74,12 @@ SIGNATURES: dict[str, tuple] = {
         [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
          c_void_p, c_void_p, c_void_p],
     ),
+    "mxfp6_moe_topk_quant_route": (
+        c_int,
+        [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_void_p, c_void_p, c_void_p],
+    ),
     "mxfp6_moe_route": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_int, c_int,

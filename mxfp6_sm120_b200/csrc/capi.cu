@@ -46,6 +46,9 @@ int moe_topk_quant(const void*, const void*, int64_t, int, int, int, int, uint8_
 int moe_route(const uint8_t*, const uint8_t*, const void*, int, int64_t, int, int, const int32_t*,
               int, int, int64_t*, int64_t*, int32_t*, uint8_t*, uint8_t*, int32_t*, int32_t*,
               cudaStream_t);
+int moe_topk_quant_route(const void*, const void*, int64_t, int, int, int, int, uint8_t*, uint8_t*,
+                         uint8_t*, float*, int32_t*, const int32_t*, int, int, int64_t*, int64_t*,
+                         int32_t*, uint8_t*, uint8_t*, int32_t*, int32_t*, cudaStream_t);
 int silu_mul_quant(const void*, int, int64_t, int, uint8_t*, uint8_t*, uint8_t*, const int64_t*,
                    const int64_t*, int, cudaStream_t);
 int moe_reduce(void*, const void*, int, const float*, const int32_t*, const void*, const void*, int,
@@ -438,6 +441,22 @@ int mxfp6_moe_route(const uint8_t* activation, const uint8_t* logical_scales, co
                    expert_map, expert_map_size, local_experts, expert_offsets, scale_offsets,
                    cursors, permuted, grouped_scales, inverse_permutation, source_tokens,
                    static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_moe_topk_quant_route(const void* hidden, const void* logits, int64_t tokens,
+                               int hidden_size, int experts, int topk, int renormalize,
+                               uint8_t* quantized, uint8_t* logical_scales, uint8_t* dense_scales,
+                               float* topk_weights, int32_t* topk_ids, const int32_t* expert_map,
+                               int expert_map_size, int local_experts, int64_t* expert_offsets,
+                               int64_t* scale_offsets, int32_t* cursors, uint8_t* permuted,
+                               uint8_t* grouped_scales, int32_t* inverse_permutation,
+                               int32_t* source_tokens, void* stream) {
+  return moe_topk_quant_route(hidden, logits, tokens, hidden_size, experts, topk, renormalize,
+                              quantized, logical_scales, dense_scales, topk_weights, topk_ids,
+                              expert_map, expert_map_size, local_experts, expert_offsets,
+                              scale_offsets, cursors, permuted, grouped_scales,
+                              inverse_permutation, source_tokens,
+                              static_cast<cudaStream_t>(stream));
 }
 
 int mxfp6_silu_and_mul_mxfp8(const void* input, int dtype, int64_t rows, int64_t inter,

@@ -31,57 +31,12 @@ __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
   return lo | (hi << 16);
 }
 
-// ---------------------------------------------------------------- top-k + quantize
-// One CTA per token.  All threads quantize the hidden row; warp 0 then does the
-// softmax top-k of that token's logits.
-__global__ void __launch_bounds__(256)
-topk_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16* __restrict__ logits,
-                  uint8_t* __restrict__ quantized, uint8_t* __restrict__ logical_scales,
-                  uint8_t* __restrict__ dense_scales, float* __restrict__ topk_weights,
-                  int32_t* __restrict__ topk_ids, int hidden_size, int experts, int topk,
-                  int renormalize) {
-  const int token = blockIdx.x;
-  const int groups = hidden_size / kScaleVec;
-  if (quantized != nullptr) {
-    const int chunks = hidden_size / 8;
-    const int rounds = (chunks + blockDim.x - 1) / blockDim.x;
-    for (int it = 0; it < rounds; ++it) {
-      const int c = it * blockDim.x + threadIdx.x;
-      const bool valid = c < chunks;
-      float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      if (valid) {
-        const uint4 raw =
-            __ldg(reinterpret_cast<const uint4*>(hidden + (int64_t)token * hidden_size) + c);
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          v[2 * i] = __uint_as_float(w[i] << 16);
-          v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-        }
-      }
-      float amax = 0.0f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
-      const float inv = ue8m0_inverse(sbits);
-      if (valid) {
-        const uint2 packed = make_uint2(e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
-                                        e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
-        reinterpret_cast<uint2*>(quantized + (int64_t)token * hidden_size)[c] = packed;
-        if ((c & 3) == 0) {
-          const int g = c >> 2;
-          const uint8_t code = static_cast<uint8_t>(sbits >> 23);
-          if (logical_scales != nullptr) logical_scales[(int64_t)token * groups + g] = code;
-          if (dense_scales != nullptr) dense_scales[packed_scale_offset(token, g, groups)] = code;
-        }
-      }
-    }
-  }
-  if (topk_ids == nullptr || threadIdx.x >= 32) return;
-  // ---- softmax top-k by warp 0; lane l owns experts l, l + 32, ...
-  const int lane = threadIdx.x;
+// FP32 softmax of one token's BF16 logits and k rounds of arg-max (ties to the
+// smaller id), by one full warp; lane l owns experts l, l + 32, ...
+__device__ __forceinline__ void warp_softmax_topk(const __nv_bfloat16* __restrict__ logits_row,
+                                                  int experts, int topk, int renormalize,
+                                                  float* __restrict__ weights_row,
+                                                  int32_t* __restrict__ ids_row, int lane) {
   constexpr int kPerLane = kMaxExperts / 32;
   float p[kPerLane];
   float vmax = -INFINITY;
@@ -91,7 +46,7 @@ topk_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16*
     p[i] = -INFINITY;
     const int e = lane + 32 * i;
     if (i < per_lane && e < experts) {
-      p[i] = __bfloat162float(logits[(int64_t)token * experts + e]);
+      p[i] = __bfloat162float(logits_row[e]);
       vmax = fmaxf(vmax, p[i]);
     }
   }
@@ -157,9 +112,64 @@ topk_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16*
   if (lane < topk) {
     float w = my_weight;
     if (renormalize) w = weight_sum > 0.0f ? w / weight_sum : 0.0f;
-    topk_weights[(int64_t)token * topk + lane] = w;
-    topk_ids[(int64_t)token * topk + lane] = my_id;
+    weights_row[lane] = w;
+    ids_row[lane] = my_id;
   }
+}
+
+// ---------------------------------------------------------------- top-k + quantize
+// One CTA per token.  All threads quantize the hidden row; warp 0 then does the
+// softmax top-k of that token's logits.
+__global__ void __launch_bounds__(256)
+topk_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16* __restrict__ logits,
+                  uint8_t* __restrict__ quantized, uint8_t* __restrict__ logical_scales,
+                  uint8_t* __restrict__ dense_scales, float* __restrict__ topk_weights,
+                  int32_t* __restrict__ topk_ids, int hidden_size, int experts, int topk,
+                  int renormalize) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int token = blockIdx.x;
+  const int groups = hidden_size / kScaleVec;
+  if (quantized != nullptr) {
+    const int chunks = hidden_size / 8;
+    const int rounds = (chunks + blockDim.x - 1) / blockDim.x;
+    for (int it = 0; it < rounds; ++it) {
+      const int c = it * blockDim.x + threadIdx.x;
+      const bool valid = c < chunks;
+      float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (valid) {
+        const uint4 raw =
+            __ldg(reinterpret_cast<const uint4*>(hidden + (int64_t)token * hidden_size) + c);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          v[2 * i] = __uint_as_float(w[i] << 16);
+          v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+      }
+      float amax = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
+      const float inv = ue8m0_inverse(sbits);
+      if (valid) {
+        const uint2 packed = make_uint2(e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
+                                        e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
+        reinterpret_cast<uint2*>(quantized + (int64_t)token * hidden_size)[c] = packed;
+        if ((c & 3) == 0) {
+          const int g = c >> 2;
+          const uint8_t code = static_cast<uint8_t>(sbits >> 23);
+          if (logical_scales != nullptr) logical_scales[(int64_t)token * groups + g] = code;
+          if (dense_scales != nullptr) dense_scales[packed_scale_offset(token, g, groups)] = code;
+        }
+      }
+    }
+  }
+  if (topk_ids == nullptr || threadIdx.x >= 32) return;
+  warp_softmax_topk(logits + (int64_t)token * experts, experts, topk, renormalize,
+                    topk_weights + (int64_t)token * topk, topk_ids + (int64_t)token * topk,
+                    threadIdx.x);
 }
 
 // ---------------------------------------------------------------- counts and offsets
@@ -251,6 +261,8 @@ route_scatter_kernel(const uint8_t* __restrict__ activation,
                      uint8_t* __restrict__ permuted, uint8_t* __restrict__ grouped_scales,
                      int32_t* __restrict__ inverse_permutation,
                      int32_t* __restrict__ source_tokens) {
+  // Lets a following GEMM start its prologue; it still waits for this grid to finish.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int64_t route = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (route >= routes) return;
@@ -279,6 +291,164 @@ route_scatter_kernel(const uint8_t* __restrict__ activation,
     inverse_permutation[route] = static_cast<int32_t>(row);
     if (source_tokens != nullptr) source_tokens[row] = static_cast<int32_t>(token);
   }
+}
+
+// ---------------------------------------------------------------- small-batch fusion
+// Decode-sized batches (tokens * topk <= 1024): one CTA does the whole front end of
+// the layer - MXFP8 quantization of the rows, softmax top-k, expert histogram and
+// offsets, row permutation - so that three kernel boundaries disappear.  The
+// reference fuses the same steps with a cooperative launch (csrc/moe.cu:620-962).
+constexpr int kFusedThreads = 1024;
+constexpr int kFusedMaxRoutes = 1024;
+
+__global__ void __launch_bounds__(kFusedThreads)
+topk_quant_route_small_kernel(const __nv_bfloat16* __restrict__ hidden,
+                              const __nv_bfloat16* __restrict__ logits,
+                              uint8_t* __restrict__ quantized, uint8_t* __restrict__ logical_scales,
+                              uint8_t* __restrict__ dense_scales, float* __restrict__ topk_weights,
+                              int32_t* __restrict__ topk_ids, int tokens, int hidden_size,
+                              int experts, int topk, int renormalize,
+                              const int32_t* __restrict__ expert_map, int map_size,
+                              int local_experts, int64_t* __restrict__ expert_offsets,
+                              int64_t* __restrict__ scale_offsets, int32_t* __restrict__ cursors,
+                              uint8_t* __restrict__ permuted, uint8_t* __restrict__ grouped_scales,
+                              int32_t* __restrict__ inverse_permutation,
+                              int32_t* __restrict__ source_tokens) {
+  __shared__ int counts[kMaxExperts];
+  __shared__ int starts[kMaxExperts];
+  __shared__ int scale_starts[kMaxExperts];
+  __shared__ int warp_sums[2][32];
+  __shared__ int route_expert[kFusedMaxRoutes];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int groups = hidden_size / kScaleVec;
+  for (int e = tid; e < kMaxExperts; e += kFusedThreads) counts[e] = 0;
+  // ---- quantize every row (4 lanes per 32-value group)
+  const int chunks = tokens * (hidden_size / 8);
+  const int rounds = (chunks + kFusedThreads - 1) / kFusedThreads;
+  for (int it = 0; it < rounds; ++it) {
+    const int c = it * kFusedThreads + tid;
+    const bool valid = c < chunks;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (valid) {
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(hidden) + c);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
+    const float inv = ue8m0_inverse(sbits);
+    if (valid) {
+      reinterpret_cast<uint2*>(quantized)[c] =
+          make_uint2(e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
+                     e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
+      if ((c & 3) == 0) {
+        const int group = c >> 2;
+        const int token = group / groups;
+        const int g = group - token * groups;
+        const uint8_t code = static_cast<uint8_t>(sbits >> 23);
+        logical_scales[group] = code;
+        if (dense_scales != nullptr) dense_scales[packed_scale_offset(token, g, groups)] = code;
+      }
+    }
+  }
+  // ---- top-k: one warp per token
+  for (int token = warp; token < tokens; token += kFusedThreads / 32) {
+    warp_softmax_topk(logits + (int64_t)token * experts, experts, topk, renormalize,
+                      topk_weights + (int64_t)token * topk, topk_ids + (int64_t)token * topk, lane);
+  }
+  __syncthreads();  // rows, scales and ids written by this CTA are visible to all its threads
+  // ---- histogram of local experts
+  const int routes = tokens * topk;
+  for (int r = tid; r < routes; r += kFusedThreads) {
+    const int e = local_expert(static_cast<int64_t>(topk_ids[r]), expert_map, map_size, local_experts);
+    route_expert[r] = e;
+    if (e >= 0) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  // ---- exclusive prefix sums of counts and 128-padded counts (one expert per thread)
+  const int cnt = tid < local_experts ? counts[tid] : 0;
+  const int pcnt = (cnt + kAtomRows - 1) / kAtomRows * kAtomRows;
+  int incl = cnt, pincl = pcnt;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, incl, d);
+    const int b = __shfl_up_sync(0xffffffffu, pincl, d);
+    if (lane >= d) {
+      incl += a;
+      pincl += b;
+    }
+  }
+  if (lane == 31) {
+    warp_sums[0][warp] = incl;
+    warp_sums[1][warp] = pincl;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int a = warp_sums[0][lane], b = warp_sums[1][lane];
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int ua = __shfl_up_sync(0xffffffffu, a, d);
+      const int ub = __shfl_up_sync(0xffffffffu, b, d);
+      if (lane >= d) {
+        a += ua;
+        b += ub;
+      }
+    }
+    warp_sums[0][lane] = a;
+    warp_sums[1][lane] = b;
+  }
+  __syncthreads();
+  const int base = warp > 0 ? warp_sums[0][warp - 1] : 0;
+  const int pbase = warp > 0 ? warp_sums[1][warp - 1] : 0;
+  if (tid < local_experts) {
+    starts[tid] = base + incl - cnt;
+    scale_starts[tid] = pbase + pincl - pcnt;
+    expert_offsets[tid] = base + incl - cnt;
+    scale_offsets[tid] = pbase + pincl - pcnt;
+    if (tid == local_experts - 1) {
+      expert_offsets[local_experts] = base + incl;
+      scale_offsets[local_experts] = pbase + pincl;
+    }
+    counts[tid] = 0;  // reused as the per-expert cursor
+  }
+  __syncthreads();
+  // ---- permutation: one warp per route
+  for (int route = warp; route < routes; route += kFusedThreads / 32) {
+    const int e = route_expert[route];
+    if (e < 0) {
+      if (lane == 0) inverse_permutation[route] = -1;
+      continue;
+    }
+    int local = 0;
+    if (lane == 0) local = atomicAdd(&counts[e], 1);
+    local = __shfl_sync(0xffffffffu, local, 0);
+    const int row = starts[e] + local;
+    const int token = route / topk;
+    const uint4* src = reinterpret_cast<const uint4*>(quantized + (int64_t)token * hidden_size);
+    uint4* dst = reinterpret_cast<uint4*>(permuted + (int64_t)row * hidden_size);
+    for (int i = lane; i < hidden_size / 16; i += 32) dst[i] = src[i];
+    const int srow = scale_starts[e] + local;
+    for (int g = lane; g < groups; g += 32) {
+      grouped_scales[packed_scale_offset(srow, g, groups)] = logical_scales[(int64_t)token * groups + g];
+    }
+    if (lane == 0) {
+      inverse_permutation[route] = row;
+      if (source_tokens != nullptr) source_tokens[row] = token;
+    }
+  }
+  // The cursors end at the per-expert counts, as after the multi-kernel path.
+  __syncthreads();
+  if (cursors != nullptr && tid < local_experts) cursors[tid] = counts[tid];
 }
 
 // ---------------------------------------------------------------- SiLU * mul + MXFP8
@@ -479,6 +649,46 @@ int moe_route(const uint8_t* activation, const uint8_t* logical_scales, const vo
         local_experts, expert_offsets, scale_offsets, cursors, permuted, grouped_scales,
         inverse_permutation, source_tokens);
   }
+  MX_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int moe_topk_quant_route(const void* hidden, const void* logits, int64_t tokens, int hidden_size,
+                         int experts, int topk, int renormalize, uint8_t* quantized,
+                         uint8_t* logical_scales, uint8_t* dense_scales, float* topk_weights,
+                         int32_t* topk_ids, const int32_t* expert_map, int map_size,
+                         int local_experts, int64_t* expert_offsets, int64_t* scale_offsets,
+                         int32_t* cursors, uint8_t* permuted, uint8_t* grouped_scales,
+                         int32_t* inverse_permutation, int32_t* source_tokens,
+                         cudaStream_t stream) {
+  MX_REQUIRE(tokens > 0 && topk > 0, "tokens and topk must be positive");
+  // One CTA copies every routed row, so the fusion only pays for a handful of tokens.
+  const bool small = tokens * topk <= kFusedMaxRoutes && tokens <= 8;
+  if (!small) {
+    if (int rc = moe_topk_quant(hidden, logits, tokens, hidden_size, experts, topk, renormalize,
+                                quantized, logical_scales, dense_scales, topk_weights, topk_ids,
+                                stream))
+      return rc;
+    return moe_route(quantized, logical_scales, topk_ids, 0, tokens, topk, hidden_size, expert_map,
+                     map_size, local_experts, expert_offsets, scale_offsets, cursors, permuted,
+                     grouped_scales, inverse_permutation, source_tokens, stream);
+  }
+  MX_REQUIRE(hidden && logits && quantized && logical_scales && topk_weights && topk_ids &&
+                 expert_offsets && scale_offsets && permuted && grouped_scales &&
+                 inverse_permutation,
+             "routing buffers must not be null");
+  MX_REQUIRE(hidden_size > 0 && hidden_size % kScaleVec == 0, "hidden size must be a multiple of 32");
+  MX_REQUIRE(experts > 0 && experts <= kMaxExperts && local_experts > 0 &&
+                 local_experts <= kMaxExperts,
+             "experts must be in [1, %d]", kMaxExperts);
+  MX_REQUIRE(topk <= kMaxTopk && topk <= experts, "topk must be in [1, %d]", kMaxTopk);
+  MX_REQUIRE(aligned16(hidden) && aligned16(quantized) && aligned16(permuted),
+             "row buffers must be 16-byte aligned");
+  topk_quant_route_small_kernel<<<1, kFusedThreads, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(hidden), static_cast<const __nv_bfloat16*>(logits),
+      quantized, logical_scales, dense_scales, topk_weights, topk_ids, (int)tokens, hidden_size,
+      experts, topk, renormalize, expert_map, map_size, local_experts, expert_offsets,
+      scale_offsets, cursors, permuted, grouped_scales, inverse_permutation, source_tokens);
   MX_CUDA(cudaGetLastError());
   return kOk;
 }

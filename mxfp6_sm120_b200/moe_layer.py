@@ -13,7 +13,7 @@ from dataclasses import dataclass
 import torch
 
 from .ops import PackedMXFP6Tensor, quantize_mxfp6
-from .moe_ops import qwen35_route_mxfp8_out, qwen35_topk_quant_out
+from .moe_ops import qwen35_topk_quant_route_out
 from .qwen35 import (
     MoeShape,
     Qwen35GroupedWorkspace,
@@ -89,8 +89,11 @@ class MoeLayer:
         the one graph."""
         e, i, h = self.local_experts, self.shape.intermediate, self.shape.hidden
         ws = state.workspace
-        qwen35_topk_quant_out(ws.quantized, ws.input_scales, ws.packed_input_scales, ws.topk_weights,
-                              ws.topk_ids, hidden, router_logits, renormalize=True)
+        qwen35_topk_quant_route_out(
+            ws.quantized, ws.input_scales, ws.packed_input_scales, ws.topk_weights, ws.topk_ids,
+            ws.permuted, ws.grouped_input_scales, ws.expert_cursors, ws.expert_offsets,
+            ws.scale_offsets, ws.inverse_permutation, hidden, router_logits,
+            source_tokens=ws.source_tokens, renormalize=True, expert_map=self.expert_map)
         shared_out = None
         overlap = with_shared and state.side_stream is not None
         if overlap:
@@ -100,10 +103,6 @@ class MoeLayer:
             with torch.cuda.stream(state.side_stream):
                 shared_out = shared_expert_out(state.shared, ws, self.shared_w1, self.shared_w2)
                 state.join.record(state.side_stream)
-        qwen35_route_mxfp8_out(ws.quantized, ws.input_scales, ws.topk_ids, ws.permuted,
-                               ws.grouped_input_scales, ws.expert_cursors, ws.expert_offsets,
-                               ws.scale_offsets, ws.inverse_permutation,
-                               source_tokens=ws.source_tokens, expert_map=self.expert_map)
         _grouped_experts_out(ws, self.w1.values.view(e, 2 * i, h * 3 // 4), self.w1.scales,
                              self.w2.values.view(e, h, i * 3 // 4), self.w2.scales)
         if overlap:

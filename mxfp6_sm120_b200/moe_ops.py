@@ -395,12 +395,49 @@ def qwen35_topk_quant_route_out(
     fused = grouped_output is not None
     if fused != (weight is not None) or fused != (weight_scales is not None):
         raise ValueError("grouped_output, weight, and weight_scales must be provided together")
-    qwen35_topk_quant_out(quantized, logical_scales, dense_scales, topk_weights, topk_ids, hidden,
-                          routed_logits, renormalize)
-    qwen35_route_mxfp8_out(quantized, logical_scales, topk_ids, permuted_activation,
-                           grouped_scales, expert_cursors, expert_offsets, scale_offsets,
-                           inverse_permutation, source_tokens=source_tokens,
-                           expert_map=expert_map)
+    if (
+        hidden.device.type != "cuda"
+        or hidden.dtype != torch.bfloat16
+        or hidden.ndim != 2
+        or hidden.shape[1] % SCALE_VECTOR_SIZE
+        or not hidden.is_contiguous()
+    ):
+        raise ValueError("hidden must be contiguous CUDA bfloat16 [B,H] with H divisible by 32")
+    batch, width = (int(v) for v in hidden.shape)
+    experts = int(routed_logits.shape[1])
+    topk = int(topk_ids.shape[1])
+    routes = batch * topk
+    local_experts = expert_offsets.numel() - 1
+    expected = (
+        (quantized, (batch, width), "quantized"),
+        (logical_scales, (batch, width // SCALE_VECTOR_SIZE), "logical_scales"),
+        (topk_weights, (batch, topk), "topk_weights"),
+        (topk_ids, (batch, topk), "topk_ids"),
+        (routed_logits, (batch, experts), "routed_logits"),
+        (permuted_activation, (routes, width), "permuted_activation"),
+        (inverse_permutation, (routes,), "inverse_permutation"),
+    )
+    for tensor, shape, name in expected:
+        if tensor.device != hidden.device or tuple(tensor.shape) != shape or not tensor.is_contiguous():
+            raise ValueError(f"{name} must be contiguous CUDA {tuple(shape)}")
+    if topk_ids.dtype != torch.int32 or topk_weights.dtype != torch.float32:
+        raise ValueError("topk_ids must be int32 and topk_weights float32")
+    if not isinstance(renormalize, bool):
+        raise TypeError("renormalize must be a bool")
+    _require_sm100(hidden.device)
+    load_library()
+    with torch.cuda.device(hidden.device):
+        check(
+            library().mxfp6_moe_topk_quant_route(
+                hidden.data_ptr(), routed_logits.data_ptr(), batch, width, experts, topk,
+                int(renormalize), _as_u8(quantized).data_ptr(), logical_scales.data_ptr(),
+                dense_scales.data_ptr(), topk_weights.data_ptr(), topk_ids.data_ptr(),
+                _ptr(expert_map), 0 if expert_map is None else expert_map.numel(), local_experts,
+                expert_offsets.data_ptr(), scale_offsets.data_ptr(), expert_cursors.data_ptr(),
+                _as_u8(permuted_activation).data_ptr(), grouped_scales.data_ptr(),
+                inverse_permutation.data_ptr(), _ptr(source_tokens), _stream(hidden.device),
+            )
+        )
     if fused:
         grouped_gemm_w6a8_out(grouped_output, permuted_activation, grouped_scales, weight,
                               weight_scales, expert_offsets, scale_offsets)
