@@ -33,11 +33,11 @@ __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
 
 // FP32 softmax of one token's BF16 logits and k rounds of arg-max (ties to the
 // smaller id), by one full warp; lane l owns experts l, l + 32, ...
-__device__ __forceinline__ void warp_softmax_topk(const __nv_bfloat16* __restrict__ logits_row,
-                                                  int experts, int topk, int renormalize,
-                                                  float* __restrict__ weights_row,
-                                                  int32_t* __restrict__ ids_row, int lane) {
-  constexpr int kPerLane = kMaxExperts / 32;
+template <int kPerLane>
+__device__ __forceinline__ void warp_softmax_topk_n(const __nv_bfloat16* __restrict__ logits_row,
+                                                    int experts, int topk, int renormalize,
+                                                    float* __restrict__ weights_row,
+                                                    int32_t* __restrict__ ids_row, int lane) {
   float p[kPerLane];
   float vmax = -INFINITY;
   const int per_lane = (experts + 31) / 32;
@@ -117,28 +117,43 @@ __device__ __forceinline__ void warp_softmax_topk(const __nv_bfloat16* __restric
   }
 }
 
+// Up to 256 experts need 8 values per lane; the general case 32.
+__device__ __forceinline__ void warp_softmax_topk(const __nv_bfloat16* __restrict__ logits_row,
+                                                  int experts, int topk, int renormalize,
+                                                  float* __restrict__ weights_row,
+                                                  int32_t* __restrict__ ids_row, int lane) {
+  if (experts <= 256) {
+    warp_softmax_topk_n<8>(logits_row, experts, topk, renormalize, weights_row, ids_row, lane);
+  } else {
+    warp_softmax_topk_n<kMaxExperts / 32>(logits_row, experts, topk, renormalize, weights_row,
+                                          ids_row, lane);
+  }
+}
+
 // ---------------------------------------------------------------- top-k + quantize
-// One CTA per token.  All threads quantize the hidden row; warp 0 then does the
-// softmax top-k of that token's logits.
+// One CTA per `tokens_per_cta` tokens (1 for decode batches, 8 otherwise).  All
+// threads quantize the rows; then one warp per token does the softmax top-k.
 __global__ void __launch_bounds__(256)
 topk_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16* __restrict__ logits,
                   uint8_t* __restrict__ quantized, uint8_t* __restrict__ logical_scales,
                   uint8_t* __restrict__ dense_scales, float* __restrict__ topk_weights,
-                  int32_t* __restrict__ topk_ids, int hidden_size, int experts, int topk,
-                  int renormalize) {
+                  int32_t* __restrict__ topk_ids, int tokens, int tokens_per_cta, int hidden_size,
+                  int experts, int topk, int renormalize) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int token = blockIdx.x;
+  const int first = blockIdx.x * tokens_per_cta;
+  const int count = min(tokens_per_cta, tokens - first);
   const int groups = hidden_size / kScaleVec;
   if (quantized != nullptr) {
-    const int chunks = hidden_size / 8;
+    const int row_chunks = hidden_size / 8;
+    const int chunks = count * row_chunks;
     const int rounds = (chunks + blockDim.x - 1) / blockDim.x;
     for (int it = 0; it < rounds; ++it) {
       const int c = it * blockDim.x + threadIdx.x;
       const bool valid = c < chunks;
       float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      const int64_t gc = (int64_t)first * row_chunks + c;  // chunk index in the whole matrix
       if (valid) {
-        const uint4 raw =
-            __ldg(reinterpret_cast<const uint4*>(hidden + (int64_t)token * hidden_size) + c);
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(hidden) + gc);
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -154,11 +169,12 @@ topk_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16*
       const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
       const float inv = ue8m0_inverse(sbits);
       if (valid) {
-        const uint2 packed = make_uint2(e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
-                                        e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
-        reinterpret_cast<uint2*>(quantized + (int64_t)token * hidden_size)[c] = packed;
+        reinterpret_cast<uint2*>(quantized)[gc] =
+            make_uint2(e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
+                       e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
         if ((c & 3) == 0) {
-          const int g = c >> 2;
+          const int token = first + c / row_chunks;
+          const int g = (c % row_chunks) >> 2;
           const uint8_t code = static_cast<uint8_t>(sbits >> 23);
           if (logical_scales != nullptr) logical_scales[(int64_t)token * groups + g] = code;
           if (dense_scales != nullptr) dense_scales[packed_scale_offset(token, g, groups)] = code;
@@ -166,10 +182,13 @@ topk_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16*
       }
     }
   }
-  if (topk_ids == nullptr || threadIdx.x >= 32) return;
-  warp_softmax_topk(logits + (int64_t)token * experts, experts, topk, renormalize,
-                    topk_weights + (int64_t)token * topk, topk_ids + (int64_t)token * topk,
-                    threadIdx.x);
+  if (topk_ids == nullptr) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int t = warp; t < count; t += blockDim.x >> 5) {
+    const int token = first + t;
+    warp_softmax_topk(logits + (int64_t)token * experts, experts, topk, renormalize,
+                      topk_weights + (int64_t)token * topk, topk_ids + (int64_t)token * topk, lane);
+  }
 }
 
 // ---------------------------------------------------------------- counts and offsets
@@ -604,10 +623,12 @@ int moe_topk_quant(const void* hidden, const void* logits, int64_t tokens, int h
     MX_REQUIRE(experts > 0 && experts <= kMaxExperts, "experts must be in [1, %d]", kMaxExperts);
     MX_REQUIRE(topk > 0 && topk <= kMaxTopk && topk <= experts, "topk must be in [1, %d]", kMaxTopk);
   }
-  topk_quant_kernel<<<(unsigned)tokens, 256, 0, stream>>>(
+  const int tokens_per_cta = tokens <= 148 ? 1 : 8;
+  const unsigned grid = (unsigned)((tokens + tokens_per_cta - 1) / tokens_per_cta);
+  topk_quant_kernel<<<grid, 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(hidden), static_cast<const __nv_bfloat16*>(logits),
-      quantized, logical_scales, dense_scales, topk_weights, topk_ids, hidden_size, experts, topk,
-      renormalize);
+      quantized, logical_scales, dense_scales, topk_weights, topk_ids, (int)tokens, tokens_per_cta,
+      hidden_size, experts, topk, renormalize);
   MX_CUDA(cudaGetLastError());
   return kOk;
 }
