@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define MXFP6_B200_ABI_VERSION 1
+#define MXFP6_B200_ABI_VERSION 2
 
 #define MXFP6_DTYPE_F16 0
 #define MXFP6_DTYPE_BF16 1
@@ -127,15 +127,22 @@ int mxfp6_gemm_w6a8_static_scratch(const uint8_t* a_values_dev, const uint8_t* a
                                    int64_t m, int64_t n, int64_t k, float alpha, void* out_dev,
                                    int out_dtype, void* stream);
 /* Plan query: fills tile_tokens, scratch splits, stages, grid, partial bytes, counter
- * bytes, cluster split factor. */
+ * bytes, cluster split factor, and 1 when the two-CTA kernel runs the problem. */
 int mxfp6_gemm_w6a8_plan(int64_t m, int64_t n, int64_t k, int tile_tokens, int splits,
-                         int64_t out_plan[7]);
+                         int64_t out_plan[8]);
 /* How launches with too few tiles split K (the stand-in for the reference's
  * MXFP6_STREAM_K switch, csrc/torch_extension.cu:35-57): 1 = thread-block clusters
  * that reduce through distributed shared memory (default, no scratch), 2 = FP32
  * partial tiles in the scratch arena, 3 = never split. */
 int mxfp6_set_split_k_mode(int mode);
 int mxfp6_get_split_k_mode(void);
+/* Dense launches with m > 128 and n % 256 == 0 run on CTA pairs (tcgen05 cta_group::2:
+ * 256 weight rows per tile, each CTA stages half of the activation tile); 0 keeps them
+ * on the single-CTA kernel.  Default 1.  Results are bit-identical either way.  No
+ * reference counterpart: the reference picks kernels in its autotuner,
+ * mxfp6_sm120/autotune.py:18-60. */
+int mxfp6_set_cta_pair_mode(int enabled);
+int mxfp6_get_cta_pair_mode(void);
 /* torch.ops.mxfp6.gemm_from_float (csrc/torch_extension.cu:1869-1925): quantize the
  * FP16/BF16 activation to MXFP8 into caller-provided staging buffers
  * (m*k bytes and mxfp6_packed_scale_bytes(m, k) bytes), then run the GEMM. */

@@ -31,6 +31,8 @@ from .ops import (
     gemm_w6a8_plan,
     is_available,
     is_stream_k_enabled,
+    set_cta_pair_mode,
+    is_cta_pair_enabled,
     set_split_k_mode,
     is_tuned_shape,
     pack_fp6,

@@ -64,6 +64,8 @@ SIGNATURES: dict[str, tuple] = {
     "mxfp6_gemm_w6a8_plan": (c_int, [c_int64, c_int64, c_int64, c_int, c_int, _I64P]),
     "mxfp6_set_split_k_mode": (c_int, [c_int]),
     "mxfp6_get_split_k_mode": (c_int, []),
+    "mxfp6_set_cta_pair_mode": (c_int, [c_int]),
+    "mxfp6_get_cta_pair_mode": (c_int, []),
     "mxfp6_gemm_from_float": (
         c_int,
         [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p, c_int,

@@ -237,6 +237,13 @@ int mxfp6_set_split_k_mode(int mode) {
 }
 int mxfp6_get_split_k_mode(void) { return default_split_mode(); }
 
+int mxfp6_set_cta_pair_mode(int enabled) {
+  set_cta_pair_mode(enabled);
+  return kOk;
+}
+
+int mxfp6_get_cta_pair_mode(void) { return cta_pair_mode(); }
+
 int mxfp6_b200_set_trace_buffer(void* trace_dev) {
   set_trace_buffer(static_cast<long long*>(trace_dev));
   return kOk;
@@ -334,7 +341,7 @@ int mxfp6_gemm_w6a8_static_scratch(const uint8_t* a_values, const uint8_t* a_sca
 }
 
 int mxfp6_gemm_w6a8_plan(int64_t m, int64_t n, int64_t k, int tile_tokens, int splits,
-                         int64_t out_plan[7]) {
+                         int64_t out_plan[8]) {
   MX_REQUIRE(out_plan != nullptr, "out_plan must not be null");
   GemmProblem p;
   if (int rc = dense_problem(&p, nullptr, nullptr, nullptr, nullptr, m, n, k, 1.0f, nullptr,
@@ -351,6 +358,7 @@ int mxfp6_gemm_w6a8_plan(int64_t m, int64_t n, int64_t k, int tile_tokens, int s
   out_plan[4] = (int64_t)((plan.partial_bytes + 255) & ~size_t(255));
   out_plan[5] = (int64_t)plan.counter_bytes;
   out_plan[6] = plan.cluster_k;
+  out_plan[7] = plan.cta_pair;
   return kOk;
 }
 

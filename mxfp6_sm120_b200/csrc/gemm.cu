@@ -858,8 +858,11 @@ int make_map(CUtensorMap* map, CUtensorMapDataType type, const void* base, uint6
   const cuuint64_t strides[1] = {row_stride_bytes};
   const cuuint32_t box[2] = {box_inner, box_rows};
   const cuuint32_t estr[2] = {1, 1};
+  // 32-bit maps describe rows of packed scale atoms (512 bytes each), copied unswizzled.
   const CUresult rc = fn(map, type, 2, const_cast<void*>(base), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         type == CU_TENSOR_MAP_DATA_TYPE_UINT32 ? CU_TENSOR_MAP_SWIZZLE_NONE
+                                                                : CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) {
     set_error("cuTensorMapEncodeTiled failed with CUresult %d (inner=%llu rows=%llu stride=%llu)",
@@ -1020,6 +1023,26 @@ int sm_count() {
 
 }  // namespace
 
+// Cached 2-D tensor map (128-byte swizzle, 128-element inner box) for other
+// translation units of the library.
+int make_tensor_map_2d(CUtensorMap* out, int type, const void* base, uint64_t inner, uint64_t rows,
+                       uint64_t stride, uint32_t box_rows) {
+  return cached_map(out, (CUtensorMapDataType)type, base, inner, rows, stride, box_rows);
+}
+
+bool pair_kernel_applies(const GemmProblem& p, int tile_tokens);
+int plan_w6a8_pair(const GemmProblem& p, int sms, GemmPlan* plan);
+int launch_w6a8_pair(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream);
+static int g_pair_mode = -1;  // -1: read MXFP6_B200_PAIR once; 0 off; 1 on
+void set_cta_pair_mode(int enabled) { g_pair_mode = enabled != 0 ? 1 : 0; }
+int cta_pair_mode() {
+  if (g_pair_mode < 0) {
+    const char* env = std::getenv("MXFP6_B200_PAIR");
+    g_pair_mode = (env != nullptr && env[0] == '0') ? 0 : 1;
+  }
+  return g_pair_mode;
+}
+
 int plan_w6a8(const GemmProblem& p, GemmPlan* plan) {
   MX_REQUIRE(p.m_total > 0, "m must be positive; got %lld", (long long)p.m_total);
   MX_REQUIRE(p.n > 0 && p.n % 8 == 0, "n must be a positive multiple of 8; got %d", p.n);
@@ -1027,6 +1050,10 @@ int plan_w6a8(const GemmProblem& p, GemmPlan* plan) {
   MX_REQUIRE(p.groups >= 1 && p.groups <= kMaxGroups, "groups must be in [1, %d]", kMaxGroups);
   MX_REQUIRE(p.groups == 1 || p.n % 128 == 0, "grouped weights need n %% 128 == 0");
   const bool grouped = p.expert_offsets != nullptr;
+  if (!grouped && p.splits <= 1 && p.cluster_k <= 1 && cta_pair_mode() == 1 &&
+      pair_kernel_applies(p, p.tile_tokens)) {
+    return plan_w6a8_pair(p, sm_count(), plan);
+  }
   int tn = p.tile_tokens;
   if (tn == 0) {
     // Rows per group that a tile should cover.
@@ -1150,6 +1177,7 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
                "split-K scratch is missing or too small (%zu + %zu bytes needed)",
                plan.partial_bytes, plan.counter_bytes);
   }
+  if (plan.cta_pair != 0) return launch_w6a8_pair(p, plan, stream);
   int device = 0;
   MX_CUDA(cudaGetDevice(&device));
   CUtensorMap tm_w, tm_a;
@@ -1216,6 +1244,7 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
 }
 
 void set_trace_buffer(long long* ptr) { g_trace = ptr; }
+long long* trace_buffer() { return g_trace; }
 void set_default_split_mode(int mode) { g_split_mode = (mode >= 1 && mode <= 3) ? mode : 1; }
 int default_split_mode() { return g_split_mode; }
 

@@ -61,6 +61,7 @@ struct GemmPlan {
   int tile_tokens = 0;  // activation rows per tile (MMA N)
   int splits = 1;      // scratch-arena split-K factor
   int cluster_k = 1;   // cluster split-K factor (CTAs per cluster)
+  int cta_pair = 0;    // 1: the two-CTA (cta_group::2) kernel computes 256-feature tiles
   int stages = 0;
   int grid = 0;
   size_t smem_bytes = 0;
@@ -80,6 +81,10 @@ int default_split_mode();
 // Diagnostics: CTA 0 of later launches writes [3][256] clock64 stamps (producer
 // issue, stage ready at the MMA warp, stage committed) to this device buffer.
 void set_trace_buffer(long long* ptr);
+long long* trace_buffer();
+// Two-CTA kernel for dense store-mode launches with m > 128 and n % 256 == 0 (default on).
+void set_cta_pair_mode(int enabled);
+int cta_pair_mode();
 
 // GEMM whose split-K scratch and status word live in a fixed array inside the
 // library image, for callers that must not allocate device memory.

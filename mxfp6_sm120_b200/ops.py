@@ -150,6 +150,15 @@ def set_split_k_mode(mode: str) -> None:
     check(library().mxfp6_set_split_k_mode(_SPLIT_MODES[mode]))
 
 
+def set_cta_pair_mode(enabled: bool) -> None:
+    """Run dense launches with m > 128 and n % 256 == 0 on CTA pairs (default) or not."""
+    check(library().mxfp6_set_cta_pair_mode(1 if enabled else 0))
+
+
+def is_cta_pair_enabled() -> bool:
+    return library().mxfp6_get_cta_pair_mode() == 1
+
+
 def is_stream_k_enabled() -> bool:
     """Whether split-K uses the workspace arena (the reference's MXFP6_STREAM_K switch)."""
     return library().mxfp6_get_split_k_mode() == 2
@@ -578,10 +587,10 @@ def quantize_mxfp6(input: torch.Tensor) -> PackedMXFP6Tensor:
 def gemm_w6a8_plan(m: int, n: int, k: int, tile_tokens: int = 0, splits: int = 0) -> dict[str, int]:
     """Tile/split-K choice the library makes for a dense problem (host arithmetic)."""
     _validate_problem(m, n, k)
-    plan = (ctypes.c_int64 * 7)()
+    plan = (ctypes.c_int64 * 8)()
     check(library().mxfp6_gemm_w6a8_plan(m, n, k, tile_tokens, splits, plan))
     keys = ("tile_tokens", "splits", "stages", "grid", "partial_bytes", "counter_bytes",
-            "cluster_k")
+            "cluster_k", "cta_pair")
     return dict(zip(keys, (int(v) for v in plan)))
 
 

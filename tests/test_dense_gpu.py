@@ -323,3 +323,38 @@ def test_cluster_split_k_matches_scratch_split_and_single_pass(mx):
             mx.set_split_k_mode("cluster")
         assert _rel_fro(outs[mode], want) <= GEMM_REL_FRO, (mode, plan)
     assert mx.gemm_w6a8_plan(24, 5120, 6144)["cluster_k"] == 3
+
+
+@pytest.mark.parametrize("m,n,k,tile", [(129, 256, 128, 0), (200, 1024, 2048, 128), (700, 1024, 2048, 256),
+                                        (1500, 5120, 1024, 0), (1500, 5120, 1024, 192)])
+def test_cta_pair_kernel_equals_single_cta_kernel(mx, m, n, k, tile):
+    """The two-CTA kernel (256 weight rows per tile) and the single-CTA kernel add the
+    same products in the same K order: outputs are bit-identical, and both meet the
+    GEMM tolerance against the oracle."""
+    gen = _cpu_gen(m + n + k + tile)
+    a = torch.randn((m, k), generator=gen).to(torch.bfloat16)
+    w = (torch.randn((n, k), generator=gen) * 0.02).to(torch.bfloat16)
+    act, wgt, (a_q, a_s, w_q, w_s) = _packed_operands(mx, a, w)
+    assert mx.is_cta_pair_enabled()
+    plan = mx.gemm_w6a8_plan(m, n, k, tile)
+    assert plan["cta_pair"] == 1 and plan["tile_tokens"] in (128, 192, 256)
+    paired = mx.gemm_w6a8_config(act, wgt, out_dtype=torch.bfloat16, tile_tokens=tile)
+    half = mx.gemm_w6a8_config(act, wgt, 0.25, out_dtype=torch.float16, tile_tokens=tile)
+    mx.set_cta_pair_mode(False)
+    try:
+        assert mx.gemm_w6a8_plan(m, n, k, tile)["cta_pair"] == 0
+        single = mx.gemm_w6a8_config(act, wgt, out_dtype=torch.bfloat16, tile_tokens=tile)
+        single_half = mx.gemm_w6a8_config(act, wgt, 0.25, out_dtype=torch.float16, tile_tokens=tile)
+    finally:
+        mx.set_cta_pair_mode(True)
+    assert torch.equal(paired, single) and torch.equal(half, single_half)
+    want = o.gemm_w6a8(a_q, a_s, w_q, w_s, out_dtype=torch.bfloat16)
+    assert _rel_fro(paired, want) <= GEMM_REL_FRO
+    assert mx.device_status() == 0
+
+
+def test_cta_pair_kernel_is_not_planned_outside_its_shapes(mx):
+    assert mx.gemm_w6a8_plan(128, 1024, 2048)["cta_pair"] == 0      # one tile of tokens
+    assert mx.gemm_w6a8_plan(512, 1000, 1024)["cta_pair"] == 0      # n not a multiple of 256
+    assert mx.gemm_w6a8_plan(512, 1024, 2048, 64)["cta_pair"] == 0  # tile the pair kernel lacks
+    assert mx.gemm_w6a8_plan(512, 1024, 2048)["cta_pair"] == 1
