@@ -1058,19 +1058,27 @@ int plan_w6a8(const GemmProblem& p, GemmPlan* plan) {
   if (tn == 0) {
     // Rows per group that a tile should cover.
     const int64_t rows = grouped ? (p.m_total + p.groups - 1) / p.groups : p.m_total;
-    if (!grouped && rows <= 16) tn = 16;
-    else if (!grouped && rows <= 32) tn = 32;
+    if (grouped) {
+      // Group sizes are device data; the mean is all the host knows.  A tile somewhat
+      // wider than the mean lets most groups finish in one row tile (measured with 256
+      // experts, top-8: 87 us at 192 against 117 us at 128 for a mean of 128 rows).
+      tn = rows <= 48 ? 64 : rows <= 96 ? 128 : 192;
+    } else if (rows <= 16) tn = 16;
+    else if (rows <= 32) tn = 32;
     else if (rows <= 64) tn = 64;
-    else if (!grouped && rows <= 96) tn = 96;
+    else if (rows <= 96) tn = 96;
     else if (rows <= 128) tn = 128;
-    else if (!grouped && rows % 256 == 0 && p.k >= 12288) tn = 256;
-    else if (!grouped) tn = 192;
-    else tn = 128;
+    else if (rows % 256 == 0 && p.k >= 12288) tn = 256;
+    else tn = 192;
   }
   const bool swiglu = p.mode == kGemmSwigluMxfp8;
   if (swiglu) {
     MX_REQUIRE(p.n % 128 == 0, "SwiGLU mode needs the intermediate size to be a multiple of 128");
     MX_REQUIRE(p.splits <= 1, "SwiGLU mode does not split K");
+    // Grouped: the SwiGLU epilogue of a 128-token tile has a single accumulator pair and
+    // is not hidden by the next tile; 64-token tiles are double buffered (169 us against
+    // 222 us per layer at 4096 tokens).
+    if (grouped && p.tile_tokens == 0) tn = 64;
     if (tn > 128) tn = 128;
     if (tn == 96) tn = 128;
     switch (tn) {

@@ -147,37 +147,66 @@ topk_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16*
     const int row_chunks = hidden_size / 8;
     const int chunks = count * row_chunks;
     const int rounds = (chunks + blockDim.x - 1) / blockDim.x;
-    for (int it = 0; it < rounds; ++it) {
-      const int c = it * blockDim.x + threadIdx.x;
-      const bool valid = c < chunks;
-      float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      const int64_t gc = (int64_t)first * row_chunks + c;  // chunk index in the whole matrix
-      if (valid) {
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(hidden) + gc);
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    // Four 16-byte loads per thread are in flight before the first one is used.
+    constexpr int kUnroll = 4;
+    const bool words = groups % 4 == 0 &&
+                       (reinterpret_cast<uintptr_t>(logical_scales) & 3) == 0 &&
+                       (reinterpret_cast<uintptr_t>(dense_scales) & 3) == 0;
+    for (int it0 = 0; it0 < rounds; it0 += kUnroll) {
+      uint4 raw[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int c = (it0 + u) * blockDim.x + threadIdx.x;
+        raw[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (c < chunks) {
+          raw[u] = __ldg(reinterpret_cast<const uint4*>(hidden) + ((int64_t)first * row_chunks + c));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int c = (it0 + u) * blockDim.x + threadIdx.x;
+        const bool valid = c < chunks;
+        const int64_t gc = (int64_t)first * row_chunks + c;  // chunk index in the whole matrix
+        float v[8];
+        const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           v[2 * i] = __uint_as_float(w[i] << 16);
           v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
         }
-      }
-      float amax = 0.0f;
+        float amax = 0.0f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
-      const float inv = ue8m0_inverse(sbits);
-      if (valid) {
-        reinterpret_cast<uint2*>(quantized)[gc] =
-            make_uint2(e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
-                       e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
-        if ((c & 3) == 0) {
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
+        const float inv = ue8m0_inverse(sbits);
+        const uint32_t code = sbits >> 23;
+        uint32_t word = code;
+        word |= __shfl_down_sync(0xffffffffu, code, 4) << 8;
+        word |= __shfl_down_sync(0xffffffffu, code, 8) << 16;
+        word |= __shfl_down_sync(0xffffffffu, code, 12) << 24;
+        if (valid) {
+          reinterpret_cast<uint2*>(quantized)[gc] =
+              make_uint2(e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
+                         e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
           const int token = first + c / row_chunks;
           const int g = (c % row_chunks) >> 2;
-          const uint8_t code = static_cast<uint8_t>(sbits >> 23);
-          if (logical_scales != nullptr) logical_scales[(int64_t)token * groups + g] = code;
-          if (dense_scales != nullptr) dense_scales[packed_scale_offset(token, g, groups)] = code;
+          if (words) {
+            // 16 lanes = 4 groups of one row (a row holds a multiple of 16 chunks).
+            if ((threadIdx.x & 15) == 0) {
+              if (logical_scales != nullptr)
+                *reinterpret_cast<uint32_t*>(logical_scales + (int64_t)token * groups + g) = word;
+              if (dense_scales != nullptr)
+                *reinterpret_cast<uint32_t*>(dense_scales +
+                                             packed_scale_offset(token, g, groups)) = word;
+            }
+          } else if ((c & 3) == 0) {
+            if (logical_scales != nullptr)
+              logical_scales[(int64_t)token * groups + g] = static_cast<uint8_t>(code);
+            if (dense_scales != nullptr)
+              dense_scales[packed_scale_offset(token, g, groups)] = static_cast<uint8_t>(code);
+          }
         }
       }
     }
@@ -474,65 +503,87 @@ topk_quant_route_small_kernel(const __nv_bfloat16* __restrict__ hidden,
 // input [rows, 2I] (gate columns first), output [rows, I] E4M3 + scales.  Scale
 // placement: logical [rows, I/32]; or packed with row -> scale row through
 // expert/scale offsets (grouped) or identity (dense).
+// One warp per row and 256 columns per pass (8 per lane): the row's expert is looked up once,
+// in a shared-memory copy of expert_offsets, and four lanes' scale codes leave as one word
+// when the layout allows it (a row of groups that is a multiple of four).
 template <class T>
 __global__ void __launch_bounds__(256)
 silu_mul_quant_kernel(const T* __restrict__ input, uint8_t* __restrict__ output,
                       uint8_t* __restrict__ logical, uint8_t* __restrict__ packed, int64_t rows,
                       int inter, const int64_t* __restrict__ expert_offsets,
                       const int64_t* __restrict__ scale_offsets, int experts) {
-  const int groups = inter / kScaleVec;
-  const int64_t chunks = rows * (inter / 8);
-  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
-  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t rounds = (chunks + nthreads - 1) / nthreads;
-  for (int64_t it = 0; it < rounds; ++it) {
-    const int64_t c = it * nthreads + tid;
-    const bool valid = c < chunks;
-    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    int64_t row = 0;
-    int col = 0;
-    if (valid) {
-      row = c / (inter / 8);
-      col = static_cast<int>(c - row * (inter / 8)) * 8;
-      const T* g_ptr = input + row * 2 * inter + col;
-      const uint4 graw = __ldg(reinterpret_cast<const uint4*>(g_ptr));
-      const uint4 uraw = __ldg(reinterpret_cast<const uint4*>(g_ptr + inter));
-      const T* gv = reinterpret_cast<const T*>(&graw);
-      const T* uv = reinterpret_cast<const T*>(&uraw);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float g = round_bf16(to_float(gv[i]));
-        const float u = round_bf16(to_float(uv[i]));
-        const float s = round_bf16(__fdiv_rn(g, 1.0f + expf(-g)));
-        v[i] = round_bf16(s * u);
-      }
+  __shared__ int row_begin[kMaxExperts + 1];
+  __shared__ int scale_begin[kMaxExperts + 1];
+  const bool grouped = expert_offsets != nullptr;
+  if (grouped) {
+    for (int e = threadIdx.x; e <= experts; e += blockDim.x) {
+      row_begin[e] = static_cast<int>(expert_offsets[e]);
+      scale_begin[e] = static_cast<int>(scale_offsets[e]);
     }
-    float amax = 0.0f;
+    __syncthreads();
+  }
+  const int lane = threadIdx.x & 31;
+  const int groups = inter / kScaleVec;
+  const bool words = groups % 4 == 0 && (reinterpret_cast<uintptr_t>(logical) & 3) == 0 &&
+                     (reinterpret_cast<uintptr_t>(packed) & 3) == 0;
+  const int warps = static_cast<int>(gridDim.x) * (blockDim.x >> 5);
+  const int first = static_cast<int>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  for (int64_t row = first; row < rows; row += warps) {
+    int64_t srow = row;
+    if (grouped) {
+      int lo = 0, hi = experts;  // largest e with row_begin[e] <= row
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (row_begin[mid] <= row) lo = mid; else hi = mid;
+      }
+      srow = scale_begin[lo] + (row - row_begin[lo]);
+    }
+    const T* in_row = input + row * 2 * inter;
+    for (int col0 = 0; col0 < inter; col0 += 256) {
+      const int col = col0 + lane * 8;
+      const bool valid = col < inter;
+      float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (valid) {
+        const uint4 graw = __ldg(reinterpret_cast<const uint4*>(in_row + col));
+        const uint4 uraw = __ldg(reinterpret_cast<const uint4*>(in_row + inter + col));
+        const T* gv = reinterpret_cast<const T*>(&graw);
+        const T* uv = reinterpret_cast<const T*>(&uraw);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
-    const float inv = ue8m0_inverse(sbits);
-    if (valid) {
-      reinterpret_cast<uint2*>(output)[c] =
-          make_uint2(e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
-                     e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
-      if ((c & 3) == 0) {
+        for (int i = 0; i < 8; ++i) {
+          const float g = round_bf16(to_float(gv[i]));
+          const float u = round_bf16(to_float(uv[i]));
+          const float sv = round_bf16(__fdiv_rn(g, 1.0f + expf(-g)));
+          v[i] = round_bf16(sv * u);
+        }
+      }
+      float amax = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
+      const float inv = ue8m0_inverse(sbits);
+      const uint32_t code = sbits >> 23;
+      uint32_t word = code;
+      word |= __shfl_down_sync(0xffffffffu, code, 4) << 8;
+      word |= __shfl_down_sync(0xffffffffu, code, 8) << 16;
+      word |= __shfl_down_sync(0xffffffffu, code, 12) << 24;
+      if (valid) {
+        *reinterpret_cast<uint2*>(output + row * inter + col) =
+            make_uint2(e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
+                       e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
         const int g = col / kScaleVec;
-        const uint8_t code = static_cast<uint8_t>(sbits >> 23);
-        if (logical != nullptr) logical[row * groups + g] = code;
-        if (packed != nullptr) {
-          int64_t srow = row;
-          if (expert_offsets != nullptr) {
-            int lo = 0, hi = experts;  // largest e with expert_offsets[e] <= row
-            while (hi - lo > 1) {
-              const int mid = (lo + hi) >> 1;
-              if (expert_offsets[mid] <= row) lo = mid; else hi = mid;
-            }
-            srow = scale_offsets[lo] + (row - expert_offsets[lo]);
+        if (words) {
+          if ((lane & 15) == 0) {
+            if (logical != nullptr)
+              *reinterpret_cast<uint32_t*>(logical + row * groups + g) = word;
+            if (packed != nullptr)
+              *reinterpret_cast<uint32_t*>(packed + packed_scale_offset(srow, g, groups)) = word;
           }
-          packed[packed_scale_offset(srow, g, groups)] = code;
+        } else if ((lane & 3) == 0) {
+          if (logical != nullptr) logical[row * groups + g] = static_cast<uint8_t>(code);
+          if (packed != nullptr)
+            packed[packed_scale_offset(srow, g, groups)] = static_cast<uint8_t>(code);
         }
       }
     }
@@ -726,9 +777,10 @@ int silu_mul_quant(const void* input, int dtype, int64_t rows, int inter, uint8_
   MX_REQUIRE(logical != nullptr || packed != nullptr, "one scale output is required");
   MX_REQUIRE((expert_offsets == nullptr) == (scale_offsets == nullptr),
              "expert_offsets and scale_offsets go together");
-  const int64_t chunks = rows * (inter / 8);
-  int64_t blocks = (chunks + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  MX_REQUIRE(expert_offsets == nullptr || (experts > 0 && experts <= kMaxExperts),
+             "experts must be in [1, %d]", kMaxExperts);
+  int64_t blocks = (rows + 7) / 8;  // one warp per row, eight warps per CTA
+  if (blocks > 148 * 8) blocks = 148 * 8;
   if (dtype == kBF16) {
     silu_mul_quant_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(input), output, logical, packed, rows, inter,

@@ -296,3 +296,28 @@ def test_moe_layer_named_config_and_graph_replay(mx, tokens):
             graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(out, first)
+
+
+@pytest.mark.parametrize("tokens,full_size", [(700, False), (4096, True)])
+def test_prefill_batches_run_w1_unfused_with_identical_bytes(mx, tokens, full_size):
+    """From 16384 routed rows on, W1 is a grouped GEMM into the front of routed_output
+    followed by the SiLU*mul/MXFP8 kernel; the fused kernel gives the same bytes."""
+    from mxfp6_sm120_b200 import qwen35
+
+    shape = mx.MoeShape() if full_size else mx.MoeShape(hidden=512, intermediate=256, experts=32, topk=4)
+    case = _layer_case(mx, tokens, shape)
+    threshold = qwen35.UNFUSED_W1_MIN_ROUTES
+    outs = {}
+    try:
+        for name, value in (("unfused", 1), ("fused", 1 << 60)):
+            qwen35.UNFUSED_W1_MIN_ROUTES = value
+            out, ws, _ = _run_layer(mx, shape, *case)
+            outs[name] = out.clone()
+    finally:
+        qwen35.UNFUSED_W1_MIN_ROUTES = threshold
+    # Rows land in their expert's block in arrival order, so only the layer output (which
+    # the reduce gathers back per token) is comparable between two runs.
+    assert torch.equal(outs["unfused"], outs["fused"])
+    if full_size:
+        assert tokens * shape.topk >= threshold  # the default takes the unfused path here
+    assert mx.device_status() == 0
