@@ -1050,7 +1050,7 @@ int plan_w6a8(const GemmProblem& p, GemmPlan* plan) {
   MX_REQUIRE(p.groups >= 1 && p.groups <= kMaxGroups, "groups must be in [1, %d]", kMaxGroups);
   MX_REQUIRE(p.groups == 1 || p.n % 128 == 0, "grouped weights need n %% 128 == 0");
   const bool grouped = p.expert_offsets != nullptr;
-  if (!grouped && p.splits <= 1 && p.cluster_k <= 1 && cta_pair_mode() == 1 &&
+  if (p.splits <= 1 && p.cluster_k <= 1 && cta_pair_mode() == 1 &&
       pair_kernel_applies(p, p.tile_tokens)) {
     return plan_w6a8_pair(p, sm_count(), plan);
   }

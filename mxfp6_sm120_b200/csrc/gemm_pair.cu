@@ -43,7 +43,47 @@ struct PairArgs {
   float alpha;
   int a_scale_row_blocks;
   long long* trace;
+  // Grouped launches: rows [expert_offsets[g], expert_offsets[g + 1]) use weight rows
+  // [g * n, (g + 1) * n) and packed scale rows from scale_offsets[g]; null = dense.
+  const int64_t* expert_offsets;
+  const int64_t* scale_offsets;
+  int groups;
 };
+
+constexpr int kPairMaxGroups = 512;
+
+struct PairWork {
+  int group, n_pair, rows;
+  int64_t row0;        // first activation row of the tile
+  int64_t scale_row0;  // packed-scale row of row0
+};
+
+// tile_prefix[g] = row tiles of groups < g; row_begin / scale_begin follow at a stride of
+// kPairMaxGroups + 1 ints.  Tiles of one group are adjacent, row tile fastest.
+template <int TN>
+__device__ __forceinline__ bool pair_decode(int t, const PairArgs& a, const int* tile_prefix,
+                                            PairWork* out) {
+  const int total = tile_prefix[a.groups] * a.n_pair_tiles;
+  if (t >= total) return false;
+  int lo = 0, hi = a.groups;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (tile_prefix[mid] * a.n_pair_tiles <= t) lo = mid; else hi = mid;
+  }
+  while (lo + 1 < a.groups && tile_prefix[lo + 1] * a.n_pair_tiles <= t) ++lo;  // empty groups
+  const int local = t - tile_prefix[lo] * a.n_pair_tiles;
+  const int mt = tile_prefix[lo + 1] - tile_prefix[lo];
+  const int m_tile = local % mt;
+  const int* row_begin = tile_prefix + (kPairMaxGroups + 1);
+  const int* scale_begin = row_begin + (kPairMaxGroups + 1);
+  out->group = lo;
+  out->n_pair = local / mt;
+  out->row0 = (int64_t)row_begin[lo] + (int64_t)m_tile * TN;
+  const int64_t left = (int64_t)row_begin[lo + 1] - out->row0;
+  out->rows = left < TN ? (int)left : TN;
+  out->scale_row0 = (int64_t)scale_begin[lo] + (int64_t)m_tile * TN;
+  return true;
+}
 
 template <int TN>
 struct PairCfg {
@@ -61,7 +101,9 @@ struct PairCfg {
   static constexpr uint32_t kStageBytes = kWTileBytes + kATileBytes;
   static constexpr uint32_t kSfStageBytes = kAtomBytes * (1 + kSfbAtoms);
   static constexpr uint32_t kEpiWarpBytes = 2048;
-  static constexpr uint32_t kFixedBytes = 1024 + 1024 + 4 * kEpiWarpBytes;
+  // align slack, barriers, three group tables, epilogue staging
+  static constexpr uint32_t kTableBytes = 3 * (512 + 1) * 4 + 4;
+  static constexpr uint32_t kFixedBytes = 1024 + 1024 + 4 * kEpiWarpBytes + ((kTableBytes + 127) / 128) * 128;
   static constexpr int kStagesRaw = (int)((232448u - kFixedBytes) / (kStageBytes + kSfStageBytes));
   static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
   static constexpr size_t kSmemBytes = kFixedBytes + (size_t)kStages * (kStageBytes + kSfStageBytes);
@@ -103,6 +145,7 @@ w6a8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fixed + 8 * (2 * C::kStages + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint8_t* epi_stage = fixed + 1024;
+  int* tile_prefix = reinterpret_cast<int*>(fixed + 1024 + 4 * C::kEpiWarpBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -134,14 +177,52 @@ w6a8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
   }
   ptx::grid_dependency_wait();
   ptx::grid_launch_dependents();
+  {
+    int* row_begin_tab = tile_prefix + (kPairMaxGroups + 1);
+    int* scale_begin_tab = row_begin_tab + (kPairMaxGroups + 1);
+    if (args.expert_offsets == nullptr) {
+      if (threadIdx.x == 0) {
+        tile_prefix[0] = 0;
+        tile_prefix[1] = (int)((args.m + TN - 1) / TN);
+        row_begin_tab[0] = 0;
+        row_begin_tab[1] = (int)args.m;
+        scale_begin_tab[0] = 0;
+      }
+    } else {
+      for (int g = threadIdx.x; g <= args.groups; g += kThreads) {
+        const int64_t first = args.expert_offsets[g];
+        row_begin_tab[g] = (int)first;
+        scale_begin_tab[g] = (int)args.scale_offsets[g];
+        if (g < args.groups) {
+          const int64_t rows = args.expert_offsets[g + 1] - first;
+          tile_prefix[g + 1] = (int)((rows + TN - 1) / TN);
+        }
+      }
+      __syncthreads();
+      if (warp == 0) {
+        int carry = 0;
+        for (int base = 0; base < args.groups; base += 32) {
+          const int g = base + lane;
+          const int v = g < args.groups ? tile_prefix[g + 1] : 0;
+          int incl = v;
+#pragma unroll
+          for (int d = 1; d < 32; d <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += up;
+          }
+          if (g < args.groups) tile_prefix[g + 1] = carry + incl;
+          carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) tile_prefix[0] = 0;
+      }
+    }
+  }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   ptx::cluster_sync_all();  // both CTAs' barriers are initialised
 
-  const int m_tiles = (int)((args.m + TN - 1) / TN);
-  const int total_tiles = m_tiles * args.n_pair_tiles;
   const int pair = blockIdx.x >> 1;
   const int pairs = gridDim.x >> 1;
   const int kb_total = args.k_blocks;
@@ -156,13 +237,11 @@ w6a8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
     constexpr uint32_t kTxPerCta = kWTileTxBytes + C::kATileBytes + kAtomBytes * (1 + C::kSfbAtoms);
     const uint32_t leader_full0 = ptx::mapa(full0, 0u);
     bool ok = true;
-    for (int t = pair; ok && t < total_tiles; t += pairs) {
-      const int m_tile = t % m_tiles;
-      const int n_pair = t / m_tiles;
-      const int w_row = n_pair * 2 * kTileF + (int)rank * kTileF;
-      const int64_t m0 = (int64_t)m_tile * TN;
-      const int a_row = (int)(m0 + rank * C::kHalf);
-      const int sfb_rb0 = (int)(m0 / kAtomRows);
+    PairWork wk;
+    for (int t = pair; ok && pair_decode<TN>(t, args, tile_prefix, &wk); t += pairs) {
+      const int w_row = wk.group * args.n + wk.n_pair * 2 * kTileF + (int)rank * kTileF;
+      const int a_row = (int)(wk.row0 + rank * C::kHalf);
+      const int sfb_rb0 = (int)(wk.scale_row0 / kAtomRows);
       const int sfa_atom0 = (w_row / kAtomRows) * kb_total;
       for (int kb = 0; kb < kb_total; ++kb) {
         ok = __all_sync(0xffffffffu,
@@ -205,9 +284,9 @@ w6a8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
     // The poll of the next stage's barrier is issued before the commit of this one, so
     // its latency overlaps the commit.
     bool ready = false;
-    for (int t = pair; ok && t < total_tiles; t += pairs) {
-      const int m_tile = t % m_tiles;
-      const uint32_t sfb_sub = (uint32_t)((((int64_t)m_tile * TN) % kAtomRows) / 32);
+    PairWork wk;
+    for (int t = pair; ok && pair_decode<TN>(t, args, tile_prefix, &wk); t += pairs) {
+      const uint32_t sfb_sub = (uint32_t)((wk.scale_row0 % kAtomRows) / 32);
       if (!__all_sync(0xffffffffu, pair_wait(tempty0 + 8 * acc, acc_phase ^ 1u, abort_flag,
                                              args.status, 203)))
         break;
@@ -267,11 +346,11 @@ w6a8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
     uint32_t acc_phase = 0;
     uint16_t* stage16 = reinterpret_cast<uint16_t*>(epi_stage + quarter * C::kEpiWarpBytes);
     const bool bf16_out = args.out_dtype == kBF16;
-    for (int t = pair; t < total_tiles; t += pairs) {
-      const int m_tile = t % m_tiles;
-      const int n_pair = t / m_tiles;
-      const int64_t row0 = (int64_t)m_tile * TN;
-      const int rows = (int)((args.m - row0) < TN ? (args.m - row0) : TN);
+    PairWork wk;
+    for (int t = pair; pair_decode<TN>(t, args, tile_prefix, &wk); t += pairs) {
+      const int n_pair = wk.n_pair;
+      const int64_t row0 = wk.row0;
+      const int rows = wk.rows;
       if (!pair_wait(tfull0 + 8 * acc, acc_phase, abort_flag, args.status, 206)) break;
       ptx::tc_fence_after();
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * TN;
@@ -373,11 +452,17 @@ long long* trace_buffer();
 int make_tensor_map_2d(CUtensorMap* out, int type, const void* base, uint64_t inner, uint64_t rows,
                        uint64_t stride, uint32_t box_rows);
 
-// tile_tokens 0 lets the planner choose among 128, 192 and 256.
+// tile_tokens 0 lets the planner choose among 128, 192 and 256.  Grouped launches
+// qualify when the mean group is large enough for those tiles.
 bool pair_kernel_applies(const GemmProblem& p, int tile_tokens) {
-  return p.groups == 1 && p.expert_offsets == nullptr && p.mode == kGemmStore &&
-         p.n % 256 == 0 && p.m_total > 128 &&
-         (tile_tokens == 0 || tile_tokens == 128 || tile_tokens == 192 || tile_tokens == 256);
+  if (p.mode != kGemmStore || p.n % 256 != 0) return false;
+  if (!(tile_tokens == 0 || tile_tokens == 128 || tile_tokens == 192 || tile_tokens == 256))
+    return false;
+  if (p.expert_offsets != nullptr) {
+    if (p.groups < 1 || p.groups > kPairMaxGroups || p.scale_offsets == nullptr) return false;
+    return tile_tokens != 0 || p.m_total > (int64_t)48 * p.groups;
+  }
+  return p.groups == 1 && p.m_total > 128;
 }
 
 namespace {
@@ -393,7 +478,13 @@ int plan_w6a8_pair(const GemmProblem& p, int sms, GemmPlan* plan) {
   const int pairs = sms / 2 > 0 ? sms / 2 : 1;
   const int64_t n_pairs = p.n / 256;
   const int64_t k_blocks = p.k / kTileK;
+  const bool grouped = p.expert_offsets != nullptr;
   int tn = p.tile_tokens;
+  if (tn == 0 && grouped) {
+    // Group sizes are device data; a tile somewhat wider than the mean group lets most
+    // groups finish in one row tile.
+    tn = p.m_total <= (int64_t)96 * p.groups ? 128 : 192;
+  }
   if (tn == 0) {
     // Cycles one CTA pair spends: per 128-K block the slower of the MMA (2 cycles per
     // token column) and the issue loop; the 256-token tile has a single accumulator, so
@@ -419,7 +510,10 @@ int plan_w6a8_pair(const GemmProblem& p, int sms, GemmPlan* plan) {
     case 256: fill_pair_plan<256>(plan); break;
     default: set_error("the CTA-pair kernel takes tile_tokens 128, 192 or 256"); return kInvalidArgument;
   }
-  const int64_t tiles = ((p.m_total + tn - 1) / tn) * n_pairs;
+  // Grouped: every group may add one ragged row tile.
+  const int64_t row_tiles = grouped ? p.m_total / tn + (p.groups < p.m_total ? p.groups : p.m_total)
+                                    : (p.m_total + tn - 1) / tn;
+  const int64_t tiles = row_tiles * n_pairs;
   plan->splits = 1;
   plan->cluster_k = 1;
   plan->cta_pair = 1;
@@ -437,7 +531,8 @@ int launch_w6a8_pair(const GemmProblem& p, const GemmPlan& plan, cudaStream_t st
   MX_CUDA(cudaGetDevice(&device));
   CUtensorMap tm_w, tm_a, tm_ws, tm_as;
   if (int rc = make_tensor_map_2d(&tm_w, (int)CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B, p.w_values,
-                                  (uint64_t)p.k, (uint64_t)p.n, (uint64_t)p.k * 3 / 4, kTileF))
+                                  (uint64_t)p.k, (uint64_t)p.groups * p.n, (uint64_t)p.k * 3 / 4,
+                                  kTileF))
     return rc;
   if (int rc = make_tensor_map_2d(&tm_a, (int)CU_TENSOR_MAP_DATA_TYPE_UINT8, p.a_values,
                                   (uint64_t)p.k, (uint64_t)p.m_total, (uint64_t)p.k,
@@ -446,7 +541,8 @@ int launch_w6a8_pair(const GemmProblem& p, const GemmPlan& plan, cudaStream_t st
   const int64_t scale_rows = p.a_scale_rows > 0 ? p.a_scale_rows : round_up64(p.m_total, kAtomRows);
   const uint64_t k_blocks = (uint64_t)(p.k / kTileK);
   if (int rc = make_tensor_map_2d(&tm_ws, (int)CU_TENSOR_MAP_DATA_TYPE_UINT32, p.w_scales, 128,
-                                  (uint64_t)(p.n / kAtomRows) * k_blocks, kAtomBytes, 1))
+                                  (uint64_t)p.groups * (p.n / kAtomRows) * k_blocks, kAtomBytes,
+                                  1))
     return rc;
   if (int rc = make_tensor_map_2d(&tm_as, (int)CU_TENSOR_MAP_DATA_TYPE_UINT32, p.a_scales, 128,
                                   (uint64_t)(scale_rows / kAtomRows) * k_blocks, kAtomBytes, 1))
@@ -465,6 +561,9 @@ int launch_w6a8_pair(const GemmProblem& p, const GemmPlan& plan, cudaStream_t st
   args.alpha = p.alpha;
   args.trace = trace_buffer();
   args.a_scale_row_blocks = (int)(scale_rows / kAtomRows);
+  args.expert_offsets = p.expert_offsets;
+  args.scale_offsets = p.scale_offsets;
+  args.groups = p.expert_offsets != nullptr ? p.groups : 1;
   const int pairs = plan.grid / 2;
   switch (tile_tokens) {
     case 128: return launch_pair_tn<128>(tm_w, tm_a, tm_ws, tm_as, args, pairs, stream);
