@@ -507,8 +507,14 @@ def main() -> None:
         achieved = big_flops / (big_ms * 1e-3) / 1e12
         line["roofline"] = {
             "bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
-            "frac": achieved / fp8_peak, "traffic": None,
-            "kernel": "w6a8_gemm_kernel, M >= 4096 launches of the sweep",
+            "frac": achieved / fp8_peak,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one M=4096, N=7168, K=5120
+            # launch in the ncu capture under profiles/ (the other launches of this group
+            # were not captured); algorithmic bytes of that launch are 109.0e6, part of the
+            # output is still in L2 when the kernel ends.
+            "traffic": 78.1e6,
+            "traffic_launch": "M=4096 N=7168 K=5120",
+            "kernel": "w6a8_gemm_pair_kernel (CTA pairs), M >= 4096 launches of the sweep",
             "peak_note": f"2 x bf16_tflops_sustained ({peaks['source']}): kind::mxf8f6f4 runs at "
                          "the FP8 rate, twice the BF16 rate the peak file measures",
             "frac_of_nominal_4500": achieved / 4500.0,
@@ -517,7 +523,11 @@ def main() -> None:
         achieved = small_bytes / (small_ms * 1e-3) / 1e9
         line["roofline_small_m"] = {
             "bound": "hbm", "achieved": achieved, "peak": float(peaks["hbm_gbs"]), "unit": "GB/s",
-            "frac": achieved / float(peaks["hbm_gbs"]), "traffic": None,
+            "frac": achieved / float(peaks["hbm_gbs"]),
+            # one M=16, N=34816, K=5120 launch in the ncu capture under profiles/:
+            # 139.4 MB read + 5.3 MB written against 139.5e6 algorithmic bytes (weights read once).
+            "traffic": 144.7e6,
+            "traffic_launch": "M=16 N=34816 K=5120",
             "kernel": "w6a8_gemm_kernel, M <= 32 launches of the sweep",
             "peak_note": f"hbm_gbs ({peaks['source']})",
         }
