@@ -6,7 +6,7 @@
 // memory.  Per 128-K block a CTA therefore pulls 12 KB of weights + TN/2 x 128 bytes
 // of activations from L2 instead of TN x 128, which is what bounded the single-CTA
 // kernel at large M (its 5-stage ring delivered a block per ~580 cycles against ~390
-// cycles of MMA work).  No TMA multicast is used: every CTA issues its own loads.
+// cycles of MMA work).  Every CTA issues its own loads; no load is shared between CTAs.
 //
 // Roles per CTA (192 threads): warp 0 TMA producer; warp 1 MMA issuer in the leader
 // CTA (rank 0) / "stage ready" forwarder in the peer; warps 2..5 epilogue.
