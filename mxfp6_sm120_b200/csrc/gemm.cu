@@ -252,6 +252,49 @@ __device__ __forceinline__ void emit_element(const KernelArgs& args, int64_t row
   }
 }
 
+// Cluster split-K reduce of this CTA's share of the token rows: ROWS rows per round, all
+// their loads from the (up to RANKS) partial tiles issued before any is used.
+template <int TN, int MODE, int ROWS, int RANKS>
+__device__ __forceinline__ void cluster_reduce_rows(const KernelArgs& args, const float* red,
+                                                    const Work& wk, int my_rank, int cluster_k,
+                                                    int f, bool f_ok, int fl, int lane,
+                                                    int64_t srow0) {
+#pragma unroll 1
+  for (int t0 = my_rank; t0 < wk.rows; t0 += ROWS * cluster_k) {
+    float vm[ROWS][RANKS], vu[ROWS][RANKS];
+#pragma unroll
+    for (int j = 0; j < ROWS; ++j) {
+      const int t = t0 + j * cluster_k;
+      const uint32_t local = ptx::smem_u32(red + t * kTileF + fl);
+#pragma unroll
+      for (int r = 0; r < RANKS; ++r) {
+        vm[j][r] = 0.0f;
+        vu[j][r] = 0.0f;
+        if (t < wk.rows && r < cluster_k) {
+          const uint32_t remote = ptx::mapa(local, (uint32_t)r);
+          vm[j][r] = ptx::ld_dsmem_f32(remote);
+          if (MODE == kModeSwiglu) vu[j][r] = ptx::ld_dsmem_f32(remote + TN * kTileF * 4);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < ROWS; ++j) {
+      const int t = t0 + j * cluster_k;
+      float main_acc = 0.0f, up_acc = 0.0f;
+#pragma unroll
+      for (int r = 0; r < RANKS; ++r) {
+        if (r < cluster_k) {
+          main_acc += vm[j][r];
+          up_acc += vu[j][r];
+        }
+      }
+      if (t < wk.rows) {  // warp-uniform: every lane of the warp has the same t
+        emit_element<MODE>(args, wk.row0 + t, f, f_ok, lane, main_acc, up_acc, srow0 + t);
+      }
+    }
+  }
+}
+
 template <int TN, int MODE, int CL>
 __global__ void __launch_bounds__(kThreads, 1)
 w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
@@ -315,14 +358,13 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     const uint32_t word = reinterpret_cast<const uint32_t*>(&args)[(threadIdx.x - 64) * 16];
     asm volatile("" ::"r"(word));
   }
-  // Everything above is independent of earlier kernels; from here on global memory
-  // written by them is read, so wait for them, then let the next kernel's prologue start.
-  ptx::grid_dependency_wait();
-  ptx::grid_launch_dependents();
   // Row-tile prefix table (one entry per group).
   int* row_begin_tab = tile_prefix + (kMaxGroups + 1);
   int* scale_begin_tab = row_begin_tab + (kMaxGroups + 1);
-  if (args.expert_offsets == nullptr) {
+  const bool dense = args.expert_offsets == nullptr;
+  if (dense) {
+    // A dense launch needs nothing from earlier kernels for its table or for the cluster
+    // handshake: both happen before the wait, off the critical path of a decode chain.
     if (threadIdx.x == 0) {
       tile_prefix[0] = 0;
       tile_prefix[1] = (int)((args.m_total + TN - 1) / TN);
@@ -330,7 +372,16 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       row_begin_tab[1] = (int)args.m_total;
       scale_begin_tab[0] = 0;
     }
-  } else {
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    if (cluster_k > 1) ptx::cluster_sync_all();
+  }
+  // Everything above is independent of earlier kernels; from here on global memory
+  // written by them is read, so wait for them, then let the next kernel's prologue start.
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
+  if (!dense) {
     for (int g = threadIdx.x; g <= args.groups; g += kThreads) {
       const int64_t first = args.expert_offsets[g];
       row_begin_tab[g] = (int)first;
@@ -357,13 +408,13 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       }
       if (lane == 0) tile_prefix[0] = 0;
     }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    // Peers must see this CTA's barriers initialised before they arrive on them.
+    if (cluster_k > 1) ptx::cluster_sync_all();
   }
-  ptx::tc_fence_before();
-  __syncthreads();
-  ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // Peers must see this CTA's barriers initialised before they arrive on them.
-  if (cluster_k > 1) ptx::cluster_sync_all();
   if (threadIdx.x == 0) MX_STAMP(1);
 
   const int kb_total = args.k_blocks;
@@ -582,43 +633,23 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           const bool f_ok = f < args.n;
           const int64_t srow0 = args.out_scale_offsets != nullptr ? wk.scale_row0 : wk.row0;
           // Token rows are dealt round-robin to the CTAs; the sum runs over the ranks
-          // in order, so the result does not depend on timing.
-          // Four rows per round: all their remote loads are issued before any is used.
-          for (int t0 = (int)my_rank; t0 < wk.rows; t0 += 4 * cluster_k) {
-            float vm[4][8], vu[4][8];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int t = t0 + j * cluster_k;
-              const uint32_t local = ptx::smem_u32(red + t * kTileF + fl);
-#pragma unroll
-              for (int r = 0; r < 8; ++r) {
-                vm[j][r] = 0.0f;
-                vu[j][r] = 0.0f;
-                if (t < wk.rows && r < cluster_k) {
-                  const uint32_t remote = ptx::mapa(local, (uint32_t)r);
-                  vm[j][r] = ptx::ld_dsmem_f32(remote);
-                  if (MODE == kModeSwiglu) vu[j][r] = ptx::ld_dsmem_f32(remote + TN * kTileF * 4);
-                }
-              }
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int t = t0 + j * cluster_k;
-              float main_acc = 0.0f, up_acc = 0.0f;
-#pragma unroll
-              for (int r = 0; r < 8; ++r) {
-                if (r < cluster_k) {
-                  main_acc += vm[j][r];
-                  up_acc += vu[j][r];
-                }
-              }
-              if (t < wk.rows) {  // warp-uniform: every lane of the warp has the same t
-                emit_element<MODE>(args, wk.row0 + t, f, f_ok, lane, main_acc, up_acc, srow0 + t);
-              }
-            }
+          // in order, so the result does not depend on timing.  A round keeps 32 remote
+          // loads in flight per lane: the fewer the ranks, the more rows per round.
+          if (cluster_k <= 2) {
+            cluster_reduce_rows<TN, MODE, 16, 2>(args, red, wk, (int)my_rank, cluster_k, f, f_ok,
+                                                 fl, lane, srow0);
+          } else if (cluster_k <= 4) {
+            cluster_reduce_rows<TN, MODE, 8, 4>(args, red, wk, (int)my_rank, cluster_k, f, f_ok, fl,
+                                                lane, srow0);
+          } else {
+            cluster_reduce_rows<TN, MODE, 4, 8>(args, red, wk, (int)my_rank, cluster_k, f, f_ok, fl,
+                                                lane, srow0);
           }
           __syncwarp();
-          if (lane < cluster_k) ptx::mbar_arrive_remote(ptx::mapa(red_empty, (uint32_t)lane));
+          // Nothing is published by this arrival (the peers' tiles were only read, and the
+          // values have been used), so it needs no release fence.
+          if (lane < cluster_k)
+            ptx::mbar_arrive_remote_relaxed(ptx::mapa(red_empty, (uint32_t)lane));
           red_phase ^= 1u;
           continue;
         }
