@@ -85,6 +85,19 @@ int mxfp6_pack_grouped_scales(const uint8_t* logical_dev, const int64_t* expert_
 int mxfp6_quantize_mxfp8(const void* input_dev, int dtype, int64_t rows, int64_t k,
                          uint8_t* values_dev, uint8_t* packed_scales_dev,
                          uint8_t* logical_scales_dev, void* stream);
+/* Residual add + RMSNorm fused into the MXFP8 quantizer.  With residual_dev: x <-
+ * round(x + residual) is written to updated_dev (may equal input_dev) first; both NULL
+ * skips the add.  Then y = round((x * rsqrt(mean(x^2) + eps)) * weight) in the input dtype
+ * (one rounding, as torch.nn.functional.rms_norm) and the rule of mxfp6_quantize_mxfp8 on
+ * y.  One pass over the row; k <= 16384.  No reference counterpart: the reference leaves
+ * the residual stream and normalisation to the serving runtime
+ * (docs/runtime-integration.md:13-22) and quantizes its BF16 output
+ * (csrc/quantization.cu:70-191). */
+int mxfp6_rmsnorm_quantize_mxfp8(const void* input_dev, const void* residual_dev,
+                                 void* updated_dev, int dtype, const void* weight_dev, float eps,
+                                 int64_t rows, int64_t k, uint8_t* values_dev,
+                                 uint8_t* packed_scales_dev, uint8_t* logical_scales_dev,
+                                 void* stream);
 /* torch.ops.mxfp6.quantize_mxfp6 (csrc/quantization.cu:193-243,406-409):
  * values are the packed 6-bit stream (rows * k * 3/4 bytes). */
 int mxfp6_quantize_mxfp6(const void* input_dev, int dtype, int64_t rows, int64_t k,

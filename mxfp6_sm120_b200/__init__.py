@@ -31,6 +31,7 @@ from .ops import (
     gemm_w6a8_plan,
     is_available,
     is_stream_k_enabled,
+    rmsnorm_quantize_mxfp8,
     set_cta_pair_mode,
     is_cta_pair_enabled,
     set_split_k_mode,
@@ -86,6 +87,15 @@ from .qwen35 import (
     qwen35_grouped_workspace_shapes,
     qwen35_moe_b1_out,
     shared_expert_out,
+)
+
+from .decoder import (
+    DecoderConfig,
+    DecoderLayer,
+    DecoderWorkspace,
+    DenseDecoder,
+    random_layer,
+    shard_layer,
 )
 
 __version__ = "0.1.0"

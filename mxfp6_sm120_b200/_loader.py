@@ -38,6 +38,11 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p],
     ),
+    "mxfp6_rmsnorm_quantize_mxfp8": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_float, c_int64, c_int64, c_void_p,
+         c_void_p, c_void_p, c_void_p],
+    ),
     "mxfp6_quantize_mxfp8": (
         c_int,
         [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p],

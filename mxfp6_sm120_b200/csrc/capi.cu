@@ -30,6 +30,8 @@ const char* last_error() { return g_error; }
 
 // ---- kernels implemented in the other translation units ------------------------
 int quantize_mxfp8(const void*, int, int64_t, int64_t, uint8_t*, uint8_t*, uint8_t*, cudaStream_t);
+int rmsnorm_quantize_mxfp8(const void*, const void*, void*, int, const void*, float, int64_t,
+                           int64_t, uint8_t*, uint8_t*, uint8_t*, cudaStream_t);
 int quantize_mxfp6(const void*, int, int64_t, int64_t, uint8_t*, uint8_t*, uint8_t*, cudaStream_t);
 int pack_fp6(const uint8_t*, int64_t, uint8_t*, cudaStream_t);
 int unpack_fp6(const uint8_t*, int64_t, int64_t, uint8_t*, cudaStream_t);
@@ -288,6 +290,13 @@ int mxfp6_quantize_mxfp8(const void* input, int dtype, int64_t rows, int64_t k, 
                          uint8_t* packed_scales, uint8_t* logical_scales, void* stream) {
   return quantize_mxfp8(input, dtype, rows, k, values, packed_scales, logical_scales,
                         static_cast<cudaStream_t>(stream));
+}
+int mxfp6_rmsnorm_quantize_mxfp8(const void* input, const void* residual, void* updated,
+                                 int dtype, const void* weight, float eps, int64_t rows, int64_t k,
+                                 uint8_t* values, uint8_t* packed_scales, uint8_t* logical_scales,
+                                 void* stream) {
+  return rmsnorm_quantize_mxfp8(input, residual, updated, dtype, weight, eps, rows, k, values,
+                                packed_scales, logical_scales, static_cast<cudaStream_t>(stream));
 }
 int mxfp6_quantize_mxfp6(const void* input, int dtype, int64_t rows, int64_t k, uint8_t* values,
                          uint8_t* packed_scales, uint8_t* logical_scales, void* stream) {

@@ -221,6 +221,136 @@ quantize_mxfp6_kernel(const T* __restrict__ in, uint8_t* __restrict__ out,
   }
 }
 
+// RMSNorm fused into the activation quantizer: one CTA per row keeps the row in registers
+// (up to kNormChunks 8-value chunks per thread), so the row is read once and only the MXFP8
+// bytes and scales are written.  y = round_to_T((x * rsqrt(mean(x^2) + eps)) * w) in FP32
+// with one rounding (the rule of torch.nn.functional.rms_norm), then the MXFP8 rule above.
+constexpr int kNormChunks = 8;  // K <= 8 * 8 * 256 = 16384
+
+template <class T>
+__device__ __forceinline__ float round_to(float v);
+template <>
+__device__ __forceinline__ float round_to<__nv_bfloat16>(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+template <>
+__device__ __forceinline__ float round_to<__half>(float v) {
+  return __half2float(__float2half_rn(v));
+}
+
+template <class T>
+__global__ void __launch_bounds__(kQuantThreads)
+rmsnorm_quantize_mxfp8_kernel(const T* in, const T* __restrict__ residual, T* updated,
+                              const T* __restrict__ weight, float eps,
+                              uint8_t* __restrict__ out, uint8_t* __restrict__ packed,
+                              uint8_t* __restrict__ logical, int64_t rows, int k,
+                              int64_t pad_begin, int64_t pad_total, bool quad_scales) {
+  __shared__ float warp_sums[kQuantThreads / 32];
+  const int row_chunks = k / 8;
+  const int groups = k / kScaleVec;
+  const int64_t row = blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(in) + row * row_chunks;
+  const uint4* wsrc = reinterpret_cast<const uint4*>(weight);
+  Vec8<T> raw[kNormChunks];
+  float sum = 0.0f;
+#pragma unroll
+  for (int u = 0; u < kNormChunks; ++u) {
+    const int c = u * kQuantThreads + threadIdx.x;
+    raw[u].raw = make_uint4(0u, 0u, 0u, 0u);
+    if (c < row_chunks) raw[u].raw = src[c];
+  }
+  if (residual != nullptr) {
+    // Residual stream: x <- round(x + r), written back (to `updated`, which may be `in`),
+    // and the norm is taken of the rounded sum.
+    const uint4* rsrc = reinterpret_cast<const uint4*>(residual) + row * row_chunks;
+    uint4* xdst = reinterpret_cast<uint4*>(updated) + row * row_chunks;
+#pragma unroll
+    for (int u = 0; u < kNormChunks; ++u) {
+      const int c = u * kQuantThreads + threadIdx.x;
+      if (c < row_chunks) {
+        Vec8<T> r;
+        r.raw = __ldg(rsrc + c);
+        float a[8], b[8];
+        raw[u].unpack(a);
+        r.unpack(b);
+        T packed8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) packed8[i] = static_cast<T>(a[i] + b[i]);
+        raw[u].raw = *reinterpret_cast<const uint4*>(packed8);
+        xdst[c] = raw[u].raw;
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kNormChunks; ++u) {
+    float v[8];
+    raw[u].unpack(v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sum = fmaf(v[i], v[i], sum);
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  float total = 0.0f;
+#pragma unroll
+  for (int w = 0; w < kQuantThreads / 32; ++w) total += warp_sums[w];
+  const float inv_rms = rsqrtf(total / static_cast<float>(k) + eps);
+#pragma unroll
+  for (int u = 0; u < kNormChunks; ++u) {
+    const int c = u * kQuantThreads + threadIdx.x;
+    const bool valid = c < row_chunks;
+    float v[8], g[8];
+    raw[u].unpack(v);
+    Vec8<T> wv;
+    wv.raw = make_uint4(0u, 0u, 0u, 0u);
+    if (valid) wv.raw = __ldg(wsrc + c);
+    wv.unpack(g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = round_to<T>((v[i] * inv_rms) * g[i]);
+    float amax = absmax8(v);
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
+    const float inv = ue8m0_inverse(sbits);
+    const uint32_t code = sbits >> 23;
+    uint32_t word = code;
+    word |= __shfl_down_sync(0xffffffffu, code, 4) << 8;
+    word |= __shfl_down_sync(0xffffffffu, code, 8) << 16;
+    word |= __shfl_down_sync(0xffffffffu, code, 12) << 24;
+    if (valid) {
+      uint32_t w2[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+            make_float2(v[4 * i] * inv, v[4 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+            make_float2(v[4 * i + 2] * inv, v[4 * i + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+        w2[i] = lo | (hi << 16);
+      }
+      reinterpret_cast<uint2*>(out)[row * row_chunks + c] = make_uint2(w2[0], w2[1]);
+      const int g_index = c >> 2;
+      if (quad_scales) {
+        if ((threadIdx.x & 15) == 0) {
+          if (logical != nullptr)
+            *reinterpret_cast<uint32_t*>(logical + row * groups + g_index) = word;
+          if (packed != nullptr)
+            *reinterpret_cast<uint32_t*>(packed + packed_scale_offset(row, g_index, groups)) = word;
+        }
+      } else if ((c & 3) == 0) {
+        if (logical != nullptr) logical[row * groups + g_index] = static_cast<uint8_t>(code);
+        if (packed != nullptr)
+          packed[packed_scale_offset(row, g_index, groups)] = static_cast<uint8_t>(code);
+      }
+    }
+  }
+  if (packed != nullptr && pad_begin < pad_total) {
+    fill_scale_padding(packed, pad_begin, pad_total, rows, groups,
+                       static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x,
+                       static_cast<int64_t>(gridDim.x) * blockDim.x);
+  }
+}
+
 int check_args(const void* in, int dtype, int64_t rows, int64_t k, const void* values) {
   MX_REQUIRE(in != nullptr && values != nullptr, "input and output pointers must not be null");
   MX_REQUIRE(dtype == kF16 || dtype == kBF16, "input must be float16 or bfloat16");
@@ -301,6 +431,45 @@ int quantize_mxfp6(const void* in, int dtype, int64_t rows, int64_t k, uint8_t* 
     quantize_mxfp6_kernel<__half><<<grid, kQuantThreads, 0, stream>>>(
         static_cast<const __half*>(in), values, packed, logical, rows, static_cast<int>(k),
         pad_begin, pad_total);
+  }
+  MX_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int rmsnorm_quantize_mxfp8(const void* in, const void* residual, void* updated, int dtype,
+                           const void* weight, float eps, int64_t rows, int64_t k, uint8_t* values,
+                           uint8_t* packed, uint8_t* logical, cudaStream_t stream) {
+  if (int rc = check_args(in, dtype, rows, k, values)) return rc;
+  MX_REQUIRE((residual == nullptr) == (updated == nullptr),
+             "residual and updated go together");
+  MX_REQUIRE(residual == nullptr || ((reinterpret_cast<uintptr_t>(residual) & 15) == 0 &&
+                                     (reinterpret_cast<uintptr_t>(updated) & 15) == 0),
+             "residual / updated must be 16-byte aligned");
+  MX_REQUIRE(weight != nullptr && (reinterpret_cast<uintptr_t>(weight) & 15) == 0,
+             "the norm weight must be a 16-byte aligned device pointer");
+  MX_REQUIRE(packed != nullptr || logical != nullptr, "at least one scale output is required");
+  MX_REQUIRE((reinterpret_cast<uintptr_t>(values) & 7) == 0, "values must be 8-byte aligned");
+  MX_REQUIRE(k % 8 == 0 && k <= kNormChunks * 8 * kQuantThreads,
+             "the fused norm keeps a row in registers: K must be at most %d; got %lld",
+             kNormChunks * 8 * kQuantThreads, (long long)k);
+  MX_REQUIRE(eps >= 0.0f, "eps must not be negative");
+  int64_t pad_begin = 0, pad_total = 0;
+  if (packed != nullptr) padding_range(rows, k, &pad_begin, &pad_total);
+  // Word-wide scale stores: a row of whole quads of groups, so that 16 consecutive
+  // threads hold four consecutive groups of one row.
+  const bool quad = (k / kScaleVec) % 4 == 0 && (reinterpret_cast<uintptr_t>(packed) & 3) == 0 &&
+                    (reinterpret_cast<uintptr_t>(logical) & 3) == 0;
+  const unsigned grid = static_cast<unsigned>(rows);
+  if (dtype == kBF16) {
+    rmsnorm_quantize_mxfp8_kernel<__nv_bfloat16><<<grid, kQuantThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(in), static_cast<const __nv_bfloat16*>(residual),
+        static_cast<__nv_bfloat16*>(updated), static_cast<const __nv_bfloat16*>(weight), eps,
+        values, packed, logical, rows, static_cast<int>(k), pad_begin, pad_total, quad);
+  } else {
+    rmsnorm_quantize_mxfp8_kernel<__half><<<grid, kQuantThreads, 0, stream>>>(
+        static_cast<const __half*>(in), static_cast<const __half*>(residual),
+        static_cast<__half*>(updated), static_cast<const __half*>(weight), eps, values, packed,
+        logical, rows, static_cast<int>(k), pad_begin, pad_total, quad);
   }
   MX_CUDA(cudaGetLastError());
   return kOk;

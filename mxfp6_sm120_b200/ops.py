@@ -553,6 +553,52 @@ def quantize_mxfp8_dual_out(
     _quantize_mxfp8_raw(input, output, packed_scales, logical_scales)
 
 
+def rmsnorm_quantize_mxfp8(
+    input: torch.Tensor,
+    weight: torch.Tensor,
+    eps: float = 1e-6,
+    *,
+    residual: torch.Tensor | None = None,
+    values: torch.Tensor | None = None,
+    scales: torch.Tensor | None = None,
+) -> MXFP8Tensor:
+    """(Residual add,) RMSNorm and MXFP8 quantization of a ``[M,K]`` activation in one pass.
+
+    With ``residual`` the input is first updated IN PLACE to ``round(input + residual)``
+    (the residual stream of a decoder layer).  Then ``y = ((x * rsqrt(mean(x^2) + eps)) *
+    weight)`` rounded once to the input dtype (the rule of
+    ``torch.nn.functional.rms_norm``) is quantized like :func:`quantize_mxfp8`.
+    ``values`` / ``scales`` let a caller reuse buffers (CUDA-graph capture).
+    """
+    rows, k = _validate_float_activation(input)
+    if residual is not None and (
+        residual.shape != input.shape or residual.dtype != input.dtype
+        or residual.device != input.device or not residual.is_contiguous()
+    ):
+        raise ValueError("residual must match the input's shape, dtype and device")
+    if weight.dtype != input.dtype or weight.shape != (k,) or not weight.is_contiguous():
+        raise ValueError("weight must be a contiguous [K] tensor of the input dtype")
+    if weight.device != input.device:
+        raise ValueError("weight must be on the input's device")
+    _require_sm100(input.device)
+    load_library()
+    if values is None:
+        values = torch.empty(rows * k, dtype=torch.uint8, device=input.device)
+    if scales is None:
+        scales = torch.empty(packed_scale_numel(rows, k), dtype=torch.uint8, device=input.device)
+    if values.numel() < rows * k or scales.numel() < packed_scale_numel(rows, k):
+        raise ValueError("values / scales are too small for the activation")
+    with torch.cuda.device(input.device):
+        check(
+            library().mxfp6_rmsnorm_quantize_mxfp8(
+                input.data_ptr(), _ptr(residual), None if residual is None else input.data_ptr(),
+                _DTYPE_CODE[input.dtype], weight.data_ptr(), float(eps), rows, k,
+                values.data_ptr(), scales.data_ptr(), None, _stream(input.device),
+            )
+        )
+    return MXFP8Tensor(values, scales, rows, k)
+
+
 def quantize_activation(input: torch.Tensor) -> MXFP8Tensor:
     """Alias of :func:`quantize_mxfp8` (the 16-to-8 activation mapping)."""
     return quantize_mxfp8(input)
