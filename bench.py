@@ -319,6 +319,72 @@ def moe_layer_latency_ep(mx, device, stream, world: int, rank: int) -> dict:
             "rows": rows}
 
 
+def decoder_step_latency(mx, device, stream, world: int, rank: int) -> dict:
+    """Decode (32 sequences, 4000-token context) and prefill (8192 tokens) step of the
+    64-layer 27B-class dense decoder, every linear W6A8, CUDA-graph replayed; under
+    torchrun the layers are tensor parallel (heads and MLP columns per rank, NCCL
+    all-reduce after the two row-parallel projections).  Max over ranks."""
+    import torch.distributed as dist
+
+    cfg = mx.DecoderConfig()
+    group = dist.group.WORLD if world > 1 else None
+    with torch.cuda.stream(stream):
+        model = mx.DenseDecoder.random(cfg, device, seed=5000, world=world, rank=rank, group=group)
+    weight_bytes = model.weight_bytes()
+
+    def timed(step, reps):
+        with torch.cuda.stream(stream):
+            step()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step()
+            graph.replay()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize(device)
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            stop.record(stream)
+            stream.synchronize()
+        t = torch.tensor([start.elapsed_time(stop) / reps], device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    out = {"config": "64 layers, hidden 5120, 24 query / 4 KV heads of 256, MLP 17408, RMSNorm; "
+                     "BF16 attention (torch SDPA), all linears W6A8; random-init weights",
+           "parallelism": "single GPU" if world == 1 else f"tp{world}",
+           "weight_bytes_per_rank": weight_bytes}
+    batch, context = 32, 4000
+    ws = model.workspace(batch)
+    cache = model.new_kv_cache(batch, context + 1)
+    gen = torch.Generator(device=device).manual_seed(5100)
+    ws.x.copy_(torch.randn((batch, cfg.hidden), generator=gen, device=device).to(torch.bfloat16))
+    decode_ms = timed(lambda: model.decode_step(ws, cache, context), 5)
+    kv_bytes = 2 * len(cache) * cache[0][0].numel() * 2
+    out["decode"] = {"sequences": batch, "context": context, "ms_per_step": round(decode_ms, 3),
+                     "tokens_per_s": round(batch / (decode_ms * 1e-3), 1),
+                     "gbs_weights_plus_kv": round((weight_bytes + kv_bytes) / (decode_ms * 1e-3) / 1e9, 1)}
+    del cache, ws
+    torch.cuda.empty_cache()
+    tokens = 8192
+    ws = model.workspace(tokens)
+    ws.x.copy_(torch.randn((tokens, cfg.hidden), generator=gen, device=device).to(torch.bfloat16))
+    prefill_ms = timed(lambda: model.prefill(ws), 2)
+    hd = cfg.head_dim
+    linear_flops = 2.0 * tokens * cfg.layers * cfg.hidden * (
+        (cfg.q_heads + 2 * cfg.kv_heads) * hd + cfg.q_heads * hd + 3 * cfg.intermediate)
+    out["prefill"] = {"tokens": tokens, "ms_per_step": round(prefill_ms, 2),
+                      "tokens_per_s": round(tokens / (prefill_ms * 1e-3), 1),
+                      "linear_tflops_whole_job": round(linear_flops / (prefill_ms * 1e-3) / 1e12, 1)}
+    del ws, model
+    torch.cuda.empty_cache()
+    return out
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -328,6 +394,7 @@ def main() -> None:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--no-moe", action="store_true")
+    parser.add_argument("--no-decoder", action="store_true")
     parser.add_argument("--no-per-shape", action="store_true",
                         help="skip the per-shape GEMM-only timing (used for profiler launch lists)")
     args = parser.parse_args()
@@ -481,6 +548,10 @@ def main() -> None:
         elif not args.no_moe:
             moe = moe_layer_latency_ep(mx, device, stream, world, rank)
 
+        decoder = None
+        if not args.no_decoder:
+            decoder = decoder_step_latency(mx, device, stream, world, rank)
+
     status = mx.device_status(device)
     if rank != 0:
         finish(world)
@@ -538,6 +609,8 @@ def main() -> None:
         line["e2e"] = e2e
     if moe is not None:
         line["moe_layer"] = moe
+    if decoder is not None:
+        line["decoder_step"] = decoder
     if not args.no_cpu_baseline and world == 1:
         base = cpu_reference_sample(os.cpu_count() or 1)
         line["cpu_baseline"] = {key: base[key] for key in ("value", "unit", "cores", "kind", "sample")}

@@ -52,6 +52,15 @@ const char* last_error();
     }                                                                        \
   } while (0)
 
+// SiLU table (silu_table.cu): s = bf16(g / (1 + expf(-g))) for every BF16 bit pattern of g.
+int silu_table(cudaStream_t stream, const uint16_t** out);
+#ifdef __CUDACC__
+// `g` must already be rounded to BF16 (its low 16 bits are zero).
+__device__ __forceinline__ float silu_bf16_lookup(const uint16_t* __restrict__ table, float g) {
+  return __uint_as_float(static_cast<uint32_t>(__ldg(table + (__float_as_uint(g) >> 16))) << 16);
+}
+#endif
+
 __host__ __device__ __forceinline__ int64_t ceil_div64(int64_t a, int64_t b) {
   return (a + b - 1) / b;
 }

@@ -511,7 +511,8 @@ __global__ void __launch_bounds__(256)
 silu_mul_quant_kernel(const T* __restrict__ input, uint8_t* __restrict__ output,
                       uint8_t* __restrict__ logical, uint8_t* __restrict__ packed, int64_t rows,
                       int inter, const int64_t* __restrict__ expert_offsets,
-                      const int64_t* __restrict__ scale_offsets, int experts) {
+                      const int64_t* __restrict__ scale_offsets, int experts,
+                      const uint16_t* __restrict__ silu_lut) {
   __shared__ int row_begin[kMaxExperts + 1];
   __shared__ int scale_begin[kMaxExperts + 1];
   const bool grouped = expert_offsets != nullptr;
@@ -552,7 +553,7 @@ silu_mul_quant_kernel(const T* __restrict__ input, uint8_t* __restrict__ output,
         for (int i = 0; i < 8; ++i) {
           const float g = round_bf16(to_float(gv[i]));
           const float u = round_bf16(to_float(uv[i]));
-          const float sv = round_bf16(__fdiv_rn(g, 1.0f + expf(-g)));
+          const float sv = silu_bf16_lookup(silu_lut, g);  // = bf16(g / (1 + expf(-g)))
           v[i] = round_bf16(sv * u);
         }
       }
@@ -779,16 +780,18 @@ int silu_mul_quant(const void* input, int dtype, int64_t rows, int inter, uint8_
              "expert_offsets and scale_offsets go together");
   MX_REQUIRE(expert_offsets == nullptr || (experts > 0 && experts <= kMaxExperts),
              "experts must be in [1, %d]", kMaxExperts);
+  const uint16_t* silu_lut = nullptr;
+  if (int rc = silu_table(stream, &silu_lut)) return rc;
   int64_t blocks = (rows + 7) / 8;  // one warp per row, eight warps per CTA
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (dtype == kBF16) {
     silu_mul_quant_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(input), output, logical, packed, rows, inter,
-        expert_offsets, scale_offsets, experts);
+        expert_offsets, scale_offsets, experts, silu_lut);
   } else {
     silu_mul_quant_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>(
         static_cast<const __half*>(input), output, logical, packed, rows, inter, expert_offsets,
-        scale_offsets, experts);
+        scale_offsets, experts, silu_lut);
   }
   MX_CUDA(cudaGetLastError());
   return kOk;

@@ -3,6 +3,8 @@
     python -m mxfp6_sm120_b200.run_shape --op gemm --m 16 --n 34816 --k 5120 --iters 3
     python -m mxfp6_sm120_b200.run_shape --op quantize --m 8192 --k 5120
     python -m mxfp6_sm120_b200.run_shape --op moe --m 32
+    python -m mxfp6_sm120_b200.run_shape --op decode --m 32 --context 4000 --layers 2
+    python -m mxfp6_sm120_b200.run_shape --op prefill --m 8192 --layers 1
 
 Prints the mean device time per call: ``--iters`` calls are captured in one CUDA graph
 and the replay is timed with CUDA events.
@@ -19,13 +21,15 @@ import mxfp6_sm120_b200 as mx
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--op", default="gemm", choices=["gemm", "quantize", "moe"])
+    parser.add_argument("--op", default="gemm", choices=["gemm", "quantize", "moe", "decode", "prefill"])
     parser.add_argument("--m", type=int, default=16)
     parser.add_argument("--n", type=int, default=34816)
     parser.add_argument("--k", type=int, default=5120)
     parser.add_argument("--iters", type=int, default=3)
     parser.add_argument("--tile", type=int, default=0)
     parser.add_argument("--splits", type=int, default=0)
+    parser.add_argument("--context", type=int, default=4000)
+    parser.add_argument("--layers", type=int, default=2)
     args = parser.parse_args()
     device = torch.device("cuda:0")
     gen = torch.Generator(device=device).manual_seed(0)
@@ -44,6 +48,21 @@ def main() -> None:
         def call():
             return mx.gemm_w6a8_config(act, weight, out_dtype=torch.bfloat16, tile_tokens=args.tile,
                                        splits=args.splits)
+    elif args.op in ("decode", "prefill"):
+        # --m sequences with --context cached tokens each, or one sequence of --m tokens,
+        # through --layers layers of the 27B-class dense decoder.
+        cfg = mx.DecoderConfig()
+        model = mx.DenseDecoder.random(cfg, device, seed=5000, layers=args.layers)
+        space = model.workspace(args.m)
+        space.x.copy_(torch.randn((args.m, cfg.hidden), generator=gen, device=device).to(torch.bfloat16))
+        if args.op == "decode":
+            cache = model.new_kv_cache(args.m, args.context + 1)
+
+            def call():
+                return model.decode_step(space, cache, args.context)
+        else:
+            def call():
+                return model.prefill(space)
     else:
         from mxfp6_sm120_b200.moe_layer import MoeLayer
 
