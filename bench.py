@@ -331,6 +331,15 @@ def decoder_step_latency(mx, device, stream, world: int, rank: int) -> dict:
     with torch.cuda.stream(stream):
         model = mx.DenseDecoder.random(cfg, device, seed=5000, world=world, rank=rank, group=group)
     weight_bytes = model.weight_bytes()
+    nccl_model = None
+    if world > 1:
+        # The product path reduces the row-parallel projections inside the residual + norm +
+        # quantize kernel over peer memory; the NCCL all-reduce variant is timed beside it.
+        from mxfp6_sm120_b200.tp_fused import SymmetricBlocks
+
+        nccl_model = model
+        peer = SymmetricBlocks(8192, cfg.hidden, device, group)
+        model = mx.DenseDecoder(cfg, nccl_model.layers, world, rank, group, peer)
 
     def timed(step, reps):
         with torch.cuda.stream(stream):
@@ -368,18 +377,25 @@ def decoder_step_latency(mx, device, stream, world: int, rank: int) -> dict:
     out["decode"] = {"sequences": batch, "context": context, "ms_per_step": round(decode_ms, 3),
                      "tokens_per_s": round(batch / (decode_ms * 1e-3), 1),
                      "gbs_weights_plus_kv": round((weight_bytes + kv_bytes) / (decode_ms * 1e-3) / 1e9, 1)}
+    if nccl_model is not None:
+        out["decode"]["all_reduce"] = "fused into the norm kernel over peer memory"
+        out["decode"]["ms_per_step_nccl_all_reduce"] = round(
+            timed(lambda: nccl_model.decode_step(ws, cache, context), 5), 3)
     del cache, ws
     torch.cuda.empty_cache()
     tokens = 8192
     ws = model.workspace(tokens)
     ws.x.copy_(torch.randn((tokens, cfg.hidden), generator=gen, device=device).to(torch.bfloat16))
     prefill_ms = timed(lambda: model.prefill(ws), 2)
+    prefill_nccl_ms = timed(lambda: nccl_model.prefill(ws), 2) if nccl_model is not None else None
     hd = cfg.head_dim
     linear_flops = 2.0 * tokens * cfg.layers * cfg.hidden * (
         (cfg.q_heads + 2 * cfg.kv_heads) * hd + cfg.q_heads * hd + 3 * cfg.intermediate)
     out["prefill"] = {"tokens": tokens, "ms_per_step": round(prefill_ms, 2),
                       "tokens_per_s": round(tokens / (prefill_ms * 1e-3), 1),
                       "linear_tflops_whole_job": round(linear_flops / (prefill_ms * 1e-3) / 1e12, 1)}
+    if prefill_nccl_ms is not None:
+        out["prefill"]["ms_per_step_nccl_all_reduce"] = round(prefill_nccl_ms, 2)
     del ws, model
     torch.cuda.empty_cache()
     return out

@@ -104,6 +104,34 @@ int mxfp6_quantize_mxfp6(const void* input_dev, int dtype, int64_t rows, int64_t
                          uint8_t* values_dev, uint8_t* packed_scales_dev,
                          uint8_t* logical_scales_dev, void* stream);
 
+/* ---- tensor-parallel decode path over peer memory ------------------------------ */
+
+/* All-reduce of a row-parallel projection fused with the residual add, RMSNorm and MXFP8
+ * quantization that consume it (the B200 successor of the reference's two-rank reducer with
+ * peer signal pointers, csrc/moe.cu:7698-7925; every wait here is bounded).
+ *
+ * Set-up, once: every rank allocates a symmetric block (flags + state + two partial
+ * buffers of partial_bytes each, a multiple of 256), sends its 64-byte CUDA IPC handle to
+ * its peers (any host channel) and opens theirs.  A row-parallel GEMM writes its BF16
+ * [rows, k] partial at block + MXFP6_TP_BLOCK_HEADER_BYTES + buffer * partial_bytes of its
+ * OWN block, alternating buffer 0 / 1 from one fused call to the next.  Then on every rank,
+ * on the stream the GEMM ran on:
+ *   x <- bf16(x + bf16(sum over ranks, in rank order, of the partials));
+ *   values / packed_scales <- MXFP8(round(x * rsqrt(mean(x^2) + eps) * weight)).
+ * blocks_host[r] is this process's mapping of rank r's block (its own allocation for
+ * r == rank).  All ranks must issue the same sequence of calls.  A peer that does not
+ * arrive within about 2 s sets device status 301 and leaves x unchanged. */
+#define MXFP6_TP_BLOCK_HEADER_BYTES 1024
+int mxfp6_tp_block_alloc(size_t partial_bytes, void** block_dev_out, unsigned char handle_out[64]);
+int mxfp6_tp_block_open(const unsigned char handle[64], void** block_dev_out);
+int mxfp6_tp_block_close(void* block_dev);
+int mxfp6_tp_block_free(void* block_dev);
+int mxfp6_tp_allreduce_rmsnorm_quantize_mxfp8(void* const* blocks_host, int world, int rank,
+                                              int buffer, size_t partial_bytes, void* x_dev,
+                                              const void* weight_dev, float eps, int64_t rows,
+                                              int64_t k, uint8_t* values_dev,
+                                              uint8_t* packed_scales_dev, void* stream);
+
 /* ---- dense W6A8 GEMM ------------------------------------------------------ */
 
 /* torch.ops.mxfp6.gemm_w6a8 (csrc/torch_extension.cu:1769-1845):

@@ -38,6 +38,15 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p],
     ),
+    "mxfp6_tp_block_alloc": (c_int, [c_size_t, POINTER(c_void_p), c_void_p]),
+    "mxfp6_tp_block_open": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "mxfp6_tp_block_close": (c_int, [c_void_p]),
+    "mxfp6_tp_block_free": (c_int, [c_void_p]),
+    "mxfp6_tp_allreduce_rmsnorm_quantize_mxfp8": (
+        c_int,
+        [POINTER(c_void_p), c_int, c_int, c_int, c_size_t, c_void_p, c_void_p, c_float, c_int64,
+         c_int64, c_void_p, c_void_p, c_void_p],
+    ),
     "mxfp6_rmsnorm_quantize_mxfp8": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_float, c_int64, c_int64, c_void_p,

@@ -30,6 +30,12 @@ const char* last_error() { return g_error; }
 
 // ---- kernels implemented in the other translation units ------------------------
 int quantize_mxfp8(const void*, int, int64_t, int64_t, uint8_t*, uint8_t*, uint8_t*, cudaStream_t);
+int tp_block_alloc(size_t, void**, unsigned char*);
+int tp_block_open(const unsigned char*, void**);
+int tp_block_close(void*);
+int tp_block_free(void*);
+int tp_allreduce_rmsnorm_quantize(void* const*, int, int, int, size_t, void*, const void*, float,
+                                  int64_t, int64_t, uint8_t*, uint8_t*, int*, cudaStream_t);
 int rmsnorm_quantize_mxfp8(const void*, const void*, void*, int, const void*, float, int64_t,
                            int64_t, uint8_t*, uint8_t*, uint8_t*, cudaStream_t);
 int quantize_mxfp6(const void*, int, int64_t, int64_t, uint8_t*, uint8_t*, uint8_t*, cudaStream_t);
@@ -297,6 +303,26 @@ int mxfp6_rmsnorm_quantize_mxfp8(const void* input, const void* residual, void* 
                                  void* stream) {
   return rmsnorm_quantize_mxfp8(input, residual, updated, dtype, weight, eps, rows, k, values,
                                 packed_scales, logical_scales, static_cast<cudaStream_t>(stream));
+}
+int mxfp6_tp_block_alloc(size_t partial_bytes, void** block, unsigned char handle[64]) {
+  return tp_block_alloc(partial_bytes, block, handle);
+}
+int mxfp6_tp_block_open(const unsigned char handle[64], void** block) {
+  return tp_block_open(handle, block);
+}
+int mxfp6_tp_block_close(void* block) { return tp_block_close(block); }
+int mxfp6_tp_block_free(void* block) { return tp_block_free(block); }
+int mxfp6_tp_allreduce_rmsnorm_quantize_mxfp8(void* const* blocks, int world, int rank, int buffer,
+                                              size_t partial_bytes, void* x, const void* weight,
+                                              float eps, int64_t rows, int64_t k, uint8_t* values,
+                                              uint8_t* packed_scales, void* stream) {
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  int* status = device_status_word(device);
+  if (status == nullptr) return kCudaError;
+  return tp_allreduce_rmsnorm_quantize(blocks, world, rank, buffer, partial_bytes, x, weight, eps,
+                                       rows, k, values, packed_scales, status,
+                                       static_cast<cudaStream_t>(stream));
 }
 int mxfp6_quantize_mxfp6(const void* input, int dtype, int64_t rows, int64_t k, uint8_t* values,
                          uint8_t* packed_scales, uint8_t* logical_scales, void* stream) {

@@ -1,0 +1,315 @@
+// Tensor-parallel decode path: all-reduce of a row-parallel projection fused with the
+// residual add, RMSNorm and MXFP8 quantization that consume it, over peer memory.
+//
+// Every rank of one node owns a "symmetric" block (one cudaMalloc, exported with CUDA IPC
+// and mapped by its peers): a flag word per rank, a small state record and two partial
+// buffers.  A row-parallel GEMM writes its [M, hidden] BF16 partial into one of its OWN
+// partial buffers (plain local stores).  The consumer kernel on every rank then
+//   1. tells every peer "my partial of this step is complete" (one 32-bit store into the
+//      peer's flag array, after a system-scope fence; the GEMM ended earlier on the stream),
+//   2. waits (bounded) until every rank's flag has reached this step,
+//   3. loads the same row from all ranks' buffers over NVLink (plain peer loads, no
+//      multicast), sums them in rank order in FP32 -> BF16 (every rank forms the same
+//      sum, so the replicas of the residual stream stay bit-identical),
+//   4. adds the residual stream, normalises, quantizes (as rmsnorm_quantize_mxfp8).
+// So the collective costs one flag round trip plus the peer loads; nothing is written to a
+// peer but the flag.  The reference's counterpart is the two-rank reducer with peer signal
+// pointers and unbounded spins (csrc/moe.cu:7698-7925).
+//
+// Buffers alternate (the projection before the first norm of a layer uses buffer 0, the one
+// before the second norm buffer 1): a rank that has passed step s + 1 has seen every peer
+// finish step s, so a buffer is rewritten only after all its readers are done.
+// The step number lives in device memory and is advanced by the last CTA of the kernel,
+// which keeps CUDA-graph replays correct.  Every wait is bounded (about 2 s): on expiry the
+// kernel records a code in the status word and returns without touching peer data.
+#include "common.cuh"
+
+#include <cuda_fp8.h>
+#include <cstring>
+
+namespace mx {
+
+constexpr int kTpMaxRanks = 8;
+constexpr int kTpThreads = 256;
+constexpr int kTpChunks = 8;  // 8-value chunks per thread: hidden <= 16384
+constexpr size_t kTpHeaderBytes = 1024;
+
+struct TpState {
+  uint32_t done_step;  // steps this rank has completed
+  uint32_t finished;   // CTAs of the running kernel that are done
+};
+
+struct TpPeers {
+  const void* partial[kTpMaxRanks];  // every rank's partial buffer of this step (peer mapped)
+  uint32_t* flags[kTpMaxRanks];      // every rank's flag array (index = sender)
+  int world;
+  int rank;
+};
+
+namespace {
+
+__device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_volatile_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_u128(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float (&v)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ uint4 pack_bf16x8(const float (&v)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rn(v[2 * i]));
+    const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rn(v[2 * i + 1]));
+    w[i] = lo | (hi << 16);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// x[row] <- bf16(x[row] + bf16(sum over ranks of partial_r[row])); then RMSNorm * weight and
+// MXFP8 with packed scales.  One CTA per row.
+__global__ void __launch_bounds__(kTpThreads)
+allreduce_rmsnorm_quantize_kernel(const TpPeers peers, TpState* state, __nv_bfloat16* x,
+                                  const __nv_bfloat16* __restrict__ weight, float eps,
+                                  uint8_t* __restrict__ out, uint8_t* __restrict__ packed,
+                                  int64_t rows, int k, int* status) {
+  __shared__ float warp_sums[kTpThreads / 32];
+  __shared__ uint32_t step_shared;
+  __shared__ int ok_shared;
+  const int row_chunks = k / 8;
+  const int groups = k / kScaleVec;
+  const int64_t row = blockIdx.x;
+
+  // ---- the cross-rank handshake -------------------------------------------------------
+  if (threadIdx.x == 0) {
+    step_shared = ld_volatile_u32(&state->done_step) + 1u;
+    ok_shared = 1;
+  }
+  __syncthreads();
+  const uint32_t step = step_shared;
+  if (blockIdx.x == 0 && threadIdx.x < peers.world) {
+    // The GEMM that wrote this rank's partial finished earlier on this stream; the fence
+    // orders its (already performed) writes before the flag for observers on other GPUs.
+    __threadfence_system();
+    st_volatile_u32(peers.flags[threadIdx.x] + peers.rank, step);
+  }
+  if (threadIdx.x < peers.world) {
+    const uint32_t* flag = peers.flags[peers.rank] + threadIdx.x;
+    const long long start = clock64();
+    bool seen = false;
+#pragma unroll 1
+    for (uint32_t spin = 0;; ++spin) {
+      if (static_cast<int32_t>(ld_volatile_u32(flag) - step) >= 0) {
+        seen = true;
+        break;
+      }
+      if ((spin & 255u) == 255u && clock64() - start > 4000000000ll) break;
+    }
+    if (!seen) {
+      ok_shared = 0;
+      atomicCAS(status, 0, 301);
+    }
+    __threadfence_system();
+  }
+  __syncthreads();
+  const bool ok = ok_shared != 0;
+
+  if (ok) {
+    // ---- all-reduce of this row + residual --------------------------------------------
+    uint4 raw[kTpChunks];
+    uint4* xrow = reinterpret_cast<uint4*>(x) + row * row_chunks;
+    float sum_sq = 0.0f;
+#pragma unroll
+    for (int u = 0; u < kTpChunks; ++u) {
+      const int c = u * kTpThreads + threadIdx.x;
+      raw[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (c < row_chunks) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < peers.world; ++r) {
+          const uint4 p =
+              ld_volatile_u128(reinterpret_cast<const uint4*>(peers.partial[r]) + row * row_chunks + c);
+          float v[8];
+          unpack_bf16x8(p, v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += v[i];
+        }
+        float xv[8];
+        unpack_bf16x8(xrow[c], xv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float reduced = __bfloat162float(__float2bfloat16_rn(acc[i]));
+          xv[i] = __bfloat162float(__float2bfloat16_rn(xv[i] + reduced));
+          sum_sq = fmaf(xv[i], xv[i], sum_sq);
+        }
+        raw[u] = pack_bf16x8(xv);
+        xrow[c] = raw[u];
+      }
+    }
+    // ---- RMSNorm + MXFP8 (as rmsnorm_quantize_mxfp8_kernel) ---------------------------
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum_sq += __shfl_xor_sync(0xffffffffu, sum_sq, d);
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = sum_sq;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kTpThreads / 32; ++w) total += warp_sums[w];
+    const float inv_rms = rsqrtf(total / static_cast<float>(k) + eps);
+    const uint4* wsrc = reinterpret_cast<const uint4*>(weight);
+#pragma unroll
+    for (int u = 0; u < kTpChunks; ++u) {
+      const int c = u * kTpThreads + threadIdx.x;
+      const bool valid = c < row_chunks;
+      float v[8], g[8];
+      unpack_bf16x8(raw[u], v);
+      uint4 wraw = make_uint4(0u, 0u, 0u, 0u);
+      if (valid) wraw = __ldg(wsrc + c);
+      unpack_bf16x8(wraw, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = round_bf16((v[i] * inv_rms) * g[i]);
+      float amax = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
+      const float inv = ue8m0_inverse(sbits);
+      const uint32_t code = sbits >> 23;
+      uint32_t word = code;
+      word |= __shfl_down_sync(0xffffffffu, code, 4) << 8;
+      word |= __shfl_down_sync(0xffffffffu, code, 8) << 16;
+      word |= __shfl_down_sync(0xffffffffu, code, 12) << 24;
+      if (valid) {
+        uint32_t w2[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+              make_float2(v[4 * i] * inv, v[4 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+          const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+              make_float2(v[4 * i + 2] * inv, v[4 * i + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+          w2[i] = lo | (hi << 16);
+        }
+        reinterpret_cast<uint2*>(out)[row * row_chunks + c] = make_uint2(w2[0], w2[1]);
+        // groups % 4 == 0 is required by the host: 16 lanes = four groups = one word.
+        if ((threadIdx.x & 15) == 0) {
+          *reinterpret_cast<uint32_t*>(packed + packed_scale_offset(row, c >> 2, groups)) = word;
+        }
+      }
+    }
+  }
+
+  // ---- the last CTA advances the step (also after a timeout, so that ranks stay aligned) --
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t done = atomicAdd(&state->finished, 1u);
+    if (done == gridDim.x - 1) {
+      state->finished = 0u;
+      st_volatile_u32(&state->done_step, step);
+      __threadfence();
+    }
+  }
+}
+
+}  // namespace
+
+// ---- symmetric block: allocation and CUDA IPC ------------------------------------------
+// Layout: [flags: kTpMaxRanks x u32 | TpState | pad to 1024 B | partial 0 | partial 1].
+int tp_block_alloc(size_t partial_bytes, void** block, unsigned char handle[64]) {
+  MX_REQUIRE(block != nullptr && handle != nullptr, "pointers must not be null");
+  MX_REQUIRE(partial_bytes > 0 && partial_bytes % 256 == 0,
+             "the partial buffer size must be a positive multiple of 256 bytes");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handles are 64 bytes");
+  void* p = nullptr;
+  const size_t bytes = kTpHeaderBytes + 2 * partial_bytes;
+  MX_CUDA(cudaMalloc(&p, bytes));
+  MX_CUDA(cudaMemset(p, 0, bytes));
+  MX_CUDA(cudaDeviceSynchronize());
+  cudaIpcMemHandle_t h;
+  MX_CUDA(cudaIpcGetMemHandle(&h, p));
+  memcpy(handle, &h, 64);
+  *block = p;
+  return kOk;
+}
+
+int tp_block_open(const unsigned char handle[64], void** block) {
+  MX_REQUIRE(block != nullptr && handle != nullptr, "pointers must not be null");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  MX_CUDA(cudaIpcOpenMemHandle(block, h, cudaIpcMemLazyEnablePeerAccess));
+  return kOk;
+}
+
+int tp_block_close(void* block) {
+  MX_CUDA(cudaIpcCloseMemHandle(block));
+  return kOk;
+}
+
+int tp_block_free(void* block) {
+  MX_CUDA(cudaFree(block));
+  return kOk;
+}
+
+int tp_allreduce_rmsnorm_quantize(void* const* blocks, int world, int rank, int buffer,
+                                  size_t partial_bytes, void* x, const void* weight, float eps,
+                                  int64_t rows, int64_t k, uint8_t* values, uint8_t* packed,
+                                  int* status, cudaStream_t stream) {
+  MX_REQUIRE(blocks != nullptr && world >= 1 && world <= kTpMaxRanks && rank >= 0 && rank < world,
+             "world must be in [1, %d] and rank inside it", kTpMaxRanks);
+  MX_REQUIRE(buffer == 0 || buffer == 1, "buffer must be 0 or 1");
+  MX_REQUIRE(x != nullptr && weight != nullptr && values != nullptr && packed != nullptr,
+             "pointers must not be null");
+  MX_REQUIRE(rows > 0 && rows <= INT32_MAX, "rows must be positive");
+  MX_REQUIRE(k > 0 && k % 128 == 0 && k <= kTpChunks * 8 * kTpThreads,
+             "k must be a multiple of 128 and at most %d; got %lld", kTpChunks * 8 * kTpThreads,
+             (long long)k);
+  MX_REQUIRE((size_t)rows * (size_t)k * 2 <= partial_bytes,
+             "the partial buffers hold %zu bytes, %lld x %lld BF16 need more", partial_bytes,
+             (long long)rows, (long long)k);
+  MX_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(weight) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(values) & 7) == 0 &&
+                 (reinterpret_cast<uintptr_t>(packed) & 3) == 0,
+             "x / weight must be 16-byte, values 8-byte, scales 4-byte aligned");
+  TpPeers peers;
+  peers.world = world;
+  peers.rank = rank;
+  for (int r = 0; r < kTpMaxRanks; ++r) {
+    peers.partial[r] = nullptr;
+    peers.flags[r] = nullptr;
+  }
+  for (int r = 0; r < world; ++r) {
+    MX_REQUIRE(blocks[r] != nullptr, "block of rank %d is null", r);
+    auto* base = static_cast<uint8_t*>(blocks[r]);
+    peers.flags[r] = reinterpret_cast<uint32_t*>(base);
+    peers.partial[r] = base + kTpHeaderBytes + (size_t)buffer * partial_bytes;
+  }
+  auto* state = reinterpret_cast<TpState*>(static_cast<uint8_t*>(blocks[rank]) +
+                                           kTpMaxRanks * sizeof(uint32_t));
+  allreduce_rmsnorm_quantize_kernel<<<(unsigned)rows, kTpThreads, 0, stream>>>(
+      peers, state, static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight),
+      eps, values, packed, rows, static_cast<int>(k), status);
+  MX_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+size_t tp_block_header_bytes() { return kTpHeaderBytes; }
+
+}  // namespace mx

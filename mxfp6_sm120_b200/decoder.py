@@ -185,20 +185,23 @@ class DenseDecoder:
     """``layers`` decoder layers of one rank, with the step functions."""
 
     def __init__(self, cfg: DecoderConfig, layers: list[DecoderLayer], world: int = 1,
-                 rank: int = 0, group=None):
+                 rank: int = 0, group=None, peer=None):
         self.cfg, self.layers, self.world, self.rank, self.group = cfg, layers, world, rank, group
         self.shape = cfg.local(world)
         self.device = layers[0].ln1.device
+        # tp_fused.SymmetricBlocks: the two all-reduces of a layer run inside the following
+        # residual + norm + quantize kernel over peer memory instead of NCCL.
+        self.peer = peer
 
     @classmethod
     def random(cls, cfg: DecoderConfig, device, seed: int = 5000, world: int = 1, rank: int = 0,
-               group=None, layers: int | None = None) -> "DenseDecoder":
+               group=None, layers: int | None = None, peer=None) -> "DenseDecoder":
         """Random-init decoder; under TP every rank draws its own local-shape weights."""
         gen = torch.Generator(device=device).manual_seed(seed + rank)
         shape = cfg.local(world)
         count = cfg.layers if layers is None else layers
         return cls(cfg, [random_layer(cfg, device, gen, shape) for _ in range(count)], world, rank,
-                   group)
+                   group, peer)
 
     def weight_bytes(self) -> int:
         total = 0
@@ -246,12 +249,30 @@ class DenseDecoder:
         if self.world > 1:
             dist.all_reduce(tensor, group=self.group)
 
+    def _projection_out(self, ws: DecoderWorkspace) -> torch.Tensor:
+        """Where a row-parallel projection writes: the next peer buffer, or ws.proj."""
+        if self.peer is not None:
+            return self.peer.next_partial(ws.tokens, self.cfg.hidden)
+        return ws.proj
+
+    def _add_norm_quantize(self, ws: DecoderWorkspace, weight: torch.Tensor) -> MXFP8Tensor:
+        """x += (all-reduced) projection output; returns MXFP8(RMSNorm(x) * weight)."""
+        if self.peer is not None:
+            return self.peer.allreduce_rmsnorm_quantize(ws.x, weight, self.cfg.eps, ws.a_values,
+                                                        ws.a_scales)
+        self._all_reduce(ws.proj)
+        return rmsnorm_quantize_mxfp8(ws.x, weight, self.cfg.eps, residual=ws.proj,
+                                      values=ws.a_values, scales=ws.a_scales)
+
     def _layer(self, ws: DecoderWorkspace, layer: DecoderLayer, attention, first: bool) -> None:
         cfg, shape = self.cfg, self.shape
         tokens, hd = ws.tokens, cfg.head_dim
         # x (+ down projection of the previous layer) -> norm -> MXFP8
-        a = rmsnorm_quantize_mxfp8(ws.x, layer.ln1, cfg.eps, residual=None if first else ws.proj,
-                                   values=ws.a_values, scales=ws.a_scales)
+        if first:
+            a = rmsnorm_quantize_mxfp8(ws.x, layer.ln1, cfg.eps, values=ws.a_values,
+                                       scales=ws.a_scales)
+        else:
+            a = self._add_norm_quantize(ws, layer.ln1)
         gemm_w6a8(a, layer.qkv, out_dtype=torch.bfloat16, out=ws.qkv)
         q_dim, kv_dim = shape.q_heads * hd, shape.kv_heads * hd
         q = ws.qkv[:, :q_dim].view(tokens, shape.q_heads, hd)
@@ -260,11 +281,9 @@ class DenseDecoder:
         attention(q, k, v, ws.attn)
         _quantize_mxfp8_raw(ws.attn, ws.b_values, ws.b_scales, None)
         b = MXFP8Tensor(ws.b_values, ws.b_scales, tokens, q_dim)
-        gemm_w6a8(b, layer.o, out_dtype=torch.bfloat16, out=ws.proj)
-        self._all_reduce(ws.proj)
+        gemm_w6a8(b, layer.o, out_dtype=torch.bfloat16, out=self._projection_out(ws))
         # x += attention output -> norm -> MXFP8
-        a = rmsnorm_quantize_mxfp8(ws.x, layer.ln2, cfg.eps, residual=ws.proj, values=ws.a_values,
-                                   scales=ws.a_scales)
+        a = self._add_norm_quantize(ws, layer.ln2)
         if ws.gate_up is not None:
             gemm_w6a8(a, layer.gate_up, out_dtype=torch.bfloat16, out=ws.gate_up)
             silu_and_mul_mxfp8_packed_out(ws.mlp_values, ws.mlp_scales, ws.gate_up)
@@ -273,13 +292,18 @@ class DenseDecoder:
                                     ws.a_values.view(tokens, cfg.hidden), ws.a_scales,
                                     layer.gate_up.values, layer.gate_up.scales)
         m = MXFP8Tensor(ws.mlp_values.view(-1), ws.mlp_scales, tokens, shape.intermediate)
-        gemm_w6a8(m, layer.down, out_dtype=torch.bfloat16, out=ws.proj)
-        self._all_reduce(ws.proj)
+        gemm_w6a8(m, layer.down, out_dtype=torch.bfloat16, out=self._projection_out(ws))
 
     def _run(self, ws: DecoderWorkspace, attention_of_layer) -> torch.Tensor:
         for index, layer in enumerate(self.layers):
             self._layer(ws, layer, attention_of_layer(index), index == 0)
-        ws.x.add_(ws.proj)  # the last layer's MLP output joins the residual stream
+        # The last layer's MLP output joins the residual stream.
+        if self.peer is not None:
+            # Same kernel; its normalised output (against the first layer's weight) is unused.
+            self._add_norm_quantize(ws, self.layers[0].ln1)
+        else:
+            self._all_reduce(ws.proj)
+            ws.x.add_(ws.proj)
         return ws.x
 
     # ------------------------------------------------------------------ the two steps

@@ -1,0 +1,115 @@
+"""Peer-memory all-reduce fused into the residual + RMSNorm + MXFP8 kernel (one node).
+
+Set-up exchanges CUDA IPC handles of one symmetric block per rank over the process group's
+host channel (``all_gather_object``); after that the data path is one kernel per
+row-parallel projection: flags and partial rows travel as plain peer stores / loads over
+NVLink.  See ``csrc/tp_fused.cu`` for the protocol.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from ._loader import check, library, load_library
+from .ops import MXFP8Tensor, _require_sm100, _stream, packed_scale_numel
+
+HEADER_BYTES = 1024
+
+
+class _DeviceBytes:
+    """Minimal ``__cuda_array_interface__`` holder: lets torch view library-owned memory."""
+
+    def __init__(self, pointer: int, size: int):
+        self.__cuda_array_interface__ = {
+            "shape": (size,), "typestr": "|u1", "data": (pointer, False), "version": 2,
+        }
+
+
+class SymmetricBlocks:
+    """This rank's symmetric block plus mappings of every peer's block."""
+
+    def __init__(self, max_rows: int, hidden: int, device: torch.device, group=None):
+        _require_sm100(device)
+        load_library()
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if self.world > 8:
+            raise ValueError("at most 8 ranks of one node")
+        self.device = device
+        self.partial_bytes = (max_rows * hidden * 2 + 255) // 256 * 256
+        own = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(device):
+            check(library().mxfp6_tp_block_alloc(self.partial_bytes, ctypes.byref(own), handle))
+        self._own = own.value
+        handles = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(handles, bytes(handle), group=group)
+        else:
+            handles[0] = bytes(handle)
+        self._opened: list[int] = []
+        pointers = []
+        for r, raw in enumerate(handles):
+            if r == self.rank:
+                pointers.append(self._own)
+                continue
+            peer = ctypes.c_void_p()
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(raw)
+            with torch.cuda.device(device):
+                check(library().mxfp6_tp_block_open(buf, ctypes.byref(peer)))
+            self._opened.append(peer.value)
+            pointers.append(peer.value)
+        self._blocks = (ctypes.c_void_p * self.world)(*pointers)
+        size = HEADER_BYTES + 2 * self.partial_bytes
+        self._bytes = torch.as_tensor(_DeviceBytes(self._own, size), device=device)
+        self._next = 0
+        if self.world > 1:
+            dist.barrier(group=group)  # every rank has mapped every block
+
+    def partial(self, buffer: int, rows: int, hidden: int) -> torch.Tensor:
+        """BF16 ``[rows, hidden]`` view of this rank's partial buffer ``buffer`` (GEMM output)."""
+        if rows * hidden * 2 > self.partial_bytes:
+            raise ValueError("the symmetric block is too small for this activation")
+        begin = HEADER_BYTES + buffer * self.partial_bytes
+        return self._bytes[begin : begin + rows * hidden * 2].view(torch.bfloat16).view(rows, hidden)
+
+    def next_partial(self, rows: int, hidden: int) -> torch.Tensor:
+        """Partial buffer the next fused call will reduce (buffers alternate per call)."""
+        return self.partial(self._next, rows, hidden)
+
+    def allreduce_rmsnorm_quantize(self, x: torch.Tensor, weight: torch.Tensor, eps: float,
+                                   values: torch.Tensor, scales: torch.Tensor) -> MXFP8Tensor:
+        """``x += sum over ranks of next_partial``; returns MXFP8(RMSNorm(x) * weight)."""
+        rows, hidden = (int(v) for v in x.shape)
+        if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not x.is_contiguous():
+            raise ValueError("x and weight must be contiguous BF16")
+        if values.numel() < rows * hidden or scales.numel() < packed_scale_numel(rows, hidden):
+            raise ValueError("values / scales are too small")
+        buffer, self._next = self._next, self._next ^ 1
+        with torch.cuda.device(self.device):
+            check(
+                library().mxfp6_tp_allreduce_rmsnorm_quantize_mxfp8(
+                    self._blocks, self.world, self.rank, buffer, self.partial_bytes, x.data_ptr(),
+                    weight.data_ptr(), float(eps), rows, hidden, values.data_ptr(),
+                    scales.data_ptr(), _stream(self.device),
+                )
+            )
+        return MXFP8Tensor(values, scales, rows, hidden)
+
+    def close(self) -> None:
+        """Unmap the peers' blocks and free this rank's (call on every rank, between steps)."""
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            if self.world > 1:
+                dist.barrier(group=self.group)
+            for pointer in self._opened:
+                check(library().mxfp6_tp_block_close(ctypes.c_void_p(pointer)))
+            self._opened = []
+            if self._own:
+                self._bytes = None
+                check(library().mxfp6_tp_block_free(ctypes.c_void_p(self._own)))
+                self._own = 0

@@ -91,6 +91,7 @@ def test_prefill_matches_oracle_and_graph_replay(mx, tokens):
     want = dec_o.prefill(x, _oracle_layers(mx, layers), cfg, cfg.local(1))
     _close(out, want)
     # one CUDA graph for the whole step, identical bytes on replay
+    torch.cuda.synchronize()
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
         ws.x.copy_(x.to(DEV))

@@ -1,0 +1,103 @@
+"""Tensor-parallel decoder on 2 GPUs: peer-memory all-reduce fused into the norm kernel
+against the NCCL path and against the unsharded model (skipped below 2 GPUs).
+
+Each rank is a child process (one process per GPU); NVLS is off and no rank leaves
+mid-step, as the pool's rules for multi-rank tests ask.  The fused kernel's waits are
+bounded, so a peer that never arrives ends as device status 301, not as a hang.
+"""
+
+from __future__ import annotations
+
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, results) -> None:
+    import torch.distributed as dist
+
+    import mxfp6_sm120_b200 as mx
+    from mxfp6_sm120_b200.tp_fused import SymmetricBlocks
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    device = torch.device("cuda", rank)
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    cfg = mx.DecoderConfig(hidden=512, q_heads=4, kv_heads=2, head_dim=128, intermediate=1024,
+                           layers=3)
+    gen = torch.Generator(device=device).manual_seed(5000)  # same weights on every rank
+    full = [mx.random_layer(cfg, device, gen) for _ in range(cfg.layers)]
+    tokens = 9
+    x = torch.randn((tokens, cfg.hidden), generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).to(device)
+
+    single = mx.DenseDecoder(cfg, full)
+    ws = single.workspace(tokens)
+    ws.x.copy_(x)
+    want = single.prefill(ws).clone()
+
+    shards = [mx.shard_layer(layer, cfg, world, rank) for layer in full]
+    nccl = mx.DenseDecoder(cfg, shards, world=world, rank=rank)
+    ws_n = nccl.workspace(tokens)
+    ws_n.x.copy_(x)
+    got_nccl = nccl.prefill(ws_n).clone()
+
+    peer = SymmetricBlocks(tokens, cfg.hidden, device)
+    fused = mx.DenseDecoder(cfg, shards, world=world, rank=rank, peer=peer)
+    ws_f = fused.workspace(tokens)
+    ws_f.x.copy_(x)
+    got_fused = fused.prefill(ws_f).clone()
+    torch.cuda.synchronize()  # the side stream below is not ordered after the default stream
+    # the same step from one CUDA graph, replayed
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        graph = torch.cuda.CUDAGraph()
+        ws_f.x.copy_(x)
+        stream.synchronize()
+        dist.barrier()
+        with torch.cuda.graph(graph, stream=stream):
+            fused.prefill(ws_f)
+        for _ in range(3):
+            ws_f.x.copy_(x)
+            graph.replay()
+        stream.synchronize()
+    replayed = ws_f.x.clone()
+    torch.cuda.synchronize()
+
+    def cos(a, b):
+        return float(torch.nn.functional.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0))
+
+    results[rank] = dict(fused_vs_nccl_equal=bool(torch.equal(got_fused, got_nccl)),
+                         fused_vs_nccl_cos=cos(got_fused, got_nccl),
+                         fused_vs_single_cos=cos(got_fused, want),
+                         replay_equal=bool(torch.equal(replayed, got_fused)),
+                         status=mx.device_status())
+    dist.barrier()
+    torch.cuda.synchronize()
+    peer.close()
+    os._exit(0)  # no NCCL teardown: every rank has reported and is between steps
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_allreduce_norm_matches_nccl_and_single_gpu():
+    import torch.multiprocessing as mp
+
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    for rank in range(world):
+        r = results[rank]
+        assert r["status"] == 0, r
+        assert r["fused_vs_nccl_cos"] >= 0.9999, r
+        assert r["fused_vs_single_cos"] >= 0.999, r
+        assert r["replay_equal"], r
