@@ -338,7 +338,7 @@ def decoder_step_latency(mx, device, stream, world: int, rank: int) -> dict:
         from mxfp6_sm120_b200.tp_fused import SymmetricBlocks
 
         nccl_model = model
-        peer = SymmetricBlocks(8192, cfg.hidden, device, group)
+        peer = SymmetricBlocks(512, cfg.hidden, device, group)
         model = mx.DenseDecoder(cfg, nccl_model.layers, world, rank, group, peer)
 
     def timed(step, reps):

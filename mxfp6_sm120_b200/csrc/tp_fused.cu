@@ -143,13 +143,24 @@ allreduce_rmsnorm_quantize_kernel(const TpPeers peers, TpState* state, __nv_bflo
       raw[u] = make_uint4(0u, 0u, 0u, 0u);
       if (c < row_chunks) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int r = 0; r < peers.world; ++r) {
-          const uint4 p =
-              ld_volatile_u128(reinterpret_cast<const uint4*>(peers.partial[r]) + row * row_chunks + c);
-          float v[8];
-          unpack_bf16x8(p, v);
+        // All ranks' loads are issued before the first is used: one NVLink round trip
+        // per chunk instead of one per rank.
+        uint4 part[kTpMaxRanks];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] += v[i];
+        for (int r = 0; r < kTpMaxRanks; ++r) {
+          if (r < peers.world) {
+            part[r] = ld_volatile_u128(reinterpret_cast<const uint4*>(peers.partial[r]) +
+                                       row * row_chunks + c);
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < kTpMaxRanks; ++r) {
+          if (r < peers.world) {
+            float v[8];
+            unpack_bf16x8(part[r], v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += v[i];
+          }
         }
         float xv[8];
         unpack_bf16x8(xrow[c], xv);
