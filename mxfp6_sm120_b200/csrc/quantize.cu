@@ -151,6 +151,91 @@ quantize_mxfp8_kernel(const T* __restrict__ in, uint8_t* __restrict__ out,
   }
 }
 
+// Lean form of the kernel above for the common case (a row of whole quads of scale groups,
+// fewer than 2^31 chunks): the general kernel spends ~140 instructions per 8 values, most
+// of them on 64-bit index arithmetic and the division that turns a group index into
+// (row, group); here the row and the position in the row advance incrementally and all
+// offsets are 32-bit, which matters because the kernel is issue-bound, not memory-bound.
+template <class T>
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_mxfp8_lean_kernel(const T* __restrict__ in, uint8_t* __restrict__ out,
+                           uint8_t* __restrict__ packed, uint8_t* __restrict__ logical,
+                           uint32_t rows, uint32_t row_chunks, uint32_t chunks,
+                           int64_t pad_begin, int64_t pad_total) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  constexpr int kUnroll = 4;
+  const uint32_t nthreads = gridDim.x * blockDim.x;
+  const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x;
+  const uint32_t groups = row_chunks >> 2;
+  const uint32_t atoms_per_rb = groups >> 2;
+  // (row, chunk in row) of this thread's current chunk, and the step of one sub-iteration.
+  const uint32_t step_rows = nthreads / row_chunks;
+  const uint32_t step_cols = nthreads - step_rows * row_chunks;
+  uint32_t row = tid / row_chunks;
+  uint32_t col = tid - row * row_chunks;
+  const uint4* src = reinterpret_cast<const uint4*>(in);
+  uint2* dst = reinterpret_cast<uint2*>(out);
+  // Every thread runs every round (the shuffles below need whole warps).
+  const uint32_t per_round = nthreads * kUnroll;
+  const uint32_t rounds = (chunks + per_round - 1) / per_round;
+  for (uint32_t it = 0; it < rounds; ++it) {
+    const uint32_t base = it * per_round + tid;
+    Vec8<T> raw[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t c = base + u * nthreads;
+      raw[u].raw = make_uint4(0u, 0u, 0u, 0u);
+      if (c < chunks) raw[u].raw = __ldg(src + c);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t c = base + u * nthreads;
+      float v[8];
+      raw[u].unpack(v);
+      float amax = absmax8(v);
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
+      const float inv = ue8m0_inverse(sbits);
+      const uint32_t code = sbits >> 23;
+      uint32_t word = code;
+      word |= __shfl_down_sync(0xffffffffu, code, 4) << 8;
+      word |= __shfl_down_sync(0xffffffffu, code, 8) << 16;
+      word |= __shfl_down_sync(0xffffffffu, code, 12) << 24;
+      if (c < chunks) {
+        uint32_t w[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+              make_float2(v[4 * i] * inv, v[4 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+          const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+              make_float2(v[4 * i + 2] * inv, v[4 * i + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+          w[i] = lo | (hi << 16);
+        }
+        dst[c] = make_uint2(w[0], w[1]);
+        if ((threadIdx.x & 15) == 0) {
+          const uint32_t g = col >> 2;  // a multiple of 4: 16 lanes = four groups of one row
+          if (logical != nullptr) *reinterpret_cast<uint32_t*>(logical + (c >> 2)) = word;
+          if (packed != nullptr) {
+            const uint32_t offset = ((row >> 7) * atoms_per_rb + (g >> 2)) * 512u +
+                                    (row & 31u) * 16u + ((row >> 5) & 3u) * 4u;
+            *reinterpret_cast<uint32_t*>(packed + offset) = word;
+          }
+        }
+      }
+      row += step_rows;
+      col += step_cols;
+      if (col >= row_chunks) {
+        col -= row_chunks;
+        ++row;
+      }
+    }
+  }
+  if (packed != nullptr && pad_begin < pad_total) {
+    fill_scale_padding(packed, pad_begin, pad_total, rows, static_cast<int>(groups), tid, nthreads);
+  }
+}
+
 // One thread per 16 consecutive K values (two per scale group); the sixteen
 // E3M2 codes leave as three 32-bit words (code i at bits 6i..6i+5).
 template <class T>
@@ -401,6 +486,20 @@ int quantize_mxfp8(const void* in, int dtype, int64_t rows, int64_t k, uint8_t* 
   const bool quad = (k / kScaleVec) % 4 == 0 && chunks < (int64_t(1) << 33) &&
                     (reinterpret_cast<uintptr_t>(packed) & 3) == 0 &&
                     (reinterpret_cast<uintptr_t>(logical) & 3) == 0;
+  // packed offsets in 32 bits: the scale buffer is rows * groups bytes plus padding.
+  if (quad && chunks < (int64_t(1) << 31) && packed_scale_bytes(rows, k) < (int64_t(1) << 31)) {
+    if (dtype == kBF16) {
+      quantize_mxfp8_lean_kernel<__nv_bfloat16><<<grid, kQuantThreads, 0, stream>>>(
+          static_cast<const __nv_bfloat16*>(in), values, packed, logical, (uint32_t)rows,
+          (uint32_t)(k / 8), (uint32_t)chunks, pad_begin, pad_total);
+    } else {
+      quantize_mxfp8_lean_kernel<__half><<<grid, kQuantThreads, 0, stream>>>(
+          static_cast<const __half*>(in), values, packed, logical, (uint32_t)rows,
+          (uint32_t)(k / 8), (uint32_t)chunks, pad_begin, pad_total);
+    }
+    MX_CUDA(cudaGetLastError());
+    return kOk;
+  }
   if (dtype == kBF16) {
     quantize_mxfp8_kernel<__nv_bfloat16><<<grid, kQuantThreads, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(in), values, packed, logical, rows,
