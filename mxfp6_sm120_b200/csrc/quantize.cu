@@ -323,7 +323,7 @@ __device__ __forceinline__ float round_to<__half>(float v) {
   return __half2float(__float2half_rn(v));
 }
 
-template <class T>
+template <class T, int kChunks>
 __global__ void __launch_bounds__(kQuantThreads)
 rmsnorm_quantize_mxfp8_kernel(const T* in, const T* __restrict__ residual, T* updated,
                               const T* __restrict__ weight, float eps,
@@ -336,10 +336,10 @@ rmsnorm_quantize_mxfp8_kernel(const T* in, const T* __restrict__ residual, T* up
   const int64_t row = blockIdx.x;
   const uint4* src = reinterpret_cast<const uint4*>(in) + row * row_chunks;
   const uint4* wsrc = reinterpret_cast<const uint4*>(weight);
-  Vec8<T> raw[kNormChunks];
+  Vec8<T> raw[kChunks];
   float sum = 0.0f;
 #pragma unroll
-  for (int u = 0; u < kNormChunks; ++u) {
+  for (int u = 0; u < kChunks; ++u) {
     const int c = u * kQuantThreads + threadIdx.x;
     raw[u].raw = make_uint4(0u, 0u, 0u, 0u);
     if (c < row_chunks) raw[u].raw = src[c];
@@ -350,7 +350,7 @@ rmsnorm_quantize_mxfp8_kernel(const T* in, const T* __restrict__ residual, T* up
     const uint4* rsrc = reinterpret_cast<const uint4*>(residual) + row * row_chunks;
     uint4* xdst = reinterpret_cast<uint4*>(updated) + row * row_chunks;
 #pragma unroll
-    for (int u = 0; u < kNormChunks; ++u) {
+    for (int u = 0; u < kChunks; ++u) {
       const int c = u * kQuantThreads + threadIdx.x;
       if (c < row_chunks) {
         Vec8<T> r;
@@ -367,7 +367,7 @@ rmsnorm_quantize_mxfp8_kernel(const T* in, const T* __restrict__ residual, T* up
     }
   }
 #pragma unroll
-  for (int u = 0; u < kNormChunks; ++u) {
+  for (int u = 0; u < kChunks; ++u) {
     float v[8];
     raw[u].unpack(v);
 #pragma unroll
@@ -382,7 +382,7 @@ rmsnorm_quantize_mxfp8_kernel(const T* in, const T* __restrict__ residual, T* up
   for (int w = 0; w < kQuantThreads / 32; ++w) total += warp_sums[w];
   const float inv_rms = rsqrtf(total / static_cast<float>(k) + eps);
 #pragma unroll
-  for (int u = 0; u < kNormChunks; ++u) {
+  for (int u = 0; u < kChunks; ++u) {
     const int c = u * kQuantThreads + threadIdx.x;
     const bool valid = c < row_chunks;
     float v[8], g[8];
@@ -559,17 +559,28 @@ int rmsnorm_quantize_mxfp8(const void* in, const void* residual, void* updated, 
   const bool quad = (k / kScaleVec) % 4 == 0 && (reinterpret_cast<uintptr_t>(packed) & 3) == 0 &&
                     (reinterpret_cast<uintptr_t>(logical) & 3) == 0;
   const unsigned grid = static_cast<unsigned>(rows);
+  // The row lives in registers: instantiate for the number of 8-value chunks a thread holds.
+  const int need = static_cast<int>((k / 8 + kQuantThreads - 1) / kQuantThreads);
+#define MX_LAUNCH_NORM(T, CH)                                                                   \
+  rmsnorm_quantize_mxfp8_kernel<T, CH><<<grid, kQuantThreads, 0, stream>>>(                     \
+      static_cast<const T*>(in), static_cast<const T*>(residual), static_cast<T*>(updated),     \
+      static_cast<const T*>(weight), eps, values, packed, logical, rows, static_cast<int>(k),   \
+      pad_begin, pad_total, quad)
+#define MX_DISPATCH_NORM(T)                    \
+  do {                                         \
+    if (need <= 1) MX_LAUNCH_NORM(T, 1);       \
+    else if (need <= 2) MX_LAUNCH_NORM(T, 2);  \
+    else if (need <= 3) MX_LAUNCH_NORM(T, 3);  \
+    else if (need <= 4) MX_LAUNCH_NORM(T, 4);  \
+    else MX_LAUNCH_NORM(T, kNormChunks);       \
+  } while (0)
   if (dtype == kBF16) {
-    rmsnorm_quantize_mxfp8_kernel<__nv_bfloat16><<<grid, kQuantThreads, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(in), static_cast<const __nv_bfloat16*>(residual),
-        static_cast<__nv_bfloat16*>(updated), static_cast<const __nv_bfloat16*>(weight), eps,
-        values, packed, logical, rows, static_cast<int>(k), pad_begin, pad_total, quad);
+    MX_DISPATCH_NORM(__nv_bfloat16);
   } else {
-    rmsnorm_quantize_mxfp8_kernel<__half><<<grid, kQuantThreads, 0, stream>>>(
-        static_cast<const __half*>(in), static_cast<const __half*>(residual),
-        static_cast<__half*>(updated), static_cast<const __half*>(weight), eps, values, packed,
-        logical, rows, static_cast<int>(k), pad_begin, pad_total, quad);
+    MX_DISPATCH_NORM(__half);
   }
+#undef MX_DISPATCH_NORM
+#undef MX_LAUNCH_NORM
   MX_CUDA(cudaGetLastError());
   return kOk;
 }

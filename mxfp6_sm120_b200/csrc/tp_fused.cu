@@ -86,6 +86,7 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float (&v)[8]) {
 
 // x[row] <- bf16(x[row] + bf16(sum over ranks of partial_r[row])); then RMSNorm * weight and
 // MXFP8 with packed scales.  One CTA per row.
+template <int kChunks>
 __global__ void __launch_bounds__(kTpThreads)
 allreduce_rmsnorm_quantize_kernel(const TpPeers peers, TpState* state, __nv_bfloat16* x,
                                   const __nv_bfloat16* __restrict__ weight, float eps,
@@ -134,11 +135,11 @@ allreduce_rmsnorm_quantize_kernel(const TpPeers peers, TpState* state, __nv_bflo
 
   if (ok) {
     // ---- all-reduce of this row + residual --------------------------------------------
-    uint4 raw[kTpChunks];
+    uint4 raw[kChunks];
     uint4* xrow = reinterpret_cast<uint4*>(x) + row * row_chunks;
     float sum_sq = 0.0f;
 #pragma unroll
-    for (int u = 0; u < kTpChunks; ++u) {
+    for (int u = 0; u < kChunks; ++u) {
       const int c = u * kTpThreads + threadIdx.x;
       raw[u] = make_uint4(0u, 0u, 0u, 0u);
       if (c < row_chunks) {
@@ -185,7 +186,7 @@ allreduce_rmsnorm_quantize_kernel(const TpPeers peers, TpState* state, __nv_bflo
     const float inv_rms = rsqrtf(total / static_cast<float>(k) + eps);
     const uint4* wsrc = reinterpret_cast<const uint4*>(weight);
 #pragma unroll
-    for (int u = 0; u < kTpChunks; ++u) {
+    for (int u = 0; u < kChunks; ++u) {
       const int c = u * kTpThreads + threadIdx.x;
       const bool valid = c < row_chunks;
       float v[8], g[8];
@@ -314,9 +315,18 @@ int tp_allreduce_rmsnorm_quantize(void* const* blocks, int world, int rank, int 
   }
   auto* state = reinterpret_cast<TpState*>(static_cast<uint8_t*>(blocks[rank]) +
                                            kTpMaxRanks * sizeof(uint32_t));
-  allreduce_rmsnorm_quantize_kernel<<<(unsigned)rows, kTpThreads, 0, stream>>>(
-      peers, state, static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight),
-      eps, values, packed, rows, static_cast<int>(k), status);
+  // The row lives in registers: instantiate for the 8-value chunks a thread holds.
+  const int need = static_cast<int>((k / 8 + kTpThreads - 1) / kTpThreads);
+#define MX_LAUNCH_TP(CH)                                                                         \
+  allreduce_rmsnorm_quantize_kernel<CH><<<(unsigned)rows, kTpThreads, 0, stream>>>(              \
+      peers, state, static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight),   \
+      eps, values, packed, rows, static_cast<int>(k), status)
+  if (need <= 1) MX_LAUNCH_TP(1);
+  else if (need <= 2) MX_LAUNCH_TP(2);
+  else if (need <= 3) MX_LAUNCH_TP(3);
+  else if (need <= 4) MX_LAUNCH_TP(4);
+  else MX_LAUNCH_TP(kTpChunks);
+#undef MX_LAUNCH_TP
   MX_CUDA(cudaGetLastError());
   return kOk;
 }
