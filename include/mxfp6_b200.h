@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define MXFP6_B200_ABI_VERSION 2
+#define MXFP6_B200_ABI_VERSION 3
 
 #define MXFP6_DTYPE_F16 0
 #define MXFP6_DTYPE_BF16 1
