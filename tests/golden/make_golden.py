@@ -135,7 +135,9 @@ def make_reference_fixtures(reference_root: Path) -> None:
 
 
 if __name__ == "__main__":
-    reference = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <checkout of the reference project>")
+    reference = Path(sys.argv[1])
     make_cvt_tables()
     make_reference_fixtures(reference)
     for name in ("cvt_tables.npz", "reference_helpers.npz"):
