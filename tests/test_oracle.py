@@ -213,3 +213,22 @@ def test_reduce_sigmoid_gate_identity():
     half = o.moe_reduce(routed, w, inv, shared, torch.tensor([0.0]))
     assert torch.equal(full.float(), torch.ones((1, 64)))
     assert torch.equal(half.float(), torch.full((1, 64), 0.5))
+
+
+def test_division_free_scale_rule_equals_the_division_for_every_half_precision_magnitude():
+    """The kernels pick the UE8M0 scale from the exponent and mantissa fields of the block
+    maximum, code = max(28, exponent - shift + (mantissa > 0x600000)) with shift 8 for the
+    E4M3 target 448 and 4 for the E3M2 target 28, instead of dividing as the reference does
+    (csrc/quantization.cu:118-127).  Both agree for every non-negative finite BF16 and FP16
+    value a block maximum can take."""
+    bf16 = (np.arange(0, 0x7F80, dtype=np.uint32) << 16).view(np.float32)
+    fp16 = np.arange(0, 0x7C00, dtype=np.uint16).view(np.float16).astype(np.float32)
+    for values in (bf16, fp16):
+        bits = values.view(np.uint32)
+        exponent = (bits >> 23).astype(np.int64)
+        bump = ((bits & 0x7FFFFF) > 0x600000).astype(np.int64)
+        for target, shift in ((448.0, 8), (28.0, 4)):
+            fast = np.maximum(28, exponent - shift + bump)
+            with np.errstate(over="ignore"):
+                want = (o._scale_bits(values, target) >> 23).astype(np.int64)
+            assert np.array_equal(fast, want), (target, np.flatnonzero(fast != want)[:5])
