@@ -126,6 +126,13 @@ int mxfp6_tp_block_alloc(size_t partial_bytes, void** block_dev_out, unsigned ch
 int mxfp6_tp_block_open(const unsigned char handle[64], void** block_dev_out);
 int mxfp6_tp_block_close(void* block_dev);
 int mxfp6_tp_block_free(void* block_dev);
+/* The plain form of the same collective: out <- bf16(sum over ranks, in rank order, of the
+ * [rows, k] BF16 partials in buffer `buffer` of every block).  Used by the MoE reducer's
+ * tensor-parallel sum (the reference's moe_reduce_tp2_out, csrc/moe.cu:7698-7925).  It counts
+ * as one step of the alternating-buffer sequence like the fused call below. */
+int mxfp6_tp_allreduce_bf16(void* const* blocks_host, int world, int rank, int buffer,
+                            size_t partial_bytes, void* out_dev, int64_t rows, int64_t k,
+                            void* stream);
 int mxfp6_tp_allreduce_rmsnorm_quantize_mxfp8(void* const* blocks_host, int world, int rank,
                                               int buffer, size_t partial_bytes, void* x_dev,
                                               const void* weight_dev, float eps, int64_t rows,

@@ -42,6 +42,10 @@ SIGNATURES: dict[str, tuple] = {
     "mxfp6_tp_block_open": (c_int, [c_void_p, POINTER(c_void_p)]),
     "mxfp6_tp_block_close": (c_int, [c_void_p]),
     "mxfp6_tp_block_free": (c_int, [c_void_p]),
+    "mxfp6_tp_allreduce_bf16": (
+        c_int,
+        [POINTER(c_void_p), c_int, c_int, c_int, c_size_t, c_void_p, c_int64, c_int64, c_void_p],
+    ),
     "mxfp6_tp_allreduce_rmsnorm_quantize_mxfp8": (
         c_int,
         [POINTER(c_void_p), c_int, c_int, c_int, c_size_t, c_void_p, c_void_p, c_float, c_int64,

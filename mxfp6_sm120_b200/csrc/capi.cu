@@ -34,6 +34,8 @@ int tp_block_alloc(size_t, void**, unsigned char*);
 int tp_block_open(const unsigned char*, void**);
 int tp_block_close(void*);
 int tp_block_free(void*);
+int tp_allreduce_sum(void* const*, int, int, int, size_t, void*, int64_t, int64_t, int*,
+                     cudaStream_t);
 int tp_allreduce_rmsnorm_quantize(void* const*, int, int, int, size_t, void*, const void*, float,
                                   int64_t, int64_t, uint8_t*, uint8_t*, int*, cudaStream_t);
 int rmsnorm_quantize_mxfp8(const void*, const void*, void*, int, const void*, float, int64_t,
@@ -312,6 +314,16 @@ int mxfp6_tp_block_open(const unsigned char handle[64], void** block) {
 }
 int mxfp6_tp_block_close(void* block) { return tp_block_close(block); }
 int mxfp6_tp_block_free(void* block) { return tp_block_free(block); }
+int mxfp6_tp_allreduce_bf16(void* const* blocks, int world, int rank, int buffer,
+                            size_t partial_bytes, void* out, int64_t rows, int64_t k,
+                            void* stream) {
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  int* status = device_status_word(device);
+  if (status == nullptr) return kCudaError;
+  return tp_allreduce_sum(blocks, world, rank, buffer, partial_bytes, out, rows, k, status,
+                          static_cast<cudaStream_t>(stream));
+}
 int mxfp6_tp_allreduce_rmsnorm_quantize_mxfp8(void* const* blocks, int world, int rank, int buffer,
                                               size_t partial_bytes, void* x, const void* weight,
                                               float eps, int64_t rows, int64_t k, uint8_t* values,

@@ -84,30 +84,18 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float (&v)[8]) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// x[row] <- bf16(x[row] + bf16(sum over ranks of partial_r[row])); then RMSNorm * weight and
-// MXFP8 with packed scales.  One CTA per row.
-template <int kChunks>
-__global__ void __launch_bounds__(kTpThreads)
-allreduce_rmsnorm_quantize_kernel(const TpPeers peers, TpState* state, __nv_bfloat16* x,
-                                  const __nv_bfloat16* __restrict__ weight, float eps,
-                                  uint8_t* __restrict__ out, uint8_t* __restrict__ packed,
-                                  int64_t rows, int k, int* status) {
-  __shared__ float warp_sums[kTpThreads / 32];
-  __shared__ uint32_t step_shared;
-  __shared__ int ok_shared;
-  const int row_chunks = k / 8;
-  const int groups = k / kScaleVec;
-  const int64_t row = blockIdx.x;
-
-  // ---- the cross-rank handshake -------------------------------------------------------
+// Signals "my partial of this step is complete" to every peer (block 0), waits (bounded)
+// for every rank's signal, and returns the step number; *ok_shared is 0 after a timeout.
+__device__ __forceinline__ uint32_t tp_handshake(const TpPeers& peers, TpState* state, int* status,
+                                                 uint32_t* step_shared, int* ok_shared) {
   if (threadIdx.x == 0) {
-    step_shared = ld_volatile_u32(&state->done_step) + 1u;
-    ok_shared = 1;
+    *step_shared = ld_volatile_u32(&state->done_step) + 1u;
+    *ok_shared = 1;
   }
   __syncthreads();
-  const uint32_t step = step_shared;
+  const uint32_t step = *step_shared;
   if (blockIdx.x == 0 && threadIdx.x < peers.world) {
-    // The GEMM that wrote this rank's partial finished earlier on this stream; the fence
+    // The kernel that wrote this rank's partial finished earlier on this stream; the fence
     // orders its (already performed) writes before the flag for observers on other GPUs.
     __threadfence_system();
     st_volatile_u32(peers.flags[threadIdx.x] + peers.rank, step);
@@ -125,12 +113,81 @@ allreduce_rmsnorm_quantize_kernel(const TpPeers peers, TpState* state, __nv_bflo
       if ((spin & 255u) == 255u && clock64() - start > 4000000000ll) break;
     }
     if (!seen) {
-      ok_shared = 0;
+      *ok_shared = 0;
       atomicCAS(status, 0, 301);
     }
     __threadfence_system();
   }
   __syncthreads();
+  return step;
+}
+
+// The last CTA advances the step (also after a timeout, so that the ranks stay aligned).
+__device__ __forceinline__ void tp_finish(TpState* state, uint32_t step) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t done = atomicAdd(&state->finished, 1u);
+    if (done == gridDim.x - 1) {
+      state->finished = 0u;
+      st_volatile_u32(&state->done_step, step);
+      __threadfence();
+    }
+  }
+}
+
+// out[row] <- bf16(sum over ranks, in rank order, of partial_r[row]): the plain all-reduce,
+// for consumers that are not a norm (the MoE reducer's tensor-parallel sum).
+__global__ void __launch_bounds__(kTpThreads)
+allreduce_sum_kernel(const TpPeers peers, TpState* state, __nv_bfloat16* out, int64_t chunks,
+                     int* status) {
+  __shared__ uint32_t step_shared;
+  __shared__ int ok_shared;
+  const uint32_t step = tp_handshake(peers, state, status, &step_shared, &ok_shared);
+  if (ok_shared != 0) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < chunks;
+         c += stride) {
+      uint4 part[kTpMaxRanks];
+#pragma unroll
+      for (int r = 0; r < kTpMaxRanks; ++r) {
+        if (r < peers.world) {
+          part[r] = ld_volatile_u128(reinterpret_cast<const uint4*>(peers.partial[r]) + c);
+        }
+      }
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < kTpMaxRanks; ++r) {
+        if (r < peers.world) {
+          float v[8];
+          unpack_bf16x8(part[r], v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += v[i];
+        }
+      }
+      reinterpret_cast<uint4*>(out)[c] = pack_bf16x8(acc);
+    }
+  }
+  tp_finish(state, step);
+}
+
+// x[row] <- bf16(x[row] + bf16(sum over ranks of partial_r[row])); then RMSNorm * weight and
+// MXFP8 with packed scales.  One CTA per row.
+template <int kChunks>
+__global__ void __launch_bounds__(kTpThreads)
+allreduce_rmsnorm_quantize_kernel(const TpPeers peers, TpState* state, __nv_bfloat16* x,
+                                  const __nv_bfloat16* __restrict__ weight, float eps,
+                                  uint8_t* __restrict__ out, uint8_t* __restrict__ packed,
+                                  int64_t rows, int k, int* status) {
+  __shared__ float warp_sums[kTpThreads / 32];
+  __shared__ uint32_t step_shared;
+  __shared__ int ok_shared;
+  const int row_chunks = k / 8;
+  const int groups = k / kScaleVec;
+  const int64_t row = blockIdx.x;
+
+  // ---- the cross-rank handshake -------------------------------------------------------
+  const uint32_t step = tp_handshake(peers, state, status, &step_shared, &ok_shared);
   const bool ok = ok_shared != 0;
 
   if (ok) {
@@ -227,17 +284,7 @@ allreduce_rmsnorm_quantize_kernel(const TpPeers peers, TpState* state, __nv_bflo
     }
   }
 
-  // ---- the last CTA advances the step (also after a timeout, so that ranks stay aligned) --
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    const uint32_t done = atomicAdd(&state->finished, 1u);
-    if (done == gridDim.x - 1) {
-      state->finished = 0u;
-      st_volatile_u32(&state->done_step, step);
-      __threadfence();
-    }
-  }
+  tp_finish(state, step);
 }
 
 }  // namespace
@@ -327,6 +374,41 @@ int tp_allreduce_rmsnorm_quantize(void* const* blocks, int world, int rank, int 
   else if (need <= 4) MX_LAUNCH_TP(4);
   else MX_LAUNCH_TP(kTpChunks);
 #undef MX_LAUNCH_TP
+  MX_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int tp_allreduce_sum(void* const* blocks, int world, int rank, int buffer, size_t partial_bytes,
+                     void* out, int64_t rows, int64_t k, int* status, cudaStream_t stream) {
+  MX_REQUIRE(blocks != nullptr && world >= 1 && world <= kTpMaxRanks && rank >= 0 && rank < world,
+             "world must be in [1, %d] and rank inside it", kTpMaxRanks);
+  MX_REQUIRE(buffer == 0 || buffer == 1, "buffer must be 0 or 1");
+  MX_REQUIRE(out != nullptr && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+             "out must be a 16-byte aligned device pointer");
+  MX_REQUIRE(rows > 0 && k > 0 && k % 8 == 0, "rows must be positive and k a multiple of 8");
+  MX_REQUIRE((size_t)rows * (size_t)k * 2 <= partial_bytes,
+             "the partial buffers hold %zu bytes, %lld x %lld BF16 need more", partial_bytes,
+             (long long)rows, (long long)k);
+  TpPeers peers;
+  peers.world = world;
+  peers.rank = rank;
+  for (int r = 0; r < kTpMaxRanks; ++r) {
+    peers.partial[r] = nullptr;
+    peers.flags[r] = nullptr;
+  }
+  for (int r = 0; r < world; ++r) {
+    MX_REQUIRE(blocks[r] != nullptr, "block of rank %d is null", r);
+    auto* base = static_cast<uint8_t*>(blocks[r]);
+    peers.flags[r] = reinterpret_cast<uint32_t*>(base);
+    peers.partial[r] = base + kTpHeaderBytes + (size_t)buffer * partial_bytes;
+  }
+  auto* state = reinterpret_cast<TpState*>(static_cast<uint8_t*>(blocks[rank]) +
+                                           kTpMaxRanks * sizeof(uint32_t));
+  const int64_t chunks = rows * k / 8;
+  int64_t grid = (chunks + kTpThreads - 1) / kTpThreads;
+  if (grid > 148 * 4) grid = 148 * 4;
+  allreduce_sum_kernel<<<(unsigned)grid, kTpThreads, 0, stream>>>(
+      peers, state, static_cast<__nv_bfloat16*>(out), chunks, status);
   MX_CUDA(cudaGetLastError());
   return kOk;
 }

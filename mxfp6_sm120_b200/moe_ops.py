@@ -711,15 +711,25 @@ def moe_reduce_tp2_out(
     shared_output: torch.Tensor | None = None,
     shared_gate: torch.Tensor | None = None,
     group=None,
+    peer=None,
 ) -> None:
     """Reduce, then sum the result over the tensor-parallel ranks.
 
     The reference fuses a 2-rank peer-pointer all-reduce with unbounded spins into
-    its reducer (csrc/moe.cu:7698-7925); here the reduce kernel is followed by an
-    NCCL all-reduce on the same stream for any world size.
+    its reducer (csrc/moe.cu:7698-7925).  Here, for any world size up to 8: with
+    ``peer`` (a ``tp_fused.SymmetricBlocks``) the reducer writes this rank's partial
+    into its symmetric block and one kernel sums all ranks' partials over peer memory
+    with bounded waits; without it an NCCL all-reduce follows the reduce kernel.
     """
     import torch.distributed as dist
 
+    if peer is not None and peer.world > 1:
+        rows, hidden = (int(v) for v in output.shape)
+        partial = peer.next_partial(rows, hidden)
+        moe_reduce_out(partial, routed_output, topk_weights, inverse_permutation, shared_output,
+                       shared_gate)
+        peer.allreduce(output)
+        return
     moe_reduce_out(output, routed_output, topk_weights, inverse_permutation, shared_output,
                    shared_gate)
     if dist.is_initialized() and dist.get_world_size(group) > 1:

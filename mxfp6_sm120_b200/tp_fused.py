@@ -100,6 +100,21 @@ class SymmetricBlocks:
             )
         return MXFP8Tensor(values, scales, rows, hidden)
 
+    def allreduce(self, out: torch.Tensor) -> torch.Tensor:
+        """``out = sum over ranks of next_partial`` (BF16 ``[rows, hidden]``, rank order)."""
+        rows, hidden = (int(v) for v in out.shape)
+        if out.dtype != torch.bfloat16 or not out.is_contiguous():
+            raise ValueError("out must be contiguous BF16")
+        buffer, self._next = self._next, self._next ^ 1
+        with torch.cuda.device(self.device):
+            check(
+                library().mxfp6_tp_allreduce_bf16(
+                    self._blocks, self.world, self.rank, buffer, self.partial_bytes,
+                    out.data_ptr(), rows, hidden, _stream(self.device),
+                )
+            )
+        return out
+
     def close(self) -> None:
         """Unmap the peers' blocks and free this rank's (call on every rank, between steps)."""
         with torch.cuda.device(self.device):

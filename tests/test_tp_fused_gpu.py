@@ -76,7 +76,27 @@ def _worker(rank: int, world: int, port: int, results) -> None:
     def cos(a, b):
         return float(torch.nn.functional.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0))
 
-    results[rank] = dict(fused_vs_nccl_equal=bool(torch.equal(got_fused, got_nccl)),
+    # MoE reducer + tensor-parallel sum: peer-memory kernel against NCCL
+    from mxfp6_sm120_b200 import moe_ops
+
+    gen_r = torch.Generator(device=device).manual_seed(77 + rank)
+    t, topk, hid = 7, 4, cfg.hidden
+    routed = torch.randn((t * topk, hid), generator=gen_r, device=device).to(torch.bfloat16)
+    weights = torch.rand((t, topk), generator=gen_r, device=device)
+    inverse = torch.randperm(t * topk, generator=gen_r, device=device).to(torch.int32)
+    out_nccl = torch.empty((t, hid), dtype=torch.bfloat16, device=device)
+    out_peer = torch.empty_like(out_nccl)
+    moe_ops.moe_reduce_tp2_out(out_nccl, routed, weights, inverse)
+    for _ in range(3):  # an odd number of steps: the buffers keep alternating correctly
+        moe_ops.moe_reduce_tp2_out(out_peer, routed, weights, inverse, peer=peer)
+    torch.cuda.synchronize()
+    moe_equal = bool(torch.equal(out_peer, out_nccl))
+    # one more plain step so that the fused decoder path above and this one leave the
+    # step parity even (every rank issues the same sequence)
+    moe_ops.moe_reduce_tp2_out(out_peer, routed, weights, inverse, peer=peer)
+    torch.cuda.synchronize()
+
+    results[rank] = dict(moe_reduce_equal=moe_equal, fused_vs_nccl_equal=bool(torch.equal(got_fused, got_nccl)),
                          fused_vs_nccl_cos=cos(got_fused, got_nccl),
                          fused_vs_single_cos=cos(got_fused, want),
                          replay_equal=bool(torch.equal(replayed, got_fused)),
@@ -103,3 +123,4 @@ def test_fused_allreduce_norm_matches_nccl_and_single_gpu():
         assert r["fused_vs_nccl_cos"] >= 0.9999, r
         assert r["fused_vs_single_cos"] >= 0.999, r
         assert r["replay_equal"], r
+        assert r["moe_reduce_equal"], r
