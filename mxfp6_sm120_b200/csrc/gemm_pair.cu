@@ -8,8 +8,8 @@
 // kernel at large M (its 5-stage ring delivered a block per ~580 cycles against ~390
 // cycles of MMA work).  Every CTA issues its own loads; no load is shared between CTAs.
 //
-// Roles per CTA (192 threads): warp 0 TMA producer; warp 1 MMA issuer in the leader
-// CTA (rank 0) / "stage ready" forwarder in the peer; warps 2..5 epilogue.
+// Roles per CTA (320 threads): warp 0 TMA producer; warp 1 MMA issuer in the leader CTA
+// (rank 0), idle in the peer; warps 2..9 epilogue, two per tensor-memory lane quarter.
 // Barriers live at the same shared-memory offsets in both CTAs; tcgen05.commit with
 // a CTA mask releases stages and publishes accumulators in both at once.
 // Every wait is bounded, as in the single-CTA kernel.
@@ -24,7 +24,8 @@ namespace {
 constexpr int kTileF = 128;
 constexpr int kTileK = 128;
 constexpr int kMmaK = 32;
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;                  // two per tensor-memory lane quarter
+constexpr int kThreads = 64 + 32 * kEpiWarps;  // producer warp, MMA warp, epilogue warps
 constexpr uint32_t kWTileBytes = kTileF * kTileK;
 constexpr uint32_t kWTileTxBytes = kWTileBytes / 4 * 3;
 constexpr uint32_t kAtomBytes = 512;
@@ -103,7 +104,8 @@ struct PairCfg {
   static constexpr uint32_t kEpiWarpBytes = 2048;
   // align slack, barriers, three group tables, epilogue staging
   static constexpr uint32_t kTableBytes = 3 * (512 + 1) * 4 + 4;
-  static constexpr uint32_t kFixedBytes = 1024 + 1024 + 4 * kEpiWarpBytes + ((kTableBytes + 127) / 128) * 128;
+  static constexpr uint32_t kFixedBytes =
+      1024 + 1024 + kEpiWarps * kEpiWarpBytes + ((kTableBytes + 127) / 128) * 128;
   static constexpr int kStagesRaw = (int)((232448u - kFixedBytes) / (kStageBytes + kSfStageBytes));
   static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
   static constexpr size_t kSmemBytes = kFixedBytes + (size_t)kStages * (kStageBytes + kSfStageBytes);
@@ -145,7 +147,7 @@ w6a8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fixed + 8 * (2 * C::kStages + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint8_t* epi_stage = fixed + 1024;
-  int* tile_prefix = reinterpret_cast<int*>(fixed + 1024 + 4 * C::kEpiWarpBytes);
+  int* tile_prefix = reinterpret_cast<int*>(fixed + 1024 + kEpiWarps * C::kEpiWarpBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -163,7 +165,7 @@ w6a8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
     }
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(tfull0 + 8 * i, 1);
-      ptx::mbar_init(tempty0 + 8 * i, 8);
+      ptx::mbar_init(tempty0 + 8 * i, 2 * kEpiWarps);
     }
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tm_w);
@@ -340,11 +342,14 @@ w6a8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
       }
     }
   } else if (warp >= 2) {
-    // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
+    // ---------------- epilogue (warps 2..9 of both CTAs) ----------------
+    // A warp reads the tensor-memory lanes of quarter warp % 4; the two warps of a quarter
+    // take alternate 32-column chunks.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     int acc = 0;
     uint32_t acc_phase = 0;
-    uint16_t* stage16 = reinterpret_cast<uint16_t*>(epi_stage + quarter * C::kEpiWarpBytes);
+    uint16_t* stage16 = reinterpret_cast<uint16_t*>(epi_stage + (warp - 2) * C::kEpiWarpBytes);
     const bool bf16_out = args.out_dtype == kBF16;
     PairWork wk;
     for (int t = pair; pair_decode<TN>(t, args, tile_prefix, &wk); t += pairs) {
@@ -356,7 +361,7 @@ w6a8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * TN;
       const int f0 = n_pair * 2 * kTileF + (int)rank * kTileF + quarter * 32;
 #pragma unroll 1
-      for (int c0 = 0; c0 < rows; c0 += 32) {
+      for (int c0 = 32 * half; c0 < rows; c0 += 32 * (kEpiWarps / 4)) {
         uint32_t r[32];
         ptx::tmem_ld_x32(t_addr + c0, r);
         ptx::tmem_ld_wait();
@@ -383,7 +388,7 @@ w6a8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
       }
       ptx::tc_fence_before();
       __syncwarp();
-      // The leader's MMA warp may reuse the buffer once all 8 epilogue warps are done.
+      // The leader's MMA warp may reuse the buffer once the epilogue warps of both CTAs are done.
       if (lane == 0) ptx::mbar_arrive_remote_relaxed(ptx::mapa(tempty0 + 8 * acc, 0u));
       if (++acc == C::kAcc) {
         acc = 0;
@@ -492,7 +497,7 @@ int plan_w6a8_pair(const GemmProblem& p, int sms, GemmPlan* plan) {
     // decide the rest.
     const int candidates[3] = {128, 192, 256};
     const int64_t block_cycles[3] = {400, 410, 530};
-    const int64_t exposed_epilogue[3] = {0, 0, 6000};
+    const int64_t exposed_epilogue[3] = {0, 0, 3000};
     int64_t best = 0;
     for (int i = 0; i < 3; ++i) {
       const int64_t tiles = ((p.m_total + candidates[i] - 1) / candidates[i]) * n_pairs;
