@@ -338,8 +338,11 @@ def decoder_step_latency(mx, device, stream, world: int, rank: int) -> dict:
         from mxfp6_sm120_b200.tp_fused import SymmetricBlocks
 
         nccl_model = model
-        peer = SymmetricBlocks(512, cfg.hidden, device, group)
-        model = mx.DenseDecoder(cfg, nccl_model.layers, world, rank, group, peer)
+        try:  # raises on every rank alike when any rank could not map a peer's block
+            peer = SymmetricBlocks(512, cfg.hidden, device, group)
+            model = mx.DenseDecoder(cfg, nccl_model.layers, world, rank, group, peer)
+        except RuntimeError:  # CUDA IPC not available between these GPUs: NCCL only
+            nccl_model = None
 
     def timed(step, reps):
         with torch.cuda.stream(stream):

@@ -43,32 +43,46 @@ class SymmetricBlocks:
         self.partial_bytes = (max_rows * hidden * 2 + 255) // 256 * 256
         own = ctypes.c_void_p()
         handle = (ctypes.c_ubyte * 64)()
-        with torch.cuda.device(device):
-            check(library().mxfp6_tp_block_alloc(self.partial_bytes, ctypes.byref(own), handle))
-        self._own = own.value
+        failure = None
+        try:
+            with torch.cuda.device(device):
+                check(library().mxfp6_tp_block_alloc(self.partial_bytes, ctypes.byref(own), handle))
+        except Exception as error:  # reported to every rank below, so that none waits alone
+            failure = f"rank {self.rank}: {error}"
+        self._own = own.value or 0
         handles = [None] * self.world
+        mine = bytes(handle) if failure is None else None
         if self.world > 1:
-            dist.all_gather_object(handles, bytes(handle), group=group)
+            dist.all_gather_object(handles, mine, group=group)
         else:
-            handles[0] = bytes(handle)
+            handles[0] = mine
         self._opened: list[int] = []
         pointers = []
-        for r, raw in enumerate(handles):
-            if r == self.rank:
-                pointers.append(self._own)
-                continue
-            peer = ctypes.c_void_p()
-            buf = (ctypes.c_ubyte * 64).from_buffer_copy(raw)
-            with torch.cuda.device(device):
-                check(library().mxfp6_tp_block_open(buf, ctypes.byref(peer)))
-            self._opened.append(peer.value)
-            pointers.append(peer.value)
+        try:
+            if any(raw is None for raw in handles):
+                raise RuntimeError(failure or "a peer could not allocate its block")
+            for r, raw in enumerate(handles):
+                if r == self.rank:
+                    pointers.append(self._own)
+                    continue
+                peer = ctypes.c_void_p()
+                buf = (ctypes.c_ubyte * 64).from_buffer_copy(raw)
+                with torch.cuda.device(device):
+                    check(library().mxfp6_tp_block_open(buf, ctypes.byref(peer)))
+                self._opened.append(peer.value)
+                pointers.append(peer.value)
+        except Exception as error:  # reported to every rank below, so that none waits alone
+            failure = f"rank {self.rank}: {error}"
+        if self.world > 1:
+            failures = [None] * self.world
+            dist.all_gather_object(failures, failure, group=group)  # also: every block is mapped
+            failure = next((f for f in failures if f is not None), None)
+        if failure is not None:
+            raise RuntimeError(f"could not map the peers' symmetric blocks ({failure})")
         self._blocks = (ctypes.c_void_p * self.world)(*pointers)
         size = HEADER_BYTES + 2 * self.partial_bytes
         self._bytes = torch.as_tensor(_DeviceBytes(self._own, size), device=device)
         self._next = 0
-        if self.world > 1:
-            dist.barrier(group=group)  # every rank has mapped every block
 
     def partial(self, buffer: int, rows: int, hidden: int) -> torch.Tensor:
         """BF16 ``[rows, hidden]`` view of this rank's partial buffer ``buffer`` (GEMM output)."""
