@@ -184,7 +184,7 @@ int mxfp6_gemm_w6a8_plan(int64_t m, int64_t n, int64_t k, int tile_tokens, int s
  * partial tiles in the scratch arena, 3 = never split. */
 int mxfp6_set_split_k_mode(int mode);
 int mxfp6_get_split_k_mode(void);
-/* Dense launches with m > 128 and n % 256 == 0 run on CTA pairs (tcgen05 cta_group::2:
+/* Dense launches with m > 128, n % 128 == 0 and n >= 256 run on CTA pairs (tcgen05 cta_group::2:
  * 256 weight rows per tile, each CTA stages half of the activation tile); 0 keeps them
  * on the single-CTA kernel.  Default 1.  Results are bit-identical either way.  No
  * reference counterpart: the reference picks kernels in its autotuner,

@@ -39,7 +39,7 @@ struct PairArgs {
   int64_t m;
   int n;
   int k_blocks;
-  int n_pair_tiles;  // n / 256
+  int n_pair_tiles;  // ceil(n / 256); with n % 256 == 128 the peer half of the last pair is empty
   int out_dtype;
   float alpha;
   int a_scale_row_blocks;
@@ -460,7 +460,9 @@ int make_tensor_map_2d(CUtensorMap* out, int type, const void* base, uint64_t in
 // tile_tokens 0 lets the planner choose among 128, 192 and 256.  Grouped launches
 // qualify when the mean group is large enough for those tiles.
 bool pair_kernel_applies(const GemmProblem& p, int tile_tokens) {
-  if (p.mode != kGemmStore || p.n % 256 != 0) return false;
+  // n % 256 == 128: the peer CTA of the last pair loads out-of-range (zero-filled or
+  // foreign) weight rows and stores nothing.
+  if (p.mode != kGemmStore || p.n % 128 != 0 || p.n < 256) return false;
   if (!(tile_tokens == 0 || tile_tokens == 128 || tile_tokens == 192 || tile_tokens == 256))
     return false;
   if (p.expert_offsets != nullptr) {
@@ -481,7 +483,7 @@ void fill_pair_plan(GemmPlan* plan) {
 
 int plan_w6a8_pair(const GemmProblem& p, int sms, GemmPlan* plan) {
   const int pairs = sms / 2 > 0 ? sms / 2 : 1;
-  const int64_t n_pairs = p.n / 256;
+  const int64_t n_pairs = (p.n + 255) / 256;
   const int64_t k_blocks = p.k / kTileK;
   const bool grouped = p.expert_offsets != nullptr;
   int tn = p.tile_tokens;
@@ -561,7 +563,7 @@ int launch_w6a8_pair(const GemmProblem& p, const GemmPlan& plan, cudaStream_t st
   args.m = p.m_total;
   args.n = p.n;
   args.k_blocks = p.k / kTileK;
-  args.n_pair_tiles = p.n / 256;
+  args.n_pair_tiles = (p.n + 255) / 256;
   args.out_dtype = p.out_dtype;
   args.alpha = p.alpha;
   args.trace = trace_buffer();

@@ -151,7 +151,7 @@ def set_split_k_mode(mode: str) -> None:
 
 
 def set_cta_pair_mode(enabled: bool) -> None:
-    """Run dense launches with m > 128 and n % 256 == 0 on CTA pairs (default) or not."""
+    """Run dense launches with m > 128, n % 128 == 0 and n >= 256 on CTA pairs (default) or not."""
     check(library().mxfp6_set_cta_pair_mode(1 if enabled else 0))
 
 

@@ -326,7 +326,8 @@ def test_cluster_split_k_matches_scratch_split_and_single_pass(mx):
 
 
 @pytest.mark.parametrize("m,n,k,tile", [(129, 256, 128, 0), (200, 1024, 2048, 128), (700, 1024, 2048, 256),
-                                        (1500, 5120, 1024, 0), (1500, 5120, 1024, 192)])
+                                        (1500, 5120, 1024, 0), (1500, 5120, 1024, 192),
+                                        (300, 384, 512, 0), (520, 896, 1024, 256)])
 def test_cta_pair_kernel_equals_single_cta_kernel(mx, m, n, k, tile):
     """The two-CTA kernel (256 weight rows per tile) and the single-CTA kernel add the
     same products in the same K order: outputs are bit-identical, and both meet the
@@ -355,6 +356,8 @@ def test_cta_pair_kernel_equals_single_cta_kernel(mx, m, n, k, tile):
 
 def test_cta_pair_kernel_is_not_planned_outside_its_shapes(mx):
     assert mx.gemm_w6a8_plan(128, 1024, 2048)["cta_pair"] == 0      # one tile of tokens
-    assert mx.gemm_w6a8_plan(512, 1000, 1024)["cta_pair"] == 0      # n not a multiple of 256
+    assert mx.gemm_w6a8_plan(512, 1000, 1024)["cta_pair"] == 0      # n not a multiple of 128
+    assert mx.gemm_w6a8_plan(512, 128, 1024)["cta_pair"] == 0       # a single weight tile
+    assert mx.gemm_w6a8_plan(512, 896, 1024)["cta_pair"] == 1       # last pair half empty
     assert mx.gemm_w6a8_plan(512, 1024, 2048, 64)["cta_pair"] == 0  # tile the pair kernel lacks
     assert mx.gemm_w6a8_plan(512, 1024, 2048)["cta_pair"] == 1
