@@ -34,10 +34,9 @@ int tp_block_alloc(size_t, void**, unsigned char*);
 int tp_block_open(const unsigned char*, void**);
 int tp_block_close(void*);
 int tp_block_free(void*);
-int tp_allreduce_sum(void* const*, int, int, int, size_t, void*, int64_t, int64_t, int*,
-                     cudaStream_t);
+int tp_allreduce_sum(void* const*, int, int, int, size_t, void*, int64_t, int64_t, cudaStream_t);
 int tp_allreduce_rmsnorm_quantize(void* const*, int, int, int, size_t, void*, const void*, float,
-                                  int64_t, int64_t, uint8_t*, uint8_t*, int*, cudaStream_t);
+                                  int64_t, int64_t, uint8_t*, uint8_t*, cudaStream_t);
 int rmsnorm_quantize_mxfp8(const void*, const void*, void*, int, const void*, float, int64_t,
                            int64_t, uint8_t*, uint8_t*, uint8_t*, cudaStream_t);
 int quantize_mxfp6(const void*, int, int64_t, int64_t, uint8_t*, uint8_t*, uint8_t*, cudaStream_t);
@@ -317,23 +316,15 @@ int mxfp6_tp_block_free(void* block) { return tp_block_free(block); }
 int mxfp6_tp_allreduce_bf16(void* const* blocks, int world, int rank, int buffer,
                             size_t partial_bytes, void* out, int64_t rows, int64_t k,
                             void* stream) {
-  int device = 0;
-  MX_CUDA(cudaGetDevice(&device));
-  int* status = device_status_word(device);
-  if (status == nullptr) return kCudaError;
-  return tp_allreduce_sum(blocks, world, rank, buffer, partial_bytes, out, rows, k, status,
+  return tp_allreduce_sum(blocks, world, rank, buffer, partial_bytes, out, rows, k,
                           static_cast<cudaStream_t>(stream));
 }
 int mxfp6_tp_allreduce_rmsnorm_quantize_mxfp8(void* const* blocks, int world, int rank, int buffer,
                                               size_t partial_bytes, void* x, const void* weight,
                                               float eps, int64_t rows, int64_t k, uint8_t* values,
                                               uint8_t* packed_scales, void* stream) {
-  int device = 0;
-  MX_CUDA(cudaGetDevice(&device));
-  int* status = device_status_word(device);
-  if (status == nullptr) return kCudaError;
   return tp_allreduce_rmsnorm_quantize(blocks, world, rank, buffer, partial_bytes, x, weight, eps,
-                                       rows, k, values, packed_scales, status,
+                                       rows, k, values, packed_scales,
                                        static_cast<cudaStream_t>(stream));
 }
 int mxfp6_quantize_mxfp6(const void* input, int dtype, int64_t rows, int64_t k, uint8_t* values,

@@ -29,6 +29,8 @@
 
 namespace mx {
 
+int* device_status_word(int device);  // gemm.cu: one status word per device
+
 constexpr int kTpMaxRanks = 8;
 constexpr int kTpThreads = 256;
 constexpr int kTpChunks = 8;  // 8-value chunks per thread: hidden <= 16384
@@ -329,7 +331,7 @@ int tp_block_free(void* block) {
 int tp_allreduce_rmsnorm_quantize(void* const* blocks, int world, int rank, int buffer,
                                   size_t partial_bytes, void* x, const void* weight, float eps,
                                   int64_t rows, int64_t k, uint8_t* values, uint8_t* packed,
-                                  int* status, cudaStream_t stream) {
+                                  cudaStream_t stream) {
   MX_REQUIRE(blocks != nullptr && world >= 1 && world <= kTpMaxRanks && rank >= 0 && rank < world,
              "world must be in [1, %d] and rank inside it", kTpMaxRanks);
   MX_REQUIRE(buffer == 0 || buffer == 1, "buffer must be 0 or 1");
@@ -347,6 +349,10 @@ int tp_allreduce_rmsnorm_quantize(void* const* blocks, int world, int rank, int 
                  (reinterpret_cast<uintptr_t>(values) & 7) == 0 &&
                  (reinterpret_cast<uintptr_t>(packed) & 3) == 0,
              "x / weight must be 16-byte, values 8-byte, scales 4-byte aligned");
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  int* status = device_status_word(device);
+  if (status == nullptr) return kCudaError;
   TpPeers peers;
   peers.world = world;
   peers.rank = rank;
@@ -379,7 +385,7 @@ int tp_allreduce_rmsnorm_quantize(void* const* blocks, int world, int rank, int 
 }
 
 int tp_allreduce_sum(void* const* blocks, int world, int rank, int buffer, size_t partial_bytes,
-                     void* out, int64_t rows, int64_t k, int* status, cudaStream_t stream) {
+                     void* out, int64_t rows, int64_t k, cudaStream_t stream) {
   MX_REQUIRE(blocks != nullptr && world >= 1 && world <= kTpMaxRanks && rank >= 0 && rank < world,
              "world must be in [1, %d] and rank inside it", kTpMaxRanks);
   MX_REQUIRE(buffer == 0 || buffer == 1, "buffer must be 0 or 1");
@@ -389,6 +395,10 @@ int tp_allreduce_sum(void* const* blocks, int world, int rank, int buffer, size_
   MX_REQUIRE((size_t)rows * (size_t)k * 2 <= partial_bytes,
              "the partial buffers hold %zu bytes, %lld x %lld BF16 need more", partial_bytes,
              (long long)rows, (long long)k);
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  int* status = device_status_word(device);
+  if (status == nullptr) return kCudaError;
   TpPeers peers;
   peers.world = world;
   peers.rank = rank;

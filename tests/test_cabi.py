@@ -126,3 +126,27 @@ def test_python_validation_mirrors_reference_errors():
     assert mx.is_available() in (True, False)
     assert mx.is_tuned_shape(32, 34816, 5120) and not mx.is_tuned_shape(33, 34816, 5120)
     assert mx.packed_scale_numel(129, 256) == 2048
+
+
+def test_decoder_side_entry_points_validate_before_any_launch():
+    """Argument checks of the fused norm and the peer-memory collectives run on the host."""
+    import ctypes as c
+
+    from mxfp6_sm120_b200._loader import library
+
+    lib = library()
+    # fused (residual +) RMSNorm + MXFP8: null input, then a residual without its output
+    assert lib.mxfp6_rmsnorm_quantize_mxfp8(None, None, None, 1, None, 1e-6, 4, 128, None, None,
+                                            None, None) == 1
+    blocks = (c.c_void_p * 2)(None, None)
+    # world outside [1, 8], a rank outside the world, a buffer index that does not exist
+    assert lib.mxfp6_tp_allreduce_bf16(blocks, 9, 0, 0, 4096, None, 4, 128, None) == 1
+    assert lib.mxfp6_tp_allreduce_bf16(blocks, 2, 2, 0, 4096, None, 4, 128, None) == 1
+    assert lib.mxfp6_tp_allreduce_bf16(blocks, 2, 0, 2, 4096, None, 4, 128, None) == 1
+    assert b"buffer" in lib.mxfp6_b200_last_error()
+    assert lib.mxfp6_tp_allreduce_rmsnorm_quantize_mxfp8(blocks, 2, 0, 0, 4096, None, None, 1e-6,
+                                                         4, 128, None, None, None) == 1
+    handle = (c.c_ubyte * 64)()
+    out = c.c_void_p()
+    assert lib.mxfp6_tp_block_alloc(100, c.byref(out), handle) == 1   # not a multiple of 256
+    assert b"256" in lib.mxfp6_b200_last_error()
