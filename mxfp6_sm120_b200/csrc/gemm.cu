@@ -136,8 +136,14 @@ __device__ __forceinline__ bool decode_work(int w, const KernelArgs& a, const in
   const int total_row_tiles = tile_prefix[a.groups];
   const int total = total_row_tiles * a.n_tiles * a.splits;
   if (w >= total) return false;
-  out->split = w % a.splits;
-  const int rest = w / a.splits;
+  // The issuing warps run this at every tile switch and share their schedulers with
+  // polling warps: the common cases (no K split, one row tile per group) avoid divisions.
+  int rest = w;
+  out->split = 0;
+  if (a.splits > 1) {
+    rest = w / a.splits;
+    out->split = w - rest * a.splits;
+  }
   out->tile_id = rest;
   // Largest g with n_tiles * tile_prefix[g] <= rest.
   int lo = 0, hi = a.groups;
@@ -150,16 +156,21 @@ __device__ __forceinline__ bool decode_work(int w, const KernelArgs& a, const in
   out->group = lo;
   const int local = rest - tile_prefix[lo] * a.n_tiles;
   const int mt = tile_prefix[lo + 1] - tile_prefix[lo];
-  out->m_tile = local % mt;
-  out->n_tile = local / mt;
+  if (mt == 1) {
+    out->m_tile = 0;
+    out->n_tile = local;
+  } else {
+    out->n_tile = local / mt;
+    out->m_tile = local - out->n_tile * mt;
+  }
   // Group extents were copied to shared memory in the prologue.
   const int* row_begin = tile_prefix + (kMaxGroups + 1);
   const int* scale_begin = row_begin + (kMaxGroups + 1);
-  const int64_t begin = row_begin[lo], end = row_begin[lo + 1], sbegin = scale_begin[lo];
-  out->row0 = begin + (int64_t)out->m_tile * TN;
-  const int64_t left = end - out->row0;
-  out->rows = left < TN ? (int)left : TN;
-  out->scale_row0 = sbegin + (int64_t)out->m_tile * TN;
+  const int first = row_begin[lo] + out->m_tile * TN;  // rows fit 32 bits (checked on the host)
+  const int left = row_begin[lo + 1] - first;
+  out->row0 = first;
+  out->rows = left < TN ? left : TN;
+  out->scale_row0 = scale_begin[lo] + out->m_tile * TN;
   return true;
 }
 
@@ -434,8 +445,8 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       Work wk;
       bool ok = true;
       for (int w = blockIdx.x; ok && decode_work<TN>(w, args, tile_prefix, &wk); w += gridDim.x) {
-        const int kb0 = (int)(((int64_t)wk.split * kb_total) / args.splits);
-        const int kb1 = (int)(((int64_t)(wk.split + 1) * kb_total) / args.splits);
+        const int kb0 = args.splits > 1 ? (wk.split * kb_total) / args.splits : 0;
+        const int kb1 = args.splits > 1 ? ((wk.split + 1) * kb_total) / args.splits : kb_total;
         const int w_row = wk.group * args.w_rows_per_group + wk.n_tile * kTileF;
         const int sfb_rb0 = (int)(wk.scale_row0 / kAtomRows);
         for (int kb = kb0; kb < kb1; kb += C::kSubs) {
@@ -510,8 +521,8 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       Work wk;
       bool ok = true;
       for (int w = blockIdx.x; ok && decode_work<TN>(w, args, tile_prefix, &wk); w += gridDim.x) {
-        const int kb0 = (int)(((int64_t)wk.split * kb_total) / args.splits);
-        const int kb1 = (int)(((int64_t)(wk.split + 1) * kb_total) / args.splits);
+        const int kb0 = args.splits > 1 ? (wk.split * kb_total) / args.splits : 0;
+        const int kb1 = args.splits > 1 ? ((wk.split + 1) * kb_total) / args.splits : kb_total;
         if (!__all_sync(0xffffffffu, bounded_wait(tempty0 + 8 * acc, acc_phase ^ 1u, abort_flag,
                                                   args.status, 102)))
           break;
@@ -1077,6 +1088,8 @@ int cta_pair_mode() {
 
 int plan_w6a8(const GemmProblem& p, GemmPlan* plan) {
   MX_REQUIRE(p.m_total > 0, "m must be positive; got %lld", (long long)p.m_total);
+  MX_REQUIRE(p.m_total <= (int64_t)INT32_MAX - 1024, "m must fit 32 bits; got %lld",
+             (long long)p.m_total);
   MX_REQUIRE(p.n > 0 && p.n % 8 == 0, "n must be a positive multiple of 8; got %d", p.n);
   MX_REQUIRE(p.k > 0 && p.k % 128 == 0, "k must be a positive multiple of 128; got %d", p.k);
   MX_REQUIRE(p.groups >= 1 && p.groups <= kMaxGroups, "groups must be in [1, %d]", kMaxGroups);

@@ -74,11 +74,12 @@ __device__ __forceinline__ bool pair_decode(int t, const PairArgs& a, const int*
   while (lo + 1 < a.groups && tile_prefix[lo + 1] * a.n_pair_tiles <= t) ++lo;  // empty groups
   const int local = t - tile_prefix[lo] * a.n_pair_tiles;
   const int mt = tile_prefix[lo + 1] - tile_prefix[lo];
-  const int m_tile = local % mt;
+  const int n_pair = mt == 1 ? local : local / mt;  // one row tile per group is the common case
+  const int m_tile = local - n_pair * mt;
   const int* row_begin = tile_prefix + (kPairMaxGroups + 1);
   const int* scale_begin = row_begin + (kPairMaxGroups + 1);
   out->group = lo;
-  out->n_pair = local / mt;
+  out->n_pair = n_pair;
   out->row0 = (int64_t)row_begin[lo] + (int64_t)m_tile * TN;
   const int64_t left = (int64_t)row_begin[lo + 1] - out->row0;
   out->rows = left < TN ? (int)left : TN;
