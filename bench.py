@@ -556,11 +556,27 @@ def main() -> None:
             h2d = sum(t.numel() * 2 for t in host_in.values())
             d2h = sum(t.numel() * 2 for t in host_out.values())
 
+            # Three streams: the copy of the next shape's activations from pinned host memory
+            # and the copy of the previous shape's output back overlap the GEMMs (PCIe is
+            # full duplex), ordered per shape by events.
+            copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
             def e2e_step():
+                copy_in.wait_stream(stream)   # the previous step's GEMMs have read the inputs
                 for key in order:
-                    acts[key].copy_(host_in[key], non_blocking=True)
+                    with torch.cuda.stream(copy_in):
+                        acts[key].copy_(host_in[key], non_blocking=True)
+                        arrived = torch.cuda.Event()
+                        arrived.record(copy_in)
+                    stream.wait_event(arrived)
                     out = run_shape(key)
-                    host_out[key].copy_(out, non_blocking=True)
+                    computed = torch.cuda.Event()
+                    computed.record(stream)
+                    copy_out.wait_event(computed)
+                    with torch.cuda.stream(copy_out):
+                        host_out[key].copy_(out, non_blocking=True)
+                stream.wait_stream(copy_in)
+                stream.wait_stream(copy_out)   # the step ends when every output is on the host
 
             e2e_step()
             stream.synchronize()
