@@ -452,9 +452,32 @@ def main() -> None:
             dist.all_reduce(out)
         return out
 
+    def run_shape_peer(key, peer):
+        """Row-parallel shape with a decode-sized output: partial into the symmetric block,
+        then one peer-memory kernel sums the ranks' partials into the output."""
+        weight, _ = layers[key[1:]]
+        partial = peer.next_partial(key[0], weight.rows)
+        mx.gemm_from_float(acts[key], weight, out_dtype=torch.bfloat16, out=partial)
+        return peer.allreduce(outs[key])
+
+    sweep_peer = None
+    if world > 1:
+        from mxfp6_sm120_b200 import tp
+        from mxfp6_sm120_b200.tp_fused import SymmetricBlocks
+
+        try:  # raises on every rank alike when any rank could not map a peer's block
+            sweep_peer = SymmetricBlocks(tp.PEER_ALLREDUCE_MAX_ROWS, max(n for n, _ in ROW_PARALLEL),
+                                         device)
+        except RuntimeError:
+            sweep_peer = None
+
     def run_sweep():
         for key in order:
-            run_shape(key)
+            weight, mode = layers[key[1:]]
+            if sweep_peer is not None and mode == "row" and key[0] <= tp.PEER_ALLREDUCE_MAX_ROWS:
+                run_shape_peer(key, sweep_peer)
+            else:
+                run_shape(key)
 
     stream = torch.cuda.Stream(device)
     with torch.cuda.stream(stream):
@@ -615,7 +638,7 @@ def main() -> None:
         "config": {"workload": WORKLOAD, "shapes": NK_SHAPES, "m_values": M_VALUES,
                    "parallelism": "single GPU" if world == 1 else
                    f"tp{world}: K=5120 projections column-parallel, 5120x6144 and 5120x17408 "
-                   "row-parallel + NCCL all-reduce",
+                   "row-parallel + all-reduce (one peer-memory kernel up to 256 rows, NCCL above)",
                    "l2": "inputs larger than L2: shapes run M-major, 270 MB of packed weights "
                          "cycle through the 126 MB L2 between reuses",
                    "graph": "one CUDA graph per step"},

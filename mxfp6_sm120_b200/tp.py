@@ -20,6 +20,9 @@ import torch
 import torch.distributed as dist
 
 SCALE_VECTOR_SIZE = 32
+# Up to this many output rows a row-parallel sum runs as one peer-memory kernel (latency
+# bound); larger outputs are bandwidth-bound collectives and go through NCCL.
+PEER_ALLREDUCE_MAX_ROWS = 256
 
 
 def _packed_scale_offset(row: torch.Tensor, group: torch.Tensor, groups: int) -> torch.Tensor:
@@ -111,14 +114,25 @@ class ColumnParallelLinear:
 class RowParallelLinear:
     """``out[M, N] = all_reduce_sum(gemm(a[:, begin:end], W[:, begin:end]))``."""
 
-    def __init__(self, ops, shard: WeightShard, group=None):
+    def __init__(self, ops, shard: WeightShard, group=None, peer=None):
         self.ops = ops
         self.shard = shard
         self.group = group
+        self.peer = peer
         self.weight = ops.PackedMXFP6Tensor(shard.values, shard.scales, shard.rows, shard.k)
 
     def __call__(self, a_local: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
                  out: torch.Tensor | None = None) -> torch.Tensor:
+        rows = int(a_local.shape[0])
+        if (self.peer is not None and self.peer.world > 1 and out_dtype == torch.bfloat16
+                and rows <= PEER_ALLREDUCE_MAX_ROWS):
+            # Decode-sized outputs: the GEMM writes into this rank's symmetric block and one
+            # kernel sums all ranks' partials over peer memory (tp_fused.SymmetricBlocks).
+            partial = self.peer.next_partial(rows, self.shard.rows)
+            self.ops.gemm_from_float(a_local, self.weight, out_dtype=out_dtype, out=partial)
+            if out is None:
+                out = torch.empty((rows, self.shard.rows), dtype=out_dtype, device=a_local.device)
+            return self.peer.allreduce(out)
         partial = self.ops.gemm_from_float(a_local, self.weight, out_dtype=out_dtype, out=out)
         if dist.is_initialized() and dist.get_world_size(self.group) > 1:
             dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
