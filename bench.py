@@ -281,9 +281,15 @@ def moe_layer_latency_ep(mx, device, stream, world: int, rank: int) -> dict:
     from mxfp6_sm120_b200.ep import ExpertParallelMoe
     from mxfp6_sm120_b200.moe_layer import MoeLayer
 
+    from mxfp6_sm120_b200.tp_fused import SymmetricBlocks
+
     shape = mx.MoeShape()
     layer = MoeLayer.random(device, shape, seed=4000)
-    moe = ExpertParallelMoe(layer)
+    try:  # raises on every rank alike when any rank could not map a peer's block
+        peer = SymmetricBlocks(ExpertParallelMoe.PEER_MAX_TOKENS, shape.hidden, device)
+    except RuntimeError:
+        peer = None
+    moe = ExpertParallelMoe(layer, peer=peer)
     del layer
     rows = []
     for batch in MOE_BATCHES:
@@ -315,7 +321,9 @@ def moe_layer_latency_ep(mx, device, stream, world: int, rank: int) -> dict:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         rows.append({"tokens": batch, "tokens_per_rank": local, "us_warm": round(float(t.item()), 1)})
     return {"config": f"expert parallel over {world} ranks ({shape.experts // world} experts each): "
-                      "all-gather dispatch, all-to-all combine, shared expert replicated",
+                      "all-gather dispatch, all-to-all combine, shared expert replicated; up to "
+                      f"{ExpertParallelMoe.PEER_MAX_TOKENS} tokens both exchanges are one "
+                      "peer-memory kernel each, above that NCCL",
             "rows": rows}
 
 

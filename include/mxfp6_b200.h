@@ -133,6 +133,20 @@ int mxfp6_tp_block_free(void* block_dev);
 int mxfp6_tp_allreduce_bf16(void* const* blocks_host, int world, int rank, int buffer,
                             size_t partial_bytes, void* out_dev, int64_t rows, int64_t k,
                             void* stream);
+/* Reduce-scatter form: out [rows_per_rank, k] <- bf16(sum over ranks of rows
+ * [rank * rows_per_rank, (rank + 1) * rows_per_rank) of every rank's [world * rows_per_rank, k]
+ * BF16 partial).  The expert-parallel combine: every rank sums the partial rows of ITS tokens
+ * (the reference leaves this exchange to the caller, csrc/moe.cu:4243-4261). */
+int mxfp6_tp_reduce_scatter_bf16(void* const* blocks_host, int world, int rank, int buffer,
+                                 size_t partial_bytes, void* out_dev, int64_t rows_per_rank,
+                                 int64_t k, void* stream);
+/* All-gather of 1..4 byte segments with one handshake: segment s of rank r, found at
+ * offsets[s] inside r's partial buffer, lands at dsts_dev[s] + r * bytes[s].  Offsets and
+ * sizes are multiples of 16.  The expert-parallel dispatch (MXFP8 rows, scale rows, top-k
+ * ids and weights of every rank's tokens). */
+int mxfp6_tp_allgather(void* const* blocks_host, int world, int rank, int buffer,
+                       size_t partial_bytes, int segments, const int64_t* offsets,
+                       const int64_t* bytes, void* const* dsts_dev, void* stream);
 int mxfp6_tp_allreduce_rmsnorm_quantize_mxfp8(void* const* blocks_host, int world, int rank,
                                               int buffer, size_t partial_bytes, void* x_dev,
                                               const void* weight_dev, float eps, int64_t rows,

@@ -46,6 +46,15 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [POINTER(c_void_p), c_int, c_int, c_int, c_size_t, c_void_p, c_int64, c_int64, c_void_p],
     ),
+    "mxfp6_tp_reduce_scatter_bf16": (
+        c_int,
+        [POINTER(c_void_p), c_int, c_int, c_int, c_size_t, c_void_p, c_int64, c_int64, c_void_p],
+    ),
+    "mxfp6_tp_allgather": (
+        c_int,
+        [POINTER(c_void_p), c_int, c_int, c_int, c_size_t, c_int, _I64P, _I64P, POINTER(c_void_p),
+         c_void_p],
+    ),
     "mxfp6_tp_allreduce_rmsnorm_quantize_mxfp8": (
         c_int,
         [POINTER(c_void_p), c_int, c_int, c_int, c_size_t, c_void_p, c_void_p, c_float, c_int64,

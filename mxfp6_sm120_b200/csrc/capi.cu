@@ -35,6 +35,9 @@ int tp_block_open(const unsigned char*, void**);
 int tp_block_close(void*);
 int tp_block_free(void*);
 int tp_allreduce_sum(void* const*, int, int, int, size_t, void*, int64_t, int64_t, cudaStream_t);
+int tp_reduce_scatter(void* const*, int, int, int, size_t, void*, int64_t, int64_t, cudaStream_t);
+int tp_allgather(void* const*, int, int, int, size_t, int, const int64_t*, const int64_t*,
+                 void* const*, cudaStream_t);
 int tp_allreduce_rmsnorm_quantize(void* const*, int, int, int, size_t, void*, const void*, float,
                                   int64_t, int64_t, uint8_t*, uint8_t*, cudaStream_t);
 int rmsnorm_quantize_mxfp8(const void*, const void*, void*, int, const void*, float, int64_t,
@@ -318,6 +321,18 @@ int mxfp6_tp_allreduce_bf16(void* const* blocks, int world, int rank, int buffer
                             void* stream) {
   return tp_allreduce_sum(blocks, world, rank, buffer, partial_bytes, out, rows, k,
                           static_cast<cudaStream_t>(stream));
+}
+int mxfp6_tp_reduce_scatter_bf16(void* const* blocks, int world, int rank, int buffer,
+                                 size_t partial_bytes, void* out, int64_t rows_per_rank, int64_t k,
+                                 void* stream) {
+  return tp_reduce_scatter(blocks, world, rank, buffer, partial_bytes, out, rows_per_rank, k,
+                           static_cast<cudaStream_t>(stream));
+}
+int mxfp6_tp_allgather(void* const* blocks, int world, int rank, int buffer, size_t partial_bytes,
+                       int segments, const int64_t* offsets, const int64_t* bytes,
+                       void* const* dsts, void* stream) {
+  return tp_allgather(blocks, world, rank, buffer, partial_bytes, segments, offsets, bytes, dsts,
+                      static_cast<cudaStream_t>(stream));
 }
 int mxfp6_tp_allreduce_rmsnorm_quantize_mxfp8(void* const* blocks, int world, int rank, int buffer,
                                               size_t partial_bytes, void* x, const void* weight,

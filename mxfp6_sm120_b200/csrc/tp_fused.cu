@@ -173,6 +173,74 @@ allreduce_sum_kernel(const TpPeers peers, TpState* state, __nv_bfloat16* out, in
   tp_finish(state, step);
 }
 
+// out <- bf16(sum over ranks of rows [first_chunk, first_chunk + chunks) of every rank's buffer):
+// the reduce-scatter form (every rank sums ITS slice of all the partials), used by the
+// expert-parallel combine.
+__global__ void __launch_bounds__(kTpThreads)
+reduce_scatter_kernel(const TpPeers peers, TpState* state, __nv_bfloat16* out, int64_t first_chunk,
+                      int64_t chunks, int* status) {
+  __shared__ uint32_t step_shared;
+  __shared__ int ok_shared;
+  const uint32_t step = tp_handshake(peers, state, status, &step_shared, &ok_shared);
+  if (ok_shared != 0) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < chunks;
+         c += stride) {
+      uint4 part[kTpMaxRanks];
+#pragma unroll
+      for (int r = 0; r < kTpMaxRanks; ++r) {
+        if (r < peers.world) {
+          part[r] = ld_volatile_u128(reinterpret_cast<const uint4*>(peers.partial[r]) +
+                                     first_chunk + c);
+        }
+      }
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < kTpMaxRanks; ++r) {
+        if (r < peers.world) {
+          float v[8];
+          unpack_bf16x8(part[r], v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += v[i];
+        }
+      }
+      reinterpret_cast<uint4*>(out)[c] = pack_bf16x8(acc);
+    }
+  }
+  tp_finish(state, step);
+}
+
+// All-gather of up to four byte segments: segment s of rank r (at seg_offset[s] inside r's
+// buffer) lands at dst[s] + r * seg_bytes[s].  One handshake for the whole payload (the
+// expert-parallel dispatch: MXFP8 rows, scale rows, top-k ids and weights).
+struct TpSegments {
+  int count;
+  int64_t offset[4];  // bytes from the start of the partial buffer, multiples of 16
+  int64_t bytes[4];   // multiples of 16
+  uint8_t* dst[4];
+};
+
+__global__ void __launch_bounds__(kTpThreads)
+allgather_kernel(const TpPeers peers, TpState* state, const TpSegments seg, int* status) {
+  __shared__ uint32_t step_shared;
+  __shared__ int ok_shared;
+  const uint32_t step = tp_handshake(peers, state, status, &step_shared, &ok_shared);
+  if (ok_shared != 0) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (int s = 0; s < seg.count; ++s) {
+      const int64_t chunks = seg.bytes[s] / 16;
+      for (int r = 0; r < peers.world; ++r) {
+        const uint4* src = reinterpret_cast<const uint4*>(
+            static_cast<const uint8_t*>(peers.partial[r]) + seg.offset[s]);
+        uint4* dst = reinterpret_cast<uint4*>(seg.dst[s] + r * seg.bytes[s]);
+        for (int64_t c = tid; c < chunks; c += stride) dst[c] = ld_volatile_u128(src + c);
+      }
+    }
+  }
+  tp_finish(state, step);
+}
+
 // x[row] <- bf16(x[row] + bf16(sum over ranks of partial_r[row])); then RMSNorm * weight and
 // MXFP8 with packed scales.  One CTA per row.
 template <int kChunks>
@@ -419,6 +487,96 @@ int tp_allreduce_sum(void* const* blocks, int world, int rank, int buffer, size_
   if (grid > 148 * 4) grid = 148 * 4;
   allreduce_sum_kernel<<<(unsigned)grid, kTpThreads, 0, stream>>>(
       peers, state, static_cast<__nv_bfloat16*>(out), chunks, status);
+  MX_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+namespace {
+// Common argument checks and the peer table of the plain collectives.
+int tp_prepare(void* const* blocks, int world, int rank, int buffer, size_t partial_bytes,
+               TpPeers* peers, TpState** state, int** status) {
+  MX_REQUIRE(blocks != nullptr && world >= 1 && world <= kTpMaxRanks && rank >= 0 && rank < world,
+             "world must be in [1, %d] and rank inside it", kTpMaxRanks);
+  MX_REQUIRE(buffer == 0 || buffer == 1, "buffer must be 0 or 1");
+  for (int r = 0; r < world; ++r) MX_REQUIRE(blocks[r] != nullptr, "block of rank %d is null", r);
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  *status = device_status_word(device);
+  if (*status == nullptr) return kCudaError;
+  peers->world = world;
+  peers->rank = rank;
+  for (int r = 0; r < kTpMaxRanks; ++r) {
+    peers->partial[r] = nullptr;
+    peers->flags[r] = nullptr;
+  }
+  for (int r = 0; r < world; ++r) {
+    auto* base = static_cast<uint8_t*>(blocks[r]);
+    peers->flags[r] = reinterpret_cast<uint32_t*>(base);
+    peers->partial[r] = base + kTpHeaderBytes + (size_t)buffer * partial_bytes;
+  }
+  *state = reinterpret_cast<TpState*>(static_cast<uint8_t*>(blocks[rank]) +
+                                      kTpMaxRanks * sizeof(uint32_t));
+  return kOk;
+}
+}  // namespace
+
+int tp_reduce_scatter(void* const* blocks, int world, int rank, int buffer, size_t partial_bytes,
+                      void* out, int64_t rows_per_rank, int64_t k, cudaStream_t stream) {
+  MX_REQUIRE(out != nullptr && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+             "out must be a 16-byte aligned device pointer");
+  MX_REQUIRE(rows_per_rank > 0 && k > 0 && k % 8 == 0,
+             "rows_per_rank must be positive and k a multiple of 8");
+  MX_REQUIRE((size_t)world * (size_t)rows_per_rank * (size_t)k * 2 <= partial_bytes,
+             "the partial buffers hold %zu bytes, %d x %lld x %lld BF16 need more", partial_bytes,
+             world, (long long)rows_per_rank, (long long)k);
+  TpPeers peers;
+  TpState* state = nullptr;
+  int* status = nullptr;
+  if (int rc = tp_prepare(blocks, world, rank, buffer, partial_bytes, &peers, &state, &status))
+    return rc;
+  const int64_t chunks = rows_per_rank * k / 8;
+  int64_t grid = (chunks + kTpThreads - 1) / kTpThreads;
+  if (grid > 148 * 4) grid = 148 * 4;
+  reduce_scatter_kernel<<<(unsigned)grid, kTpThreads, 0, stream>>>(
+      peers, state, static_cast<__nv_bfloat16*>(out), (int64_t)rank * chunks, chunks, status);
+  MX_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+int tp_allgather(void* const* blocks, int world, int rank, int buffer, size_t partial_bytes,
+                 int segments, const int64_t* offsets, const int64_t* bytes, void* const* dsts,
+                 cudaStream_t stream) {
+  MX_REQUIRE(segments >= 1 && segments <= 4 && offsets != nullptr && bytes != nullptr &&
+                 dsts != nullptr,
+             "one to four segments with their offsets, sizes and destinations");
+  TpSegments seg;
+  seg.count = segments;
+  int64_t largest = 0;
+  for (int s = 0; s < 4; ++s) {
+    seg.offset[s] = 0;
+    seg.bytes[s] = 0;
+    seg.dst[s] = nullptr;
+  }
+  for (int s = 0; s < segments; ++s) {
+    MX_REQUIRE(offsets[s] >= 0 && bytes[s] > 0 && offsets[s] % 16 == 0 && bytes[s] % 16 == 0 &&
+                   (size_t)(offsets[s] + bytes[s]) <= partial_bytes,
+               "segment %d must be 16-byte granular and inside the partial buffer", s);
+    MX_REQUIRE(dsts[s] != nullptr && (reinterpret_cast<uintptr_t>(dsts[s]) & 15) == 0,
+               "destination %d must be a 16-byte aligned device pointer", s);
+    seg.offset[s] = offsets[s];
+    seg.bytes[s] = bytes[s];
+    seg.dst[s] = static_cast<uint8_t*>(dsts[s]);
+    if (bytes[s] > largest) largest = bytes[s];
+  }
+  TpPeers peers;
+  TpState* state = nullptr;
+  int* status = nullptr;
+  if (int rc = tp_prepare(blocks, world, rank, buffer, partial_bytes, &peers, &state, &status))
+    return rc;
+  int64_t grid = (largest / 16 + kTpThreads - 1) / kTpThreads;
+  if (grid > 148 * 2) grid = 148 * 2;
+  if (grid < 1) grid = 1;
+  allgather_kernel<<<(unsigned)grid, kTpThreads, 0, stream>>>(peers, state, seg, status);
   MX_CUDA(cudaGetLastError());
   return kOk;
 }

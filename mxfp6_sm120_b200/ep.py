@@ -25,7 +25,7 @@ compute stream through ``torch.distributed`` (NCCL over NVLink).
 
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 
 import torch
 import torch.distributed as dist
@@ -87,13 +87,23 @@ class EpState:
     ones: torch.Tensor                   # [B_local, G] combine weights
     gather_index: torch.Tensor           # [B_local * G] row of partial g for token t
     output: torch.Tensor
+    # peer-memory exchange (decode batches): dispatch payload offsets in buffer 0 of the
+    # symmetric block, the summed partial rows of this rank's tokens, and a trivial index
+    dispatch: tuple | None = None
+    combined: torch.Tensor | None = None
+    identity: torch.Tensor | None = None
 
 
 class ExpertParallelMoe:
     """One MoE layer whose routed experts are sharded over ``group``."""
 
-    def __init__(self, layer: MoeLayer, group=None):
+    # Up to this many tokens over all ranks the two exchanges run as one peer-memory kernel
+    # each (tp_fused.SymmetricBlocks) instead of four all-gathers and an all-to-all.
+    PEER_MAX_TOKENS = 512
+
+    def __init__(self, layer: MoeLayer, group=None, peer=None):
         self.group = group
+        self.peer = peer
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.shape = layer.shape
@@ -112,6 +122,8 @@ class ExpertParallelMoe:
         local_shape = MoeShape(shape.hidden, shape.intermediate, self.local_experts, shape.topk)
         index = (torch.arange(world).view(1, world) * local_tokens
                  + torch.arange(local_tokens).view(local_tokens, 1)).reshape(-1)
+        if self.peer is not None and world > 1 and total <= self.PEER_MAX_TOKENS:
+            return self._peer_state(local_tokens, local_shape, index)
         return EpState(
             Qwen35GroupedWorkspace.allocate(local_tokens, device, shape),
             Qwen35GroupedWorkspace.allocate(total, device, local_shape),
@@ -121,6 +133,45 @@ class ExpertParallelMoe:
             torch.ones((local_tokens, world), dtype=torch.float32, device=device),
             index.to(torch.int32).to(device),
             torch.empty((local_tokens, shape.hidden), dtype=torch.bfloat16, device=device),
+        )
+
+    def _peer_state(self, local_tokens: int, local_shape: MoeShape, index: torch.Tensor) -> EpState:
+        """State whose exchanged tensors live in the symmetric block: this rank's MXFP8 rows,
+        scale rows, top-k ids and weights in buffer 0 (written in place by the top-k kernel),
+        its partial outputs for every token in buffer 1."""
+        device = self.w1.values.device
+        shape, world, peer = self.shape, self.world, self.peer
+        total = local_tokens * world
+
+        def align(v: int) -> int:
+            return (v + 255) // 256 * 256
+
+        q_bytes = local_tokens * shape.hidden
+        s_bytes = local_tokens * shape.hidden // 32
+        k_bytes = local_tokens * shape.topk * 4
+        off_q, off_s = 0, align(q_bytes)
+        off_i = off_s + align(s_bytes)
+        off_w = off_i + align(k_bytes)
+        local = Qwen35GroupedWorkspace.allocate(local_tokens, device, shape)
+        local = replace(
+            local,
+            quantized=peer.view(0, off_q, (local_tokens, shape.hidden), torch.uint8),
+            input_scales=peer.view(0, off_s, (local_tokens, shape.hidden // 32), torch.uint8),
+            topk_ids=peer.view(0, off_i, (local_tokens, shape.topk), torch.int32),
+            topk_weights=peer.view(0, off_w, (local_tokens, shape.topk), torch.float32),
+        )
+        return EpState(
+            local,
+            Qwen35GroupedWorkspace.allocate(total, device, local_shape),
+            SharedExpertWorkspace.allocate(local_tokens, device, shape),
+            peer.view(1, 0, (total, shape.hidden), torch.bfloat16),
+            torch.empty((0,), dtype=torch.bfloat16, device=device),
+            torch.ones((local_tokens, 1), dtype=torch.float32, device=device),
+            index.to(torch.int32).to(device),
+            torch.empty((local_tokens, shape.hidden), dtype=torch.bfloat16, device=device),
+            dispatch=(off_q, off_s, off_i, off_w),
+            combined=torch.empty((local_tokens, shape.hidden), dtype=torch.bfloat16, device=device),
+            identity=torch.arange(local_tokens, dtype=torch.int32, device=device),
         )
 
     def forward(self, state: EpState, hidden: torch.Tensor, router_logits: torch.Tensor,
@@ -133,7 +184,11 @@ class ExpertParallelMoe:
                               loc.topk_weights, loc.topk_ids, hidden, router_logits,
                               renormalize=True)
         # 2. dispatch: rows, scales, ids and weights of every rank
-        if self.world > 1:
+        if state.dispatch is not None:
+            off_q, off_s, off_i, off_w = state.dispatch
+            self.peer.allgather(0, [(off_q, ws.quantized), (off_s, ws.input_scales),
+                                    (off_i, ws.topk_ids), (off_w, ws.topk_weights)])
+        elif self.world > 1:
             dist.all_gather_into_tensor(ws.quantized, loc.quantized, group=self.group)
             dist.all_gather_into_tensor(ws.input_scales, loc.input_scales, group=self.group)
             dist.all_gather_into_tensor(ws.topk_ids, loc.topk_ids, group=self.group)
@@ -152,6 +207,13 @@ class ExpertParallelMoe:
                              self.w2.values.view(e, h, i * 3 // 4), self.w2.scales)
         moe_reduce_out(state.partial, ws.routed_output, ws.topk_weights, ws.inverse_permutation)
         # 4. combine: partial rows of my tokens from every rank
+        if state.dispatch is not None:
+            # one kernel sums them over peer memory; the shared expert joins in the last reduce
+            self.peer.reduce_scatter(1, state.combined)
+            shared_out = shared_expert_out(state.shared, loc, self.shared_w1, self.shared_w2)
+            moe_reduce_out(state.output, state.combined, state.ones, state.identity, shared_out,
+                           shared_gate)
+            return state.output
         if self.world > 1:
             dist.all_to_all_single(state.received, state.partial, group=self.group)
         else:

@@ -129,6 +129,51 @@ class SymmetricBlocks:
             )
         return out
 
+    def allgather(self, buffer: int, segments) -> None:
+        """``segments`` = up to four ``(offset_bytes, tensor)``: the ``tensor.nbytes / world``
+        bytes at ``offset_bytes`` of every rank's partial buffer ``buffer`` are gathered into
+        ``tensor`` in rank order.  One handshake for all segments."""
+        count = len(segments)
+        offsets = (ctypes.c_int64 * count)(*[int(o) for o, _ in segments])
+        sizes = (ctypes.c_int64 * count)(
+            *[t.numel() * t.element_size() // self.world for _, t in segments])
+        dsts = (ctypes.c_void_p * count)(*[t.data_ptr() for _, t in segments])
+        self._next = buffer ^ 1
+        with torch.cuda.device(self.device):
+            check(
+                library().mxfp6_tp_allgather(
+                    self._blocks, self.world, self.rank, buffer, self.partial_bytes, count, offsets,
+                    sizes, dsts, _stream(self.device),
+                )
+            )
+
+    def reduce_scatter(self, buffer: int, out: torch.Tensor) -> torch.Tensor:
+        """``out [rows, hidden]`` = sum over ranks of rows ``[rank * rows, (rank + 1) * rows)``
+        of every rank's BF16 ``[world * rows, hidden]`` partial in buffer ``buffer``."""
+        rows, hidden = (int(v) for v in out.shape)
+        if out.dtype != torch.bfloat16 or not out.is_contiguous():
+            raise ValueError("out must be contiguous BF16")
+        self._next = buffer ^ 1
+        with torch.cuda.device(self.device):
+            check(
+                library().mxfp6_tp_reduce_scatter_bf16(
+                    self._blocks, self.world, self.rank, buffer, self.partial_bytes,
+                    out.data_ptr(), rows, hidden, _stream(self.device),
+                )
+            )
+        return out
+
+    def view(self, buffer: int, offset: int, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """Typed view of ``shape`` at ``offset`` bytes inside this rank's partial buffer."""
+        elements = 1
+        for d in shape:
+            elements *= d
+        size = elements * torch.empty((), dtype=dtype).element_size()
+        if offset % 16 or offset + size > self.partial_bytes:
+            raise ValueError("view must be 16-byte aligned and inside the partial buffer")
+        begin = HEADER_BYTES + buffer * self.partial_bytes + offset
+        return self._bytes[begin : begin + size].view(dtype).view(shape)
+
     def close(self) -> None:
         """Unmap the peers' blocks and free this rank's (call on every rank, between steps)."""
         with torch.cuda.device(self.device):

@@ -50,7 +50,30 @@ def _worker(rank: int, world: int, port: int, results) -> None:
     torch.cuda.synchronize()
     cos = torch.nn.functional.cosine_similarity(got.float().flatten(), want[mine].float().flatten(), dim=0)
     same_ids = torch.equal(ep_state.local.topk_ids, state.workspace.topk_ids[mine])
-    results[rank] = (bool(same_ids), float(cos), mx.device_status())
+    # the same layer with both exchanges over peer memory (one kernel each), eager and replayed
+    from mxfp6_sm120_b200.tp_fused import SymmetricBlocks
+
+    peer = SymmetricBlocks(world * local_tokens, shape.hidden, device)
+    moe_p = ExpertParallelMoe(layer, peer=peer)
+    state_p = moe_p.state(local_tokens)
+    assert state_p.dispatch is not None
+    args = (hidden[mine].contiguous(), logits[mine].contiguous(), gate[mine].contiguous())
+    got_p = moe_p.forward(state_p, *args).clone()
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            moe_p.forward(state_p, *args)
+        for _ in range(3):
+            graph.replay()
+        stream.synchronize()
+    replay_equal = bool(torch.equal(state_p.output, got_p))
+    cos_p = torch.nn.functional.cosine_similarity(got_p.float().flatten(), want[mine].float().flatten(), dim=0)
+    same_ids_p = torch.equal(state_p.local.topk_ids, state.workspace.topk_ids[mine])
+    results[rank] = (bool(same_ids and same_ids_p), float(min(cos, cos_p)), mx.device_status(),
+                     replay_equal)
     dist.barrier()
     torch.cuda.synchronize()
     os._exit(0)  # no NCCL teardown: every rank has reported and is between steps
@@ -65,5 +88,5 @@ def test_expert_parallel_matches_single_gpu_layer():
     results = manager.dict()
     mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
     for rank in range(world):
-        same_ids, cos, status = results[rank]
-        assert same_ids and cos >= 0.999 and status == 0
+        same_ids, cos, status, replay_equal = results[rank]
+        assert same_ids and cos >= 0.999 and status == 0 and replay_equal
