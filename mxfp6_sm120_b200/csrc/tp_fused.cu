@@ -228,13 +228,16 @@ allgather_kernel(const TpPeers peers, TpState* state, const TpSegments seg, int*
   if (ok_shared != 0) {
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    // (rank, chunk) pairs are dealt to the threads, so that the loads from different peers
+    // are in flight together instead of one NVLink round trip after the other.
     for (int s = 0; s < seg.count; ++s) {
       const int64_t chunks = seg.bytes[s] / 16;
-      for (int r = 0; r < peers.world; ++r) {
+      for (int64_t idx = tid; idx < chunks * peers.world; idx += stride) {
+        const int r = static_cast<int>(idx / chunks);
+        const int64_t c = idx - r * chunks;
         const uint4* src = reinterpret_cast<const uint4*>(
             static_cast<const uint8_t*>(peers.partial[r]) + seg.offset[s]);
-        uint4* dst = reinterpret_cast<uint4*>(seg.dst[s] + r * seg.bytes[s]);
-        for (int64_t c = tid; c < chunks; c += stride) dst[c] = ld_volatile_u128(src + c);
+        reinterpret_cast<uint4*>(seg.dst[s] + r * seg.bytes[s])[c] = ld_volatile_u128(src + c);
       }
     }
   }
@@ -573,7 +576,7 @@ int tp_allgather(void* const* blocks, int world, int rank, int buffer, size_t pa
   int* status = nullptr;
   if (int rc = tp_prepare(blocks, world, rank, buffer, partial_bytes, &peers, &state, &status))
     return rc;
-  int64_t grid = (largest / 16 + kTpThreads - 1) / kTpThreads;
+  int64_t grid = (largest / 16 * world + kTpThreads - 1) / kTpThreads;
   if (grid > 148 * 2) grid = 148 * 2;
   if (grid < 1) grid = 1;
   allgather_kernel<<<(unsigned)grid, kTpThreads, 0, stream>>>(peers, state, seg, status);
