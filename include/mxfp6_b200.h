@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define MXFP6_B200_ABI_VERSION 3
+#define MXFP6_B200_ABI_VERSION 4
 
 #define MXFP6_DTYPE_F16 0
 #define MXFP6_DTYPE_BF16 1
@@ -44,11 +44,6 @@ const char* mxfp6_b200_last_error(void);
 /* Synchronises the current device and reads the status word that kernels with
  * bounded waits write when a wait expires (0 = none did).  `reset` != 0 clears it. */
 int mxfp6_b200_device_status(int* value, int reset);
-
-/* Diagnostics: CTA 0 of every later GEMM launch writes 3 x 256 int64 cycle stamps
- * (stage issued by the TMA warp, stage seen ready by the MMA warp, stage committed)
- * into trace_dev; NULL switches tracing off. */
-int mxfp6_b200_set_trace_buffer(void* trace_dev);
 
 /* ---- layout utilities ------------------------------------------------- */
 
@@ -126,6 +121,14 @@ int mxfp6_tp_block_alloc(size_t partial_bytes, void** block_dev_out, unsigned ch
 int mxfp6_tp_block_open(const unsigned char handle[64], void** block_dev_out);
 int mxfp6_tp_block_close(void* block_dev);
 int mxfp6_tp_block_free(void* block_dev);
+/* Consecutive collectives on one set of blocks must alternate the two partial buffers: a
+ * rank that has passed step s + 1 has seen every peer finish step s, nothing more.  The
+ * last buffer is recorded in the block; a step that names it again (a replayed graph with
+ * an odd number of collectives) sets device status 302 and moves no data.
+ * The limit of the flag wait (the reference's spin is unbounded, csrc/moe.cu:7774,7795),
+ * in GPU clock ticks (about 1.9e9 per second); the default is about two seconds. */
+int mxfp6_tp_set_wait_limit(int64_t clock_ticks);
+int64_t mxfp6_tp_get_wait_limit(void);
 /* The plain form of the same collective: out <- bf16(sum over ranks, in rank order, of the
  * [rows, k] BF16 partials in buffer `buffer` of every block).  Used by the MoE reducer's
  * tensor-parallel sum (the reference's moe_reduce_tp2_out, csrc/moe.cu:7698-7925).  It counts
@@ -189,9 +192,34 @@ int mxfp6_gemm_w6a8_static_scratch(const uint8_t* a_values_dev, const uint8_t* a
                                    int64_t m, int64_t n, int64_t k, float alpha, void* out_dev,
                                    int out_dtype, void* stream);
 /* Plan query: fills tile_tokens, scratch splits, stages, grid, partial bytes, counter
- * bytes, cluster split factor, and 1 when the two-CTA kernel runs the problem. */
+ * bytes, cluster split factor, 1 when the two-CTA kernel runs the problem, the kernel
+ * family (0 persistent single-CTA, 1 CTA pair, 2 weight streaming) and the dynamic shared
+ * memory of a CTA.  A registered override of the exact problem (mxfp6_set_w6a8_config)
+ * is applied when tile_tokens and splits are both 0. */
 int mxfp6_gemm_w6a8_plan(int64_t m, int64_t n, int64_t k, int tile_tokens, int splits,
-                         int64_t out_plan[8]);
+                         int64_t out_plan[10]);
+/* Dense launches of at most 32 rows run on the weight-streaming kernel (two CTAs per SM,
+ * weights prefetched ahead of the programmatic-launch wait, cluster push reduction);
+ * 0 sends them to the persistent kernel instead.  Default 1. */
+int mxfp6_set_stream_kernel_mode(int enabled);
+int mxfp6_get_stream_kernel_mode(void);
+/* torch.ops.mxfp6.w6a8_config_abi (csrc/torch_extension.cu:1169-1172, schema :2138):
+ * names the set of explicit configurations; ids are only meaningful under the same string. */
+const char* mxfp6_w6a8_config_abi(void);
+int mxfp6_w6a8_config_count(void);
+/* out = {kernel family, tile_tokens, cluster_k, scratch splits} of a configuration id. */
+int mxfp6_w6a8_config_describe(int config_id, int out[4]);
+/* torch.ops.mxfp6.set_w6a8_config (csrc/torch_extension.cu:1139-1167, schema :2135):
+ * later mxfp6_gemm_w6a8 / mxfp6_gemm_from_float calls on the current device with exactly
+ * this (m, n, k, out_dtype) run configuration `config_id`; a negative id erases the entry.
+ * A configuration that cannot run the problem is rejected here. */
+int mxfp6_set_w6a8_config(int64_t m, int64_t n, int64_t k, int out_dtype, int config_id);
+/* torch.ops.mxfp6.gemm_w6a8_config (csrc/torch_extension.cu:1847-1867, schema :2127):
+ * one launch of an explicit configuration; scratch splits use the workspace arena. */
+int mxfp6_gemm_w6a8_config(const uint8_t* a_values_dev, const uint8_t* a_scales_dev,
+                           const uint8_t* w_values_dev, const uint8_t* w_scales_dev, int64_t m,
+                           int64_t n, int64_t k, float alpha, void* out_dev, int out_dtype,
+                           int config_id, void* stream);
 /* How launches with too few tiles split K (the stand-in for the reference's
  * MXFP6_STREAM_K switch, csrc/torch_extension.cu:35-57): 1 = thread-block clusters
  * that reduce through distributed shared memory (default, no scratch), 2 = FP32

@@ -34,6 +34,11 @@ from .ops import (
     rmsnorm_quantize_mxfp8,
     set_cta_pair_mode,
     is_cta_pair_enabled,
+    set_stream_kernel_mode,
+    is_stream_kernel_enabled,
+    set_w6a8_config,
+    w6a8_config_abi,
+    w6a8_configs,
     set_split_k_mode,
     is_tuned_shape,
     pack_fp6,

@@ -25,7 +25,6 @@ SIGNATURES: dict[str, tuple] = {
     "mxfp6_b200_abi_version": (c_int, []),
     "mxfp6_b200_last_error": (c_char_p, []),
     "mxfp6_b200_device_status": (c_int, [_IP, c_int]),
-    "mxfp6_b200_set_trace_buffer": (c_int, [c_void_p]),
     "mxfp6_pack_fp6": (c_int, [c_void_p, c_int64, c_void_p, c_void_p]),
     "mxfp6_unpack_fp6": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "mxfp6_pad_fp6": (c_int, [c_void_p, c_int64, c_void_p, c_void_p]),
@@ -42,6 +41,8 @@ SIGNATURES: dict[str, tuple] = {
     "mxfp6_tp_block_open": (c_int, [c_void_p, POINTER(c_void_p)]),
     "mxfp6_tp_block_close": (c_int, [c_void_p]),
     "mxfp6_tp_block_free": (c_int, [c_void_p]),
+    "mxfp6_tp_set_wait_limit": (c_int, [c_int64]),
+    "mxfp6_tp_get_wait_limit": (c_int64, []),
     "mxfp6_tp_allreduce_bf16": (
         c_int,
         [POINTER(c_void_p), c_int, c_int, c_int, c_size_t, c_void_p, c_int64, c_int64, c_void_p],
@@ -89,6 +90,17 @@ SIGNATURES: dict[str, tuple] = {
          c_int, c_int, c_int, c_void_p, c_size_t, c_void_p],
     ),
     "mxfp6_gemm_w6a8_plan": (c_int, [c_int64, c_int64, c_int64, c_int, c_int, _I64P]),
+    "mxfp6_set_stream_kernel_mode": (c_int, [c_int]),
+    "mxfp6_get_stream_kernel_mode": (c_int, []),
+    "mxfp6_w6a8_config_abi": (c_char_p, []),
+    "mxfp6_w6a8_config_count": (c_int, []),
+    "mxfp6_w6a8_config_describe": (c_int, [c_int, _IP]),
+    "mxfp6_set_w6a8_config": (c_int, [c_int64, c_int64, c_int64, c_int, c_int]),
+    "mxfp6_gemm_w6a8_config": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p,
+         c_int, c_int, c_void_p],
+    ),
     "mxfp6_set_split_k_mode": (c_int, [c_int]),
     "mxfp6_get_split_k_mode": (c_int, []),
     "mxfp6_set_cta_pair_mode": (c_int, [c_int]),

@@ -9,8 +9,11 @@
 #include "gemm.cuh"
 
 #include <algorithm>
+#include <map>
 #include <mutex>
 #include <set>
+#include <shared_mutex>
+#include <tuple>
 #include <unordered_map>
 #include <vector>
 
@@ -30,6 +33,8 @@ const char* last_error() { return g_error; }
 
 // ---- kernels implemented in the other translation units ------------------------
 int quantize_mxfp8(const void*, int, int64_t, int64_t, uint8_t*, uint8_t*, uint8_t*, cudaStream_t);
+void tp_set_wait_limit(long long);
+long long tp_wait_limit();
 int tp_block_alloc(size_t, void**, unsigned char*);
 int tp_block_open(const unsigned char*, void**);
 int tp_block_close(void*);
@@ -65,6 +70,80 @@ int silu_mul_quant(const void*, int, int64_t, int, uint8_t*, uint8_t*, uint8_t*,
                    const int64_t*, int, cudaStream_t);
 int moe_reduce(void*, const void*, int, const float*, const int32_t*, const void*, const void*, int,
                int, int64_t, int, int, int64_t, cudaStream_t);
+
+// ---- explicit configurations and the per-shape override registry -----------------
+// Ids: 0-15 weight-streaming kernel (tile 16: 0-7, tile 32: 8-15; cluster_k = id % 8 + 1);
+// 16-31 persistent kernel, cluster split (tiles 16, 32, 64, 96 x cluster_k 1, 2, 4, 8);
+// 32-34 persistent kernel, tiles 128, 192, 256, no split; 35-37 CTA-pair kernel, tiles
+// 128, 192, 256; 38-49 persistent kernel, scratch split (tiles 16, 32, 64, 96 x splits 2, 4, 8).
+const char* const kW6A8ConfigAbi = "b200-w6a8-50-v1";
+
+int describe_w6a8_candidate(int id, int out[4]) {
+  MX_REQUIRE(id >= 0 && id < kW6A8Candidates, "config_id must be in [0, %d]; got %d",
+             kW6A8Candidates - 1, id);
+  static const int narrow[4] = {16, 32, 64, 96};
+  static const int wide[3] = {128, 192, 256};
+  static const int pow2[4] = {1, 2, 4, 8};
+  int kernel = kKernelPersistent, tile = 0, cluster_k = 1, splits = 1;
+  if (id < 16) {
+    kernel = kKernelStream;
+    tile = id < 8 ? 16 : 32;
+    cluster_k = id % 8 + 1;
+  } else if (id < 32) {
+    tile = narrow[(id - 16) / 4];
+    cluster_k = pow2[(id - 16) % 4];
+  } else if (id < 35) {
+    tile = wide[id - 32];
+  } else if (id < 38) {
+    kernel = kKernelPair;
+    tile = wide[id - 35];
+  } else {
+    tile = narrow[(id - 38) / 3];
+    splits = pow2[(id - 38) % 3 + 1];
+  }
+  out[0] = kernel;
+  out[1] = tile;
+  out[2] = cluster_k;
+  out[3] = splits;
+  return kOk;
+}
+
+int apply_w6a8_candidate(int id, GemmProblem* p) {
+  int c[4];
+  if (int rc = describe_w6a8_candidate(id, c)) return rc;
+  p->force_kernel = c[0];
+  p->tile_tokens = c[1];
+  p->cluster_k = c[2] > 1 || c[0] == kKernelStream ? c[2] : 0;
+  p->splits = c[3] > 1 ? c[3] : 1;
+  // A persistent-kernel candidate without any split must not pick one up from the default mode.
+  p->split_mode = c[3] > 1 ? 2 : (c[2] > 1 || c[0] == kKernelStream ? 1 : 3);
+  return kOk;
+}
+
+namespace {
+using ShapeKey = std::tuple<int, int64_t, int64_t, int64_t, int>;  // device, m, n, k, out dtype
+std::shared_mutex g_override_mutex;
+std::map<ShapeKey, int> g_overrides;
+
+// Installs the override of this exact problem, if one is registered
+// (the reference looks its map up first too, csrc/torch_extension.cu:1192-1199).
+int apply_override(GemmProblem* p) {
+  {
+    std::shared_lock<std::shared_mutex> lock(g_override_mutex);
+    if (g_overrides.empty()) return kOk;  // the common case; also keeps planning free of CUDA calls
+  }
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  int id = -1;
+  {
+    std::shared_lock<std::shared_mutex> lock(g_override_mutex);
+    auto it = g_overrides.find(ShapeKey{device, p->m_total, p->n, p->k, p->out_dtype});
+    if (it == g_overrides.end()) return kOk;
+    id = it->second;
+  }
+  return apply_w6a8_candidate(id, p);
+}
+}  // namespace
 
 // ---- workspace arena ------------------------------------------------------------
 namespace {
@@ -208,6 +287,9 @@ int dense_problem(GemmProblem* p, const uint8_t* a_values, const uint8_t* a_scal
 }  // namespace
 
 int run_gemm_with_arena(GemmProblem& p, cudaStream_t stream) {
+  if (p.force_kernel < 0 && p.tile_tokens == 0) {
+    if (int rc = apply_override(&p)) return rc;
+  }
   GemmPlan plan;
   if (int rc = plan_w6a8(p, &plan)) return rc;
   Scratch scratch;
@@ -255,11 +337,6 @@ int mxfp6_set_cta_pair_mode(int enabled) {
 }
 
 int mxfp6_get_cta_pair_mode(void) { return cta_pair_mode(); }
-
-int mxfp6_b200_set_trace_buffer(void* trace_dev) {
-  set_trace_buffer(static_cast<long long*>(trace_dev));
-  return kOk;
-}
 
 int mxfp6_pack_fp6(const uint8_t* codes, int64_t n, uint8_t* packed, void* stream) {
   return pack_fp6(codes, n, packed, static_cast<cudaStream_t>(stream));
@@ -315,6 +392,12 @@ int mxfp6_tp_block_open(const unsigned char handle[64], void** block) {
   return tp_block_open(handle, block);
 }
 int mxfp6_tp_block_close(void* block) { return tp_block_close(block); }
+int mxfp6_tp_set_wait_limit(int64_t clock_ticks) {
+  MX_REQUIRE(clock_ticks > 0, "the wait limit must be positive");
+  tp_set_wait_limit((long long)clock_ticks);
+  return kOk;
+}
+int64_t mxfp6_tp_get_wait_limit(void) { return (int64_t)tp_wait_limit(); }
 int mxfp6_tp_block_free(void* block) { return tp_block_free(block); }
 int mxfp6_tp_allreduce_bf16(void* const* blocks, int world, int rank, int buffer,
                             size_t partial_bytes, void* out, int64_t rows, int64_t k,
@@ -393,8 +476,62 @@ int mxfp6_gemm_w6a8_static_scratch(const uint8_t* a_values, const uint8_t* a_sca
   return launch_w6a8_static_scratch(p, static_cast<cudaStream_t>(stream));
 }
 
+int mxfp6_set_stream_kernel_mode(int enabled) {
+  set_stream_kernel_mode(enabled);
+  return kOk;
+}
+int mxfp6_get_stream_kernel_mode(void) { return stream_kernel_mode(); }
+
+const char* mxfp6_w6a8_config_abi(void) { return kW6A8ConfigAbi; }
+int mxfp6_w6a8_config_count(void) { return kW6A8Candidates; }
+int mxfp6_w6a8_config_describe(int config_id, int out[4]) {
+  MX_REQUIRE(out != nullptr, "out must not be null");
+  return describe_w6a8_candidate(config_id, out);
+}
+
+int mxfp6_set_w6a8_config(int64_t m, int64_t n, int64_t k, int out_dtype, int config_id) {
+  MX_REQUIRE(m > 0, "m must be positive; got %lld", (long long)m);
+  MX_REQUIRE(n > 0 && n % 8 == 0, "n must be a positive multiple of 8; got %lld", (long long)n);
+  MX_REQUIRE(k > 0 && k % 128 == 0, "k must be a positive multiple of 128; got %lld",
+             (long long)k);
+  MX_REQUIRE(out_dtype == kF16 || out_dtype == kBF16, "out_dtype must be float16 or bfloat16");
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  const ShapeKey key{device, m, n, k, out_dtype};
+  if (config_id < 0) {
+    std::unique_lock<std::shared_mutex> lock(g_override_mutex);
+    g_overrides.erase(key);
+    return kOk;
+  }
+  MX_REQUIRE(config_id < kW6A8Candidates, "config_id must be in [0, %d], or negative to erase; got %d",
+             kW6A8Candidates - 1, config_id);
+  // Reject a configuration that cannot run this problem now, not at the first launch.
+  GemmProblem p;
+  if (int rc = dense_problem(&p, nullptr, nullptr, nullptr, nullptr, m, n, k, 1.0f, nullptr,
+                             out_dtype))
+    return rc;
+  if (int rc = apply_w6a8_candidate(config_id, &p)) return rc;
+  GemmPlan plan;
+  if (int rc = plan_w6a8(p, &plan)) return rc;
+  std::unique_lock<std::shared_mutex> lock(g_override_mutex);
+  g_overrides[key] = config_id;
+  return kOk;
+}
+
+int mxfp6_gemm_w6a8_config(const uint8_t* a_values, const uint8_t* a_scales,
+                           const uint8_t* w_values, const uint8_t* w_scales, int64_t m, int64_t n,
+                           int64_t k, float alpha, void* out, int out_dtype, int config_id,
+                           void* stream) {
+  GemmProblem p;
+  if (int rc = dense_problem(&p, a_values, a_scales, w_values, w_scales, m, n, k, alpha, out,
+                             out_dtype))
+    return rc;
+  if (int rc = apply_w6a8_candidate(config_id, &p)) return rc;
+  return run_gemm_with_arena(p, static_cast<cudaStream_t>(stream));
+}
+
 int mxfp6_gemm_w6a8_plan(int64_t m, int64_t n, int64_t k, int tile_tokens, int splits,
-                         int64_t out_plan[8]) {
+                         int64_t out_plan[10]) {
   MX_REQUIRE(out_plan != nullptr, "out_plan must not be null");
   GemmProblem p;
   if (int rc = dense_problem(&p, nullptr, nullptr, nullptr, nullptr, m, n, k, 1.0f, nullptr,
@@ -402,6 +539,9 @@ int mxfp6_gemm_w6a8_plan(int64_t m, int64_t n, int64_t k, int tile_tokens, int s
     return rc;
   p.tile_tokens = tile_tokens;
   p.splits = splits;
+  if (tile_tokens == 0 && splits == 0) {
+    if (int rc = apply_override(&p)) return rc;
+  }
   GemmPlan plan;
   if (int rc = plan_w6a8(p, &plan)) return rc;
   out_plan[0] = plan.tile_tokens;
@@ -412,6 +552,8 @@ int mxfp6_gemm_w6a8_plan(int64_t m, int64_t n, int64_t k, int tile_tokens, int s
   out_plan[5] = (int64_t)plan.counter_bytes;
   out_plan[6] = plan.cluster_k;
   out_plan[7] = plan.cta_pair;
+  out_plan[8] = plan.kernel;
+  out_plan[9] = (int64_t)plan.smem_bytes;
   return kOk;
 }
 

@@ -23,6 +23,7 @@
 // word, lets its copies drain, frees tensor memory and returns.
 #include "gemm.cuh"
 #include "ptx.cuh"
+#include "wait.cuh"
 
 #include <cuda_fp8.h>
 
@@ -45,7 +46,6 @@ constexpr uint32_t kWTileBytes = kTileF * kTileK;  // padded 6-bit rows: 128 B p
 // read from global memory (12 of every 16 shared-memory bytes), measured on B200.
 constexpr uint32_t kWTileTxBytes = kWTileBytes / 4 * 3;
 constexpr uint32_t kAtomBytes = 512;
-constexpr long long kWaitCycles = 4000000000ll;    // about two seconds
 
 struct KernelArgs {
   const uint8_t* w_scales;
@@ -64,7 +64,6 @@ struct KernelArgs {
   int splits;
   int out_dtype;
   float alpha;
-  uint32_t w_tx_bytes;  // bytes one weight-tile TMA adds to the mbarrier
   int a_scale_row_blocks;  // 128-row blocks present in the activation scale buffer
   // SwiGLU mode: weight matrices hold 2 * n rows (gate rows first, then up rows);
   // the output is E4M3 [m_total, n] with UE8M0 scales per 32 features, logical
@@ -77,7 +76,6 @@ struct KernelArgs {
   uint8_t* out_packed_scales;
   uint8_t* out_logical_scales;
   const int64_t* out_scale_offsets;
-  long long* trace;        // optional [3][256] cycle stamps of CTA 0 (diagnostics), or null
   const uint16_t* silu_lut;  // SwiGLU mode: bf16(silu(g)) for every BF16 g (silu_table.cu)
 };
 
@@ -172,55 +170,6 @@ __device__ __forceinline__ bool decode_work(int w, const KernelArgs& a, const in
   out->rows = left < TN ? left : TN;
   out->scale_row0 = scale_begin[lo] + out->m_tile * TN;
   return true;
-}
-
-__device__ __forceinline__ long long global_ns() {
-  long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Launch timeline of CTA 0 (diagnostics): trace[768] counts launches, slot s of
-// launch l is trace[776 + 8 * (l % 60) + s] in nanoseconds of the global timer.
-#define MX_STAMP(slot_index)                                                         \
-  do {                                                                               \
-    if (args.trace != nullptr && blockIdx.x == 0)                                    \
-      args.trace[776 + 8 * (*launch_slot) + (slot_index)] = global_ns();             \
-  } while (0)
-
-__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile int* abort,
-                                             int* status, int code) {
-  if (ptx::mbar_try_wait(bar, parity)) return true;
-  const long long start = clock64();
-#pragma unroll 1
-  for (uint32_t spin = 0;; ++spin) {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
-    if ((spin & 63u) == 63u) {
-      if (*abort != 0) return false;
-      if (clock64() - start > kWaitCycles) {
-        *abort = 1;
-        atomicCAS(status, 0, code);
-        return false;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ bool bounded_wait_cluster(uint32_t bar, uint32_t parity,
-                                                     volatile int* abort, int* status, int code) {
-  if (ptx::mbar_try_wait_cluster(bar, parity)) return true;
-  const long long start = clock64();
-#pragma unroll 1
-  for (uint32_t spin = 0;; ++spin) {
-    if (ptx::mbar_try_wait_cluster(bar, parity)) return true;
-    if ((spin & 63u) == 63u) {
-      if (*abort != 0) return false;
-      if (clock64() - start > kWaitCycles) {
-        *abort = 1;
-        atomicCAS(status, 0, code);
-        return false;
-      }
-    }
-  }
 }
 
 // Final value(s) of one (token row, feature) element -> global memory.  In SwiGLU
@@ -323,7 +272,6 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fixed + 8 * (2 * C::kStages + 6));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
-  volatile int* launch_slot = reinterpret_cast<volatile int*>(tmem_slot + 3);
   // Three tables of kMaxGroups + 1 ints: row-tile prefix, first row, first scale row.
   int* tile_prefix = reinterpret_cast<int*>(fixed + 1024);
   uint8_t* epi_stage = fixed + 8192;                          // 4 x kEpiWarpBytes
@@ -342,10 +290,6 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     *last_flag = 0;
-    if (args.trace != nullptr && blockIdx.x == 0) {
-      *launch_slot = (int)(atomicAdd((unsigned long long*)(args.trace + 768), 1ull) % 60ull);
-      args.trace[776 + 8 * (*launch_slot)] = global_ns();
-    }
     for (int s = 0; s < C::kStages; ++s) {
       ptx::mbar_init(full0 + 8 * s, 1);
       ptx::mbar_init(empty0 + 8 * s, 1);
@@ -427,7 +371,6 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     if (cluster_k > 1) ptx::cluster_sync_all();
   }
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) MX_STAMP(1);
 
   const int kb_total = args.k_blocks;
 
@@ -438,10 +381,9 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     {
       int stage = 0;
       uint32_t phase = 0;
-      const uint32_t tx_sub = C::kWTiles * args.w_tx_bytes + C::kATileBytes +
+      const uint32_t tx_sub = C::kWTiles * kWTileTxBytes + C::kATileBytes +
                               kAtomBytes * (C::kWTiles + C::kSfbAtoms);
       const int atoms_per_rb = kb_total;  // k/128 atoms per 128-row block
-      int trace_i = 0;
       Work wk;
       bool ok = true;
       for (int w = blockIdx.x; ok && decode_work<TN>(w, args, tile_prefix, &wk); w += gridDim.x) {
@@ -455,11 +397,6 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                                                     args.status, 101));
           if (!ok) break;
           const uint32_t bar = full0 + 8 * stage;
-          if (args.trace != nullptr && blockIdx.x == 0 && trace_i < 256) {
-            if (lane == 0 && trace_i == 0) MX_STAMP(2);
-            if (lane == 0) args.trace[trace_i] = clock64();
-            ++trace_i;
-          }
           if (ptx::elect_one()) {
             ptx::mbar_arrive_expect_tx(bar, tx_sub * nsub);
             for (int sub = 0; sub < nsub; ++sub) {
@@ -517,7 +454,6 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       constexpr uint32_t kIdesc = (4u << 7) | (0u << 10) | ((uint32_t)(TN >> 3) << 17) |
                                   (1u << 23) | ((uint32_t)(kTileF >> 4) << 24);
       uint32_t sf_set = 0;
-      int trace_i = 0;
       Work wk;
       bool ok = true;
       for (int w = blockIdx.x; ok && decode_work<TN>(w, args, tile_prefix, &wk); w += gridDim.x) {
@@ -535,10 +471,6 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                           bounded_wait(full0 + 8 * stage, phase, abort_flag, args.status, 103));
           if (!ok) break;
           ptx::tc_fence_after();
-          if (args.trace != nullptr && blockIdx.x == 0 && trace_i < 256 && lane == 0) {
-            if (trace_i == 0) MX_STAMP(3);
-            args.trace[256 + trace_i] = clock64();
-          }
           if (ptx::elect_one()) {
             const uint32_t sf = ptx::smem_u32(sf_tiles + (size_t)stage * C::kSfStageBytes);
             for (int sub = 0; sub < nsub; ++sub) {
@@ -575,10 +507,6 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             ptx::tc_commit(empty0 + 8 * stage);
           }
           __syncwarp();
-          if (args.trace != nullptr && blockIdx.x == 0 && trace_i < 256) {
-            if (lane == 0) args.trace[512 + trace_i] = clock64();
-            ++trace_i;
-          }
           if (++stage == C::kStages) {
             stage = 0;
             phase ^= 1u;
@@ -587,7 +515,6 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         if (!ok) break;
         if (ptx::elect_one()) ptx::tc_commit(tfull0 + 8 * acc);
         __syncwarp();
-        if (lane == 0) MX_STAMP(4);
         if (++acc == C::kAcc) {
           acc = 0;
           acc_phase ^= 1u;
@@ -607,7 +534,6 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     Work wk;
     for (int w = blockIdx.x; decode_work<TN>(w, args, tile_prefix, &wk); w += gridDim.x) {
       bool ready = bounded_wait(tfull0 + 8 * acc, acc_phase, abort_flag, args.status, 104);
-      if (etid == 0) MX_STAMP(5);
       if constexpr (C::kClusterOk) {
         if (cluster_k > 1) {
           // ---- cluster split-K: partial tile -> own shared memory -> peers reduce ----
@@ -854,7 +780,6 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   }
 
   // ---------------- teardown ----------------
-  if (threadIdx.x == 64) MX_STAMP(6);
   ptx::tc_fence_before();
   __syncthreads();
   if (*abort_flag != 0) {
@@ -866,7 +791,6 @@ w6a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, C::kTmemCols);
   }
-  if (threadIdx.x == 32) MX_STAMP(7);
 }
 
 // ------------------------------------------------------------------ host side
@@ -963,7 +887,6 @@ int cached_map(CUtensorMap* out, CUtensorMapDataType type, const void* base, uin
   return kOk;
 }
 
-long long* g_trace = nullptr;
 int g_split_mode = 1;
 
 bool use_pdl() {
@@ -1073,6 +996,9 @@ int make_tensor_map_2d(CUtensorMap* out, int type, const void* base, uint64_t in
   return cached_map(out, (CUtensorMapDataType)type, base, inner, rows, stride, box_rows);
 }
 
+bool stream_kernel_applies(const GemmProblem& p);
+int plan_w6a8_stream(const GemmProblem& p, int sms, GemmPlan* plan);
+int launch_w6a8_stream(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream);
 bool pair_kernel_applies(const GemmProblem& p, int tile_tokens);
 int plan_w6a8_pair(const GemmProblem& p, int sms, GemmPlan* plan);
 int launch_w6a8_pair(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream);
@@ -1095,7 +1021,22 @@ int plan_w6a8(const GemmProblem& p, GemmPlan* plan) {
   MX_REQUIRE(p.groups >= 1 && p.groups <= kMaxGroups, "groups must be in [1, %d]", kMaxGroups);
   MX_REQUIRE(p.groups == 1 || p.n % 128 == 0, "grouped weights need n %% 128 == 0");
   const bool grouped = p.expert_offsets != nullptr;
-  if (p.splits <= 1 && p.cluster_k <= 1 && cta_pair_mode() == 1 &&
+  if (p.force_kernel == kKernelStream) {
+    MX_REQUIRE(stream_kernel_applies(p),
+               "the weight-streaming kernel takes dense launches of at most 32 rows with "
+               "tile_tokens 16 or 32 and no scratch split");
+    return plan_w6a8_stream(p, sm_count(), plan);
+  }
+  if (p.force_kernel == kKernelPair) {
+    MX_REQUIRE(p.splits <= 1 && p.cluster_k <= 1 && pair_kernel_applies(p, p.tile_tokens),
+               "the CTA-pair kernel takes dense launches with m > 128, n %% 128 == 0, n >= 256 and "
+               "tile_tokens 128, 192 or 256");
+    return plan_w6a8_pair(p, sm_count(), plan);
+  }
+  if (p.force_kernel < 0 && stream_kernel_mode() == 1 && stream_kernel_applies(p)) {
+    return plan_w6a8_stream(p, sm_count(), plan);
+  }
+  if (p.force_kernel < 0 && p.splits <= 1 && p.cluster_k <= 1 && cta_pair_mode() == 1 &&
       pair_kernel_applies(p, p.tile_tokens)) {
     return plan_w6a8_pair(p, sm_count(), plan);
   }
@@ -1233,6 +1174,7 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
                "split-K scratch is missing or too small (%zu + %zu bytes needed)",
                plan.partial_bytes, plan.counter_bytes);
   }
+  if (plan.kernel == kKernelStream) return launch_w6a8_stream(p, plan, stream);
   if (plan.cta_pair != 0) return launch_w6a8_pair(p, plan, stream);
   int device = 0;
   MX_CUDA(cudaGetDevice(&device));
@@ -1267,12 +1209,6 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
   args.cluster_k = plan.cluster_k;
   args.out_dtype = p.out_dtype;
   args.alpha = p.alpha;
-  static const uint32_t w_tx = []() {
-    const char* env = std::getenv("MXFP6_B200_W_TX_BYTES");
-    return env != nullptr ? (uint32_t)std::atoi(env) : kWTileTxBytes;
-  }();
-  args.w_tx_bytes = w_tx;
-  args.trace = g_trace;
   args.silu_lut = nullptr;
   if (swiglu) {
     if (int rc = silu_table(stream, &args.silu_lut)) return rc;
@@ -1303,8 +1239,6 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
   return kInvalidArgument;
 }
 
-void set_trace_buffer(long long* ptr) { g_trace = ptr; }
-long long* trace_buffer() { return g_trace; }
 void set_default_split_mode(int mode) { g_split_mode = (mode >= 1 && mode <= 3) ? mode : 1; }
 int default_split_mode() { return g_split_mode; }
 

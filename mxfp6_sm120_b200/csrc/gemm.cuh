@@ -14,6 +14,13 @@ enum GemmMode : int {
   kGemmSwigluMxfp8 = 1,
 };
 
+// Kernel family a plan runs on.
+enum GemmKernel : int {
+  kKernelPersistent = 0,  // gemm.cu: one CTA per tile, any mode, cluster or scratch split-K
+  kKernelPair = 1,        // gemm_pair.cu: CTA pairs (cta_group::2), m > 128
+  kKernelStream = 2,      // gemm_stream.cu: decode batches, two CTAs per SM, weight prefetch
+};
+
 struct GemmProblem {
   // Weights: `groups` matrices of [n, k] E3M2 codes, packed rows of k*3/4 bytes,
   // stored back to back; packed scales likewise (n % 128 == 0 when groups > 1).
@@ -55,9 +62,11 @@ struct GemmProblem {
   // Optional overrides (0 = choose from the static table).
   int tile_tokens = 0;
   int splits = 0;
+  int force_kernel = -1;  // a GemmKernel value, or -1 = choose
 };
 
 struct GemmPlan {
+  int kernel = kKernelPersistent;
   int tile_tokens = 0;  // activation rows per tile (MMA N)
   int splits = 1;      // scratch-arena split-K factor
   int cluster_k = 1;   // cluster split-K factor (CTAs per cluster)
@@ -74,14 +83,22 @@ int plan_w6a8(const GemmProblem& p, GemmPlan* plan);
 // Launches the kernel on `stream`; the plan must come from plan_w6a8.
 int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream);
 
+// Explicit configurations ("candidates") of the dense GEMM, the counterpart of the
+// reference's 30 ahead-of-time kernels (csrc/torch_extension.cu:979-1137): an id names a
+// kernel family, a token tile and a K split.  apply_w6a8_candidate writes the overrides
+// of candidate `id` into `p`.
+constexpr int kW6A8Candidates = 50;
+extern const char* const kW6A8ConfigAbi;
+int describe_w6a8_candidate(int id, int out[4]);  // kernel, tile_tokens, cluster_k, splits
+int apply_w6a8_candidate(int id, GemmProblem* p);
+
 // Process-wide default of GemmProblem::split_mode (1 = cluster, 2 = scratch arena, 3 = off).
 void set_default_split_mode(int mode);
 int default_split_mode();
 
-// Diagnostics: CTA 0 of later launches writes [3][256] clock64 stamps (producer
-// issue, stage ready at the MMA warp, stage committed) to this device buffer.
-void set_trace_buffer(long long* ptr);
-long long* trace_buffer();
+// Weight-streaming kernel for dense launches of at most 32 rows (default on).
+void set_stream_kernel_mode(int enabled);
+int stream_kernel_mode();
 // Two-CTA kernel for dense store-mode launches with m > 128 and n % 256 == 0 (default on).
 void set_cta_pair_mode(int enabled);
 int cta_pair_mode();

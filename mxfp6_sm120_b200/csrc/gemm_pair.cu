@@ -43,7 +43,6 @@ struct PairArgs {
   int out_dtype;
   float alpha;
   int a_scale_row_blocks;
-  long long* trace;
   // Grouped launches: rows [expert_offsets[g], expert_offsets[g + 1]) use weight rows
   // [g * n, (g + 1) * n) and packed scale rows from scale_offsets[g]; null = dense.
   const int64_t* expert_offsets;
@@ -454,7 +453,6 @@ int launch_pair_tn(const CUtensorMap& tm_w, const CUtensorMap& tm_a, const CUten
 
 }  // namespace
 
-long long* trace_buffer();
 int make_tensor_map_2d(CUtensorMap* out, int type, const void* base, uint64_t inner, uint64_t rows,
                        uint64_t stride, uint32_t box_rows);
 
@@ -525,6 +523,7 @@ int plan_w6a8_pair(const GemmProblem& p, int sms, GemmPlan* plan) {
   plan->splits = 1;
   plan->cluster_k = 1;
   plan->cta_pair = 1;
+  plan->kernel = kKernelPair;
   plan->grid = 2 * (int)(tiles < pairs ? tiles : pairs);
   plan->partial_bytes = 0;
   plan->counter_bytes = 0;
@@ -567,7 +566,6 @@ int launch_w6a8_pair(const GemmProblem& p, const GemmPlan& plan, cudaStream_t st
   args.n_pair_tiles = (p.n + 255) / 256;
   args.out_dtype = p.out_dtype;
   args.alpha = p.alpha;
-  args.trace = trace_buffer();
   args.a_scale_row_blocks = (int)(scale_rows / kAtomRows);
   args.expert_offsets = p.expert_offsets;
   args.scale_offsets = p.scale_offsets;

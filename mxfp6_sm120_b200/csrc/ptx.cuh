@@ -114,6 +114,28 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t cluster_addr) {
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr));
   return v;
 }
+// Bulk copy from this CTA's shared memory into a peer CTA's; the byte count completes on
+// a barrier of the DESTINATION CTA (both arguments are shared::cluster addresses from mapa).
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t cluster_dst, uint32_t src,
+                                                  uint32_t bytes, uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(cluster_dst),
+      "r"(src), "r"(bytes), "r"(cluster_bar)
+      : "memory");
+}
+// Split cluster barrier, usable from divergent code: every thread of the cluster arrives once.
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+}
+// Arrival that publishes nothing: for barriers that only order lifetimes (a CTA may exit,
+// a buffer may be reused) after events the arriving thread has itself observed.
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");

@@ -162,7 +162,11 @@ quantize_mxfp8_lean_kernel(const T* __restrict__ in, uint8_t* __restrict__ out,
                            uint8_t* __restrict__ packed, uint8_t* __restrict__ logical,
                            uint32_t rows, uint32_t row_chunks, uint32_t chunks,
                            int64_t pad_begin, int64_t pad_total) {
+  // Decode batches are launched as programmatic dependents: the GEMM that follows may
+  // start (and prefetch its weights) at once, and this kernel itself may become resident
+  // while the kernel before it still runs; it reads and writes nothing before the wait.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr int kUnroll = 4;
   const uint32_t nthreads = gridDim.x * blockDim.x;
   const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x;
@@ -488,16 +492,28 @@ int quantize_mxfp8(const void* in, int dtype, int64_t rows, int64_t k, uint8_t* 
                     (reinterpret_cast<uintptr_t>(logical) & 3) == 0;
   // packed offsets in 32 bits: the scale buffer is rows * groups bytes plus padding.
   if (quad && chunks < (int64_t(1) << 31) && packed_scale_bytes(rows, k) < (int64_t(1) << 31)) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)grid);
+    config.blockDim = dim3(kQuantThreads);
+    config.stream = stream;
+    // Small grids only: a large quantizer that became resident early would sit on SM
+    // slots of the kernel it waits for.
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = grid <= 148 ? 1 : 0;
     if (dtype == kBF16) {
-      quantize_mxfp8_lean_kernel<__nv_bfloat16><<<grid, kQuantThreads, 0, stream>>>(
-          static_cast<const __nv_bfloat16*>(in), values, packed, logical, (uint32_t)rows,
-          (uint32_t)(k / 8), (uint32_t)chunks, pad_begin, pad_total);
+      MX_CUDA(cudaLaunchKernelEx(&config, quantize_mxfp8_lean_kernel<__nv_bfloat16>,
+                                 static_cast<const __nv_bfloat16*>(in), values, packed, logical,
+                                 (uint32_t)rows, (uint32_t)(k / 8), (uint32_t)chunks, pad_begin,
+                                 pad_total));
     } else {
-      quantize_mxfp8_lean_kernel<__half><<<grid, kQuantThreads, 0, stream>>>(
-          static_cast<const __half*>(in), values, packed, logical, (uint32_t)rows,
-          (uint32_t)(k / 8), (uint32_t)chunks, pad_begin, pad_total);
+      MX_CUDA(cudaLaunchKernelEx(&config, quantize_mxfp8_lean_kernel<__half>,
+                                 static_cast<const __half*>(in), values, packed, logical,
+                                 (uint32_t)rows, (uint32_t)(k / 8), (uint32_t)chunks, pad_begin,
+                                 pad_total));
     }
-    MX_CUDA(cudaGetLastError());
     return kOk;
   }
   if (dtype == kBF16) {

@@ -20,8 +20,12 @@
 // before the second norm buffer 1): a rank that has passed step s + 1 has seen every peer
 // finish step s, so a buffer is rewritten only after all its readers are done.
 // The step number lives in device memory and is advanced by the last CTA of the kernel,
-// which keeps CUDA-graph replays correct.  Every wait is bounded (about 2 s): on expiry the
-// kernel records a code in the status word and returns without touching peer data.
+// which keeps CUDA-graph replays correct.  So does the number of the buffer the last step
+// used: a step that names the same buffer again (a captured graph with an odd number of
+// collectives, replayed) records code 302 and moves no data instead of racing with a peer
+// that may still be reading.  Every wait is bounded (about 2 s unless
+// mxfp6_tp_set_wait_limit shortens it): on expiry the kernel records code 301 in the
+// status word and returns without touching peer data.
 #include "common.cuh"
 
 #include <cuda_fp8.h>
@@ -37,8 +41,9 @@ constexpr int kTpChunks = 8;  // 8-value chunks per thread: hidden <= 16384
 constexpr size_t kTpHeaderBytes = 1024;
 
 struct TpState {
-  uint32_t done_step;  // steps this rank has completed
-  uint32_t finished;   // CTAs of the running kernel that are done
+  uint32_t done_step;    // steps this rank has completed
+  uint32_t finished;     // CTAs of the running kernel that are done
+  uint32_t last_buffer;  // 1 + the partial buffer the last completed step used (0: none yet)
 };
 
 struct TpPeers {
@@ -46,6 +51,8 @@ struct TpPeers {
   uint32_t* flags[kTpMaxRanks];      // every rank's flag array (index = sender)
   int world;
   int rank;
+  int buffer;             // which of the two partial buffers this step reads
+  long long wait_cycles;  // limit of the flag wait in clock64 ticks
 };
 
 namespace {
@@ -93,6 +100,13 @@ __device__ __forceinline__ uint32_t tp_handshake(const TpPeers& peers, TpState* 
   if (threadIdx.x == 0) {
     *step_shared = ld_volatile_u32(&state->done_step) + 1u;
     *ok_shared = 1;
+    // Two steps in a row on one buffer: a peer may still be reading what the producer of
+    // this step has just overwritten.  The handshake still runs (the ranks stay in step),
+    // the data phase does not.
+    if (peers.world > 1 && ld_volatile_u32(&state->last_buffer) == (uint32_t)peers.buffer + 1u) {
+      *ok_shared = 0;
+      atomicCAS(status, 0, 302);
+    }
   }
   __syncthreads();
   const uint32_t step = *step_shared;
@@ -112,7 +126,7 @@ __device__ __forceinline__ uint32_t tp_handshake(const TpPeers& peers, TpState* 
         seen = true;
         break;
       }
-      if ((spin & 255u) == 255u && clock64() - start > 4000000000ll) break;
+      if ((spin & 255u) == 255u && clock64() - start > peers.wait_cycles) break;
     }
     if (!seen) {
       *ok_shared = 0;
@@ -125,13 +139,14 @@ __device__ __forceinline__ uint32_t tp_handshake(const TpPeers& peers, TpState* 
 }
 
 // The last CTA advances the step (also after a timeout, so that the ranks stay aligned).
-__device__ __forceinline__ void tp_finish(TpState* state, uint32_t step) {
+__device__ __forceinline__ void tp_finish(TpState* state, uint32_t step, int buffer) {
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
     const uint32_t done = atomicAdd(&state->finished, 1u);
     if (done == gridDim.x - 1) {
       state->finished = 0u;
+      st_volatile_u32(&state->last_buffer, (uint32_t)buffer + 1u);
       st_volatile_u32(&state->done_step, step);
       __threadfence();
     }
@@ -170,7 +185,7 @@ allreduce_sum_kernel(const TpPeers peers, TpState* state, __nv_bfloat16* out, in
       reinterpret_cast<uint4*>(out)[c] = pack_bf16x8(acc);
     }
   }
-  tp_finish(state, step);
+  tp_finish(state, step, peers.buffer);
 }
 
 // out <- bf16(sum over ranks of rows [first_chunk, first_chunk + chunks) of every rank's buffer):
@@ -207,7 +222,7 @@ reduce_scatter_kernel(const TpPeers peers, TpState* state, __nv_bfloat16* out, i
       reinterpret_cast<uint4*>(out)[c] = pack_bf16x8(acc);
     }
   }
-  tp_finish(state, step);
+  tp_finish(state, step, peers.buffer);
 }
 
 // All-gather of up to four byte segments: segment s of rank r (at seg_offset[s] inside r's
@@ -241,7 +256,7 @@ allgather_kernel(const TpPeers peers, TpState* state, const TpSegments seg, int*
       }
     }
   }
-  tp_finish(state, step);
+  tp_finish(state, step, peers.buffer);
 }
 
 // x[row] <- bf16(x[row] + bf16(sum over ranks of partial_r[row])); then RMSNorm * weight and
@@ -357,10 +372,19 @@ allreduce_rmsnorm_quantize_kernel(const TpPeers peers, TpState* state, __nv_bflo
     }
   }
 
-  tp_finish(state, step);
+  tp_finish(state, step, peers.buffer);
 }
 
 }  // namespace
+
+namespace {
+long long g_tp_wait_cycles = 4000000000ll;  // about two seconds
+}
+// Limit of the cross-rank flag wait, in clock64 ticks (about 1.9e9 per second).
+void tp_set_wait_limit(long long cycles) {
+  g_tp_wait_cycles = cycles < 1000 ? 1000 : (cycles > 40000000000ll ? 40000000000ll : cycles);
+}
+long long tp_wait_limit() { return g_tp_wait_cycles; }
 
 // ---- symmetric block: allocation and CUDA IPC ------------------------------------------
 // Layout: [flags: kTpMaxRanks x u32 | TpState | pad to 1024 B | partial 0 | partial 1].
@@ -427,6 +451,8 @@ int tp_allreduce_rmsnorm_quantize(void* const* blocks, int world, int rank, int 
   TpPeers peers;
   peers.world = world;
   peers.rank = rank;
+  peers.buffer = buffer;
+  peers.wait_cycles = g_tp_wait_cycles;
   for (int r = 0; r < kTpMaxRanks; ++r) {
     peers.partial[r] = nullptr;
     peers.flags[r] = nullptr;
@@ -473,6 +499,8 @@ int tp_allreduce_sum(void* const* blocks, int world, int rank, int buffer, size_
   TpPeers peers;
   peers.world = world;
   peers.rank = rank;
+  peers.buffer = buffer;
+  peers.wait_cycles = g_tp_wait_cycles;
   for (int r = 0; r < kTpMaxRanks; ++r) {
     peers.partial[r] = nullptr;
     peers.flags[r] = nullptr;
@@ -508,6 +536,8 @@ int tp_prepare(void* const* blocks, int world, int rank, int buffer, size_t part
   if (*status == nullptr) return kCudaError;
   peers->world = world;
   peers->rank = rank;
+  peers->buffer = buffer;
+  peers->wait_cycles = g_tp_wait_cycles;
   for (int r = 0; r < kTpMaxRanks; ++r) {
     peers->partial[r] = nullptr;
     peers->flags[r] = nullptr;

@@ -159,6 +159,68 @@ def is_cta_pair_enabled() -> bool:
     return library().mxfp6_get_cta_pair_mode() == 1
 
 
+def set_stream_kernel_mode(enabled: bool) -> None:
+    """Run dense launches of at most 32 rows on the weight-streaming kernel (default) or not."""
+    check(library().mxfp6_set_stream_kernel_mode(1 if enabled else 0))
+
+
+def is_stream_kernel_enabled() -> bool:
+    return library().mxfp6_get_stream_kernel_mode() == 1
+
+
+_KERNEL_NAMES = ("persistent", "cta_pair", "stream")
+
+
+def w6a8_config_abi(anchor: torch.Tensor | None = None) -> str:
+    """Name of the set of explicit GEMM configurations (ids mean nothing under another name).
+
+    ``anchor`` is accepted for the reference's signature (it only selects the device there).
+    """
+    return library().mxfp6_w6a8_config_abi().decode()
+
+
+def w6a8_configs() -> list[dict[str, int | str]]:
+    """Every explicit configuration: id, kernel family, token tile, cluster and scratch split."""
+    lib = library()
+    rows = []
+    for config_id in range(lib.mxfp6_w6a8_config_count()):
+        out = (ctypes.c_int * 4)()
+        check(lib.mxfp6_w6a8_config_describe(config_id, out))
+        rows.append({"config_id": config_id, "kernel": _KERNEL_NAMES[out[0]],
+                     "tile_tokens": int(out[1]), "cluster_k": int(out[2]), "splits": int(out[3])})
+    return rows
+
+
+def set_w6a8_config(
+    anchor: torch.Tensor | torch.device | str | int | None,
+    m: int,
+    n: int,
+    k: int,
+    config_id: int,
+    swizzle: int = 1,
+    raster_order: int = 0,
+    output_dtype: torch.dtype | None = None,
+) -> bool:
+    """Pin one exact ``(m, n, k, output dtype)`` problem on ``anchor``'s device to a configuration.
+
+    Later :func:`gemm_w6a8` / :func:`gemm_from_float` calls with that shape run
+    ``config_id`` (see :func:`w6a8_configs`); a negative id removes the entry.
+    ``swizzle`` and ``raster_order`` are scheduler knobs of the reference's kernels
+    and are validated, then ignored: the kernels here have one tile order.
+    """
+    if swizzle not in (1, 2, 4, 8):
+        raise ValueError(f"swizzle must be 1, 2, 4 or 8; got {swizzle}")
+    if raster_order not in (0, 1, 2):
+        raise ValueError(f"raster_order must be 0, 1 or 2; got {raster_order}")
+    _validate_problem(m, n, k)
+    dtype = _validate_output_dtype(torch.float16 if output_dtype is None else output_dtype)
+    device = anchor.device if isinstance(anchor, torch.Tensor) else anchor
+    resolved = _resolve_device(device)
+    with torch.cuda.device(resolved):
+        check(library().mxfp6_set_w6a8_config(m, n, k, _DTYPE_CODE[dtype], int(config_id)))
+    return True
+
+
 def is_stream_k_enabled() -> bool:
     """Whether split-K uses the workspace arena (the reference's MXFP6_STREAM_K switch)."""
     return library().mxfp6_get_split_k_mode() == 2
@@ -633,11 +695,13 @@ def quantize_mxfp6(input: torch.Tensor) -> PackedMXFP6Tensor:
 def gemm_w6a8_plan(m: int, n: int, k: int, tile_tokens: int = 0, splits: int = 0) -> dict[str, int]:
     """Tile/split-K choice the library makes for a dense problem (host arithmetic)."""
     _validate_problem(m, n, k)
-    plan = (ctypes.c_int64 * 8)()
+    plan = (ctypes.c_int64 * 10)()
     check(library().mxfp6_gemm_w6a8_plan(m, n, k, tile_tokens, splits, plan))
     keys = ("tile_tokens", "splits", "stages", "grid", "partial_bytes", "counter_bytes",
-            "cluster_k", "cta_pair")
-    return dict(zip(keys, (int(v) for v in plan)))
+            "cluster_k", "cta_pair", "kernel", "smem_bytes")
+    out = dict(zip(keys, (int(v) for v in plan)))
+    out["kernel"] = _KERNEL_NAMES[out["kernel"]]
+    return out
 
 
 def gemm_w6a8(
@@ -700,12 +764,27 @@ def gemm_w6a8_config(
     tile_tokens: int = 0,
     splits: int = 0,
     scratch: torch.Tensor | None = None,
+    config_id: int | None = None,
+    out: torch.Tensor | None = None,
 ) -> torch.Tensor:
-    """Run one explicit tile/split-K configuration with caller-owned scratch."""
+    """Run one explicit configuration: ``config_id`` (see :func:`w6a8_configs`), or a
+    tile/split-K pair of the persistent kernel with caller-owned scratch."""
     out_dtype = _validate_output_dtype(out_dtype)
     _validate_problem(a.rows, b.rows, a.k)
     _require_sm100(a.device)
     load_library()
+    if config_id is not None:
+        if out is None:
+            out = torch.empty((a.rows, b.rows), dtype=out_dtype, device=a.device)
+        with torch.cuda.device(a.device):
+            check(
+                library().mxfp6_gemm_w6a8_config(
+                    a.values.data_ptr(), a.scales.data_ptr(), b.values.data_ptr(),
+                    b.scales.data_ptr(), a.rows, b.rows, a.k, float(alpha), out.data_ptr(),
+                    _DTYPE_CODE[out_dtype], int(config_id), _stream(a.device),
+                )
+            )
+        return out
     plan = gemm_w6a8_plan(a.rows, b.rows, a.k, tile_tokens, splits)
     need = plan["partial_bytes"] + plan["counter_bytes"]
     if need and (scratch is None or scratch.numel() * scratch.element_size() < need):

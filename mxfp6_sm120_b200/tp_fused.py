@@ -83,6 +83,24 @@ class SymmetricBlocks:
         size = HEADER_BYTES + 2 * self.partial_bytes
         self._bytes = torch.as_tensor(_DeviceBytes(self._own, size), device=device)
         self._next = 0
+        self._last: int | None = None
+
+    def _take(self, buffer: int) -> int:
+        """Books ``buffer`` for the next collective.
+
+        Two collectives in a row on one buffer are refused: passing the handshake of a step
+        proves that the peers have STARTED it, not that they have finished reading this
+        rank's buffer.  (The kernels check the same on the device, status 302, which also
+        covers a replayed CUDA graph that ends and starts on the same buffer.)"""
+        if buffer not in (0, 1):
+            raise ValueError("buffer must be 0 or 1")
+        if self.world > 1 and buffer == self._last:
+            raise ValueError(
+                f"buffer {buffer} was used by the previous collective; consecutive collectives "
+                "must alternate the two partial buffers")
+        self._last = buffer
+        self._next = buffer ^ 1
+        return buffer
 
     def partial(self, buffer: int, rows: int, hidden: int) -> torch.Tensor:
         """BF16 ``[rows, hidden]`` view of this rank's partial buffer ``buffer`` (GEMM output)."""
@@ -103,7 +121,7 @@ class SymmetricBlocks:
             raise ValueError("x and weight must be contiguous BF16")
         if values.numel() < rows * hidden or scales.numel() < packed_scale_numel(rows, hidden):
             raise ValueError("values / scales are too small")
-        buffer, self._next = self._next, self._next ^ 1
+        buffer = self._take(self._next)
         with torch.cuda.device(self.device):
             check(
                 library().mxfp6_tp_allreduce_rmsnorm_quantize_mxfp8(
@@ -119,7 +137,7 @@ class SymmetricBlocks:
         rows, hidden = (int(v) for v in out.shape)
         if out.dtype != torch.bfloat16 or not out.is_contiguous():
             raise ValueError("out must be contiguous BF16")
-        buffer, self._next = self._next, self._next ^ 1
+        buffer = self._take(self._next)
         with torch.cuda.device(self.device):
             check(
                 library().mxfp6_tp_allreduce_bf16(
@@ -138,7 +156,7 @@ class SymmetricBlocks:
         sizes = (ctypes.c_int64 * count)(
             *[t.numel() * t.element_size() // self.world for _, t in segments])
         dsts = (ctypes.c_void_p * count)(*[t.data_ptr() for _, t in segments])
-        self._next = buffer ^ 1
+        self._take(buffer)
         with torch.cuda.device(self.device):
             check(
                 library().mxfp6_tp_allgather(
@@ -153,7 +171,7 @@ class SymmetricBlocks:
         rows, hidden = (int(v) for v in out.shape)
         if out.dtype != torch.bfloat16 or not out.is_contiguous():
             raise ValueError("out must be contiguous BF16")
-        self._next = buffer ^ 1
+        self._take(buffer)
         with torch.cuda.device(self.device):
             check(
                 library().mxfp6_tp_reduce_scatter_bf16(
@@ -179,10 +197,14 @@ class SymmetricBlocks:
         with torch.cuda.device(self.device):
             torch.cuda.synchronize(self.device)
             if self.world > 1:
-                dist.barrier(group=self.group)
+                dist.barrier(group=self.group)  # no kernel of any rank still uses a block
             for pointer in self._opened:
                 check(library().mxfp6_tp_block_close(ctypes.c_void_p(pointer)))
             self._opened = []
+            if self.world > 1:
+                # An exported allocation may be freed only after every importer has closed
+                # its mapping of it.
+                dist.barrier(group=self.group)
             if self._own:
                 self._bytes = None
                 check(library().mxfp6_tp_block_free(ctypes.c_void_p(self._own)))

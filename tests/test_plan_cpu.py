@@ -16,10 +16,21 @@ def test_named_sweep_plans(m, n, k):
     tile = plan["tile_tokens"]
     assert tile >= min(m, 16) and tile in (16, 32, 64, 96, 128, 192, 256)
     assert plan["splits"] == 1 and plan["partial_bytes"] == 0      # cluster split-K needs no scratch
-    if m <= 96:
+    n_tiles = (n + 127) // 128
+    if m <= 32:
+        # decode batches: the weight-streaming kernel, two CTAs per SM
+        assert plan["kernel"] == "stream" and plan["cta_pair"] == 0 and tile == (16 if m <= 16 else 32)
+        assert plan["smem_bytes"] <= (233472 // 2 - 1024) and plan["stages"] >= 4
+        if 2 * n_tiles <= 240:
+            # too few tiles: clusters split K; a launch fills at most 240 of the 296 CTA slots
+            assert 2 <= plan["cluster_k"] <= 8
+            assert plan["grid"] == n_tiles * plan["cluster_k"] <= 240
+            assert n_tiles * (plan["cluster_k"] + 1) > 240 or plan["cluster_k"] == 8
+        else:
+            assert plan["cluster_k"] == 1 and plan["grid"] == n_tiles <= 288
+    elif m <= 96:
         # one row tile of exactly the batch's width class, weights streamed once
-        assert plan["cta_pair"] == 0 and tile >= m
-        n_tiles = (n + 127) // 128
+        assert plan["kernel"] == "persistent" and plan["cta_pair"] == 0 and tile >= m
         if 2 * n_tiles <= 148:
             # too few tiles for the GPU: clusters split K, and every cluster fits the GPU
             assert 2 <= plan["cluster_k"] <= 8
@@ -28,7 +39,7 @@ def test_named_sweep_plans(m, n, k):
             assert plan["cluster_k"] == 1 and plan["grid"] == min(n_tiles, 148)
     else:
         # prefill batches run on CTA pairs: 256 weight rows per tile, an even grid
-        assert plan["cta_pair"] == 1 and tile in (128, 192, 256)
+        assert plan["cta_pair"] == 1 and plan["kernel"] == "cta_pair" and tile in (128, 192, 256)
         assert plan["cluster_k"] == 1 and plan["grid"] % 2 == 0 and plan["grid"] <= 148
         pair_tiles = -(-m // tile) * -(-n // 256)
         assert plan["grid"] == 2 * min(pair_tiles, 74)
@@ -62,8 +73,43 @@ def test_split_k_mode_switch_changes_the_plan():
         mx.set_split_k_mode("cluster")
     assert mx.gemm_w6a8_plan(16, 2048, 5120)["cluster_k"] == 8
     try:
+        mx.set_stream_kernel_mode(False)
+        plan = mx.gemm_w6a8_plan(16, 7168, 5120)
+        assert plan["kernel"] == "persistent" and plan["cluster_k"] == 2 and plan["grid"] == 112
+    finally:
+        mx.set_stream_kernel_mode(True)
+    assert mx.gemm_w6a8_plan(16, 7168, 5120)["kernel"] == "stream"
+    try:
         mx.set_cta_pair_mode(False)
         assert mx.gemm_w6a8_plan(4096, 7168, 5120)["cta_pair"] == 0
     finally:
         mx.set_cta_pair_mode(True)
     assert mx.gemm_w6a8_plan(4096, 7168, 5120)["cta_pair"] == 1
+
+
+def test_grid_of_the_streaming_kernel_without_a_split():
+    # more tiles than CTA slots: equal shares, every CTA walks the same number of tiles
+    plan = mx.gemm_w6a8_plan(8, 128 * 400, 1024)
+    assert plan["kernel"] == "stream" and plan["cluster_k"] == 1 and plan["grid"] == 200
+    plan = mx.gemm_w6a8_plan(8, 128 * 272, 5120)
+    assert plan["grid"] == 272
+    # k shorter than the cluster: the split stops at k / 128
+    assert mx.gemm_w6a8_plan(8, 1024, 256)["cluster_k"] == 2
+
+
+def test_explicit_configurations_are_described_and_validated():
+    assert mx.w6a8_config_abi() == "b200-w6a8-50-v1"
+    configs = mx.w6a8_configs()
+    assert len(configs) == 50 and [c["config_id"] for c in configs] == list(range(50))
+    assert configs[0] == {"config_id": 0, "kernel": "stream", "tile_tokens": 16, "cluster_k": 1,
+                          "splits": 1}
+    assert configs[15]["kernel"] == "stream" and configs[15]["tile_tokens"] == 32 and configs[15]["cluster_k"] == 8
+    assert configs[16]["kernel"] == "persistent" and configs[31]["tile_tokens"] == 96
+    assert {c["tile_tokens"] for c in configs if c["kernel"] == "cta_pair"} == {128, 192, 256}
+    assert {c["splits"] for c in configs[38:]} == {2, 4, 8}
+    from mxfp6_sm120_b200._loader import library
+
+    lib = library()
+    out = (__import__("ctypes").c_int * 4)()
+    assert lib.mxfp6_w6a8_config_describe(50, out) == 1          # out of range
+    assert lib.mxfp6_w6a8_config_describe(-1, out) == 1
