@@ -184,7 +184,9 @@ int mxfp6_gemm_w6a8_ex(const uint8_t* a_values_dev, const uint8_t* a_scales_dev,
  * cudaMalloc / cudaFree / stream-ordered allocation.  A problem whose plan needs
  * more scratch than that is rejected with MXFP6_ERR_INVALID_ARGUMENT and a message
  * that gives both sizes.  The first call on each device looks up the array's device
- * address; make that call outside any stream capture.  All calls share the one
+ * address, and the first launch of each tile width on a device sets a kernel attribute
+ * and loads its code: make one call per batch-size class (m <= 16, 32, 64, 96, 128,
+ * larger) outside any stream capture first.  All calls share the one
  * array: the counters are cleared on the stream at every call, and two calls whose
  * kernels overlap on the GPU (different streams) race on it. */
 int mxfp6_gemm_w6a8_static_scratch(const uint8_t* a_values_dev, const uint8_t* a_scales_dev,

@@ -1243,9 +1243,14 @@ void set_default_split_mode(int mode) { g_split_mode = (mode >= 1 && mode <= 3) 
 int default_split_mode() { return g_split_mode; }
 
 // One status word per device, allocated on first use and never freed.
+namespace {
+std::mutex g_status_mutex;
+int* g_status_words[64] = {};
+}  // namespace
+
 int* device_status_word(int device) {
-  static std::mutex mutex;
-  static int* words[64] = {};
+  std::mutex& mutex = g_status_mutex;
+  int** words = g_status_words;
   if (device < 0 || device >= 64) {
     set_error("device index %d out of range", device);
     return nullptr;
@@ -1325,11 +1330,23 @@ int launch_w6a8_static_scratch(GemmProblem& p, cudaStream_t stream) {
 }
 
 int read_device_status(int device, int* value, bool reset) {
-  int* word = device_status_word(device);
-  if (word == nullptr) return kCudaError;
+  if (device < 0 || device >= 64) {
+    set_error("device index %d out of range", device);
+    return kInvalidArgument;
+  }
+  // Reading never allocates: a device whose ordinary status word does not exist yet has
+  // launched no kernel that could have set it.
+  int* word = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_status_mutex);
+    word = g_status_words[device];
+  }
   MX_CUDA(cudaDeviceSynchronize());
-  MX_CUDA(cudaMemcpy(value, word, sizeof(int), cudaMemcpyDeviceToHost));
-  if (reset && *value != 0) MX_CUDA(cudaMemset(word, 0, sizeof(int)));
+  *value = 0;
+  if (word != nullptr) {
+    MX_CUDA(cudaMemcpy(value, word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (reset && *value != 0) MX_CUDA(cudaMemset(word, 0, sizeof(int)));
+  }
   // Fold in the status word of the allocation-free entry point, if it was used here.
   unsigned char* base = nullptr;
   {

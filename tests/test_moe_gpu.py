@@ -273,9 +273,10 @@ def test_moe_layer_small_shape(mx, tokens):
     assert _rel_fro(out, want) <= 2e-2
 
 
-@pytest.mark.parametrize("tokens", [1, 8, 32])
+@pytest.mark.parametrize("tokens", [1, 2, 4, 8, 16, 24, 32, 64, 96])
 def test_moe_layer_named_config_and_graph_replay(mx, tokens):
-    """Hidden 2048, 256 experts, top-8, intermediate 512, shared expert with sigmoid gate."""
+    """Hidden 2048, 256 experts, top-8, intermediate 512, shared expert with sigmoid gate:
+    every decode batch of the named configuration against the decoded CPU layer."""
     shape = mx.MoeShape()
     case = _layer_case(mx, tokens, shape)
     out, ws, step = _run_layer(mx, shape, *case)
@@ -283,6 +284,10 @@ def test_moe_layer_named_config_and_graph_replay(mx, tokens):
     assert torch.equal(ws.topk_ids.cpu(), want_ids)
     cos = torch.nn.functional.cosine_similarity(out.float().cpu().flatten(), want.float().flatten(), dim=0)
     assert float(cos) >= 0.999
+    per_token = torch.nn.functional.cosine_similarity(out.float().cpu(), want.float(), dim=1)
+    assert float(per_token.min()) >= 0.999
+    if tokens not in (1, 8, 32):
+        return
     # the whole layer replays from one CUDA graph with identical results
     first = out.clone()
     side = torch.cuda.Stream()
@@ -320,4 +325,27 @@ def test_prefill_batches_run_w1_unfused_with_identical_bytes(mx, tokens, full_si
     assert torch.equal(outs["unfused"], outs["fused"])
     if full_size:
         assert tokens * shape.topk >= threshold  # the default takes the unfused path here
+    assert mx.device_status() == 0
+
+
+def test_moe_layer_named_config_prefill_batch_against_oracle(mx):
+    """4096 tokens of the named configuration: expert ids of the whole batch against the
+    oracle's softmax top-k, and the layer output of 16 sampled tokens against the decoded
+    CPU layer run on those tokens alone (a token's output depends on no other token)."""
+    shape = mx.MoeShape()
+    tokens = 4096
+    case = _layer_case(mx, tokens, shape)
+    w1, w2, sw1, sw2, hidden, logits, gate = case
+    out, ws, _ = _run_layer(mx, shape, *case)
+    _, want_ids_all = o.softmax_topk(logits, shape.topk, True)
+    assert torch.equal(ws.topk_ids.cpu(), want_ids_all)
+    sample = torch.tensor([0, 1, 2, 127, 128, 129, 1000, 2047, 2048, 3000, 3333, 4000, 4093, 4094,
+                           4095, 777])
+    want, want_ids = _oracle_layer(mx, shape, w1, w2, sw1, sw2, hidden[sample], logits[sample],
+                                   gate[sample], ids=ws.topk_ids.cpu()[sample])
+    assert torch.equal(ws.topk_ids.cpu()[sample], want_ids)
+    got = out.float().cpu()[sample]
+    per_token = torch.nn.functional.cosine_similarity(got, want.float(), dim=1)
+    assert float(per_token.min()) >= 0.999
+    assert _rel_fro(got, want) <= 2e-2
     assert mx.device_status() == 0

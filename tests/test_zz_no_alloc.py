@@ -55,13 +55,30 @@ def test_static_scratch_gemm_matches_regular_entry_point(mx):
         assert _call(lib, "mxfp6_gemm_w6a8_static_scratch", act, wgt, got) == 0
         torch.cuda.synchronize()
         assert torch.equal(got, want)  # same kernel, same plan: bit-identical
-    # a shape without split-K takes the same entry point and needs no scratch at all
-    act2, wgt2 = _operands(mx, 40, 1024, 1024, seed=6)
-    want2 = mx.gemm_w6a8(act2, wgt2, out_dtype=torch.bfloat16)
+    # a problem with enough tiles takes the same entry point without any split or scratch
+    mx.set_split_k_mode("workspace")
+    try:
+        plan2 = mx.gemm_w6a8_plan(40, 16384, 1024)
+        assert plan2["splits"] == 1 and plan2["partial_bytes"] == 0
+        act2, wgt2 = _operands(mx, 40, 16384, 1024, seed=6)
+        want2 = torch.empty((40, 16384), dtype=torch.bfloat16, device=DEV)
+        assert _call(lib, "mxfp6_gemm_w6a8_ex", act2, wgt2, want2, (0, 0, None, 0)) == 0
+    finally:
+        mx.set_split_k_mode("cluster")
     got2 = torch.empty_like(want2)
     assert _call(lib, "mxfp6_gemm_w6a8_static_scratch", act2, wgt2, got2) == 0
     torch.cuda.synchronize()
     assert torch.equal(got2, want2)
+    # the headline property: a warmed-up call leaves the device's free memory as it found it
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        assert _call(lib, "mxfp6_gemm_w6a8_static_scratch", act, wgt, got) == 0
+        assert _call(lib, "mxfp6_gemm_w6a8_static_scratch", act2, wgt2, got2) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert torch.equal(got, want) and torch.equal(got2, want2)
     assert mx.device_status() == 0
 
 
