@@ -200,7 +200,7 @@ int mxfp6_gemm_w6a8_static_scratch(const uint8_t* a_values_dev, const uint8_t* a
  * is applied when tile_tokens and splits are both 0. */
 int mxfp6_gemm_w6a8_plan(int64_t m, int64_t n, int64_t k, int tile_tokens, int splits,
                          int64_t out_plan[10]);
-/* Dense launches of at most 32 rows run on the weight-streaming kernel (two CTAs per SM,
+/* Dense launches of at most 64 rows run on the weight-streaming kernel (two CTAs per SM,
  * weights prefetched ahead of the programmatic-launch wait, cluster push reduction);
  * 0 sends them to the persistent kernel instead.  Default 1. */
 int mxfp6_set_stream_kernel_mode(int enabled);

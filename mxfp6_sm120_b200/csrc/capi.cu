@@ -75,8 +75,9 @@ int moe_reduce(void*, const void*, int, const float*, const int32_t*, const void
 // Ids: 0-15 weight-streaming kernel (tile 16: 0-7, tile 32: 8-15; cluster_k = id % 8 + 1);
 // 16-31 persistent kernel, cluster split (tiles 16, 32, 64, 96 x cluster_k 1, 2, 4, 8);
 // 32-34 persistent kernel, tiles 128, 192, 256, no split; 35-37 CTA-pair kernel, tiles
-// 128, 192, 256; 38-49 persistent kernel, scratch split (tiles 16, 32, 64, 96 x splits 2, 4, 8).
-const char* const kW6A8ConfigAbi = "b200-w6a8-50-v1";
+// 128, 192, 256; 38-49 persistent kernel, scratch split (tiles 16, 32, 64, 96 x splits 2, 4, 8);
+// 50-57 weight-streaming kernel, tile 64 (cluster_k = id - 49).
+const char* const kW6A8ConfigAbi = "b200-w6a8-58-v1";
 
 int describe_w6a8_candidate(int id, int out[4]) {
   MX_REQUIRE(id >= 0 && id < kW6A8Candidates, "config_id must be in [0, %d]; got %d",
@@ -97,9 +98,13 @@ int describe_w6a8_candidate(int id, int out[4]) {
   } else if (id < 38) {
     kernel = kKernelPair;
     tile = wide[id - 35];
-  } else {
+  } else if (id < 50) {
     tile = narrow[(id - 38) / 3];
     splits = pow2[(id - 38) % 3 + 1];
+  } else {
+    kernel = kKernelStream;
+    tile = 64;
+    cluster_k = id - 49;
   }
   out[0] = kernel;
   out[1] = tile;

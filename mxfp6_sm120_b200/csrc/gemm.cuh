@@ -87,7 +87,7 @@ int launch_w6a8(const GemmProblem& p, const GemmPlan& plan, cudaStream_t stream)
 // reference's 30 ahead-of-time kernels (csrc/torch_extension.cu:979-1137): an id names a
 // kernel family, a token tile and a K split.  apply_w6a8_candidate writes the overrides
 // of candidate `id` into `p`.
-constexpr int kW6A8Candidates = 50;
+constexpr int kW6A8Candidates = 58;
 extern const char* const kW6A8ConfigAbi;
 int describe_w6a8_candidate(int id, int out[4]);  // kernel, tile_tokens, cluster_k, splits
 int apply_w6a8_candidate(int id, GemmProblem* p);

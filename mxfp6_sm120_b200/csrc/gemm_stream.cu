@@ -1,4 +1,4 @@
-// Weight-streaming W6A8 GEMM for decode batches: dense, m <= 32, FP16/BF16 output.
+// Weight-streaming W6A8 GEMM for decode batches: dense, m <= 64, FP16/BF16 output.
 //
 // The reference serves this regime with its swapped-AB CUTLASS SM120 kernels and the
 // per-M dispatch tables (csrc/include/mxfp6_gemm/kernel_swapped.hpp:98-317,
@@ -98,7 +98,7 @@ struct SCfg {
   static constexpr int kSfCol = 2 * TN;
   static constexpr int kSfSets = 4;
   static constexpr int kColsUsed = kSfCol + 2 * kSfSets * 8;
-  static constexpr int kTmemCols = 128;  // of the SM's 512; two CTAs share the SM
+  static constexpr int kTmemCols = TN <= 32 ? 128 : 256;  // of the SM's 512; two CTAs share it
   static_assert(kColsUsed <= kTmemCols, "accumulator and scale columns exceed the allocation");
   // An SM has 228 KB of shared memory and reserves 1 KB per resident CTA; two CTAs share it.
   static constexpr size_t kBudget = 233472 / 2 - 1024;
@@ -560,18 +560,20 @@ extern "C" int mxfp6_debug_stream_stamps(long long* host_out, unsigned int* laun
 void set_stream_kernel_mode(int enabled) { g_stream_mode = enabled != 0 ? 1 : 0; }
 int stream_kernel_mode() { return g_stream_mode; }
 
-// Dense FP16/BF16 launches of at most 32 rows whose K split (if any) stays inside a cluster.
+// Dense FP16/BF16 launches of at most 64 rows whose K split (if any) stays inside a cluster.
 bool stream_kernel_applies(const GemmProblem& p) {
   if (p.expert_offsets != nullptr || p.groups != 1 || p.mode != kGemmStore) return false;
-  if (p.m_total > 32 || p.splits > 1) return false;
-  if (p.tile_tokens != 0 && p.tile_tokens != 16 && p.tile_tokens != 32) return false;
+  if (p.m_total > 64 || p.splits > 1) return false;
+  if (p.tile_tokens != 0 && p.tile_tokens != 16 && p.tile_tokens != 32 && p.tile_tokens != 64)
+    return false;
   if (p.tile_tokens != 0 && p.tile_tokens < p.m_total) return false;
   const int mode = p.split_mode != 0 ? p.split_mode : default_split_mode();
   return mode != 2;  // mode 2 asks for the scratch-arena split of the persistent kernel
 }
 
 int plan_w6a8_stream(const GemmProblem& p, int sms, GemmPlan* plan) {
-  const int tn = p.tile_tokens != 0 ? p.tile_tokens : (p.m_total <= 16 ? 16 : 32);
+  const int tn =
+      p.tile_tokens != 0 ? p.tile_tokens : (p.m_total <= 16 ? 16 : p.m_total <= 32 ? 32 : 64);
   const int n_tiles = (p.n + kTileF - 1) / kTileF;
   const int k_blocks = p.k / kTileK;
   const int mode = p.split_mode != 0 ? p.split_mode : default_split_mode();
@@ -594,8 +596,9 @@ int plan_w6a8_stream(const GemmProblem& p, int sms, GemmPlan* plan) {
   plan->cluster_k = ck;
   plan->cta_pair = 0;
   plan->kernel = kKernelStream;
-  plan->stages = tn == 16 ? SCfg<16>::kStages : SCfg<32>::kStages;
-  plan->smem_bytes = tn == 16 ? SCfg<16>::kSmemBytes : SCfg<32>::kSmemBytes;
+  plan->stages = tn == 16 ? SCfg<16>::kStages : tn == 32 ? SCfg<32>::kStages : SCfg<64>::kStages;
+  plan->smem_bytes =
+      tn == 16 ? SCfg<16>::kSmemBytes : tn == 32 ? SCfg<32>::kSmemBytes : SCfg<64>::kSmemBytes;
   if (ck > 1) {
     plan->grid = n_tiles * ck;
   } else {
@@ -635,7 +638,9 @@ int launch_w6a8_stream(const GemmProblem& p, const GemmPlan& plan, cudaStream_t 
   args.alpha = p.alpha;
   if (plan.tile_tokens == 16) return launch_tn<16>(tm_w, tm_a, args, plan, stream);
   if (plan.tile_tokens == 32) return launch_tn<32>(tm_w, tm_a, args, plan, stream);
-  set_error("the weight-streaming kernel has tiles of 16 and 32 rows; got %d", plan.tile_tokens);
+  if (plan.tile_tokens == 64) return launch_tn<64>(tm_w, tm_a, args, plan, stream);
+  set_error("the weight-streaming kernel has tiles of 16, 32 and 64 rows; got %d",
+            plan.tile_tokens);
   return kInvalidArgument;
 }
 

@@ -14,6 +14,8 @@
 #include <cuda_fp8.h>
 #include <cuda_fp6.h>
 
+#include <algorithm>
+
 namespace mx {
 namespace {
 
@@ -66,6 +68,23 @@ __device__ __forceinline__ void fill_scale_padding(uint8_t* packed, int64_t begi
     const int64_t row = (atom / atoms_per_rb) * kAtomRows + ((within % 16) / 4) * 32 + within / 16;
     const int64_t g = (atom % atoms_per_rb) * kAtomGroups + within % 4;
     if (row >= rows || g >= groups) packed[idx] = kUe8m0One;
+  }
+}
+
+// The same for buffers whose rows hold whole quads of groups (the lean kernel's case): the
+// padding is then whole 32-bit words (four groups of one row), all in the last 128-row
+// block, and every index fits 32 bits.  A decode batch of one row has 127 rows of padding,
+// forty times its payload, so this loop must not crawl.
+__device__ __forceinline__ void fill_scale_padding_words(uint8_t* packed, uint32_t begin,
+                                                         uint32_t total, uint32_t rows,
+                                                         uint32_t tid, uint32_t nthreads) {
+  const uint32_t valid = rows & 127u;  // rows of the last block that hold real scales
+  uint32_t* words = reinterpret_cast<uint32_t*>(packed + begin);
+  const uint32_t count = (total - begin) >> 2;
+  for (uint32_t w = tid; w < count; w += nthreads) {
+    const uint32_t in_atom = w & 127u;  // word (r % 32) * 4 + r / 32 of its atom
+    const uint32_t row = ((in_atom & 3u) << 5) + (in_atom >> 2);
+    if (row >= valid) words[w] = 0x7f7f7f7fu;
   }
 }
 
@@ -236,7 +255,8 @@ quantize_mxfp8_lean_kernel(const T* __restrict__ in, uint8_t* __restrict__ out,
     }
   }
   if (packed != nullptr && pad_begin < pad_total) {
-    fill_scale_padding(packed, pad_begin, pad_total, rows, static_cast<int>(groups), tid, nthreads);
+    fill_scale_padding_words(packed, static_cast<uint32_t>(pad_begin),
+                             static_cast<uint32_t>(pad_total), rows, tid, nthreads);
   }
 }
 
@@ -492,6 +512,9 @@ int quantize_mxfp8(const void* in, int dtype, int64_t rows, int64_t k, uint8_t* 
                     (reinterpret_cast<uintptr_t>(logical) & 3) == 0;
   // packed offsets in 32 bits: the scale buffer is rows * groups bytes plus padding.
   if (quad && chunks < (int64_t(1) << 31) && packed_scale_bytes(rows, k) < (int64_t(1) << 31)) {
+    // A batch of a few rows has more padding words to write than chunks to quantize.
+    const int64_t pad_ctas = ((pad_total - pad_begin) / 4 + 4 * kQuantThreads - 1) / (4 * kQuantThreads);
+    const int grid = (int)std::max<int64_t>(grid_for(chunks), std::min<int64_t>(pad_ctas, 148));
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)grid);
     config.blockDim = dim3(kQuantThreads);

@@ -160,7 +160,7 @@ def is_cta_pair_enabled() -> bool:
 
 
 def set_stream_kernel_mode(enabled: bool) -> None:
-    """Run dense launches of at most 32 rows on the weight-streaming kernel (default) or not."""
+    """Run dense launches of at most 64 rows on the weight-streaming kernel (default) or not."""
     check(library().mxfp6_set_stream_kernel_mode(1 if enabled else 0))
 
 

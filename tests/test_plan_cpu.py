@@ -17,10 +17,11 @@ def test_named_sweep_plans(m, n, k):
     assert tile >= min(m, 16) and tile in (16, 32, 64, 96, 128, 192, 256)
     assert plan["splits"] == 1 and plan["partial_bytes"] == 0      # cluster split-K needs no scratch
     n_tiles = (n + 127) // 128
-    if m <= 32:
+    if m <= 64 and not (m > 32 and 2 * n_tiles > 240):
         # decode batches: the weight-streaming kernel, two CTAs per SM
-        assert plan["kernel"] == "stream" and plan["cta_pair"] == 0 and tile == (16 if m <= 16 else 32)
-        assert plan["smem_bytes"] <= (233472 // 2 - 1024) and plan["stages"] >= 4
+        assert plan["kernel"] == "stream" and plan["cta_pair"] == 0
+        assert tile == (16 if m <= 16 else 32 if m <= 32 else 64)
+        assert plan["smem_bytes"] <= (233472 // 2 - 1024) and plan["stages"] >= 3
         if 2 * n_tiles <= 240:
             # too few tiles: clusters split K; a launch fills at most 240 of the 296 CTA slots
             assert 2 <= plan["cluster_k"] <= 8
@@ -98,18 +99,20 @@ def test_grid_of_the_streaming_kernel_without_a_split():
 
 
 def test_explicit_configurations_are_described_and_validated():
-    assert mx.w6a8_config_abi() == "b200-w6a8-50-v1"
+    assert mx.w6a8_config_abi() == "b200-w6a8-58-v1"
     configs = mx.w6a8_configs()
-    assert len(configs) == 50 and [c["config_id"] for c in configs] == list(range(50))
+    assert len(configs) == 58 and [c["config_id"] for c in configs] == list(range(58))
     assert configs[0] == {"config_id": 0, "kernel": "stream", "tile_tokens": 16, "cluster_k": 1,
                           "splits": 1}
     assert configs[15]["kernel"] == "stream" and configs[15]["tile_tokens"] == 32 and configs[15]["cluster_k"] == 8
     assert configs[16]["kernel"] == "persistent" and configs[31]["tile_tokens"] == 96
     assert {c["tile_tokens"] for c in configs if c["kernel"] == "cta_pair"} == {128, 192, 256}
-    assert {c["splits"] for c in configs[38:]} == {2, 4, 8}
+    assert {c["splits"] for c in configs[38:50]} == {2, 4, 8}
+    assert all(c["kernel"] == "stream" and c["tile_tokens"] == 64 for c in configs[50:])
+    assert [c["cluster_k"] for c in configs[50:]] == list(range(1, 9))
     from mxfp6_sm120_b200._loader import library
 
     lib = library()
     out = (__import__("ctypes").c_int * 4)()
-    assert lib.mxfp6_w6a8_config_describe(50, out) == 1          # out of range
+    assert lib.mxfp6_w6a8_config_describe(58, out) == 1          # out of range
     assert lib.mxfp6_w6a8_config_describe(-1, out) == 1

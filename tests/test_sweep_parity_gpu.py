@@ -2,7 +2,7 @@
 
 The five projections of the 27B-class decoder at decode and prefill batch sizes, each
 through the DEFAULT plan (the one ``bench.py`` gets: the weight-streaming kernel with its
-cluster split for m <= 32, the persistent kernel up to 96 rows, CTA pairs above), compared
+cluster split up to 64 rows, the persistent kernel up to 96 rows, CTA pairs above), compared
 with the CPU oracle (decoded FP32 matmul on the same codes, the reference's
 ``reference_gemm``, tests/test_ops.py:1426-1435) on sampled output columns: the first and
 last 130 features (tile edges on both sides) and a few inside.  Tolerance: rel-Frobenius
@@ -24,19 +24,20 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 GEMM_REL_FRO = 1.0e-3
 NK = [(7168, 5120), (5120, 6144), (34816, 5120), (5120, 17408), (2048, 5120)]
-M_VALUES = [1, 8, 32, 96, 512]
+M_VALUES = [1, 8, 32, 64, 96, 512]
 
 
 def _expected_plan(m: int, n: int, k: int) -> dict:
     n_tiles = n // 128
-    if m <= 32:
-        ck = min(8, 240 // n_tiles, k // 128) if 2 * n_tiles <= 240 else 1
-        return {"kernel": "stream", "tile_tokens": 16 if m <= 16 else 32, "cluster_k": max(ck, 1),
-                "cta_pair": 0, "splits": 1}
+    split = 2 * n_tiles <= 240
+    if m <= 32 or (m <= 64 and split):
+        ck = min(8, 240 // n_tiles, k // 128) if split else 1
+        return {"kernel": "stream", "tile_tokens": 16 if m <= 16 else 32 if m <= 32 else 64,
+                "cluster_k": max(ck, 1), "cta_pair": 0, "splits": 1}
     if m <= 96:
         ck = min(8, (148 - 16) // n_tiles, k // 128) if 2 * n_tiles <= 148 else 1
-        return {"kernel": "persistent", "tile_tokens": 96, "cluster_k": ck if ck >= 2 else 1,
-                "cta_pair": 0, "splits": 1}
+        return {"kernel": "persistent", "tile_tokens": 64 if m <= 64 else 96,
+                "cluster_k": ck if ck >= 2 else 1, "cta_pair": 0, "splits": 1}
     return {"kernel": "cta_pair", "cluster_k": 1, "cta_pair": 1, "splits": 1}
 
 
@@ -89,7 +90,7 @@ def test_default_plan_matches_oracle_on_sampled_columns(mx, weights, m, n, k):
     assert mx.device_status() == 0
 
 
-@pytest.mark.parametrize("config_id,m", [(3, 16), (7, 1), (10, 24), (21, 24), (35, 300), (40, 16)])
+@pytest.mark.parametrize("config_id,m", [(3, 16), (7, 1), (10, 24), (21, 24), (35, 300), (40, 16), (53, 50)])
 def test_explicit_configuration_and_override_registry(mx, weights, config_id, m):
     """``gemm_w6a8_config(config_id=...)`` runs the named configuration; ``set_w6a8_config``
     makes the plain call take it for exactly that shape and output dtype
@@ -120,7 +121,7 @@ def test_explicit_configuration_and_override_registry(mx, weights, config_id, m)
     back = mx.gemm_w6a8_plan(m, n, k)
     assert back == mx.gemm_w6a8_plan(m, n, k) and torch.equal(mx.gemm_w6a8(act, wgt, out_dtype=torch.bfloat16), default)
     with pytest.raises(ValueError):
-        mx.set_w6a8_config(a, m, n, k, 50, output_dtype=torch.bfloat16)       # no such id
+        mx.set_w6a8_config(a, m, n, k, 58, output_dtype=torch.bfloat16)       # no such id
     with pytest.raises(ValueError):
         mx.set_w6a8_config(a, 64, n, k, 3, output_dtype=torch.bfloat16)       # 16-row tile, 64 rows
     with pytest.raises(ValueError):
