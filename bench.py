@@ -587,14 +587,26 @@ def main() -> None:
     layers, acts = build_sweep(mx, device, rank, world)
     outs = {key: torch.empty((key[0], layers[key[1:]][0].rows), dtype=torch.bfloat16, device=device)
             for key in acts}
-    order = [(m, n, k) for m in M_VALUES for (n, k) in NK_SHAPES]
+    # M-major.  Sharded, the two row-parallel projections of a batch size go first, so
+    # that their sums run beside the three column-parallel GEMMs that follow.
+    shapes = NK_SHAPES if world == 1 else (
+        [s for s in NK_SHAPES if s in ROW_PARALLEL] + [s for s in NK_SHAPES if s not in ROW_PARALLEL])
+    order = [(m, n, k) for m in M_VALUES for (n, k) in shapes]
+
+    # Prefill-sized row-parallel sums (NCCL, bandwidth bound) run on a side stream beside the
+    # GEMMs of the following shapes; the sweep's shapes do not depend on one another.
+    reduce_stream = torch.cuda.Stream(device) if world > 1 else None
 
     def run_shape(key, a=None):
         weight, mode = layers[key[1:]]
         out = mx.gemm_from_float(acts[key] if a is None else a, weight, out_dtype=torch.bfloat16,
                                  out=outs[key])
         if mode == "row" and world > 1:
-            dist.all_reduce(out)
+            computed = torch.cuda.Event()
+            computed.record(torch.cuda.current_stream(device))
+            reduce_stream.wait_event(computed)
+            with torch.cuda.stream(reduce_stream):
+                dist.all_reduce(out)
         return out
 
     def run_shape_peer(key, peer):
@@ -623,6 +635,8 @@ def main() -> None:
                 run_shape_peer(key, sweep_peer)
             else:
                 run_shape(key)
+        if reduce_stream is not None:
+            torch.cuda.current_stream(device).wait_stream(reduce_stream)  # the step ends with its sums
 
     stream = torch.cuda.Stream(device)
     with torch.cuda.stream(stream):
@@ -834,7 +848,8 @@ def main() -> None:
         "config": {"workload": WORKLOAD, "shapes": NK_SHAPES, "m_values": M_VALUES,
                    "parallelism": "single GPU" if world == 1 else
                    f"tp{world}: K=5120 projections column-parallel, 5120x6144 and 5120x17408 "
-                   "row-parallel + all-reduce (one peer-memory kernel up to 256 rows, NCCL above)",
+                   "row-parallel + all-reduce (one peer-memory kernel up to 256 rows; NCCL above, "
+                   "on a side stream beside the following shapes' GEMMs)",
                    "l2": "inputs larger than L2: shapes run M-major, 270 MB of packed weights "
                          "cycle through the 126 MB L2 between reuses",
                    "graph": "one CUDA graph per step"},

@@ -1,4 +1,5 @@
-"""Expert-parallel MoE on 2 GPUs against the single-GPU layer (skipped below 2 GPUs).
+"""Expert-parallel MoE on 2, 4 and 8 GPUs against the single-GPU layer (each case is
+skipped when the box has fewer GPUs).
 
 Each rank is a child process (one process per GPU, NCCL).  With NVLS off and no
 rank leaving mid-step, as the pool's rules for multi-rank tests ask.
@@ -42,7 +43,7 @@ def _worker(rank: int, world: int, port: int, results) -> None:
     # single-GPU result over all tokens
     state = layer.workspace(world * local_tokens)
     want = layer.forward(state, hidden, logits, gate).clone()
-    # expert parallel over the two ranks
+    # expert parallel over the ranks
     mine = slice(rank * local_tokens, (rank + 1) * local_tokens)
     moe = ExpertParallelMoe(layer)
     ep_state = moe.state(local_tokens)
@@ -79,11 +80,12 @@ def _worker(rank: int, world: int, port: int, results) -> None:
     os._exit(0)  # no NCCL teardown: every rank has reported and is between steps
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_expert_parallel_matches_single_gpu_layer():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_matches_single_gpu_layer(world):
     import torch.multiprocessing as mp
 
-    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     manager = mp.Manager()
     results = manager.dict()
     mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
