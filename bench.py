@@ -591,7 +591,10 @@ def main() -> None:
     # that their sums run beside the three column-parallel GEMMs that follow.
     shapes = NK_SHAPES if world == 1 else (
         [s for s in NK_SHAPES if s in ROW_PARALLEL] + [s for s in NK_SHAPES if s not in ROW_PARALLEL])
-    order = [(m, n, k) for m in M_VALUES for (n, k) in shapes]
+    # Sharded, the large batches also go first: their sums are the long pole (two times 84 MB
+    # at 8192 rows) and then run beside everything that follows instead of after it.
+    m_order = M_VALUES if world == 1 else sorted(M_VALUES, reverse=True)
+    order = [(m, n, k) for m in m_order for (n, k) in shapes]
 
     # Prefill-sized row-parallel sums (NCCL, bandwidth bound) run on a side stream beside the
     # GEMMs of the following shapes; the sweep's shapes do not depend on one another.

@@ -136,6 +136,13 @@ int64_t mxfp6_tp_get_wait_limit(void);
 int mxfp6_tp_allreduce_bf16(void* const* blocks_host, int world, int rank, int buffer,
                             size_t partial_bytes, void* out_dev, int64_t rows, int64_t k,
                             void* stream);
+/* The same sum for bandwidth-bound sizes, in two launches that count as two steps on ONE
+ * buffer: every rank sums its slice of rows (rows % world == 0) over all ranks in place,
+ * then all ranks gather the reduced slices into out.  2 * (world - 1) / world of the
+ * tensor crosses NVLink per rank instead of world - 1 times the tensor. */
+int mxfp6_tp_allreduce_two_phase_bf16(void* const* blocks_host, int world, int rank, int buffer,
+                                      size_t partial_bytes, void* out_dev, int64_t rows,
+                                      int64_t k, void* stream);
 /* Reduce-scatter form: out [rows_per_rank, k] <- bf16(sum over ranks of rows
  * [rank * rows_per_rank, (rank + 1) * rows_per_rank) of every rank's [world * rows_per_rank, k]
  * BF16 partial).  The expert-parallel combine: every rank sums the partial rows of ITS tokens
@@ -312,6 +319,63 @@ int mxfp6_silu_and_mul_mxfp8(const void* input_dev, int dtype, int64_t rows, int
                              uint8_t* output_dev, uint8_t* logical_scales_dev,
                              uint8_t* packed_scales_dev, const int64_t* expert_offsets_dev,
                              const int64_t* scale_offsets_dev, int experts, void* stream);
+/* ---- decode batches: one single-row GEMM per route, no permutation ------------------
+ * Route r = token * lanes + lane, lanes = topk + (include_shared ? 1 : 0); its expert is
+ * topk_ids[token, lane] (int32, or int64 with ids_are_int64), the lane after the last routed
+ * one is the always-on shared expert: the last matrix of the stack, or a separate matrix.
+ * Routes whose id is outside [0, experts) are left unwritten.  Activation scales are LOGICAL
+ * [rows, k/32]; activation_rows is tokens (all lanes of a token read one row) or
+ * tokens * lanes.  n % 128 == 0, k % 128 == 0, k <= 8192.
+ *
+ * torch.ops.mxfp6.array_gemm_w6a8_out (schema csrc/moe.cu:10048-10051, host :6713-6864):
+ * output FP16/BF16 [routes, n]. */
+int mxfp6_array_gemm_w6a8(void* output_dev, int out_dtype, const uint8_t* activation_dev,
+                          const uint8_t* logical_scales_dev, int64_t activation_rows,
+                          const uint8_t* weight_dev, const uint8_t* weight_scales_dev, int experts,
+                          const void* topk_ids_dev, int ids_are_int64, int64_t tokens, int topk,
+                          int include_shared, int64_t n, int64_t k, void* stream);
+/* torch.ops.mxfp6.array_gemm_w6a8_silu_mxfp8_out and qwen35_w1_splitk_silu_mxfp8_out (schemas
+ * csrc/moe.cu:10052-10057, 10089-10096; hosts :6866-6982, :8648-8916): weights hold 2 * inter
+ * rows per expert (gate rows, then up rows); output E4M3 [routes, inter] with logical scales
+ * [routes, inter / 32].  shared_weight (one expert, with its scales) may be NULL. */
+int mxfp6_array_gemm_w6a8_silu_mxfp8(uint8_t* output_dev, uint8_t* output_scales_dev,
+                                     const uint8_t* activation_dev,
+                                     const uint8_t* logical_scales_dev, int64_t activation_rows,
+                                     const uint8_t* weight_dev, const uint8_t* weight_scales_dev,
+                                     int experts, const uint8_t* shared_weight_dev,
+                                     const uint8_t* shared_weight_scales_dev,
+                                     const void* topk_ids_dev, int ids_are_int64, int64_t tokens,
+                                     int topk, int include_shared, int64_t inter, int64_t k,
+                                     void* stream);
+/* torch.ops.mxfp6.array_gemm_w6a8_reduce_out and qwen35_w2_splitk_reduce_out (schemas
+ * csrc/moe.cu:10058-10065, 10097-10103; hosts :6984-7393, :9120-9396): activation
+ * [tokens * lanes, k] with lanes = topk + compute_shared;
+ * output[t] = cast(sigmoid(gate[t]) * shared[t] + sum_l w[t, l] * cast(routed[t, l])), FP32,
+ * shared term first, where the shared row is computed here (compute_shared), given
+ * (shared_output_dev, [tokens, n] of the output type) or absent.  At most 9 lanes, k <= 2048. */
+int mxfp6_array_gemm_w6a8_reduce(void* output_dev, int out_dtype, const uint8_t* activation_dev,
+                                 const uint8_t* logical_scales_dev, const uint8_t* weight_dev,
+                                 const uint8_t* weight_scales_dev, int experts,
+                                 const uint8_t* shared_weight_dev,
+                                 const uint8_t* shared_weight_scales_dev, const void* topk_ids_dev,
+                                 int ids_are_int64, const float* topk_weights_dev,
+                                 const void* shared_gate_dev, int gate_dtype, int gate_stride,
+                                 const void* shared_output_dev, int compute_shared, int64_t tokens,
+                                 int topk, int64_t n, int64_t k, void* stream);
+/* torch.ops.mxfp6.moe_reduce_array_out (schema csrc/moe.cu:10129-10131, kernel :8237-8282):
+ * combined [tokens * (topk + 1), hidden], the shared row last of each token. */
+int mxfp6_moe_reduce_array(void* output_dev, const void* combined_dev, int dtype,
+                           const float* topk_weights_dev, const void* shared_gate_dev,
+                           int gate_dtype, int gate_stride, int64_t tokens, int topk,
+                           int64_t hidden_size, void* stream);
+/* Router half of torch.ops.mxfp6.qwen35_router_quant_out (schema csrc/moe.cu:10066-10072, kernel
+ * :237-511): routed_logits[b, e] = bf16(hidden[b] . gate[e]) in FP32 for e < routed_experts;
+ * the shared expert's gate logit (row routed_experts of gate_weight when gate_rows says so,
+ * else shared_gate_weight) goes to shared_gate[b].  All BF16. */
+int mxfp6_moe_router_logits(const void* hidden_dev, const void* gate_weight_dev,
+                            const void* shared_gate_weight_dev, void* routed_logits_dev,
+                            void* shared_gate_dev, int64_t batch, int64_t k, int routed_experts,
+                            int gate_rows, void* stream);
 /* torch.ops.mxfp6.moe_reduce_out (csrc/moe.cu:7927-8082, host :8377-8531):
  * out[t] = cast(sigmoid(gate[t]) * shared[t] + sum_r w[t,r] * routed[inv[t,r]]), FP32.
  * shared / shared_gate may be NULL; gate dtype 0/1/2 = f16/bf16/f32; gate_stride is

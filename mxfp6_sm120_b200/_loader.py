@@ -47,6 +47,10 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [POINTER(c_void_p), c_int, c_int, c_int, c_size_t, c_void_p, c_int64, c_int64, c_void_p],
     ),
+    "mxfp6_tp_allreduce_two_phase_bf16": (
+        c_int,
+        [POINTER(c_void_p), c_int, c_int, c_int, c_size_t, c_void_p, c_int64, c_int64, c_void_p],
+    ),
     "mxfp6_tp_reduce_scatter_bf16": (
         c_int,
         [POINTER(c_void_p), c_int, c_int, c_int, c_size_t, c_void_p, c_int64, c_int64, c_void_p],
@@ -109,6 +113,31 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p, c_int,
          c_void_p, c_void_p, c_void_p],
+    ),
+    "mxfp6_array_gemm_w6a8": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int,
+         c_int64, c_int, c_int, c_int64, c_int64, c_void_p],
+    ),
+    "mxfp6_array_gemm_w6a8_silu_mxfp8": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p,
+         c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int64, c_int64, c_void_p],
+    ),
+    "mxfp6_array_gemm_w6a8_reduce": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+         c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int64, c_int,
+         c_int64, c_int64, c_void_p],
+    ),
+    "mxfp6_moe_reduce_array": (
+        c_int,
+        [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int64,
+         c_void_p],
+    ),
+    "mxfp6_moe_router_logits": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p],
     ),
     "mxfp6_moe_topk_quant": (
         c_int,

@@ -41,6 +41,8 @@ int tp_block_close(void*);
 int tp_block_free(void*);
 int tp_allreduce_sum(void* const*, int, int, int, size_t, void*, int64_t, int64_t, cudaStream_t);
 int tp_reduce_scatter(void* const*, int, int, int, size_t, void*, int64_t, int64_t, cudaStream_t);
+int tp_allreduce_two_phase(void* const*, int, int, int, size_t, void*, int64_t, int64_t,
+                           cudaStream_t);
 int tp_allgather(void* const*, int, int, int, size_t, int, const int64_t*, const int64_t*,
                  void* const*, cudaStream_t);
 int tp_allreduce_rmsnorm_quantize(void* const*, int, int, int, size_t, void*, const void*, float,
@@ -70,6 +72,18 @@ int silu_mul_quant(const void*, int, int64_t, int, uint8_t*, uint8_t*, uint8_t*,
                    const int64_t*, int, cudaStream_t);
 int moe_reduce(void*, const void*, int, const float*, const int32_t*, const void*, const void*, int,
                int, int64_t, int, int, int64_t, cudaStream_t);
+
+int moe_route_gemm(void*, uint8_t*, int, int, const uint8_t*, const uint8_t*, int64_t,
+                   const uint8_t*, const uint8_t*, int, const uint8_t*, const uint8_t*,
+                   const void*, int, int64_t, int, int, int64_t, int64_t, cudaStream_t);
+int moe_route_w2_reduce(void*, int, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*,
+                        int, const uint8_t*, const uint8_t*, const void*, int, const float*,
+                        const void*, int, int, const void*, int, int64_t, int, int64_t, int64_t,
+                        cudaStream_t);
+int moe_reduce_array(void*, const void*, int, const float*, const void*, int, int, int64_t, int,
+                     int64_t, cudaStream_t);
+int moe_router_logits(const void*, const void*, const void*, void*, void*, int64_t, int64_t, int,
+                      int, cudaStream_t);
 
 // ---- explicit configurations and the per-shape override registry -----------------
 // Ids: 0-15 weight-streaming kernel (tile 16: 0-7, tile 32: 8-15; cluster_k = id % 8 + 1);
@@ -410,6 +424,12 @@ int mxfp6_tp_allreduce_bf16(void* const* blocks, int world, int rank, int buffer
   return tp_allreduce_sum(blocks, world, rank, buffer, partial_bytes, out, rows, k,
                           static_cast<cudaStream_t>(stream));
 }
+int mxfp6_tp_allreduce_two_phase_bf16(void* const* blocks, int world, int rank, int buffer,
+                                      size_t partial_bytes, void* out, int64_t rows, int64_t k,
+                                      void* stream) {
+  return tp_allreduce_two_phase(blocks, world, rank, buffer, partial_bytes, out, rows, k,
+                                static_cast<cudaStream_t>(stream));
+}
 int mxfp6_tp_reduce_scatter_bf16(void* const* blocks, int world, int rank, int buffer,
                                  size_t partial_bytes, void* out, int64_t rows_per_rank, int64_t k,
                                  void* stream) {
@@ -683,6 +703,59 @@ int mxfp6_moe_reduce(void* out, const void* routed, int dtype, const float* topk
   return moe_reduce(out, routed, dtype, topk_weights, inverse_permutation, shared, shared_gate,
                     gate_dtype, gate_stride, tokens, hidden_size, topk, routed_rows,
                     static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_array_gemm_w6a8(void* output, int out_dtype, const uint8_t* activation,
+                          const uint8_t* logical_scales, int64_t activation_rows,
+                          const uint8_t* weight, const uint8_t* weight_scales, int experts,
+                          const void* topk_ids, int ids_are_int64, int64_t tokens, int topk,
+                          int include_shared, int64_t n, int64_t k, void* stream) {
+  return moe_route_gemm(output, nullptr, out_dtype, 0, activation, logical_scales, activation_rows,
+                        weight, weight_scales, experts, nullptr, nullptr, topk_ids, ids_are_int64,
+                        tokens, topk, include_shared, n, k, static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_array_gemm_w6a8_silu_mxfp8(uint8_t* output, uint8_t* output_scales,
+                                     const uint8_t* activation, const uint8_t* logical_scales,
+                                     int64_t activation_rows, const uint8_t* weight,
+                                     const uint8_t* weight_scales, int experts,
+                                     const uint8_t* shared_weight,
+                                     const uint8_t* shared_weight_scales, const void* topk_ids,
+                                     int ids_are_int64, int64_t tokens, int topk,
+                                     int include_shared, int64_t inter, int64_t k, void* stream) {
+  return moe_route_gemm(output, output_scales, kBF16, 1, activation, logical_scales,
+                        activation_rows, weight, weight_scales, experts, shared_weight,
+                        shared_weight_scales, topk_ids, ids_are_int64, tokens, topk,
+                        include_shared, inter, k, static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_array_gemm_w6a8_reduce(void* output, int out_dtype, const uint8_t* activation,
+                                 const uint8_t* logical_scales, const uint8_t* weight,
+                                 const uint8_t* weight_scales, int experts,
+                                 const uint8_t* shared_weight, const uint8_t* shared_weight_scales,
+                                 const void* topk_ids, int ids_are_int64, const float* topk_weights,
+                                 const void* shared_gate, int gate_dtype, int gate_stride,
+                                 const void* shared_output, int compute_shared, int64_t tokens,
+                                 int topk, int64_t n, int64_t k, void* stream) {
+  return moe_route_w2_reduce(output, out_dtype, activation, logical_scales, weight, weight_scales,
+                             experts, shared_weight, shared_weight_scales, topk_ids, ids_are_int64,
+                             topk_weights, shared_gate, gate_dtype, gate_stride, shared_output,
+                             compute_shared, tokens, topk, n, k, static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_moe_reduce_array(void* output, const void* combined, int dtype, const float* topk_weights,
+                           const void* shared_gate, int gate_dtype, int gate_stride, int64_t tokens,
+                           int topk, int64_t hidden_size, void* stream) {
+  return moe_reduce_array(output, combined, dtype, topk_weights, shared_gate, gate_dtype,
+                          gate_stride, tokens, topk, hidden_size, static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_moe_router_logits(const void* hidden, const void* gate_weight,
+                            const void* shared_gate_weight, void* routed_logits, void* shared_gate,
+                            int64_t batch, int64_t k, int routed_experts, int gate_rows,
+                            void* stream) {
+  return moe_router_logits(hidden, gate_weight, shared_gate_weight, routed_logits, shared_gate,
+                           batch, k, routed_experts, gate_rows, static_cast<cudaStream_t>(stream));
 }
 
 int mxfp6_workspace_begin_planning(void) {

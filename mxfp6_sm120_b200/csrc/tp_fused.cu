@@ -52,6 +52,7 @@ struct TpPeers {
   int world;
   int rank;
   int buffer;             // which of the two partial buffers this step reads
+  int second_phase;       // 1: this step re-reads the buffer of the step before it (see below)
   long long wait_cycles;  // limit of the flag wait in clock64 ticks
 };
 
@@ -103,7 +104,10 @@ __device__ __forceinline__ uint32_t tp_handshake(const TpPeers& peers, TpState* 
     // Two steps in a row on one buffer: a peer may still be reading what the producer of
     // this step has just overwritten.  The handshake still runs (the ranks stay in step),
     // the data phase does not.
-    if (peers.world > 1 && ld_volatile_u32(&state->last_buffer) == (uint32_t)peers.buffer + 1u) {
+    // (The second phase of a two-phase all-reduce gathers the slices the first phase has
+    // just reduced in place: nothing produced that buffer again in between.)
+    if (peers.world > 1 && peers.second_phase == 0 &&
+        ld_volatile_u32(&state->last_buffer) == (uint32_t)peers.buffer + 1u) {
       *ok_shared = 0;
       atomicCAS(status, 0, 302);
     }
@@ -230,6 +234,7 @@ reduce_scatter_kernel(const TpPeers peers, TpState* state, __nv_bfloat16* out, i
 // expert-parallel dispatch: MXFP8 rows, scale rows, top-k ids and weights).
 struct TpSegments {
   int count;
+  int rank_strided;   // 1: rank r's segment starts at offset + r * bytes (slices of one tensor)
   int64_t offset[4];  // bytes from the start of the partial buffer, multiples of 16
   int64_t bytes[4];   // multiples of 16
   uint8_t* dst[4];
@@ -247,12 +252,29 @@ allgather_kernel(const TpPeers peers, TpState* state, const TpSegments seg, int*
     // are in flight together instead of one NVLink round trip after the other.
     for (int s = 0; s < seg.count; ++s) {
       const int64_t chunks = seg.bytes[s] / 16;
-      for (int64_t idx = tid; idx < chunks * peers.world; idx += stride) {
-        const int r = static_cast<int>(idx / chunks);
-        const int64_t c = idx - r * chunks;
-        const uint4* src = reinterpret_cast<const uint4*>(
-            static_cast<const uint8_t*>(peers.partial[r]) + seg.offset[s]);
-        reinterpret_cast<uint4*>(seg.dst[s] + r * seg.bytes[s])[c] = ld_volatile_u128(src + c);
+      const int64_t total = chunks * peers.world;
+      // Four loads in flight per thread: a bandwidth-bound gather needs megabytes on the wire.
+      for (int64_t base = tid; base < total; base += 4 * stride) {
+        uint4 v[4];
+        int64_t at[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int64_t idx = base + u * stride;
+          at[u] = -1;
+          if (idx < total) {
+            const int r = static_cast<int>(idx / chunks);
+            const int64_t c = idx - r * chunks;
+            const uint4* src = reinterpret_cast<const uint4*>(
+                static_cast<const uint8_t*>(peers.partial[r]) + seg.offset[s] +
+                (seg.rank_strided != 0 ? r * seg.bytes[s] : 0));
+            v[u] = ld_volatile_u128(src + c);
+            at[u] = r * chunks + c;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (at[u] >= 0) reinterpret_cast<uint4*>(seg.dst[s])[at[u]] = v[u];
+        }
       }
     }
   }
@@ -452,6 +474,7 @@ int tp_allreduce_rmsnorm_quantize(void* const* blocks, int world, int rank, int 
   peers.world = world;
   peers.rank = rank;
   peers.buffer = buffer;
+  peers.second_phase = 0;
   peers.wait_cycles = g_tp_wait_cycles;
   for (int r = 0; r < kTpMaxRanks; ++r) {
     peers.partial[r] = nullptr;
@@ -500,6 +523,7 @@ int tp_allreduce_sum(void* const* blocks, int world, int rank, int buffer, size_
   peers.world = world;
   peers.rank = rank;
   peers.buffer = buffer;
+  peers.second_phase = 0;
   peers.wait_cycles = g_tp_wait_cycles;
   for (int r = 0; r < kTpMaxRanks; ++r) {
     peers.partial[r] = nullptr;
@@ -537,6 +561,7 @@ int tp_prepare(void* const* blocks, int world, int rank, int buffer, size_t part
   peers->world = world;
   peers->rank = rank;
   peers->buffer = buffer;
+  peers->second_phase = 0;
   peers->wait_cycles = g_tp_wait_cycles;
   for (int r = 0; r < kTpMaxRanks; ++r) {
     peers->partial[r] = nullptr;
@@ -584,6 +609,7 @@ int tp_allgather(void* const* blocks, int world, int rank, int buffer, size_t pa
              "one to four segments with their offsets, sizes and destinations");
   TpSegments seg;
   seg.count = segments;
+  seg.rank_strided = 0;
   int64_t largest = 0;
   for (int s = 0; s < 4; ++s) {
     seg.offset[s] = 0;
@@ -606,8 +632,55 @@ int tp_allgather(void* const* blocks, int world, int rank, int buffer, size_t pa
   int* status = nullptr;
   if (int rc = tp_prepare(blocks, world, rank, buffer, partial_bytes, &peers, &state, &status))
     return rc;
-  int64_t grid = (largest / 16 * world + kTpThreads - 1) / kTpThreads;
-  if (grid > 148 * 2) grid = 148 * 2;
+  int64_t grid = (largest / 16 * world + 4 * kTpThreads - 1) / (4 * kTpThreads);
+  if (grid > 148 * 4) grid = 148 * 4;
+  if (grid < 1) grid = 1;
+  allgather_kernel<<<(unsigned)grid, kTpThreads, 0, stream>>>(peers, state, seg, status);
+  MX_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+// All-reduce of a bandwidth-bound [rows, k] BF16 partial in two launches over buffer
+// `buffer`: every rank first sums ITS slice of rows over all ranks and writes the sums over
+// its own copy of that slice (nobody else reads that part of its buffer in this phase), then
+// all ranks gather the reduced slices.  Each rank moves 2 * (world - 1) / world of the tensor
+// over NVLink, as a ring does, but in one hop and on all links at once.
+int tp_allreduce_two_phase(void* const* blocks, int world, int rank, int buffer,
+                           size_t partial_bytes, void* out, int64_t rows, int64_t k,
+                           cudaStream_t stream) {
+  MX_REQUIRE(out != nullptr && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+             "out must be a 16-byte aligned device pointer");
+  MX_REQUIRE(rows > 0 && k > 0 && k % 8 == 0 && world >= 1 && rows % world == 0,
+             "rows must be a positive multiple of the world size and k a multiple of 8");
+  MX_REQUIRE((size_t)rows * (size_t)k * 2 <= partial_bytes,
+             "the partial buffers hold %zu bytes, %lld x %lld BF16 need more", partial_bytes,
+             (long long)rows, (long long)k);
+  TpPeers peers;
+  TpState* state = nullptr;
+  int* status = nullptr;
+  if (int rc = tp_prepare(blocks, world, rank, buffer, partial_bytes, &peers, &state, &status))
+    return rc;
+  const int64_t slice_chunks = rows / world * k / 8;
+  int64_t grid = (slice_chunks + kTpThreads - 1) / kTpThreads;
+  if (grid > 148 * 4) grid = 148 * 4;
+  auto* mine = static_cast<__nv_bfloat16*>(const_cast<void*>(peers.partial[rank])) +
+               (int64_t)rank * slice_chunks * 8;
+  reduce_scatter_kernel<<<(unsigned)grid, kTpThreads, 0, stream>>>(
+      peers, state, mine, (int64_t)rank * slice_chunks, slice_chunks, status);
+  MX_CUDA(cudaGetLastError());
+  TpSegments seg;
+  seg.count = 1;
+  seg.rank_strided = 1;
+  for (int s = 0; s < 4; ++s) {
+    seg.offset[s] = 0;
+    seg.bytes[s] = 0;
+    seg.dst[s] = nullptr;
+  }
+  seg.bytes[0] = slice_chunks * 16;
+  seg.dst[0] = static_cast<uint8_t*>(out);
+  peers.second_phase = 1;
+  grid = (slice_chunks * world + 4 * kTpThreads - 1) / (4 * kTpThreads);
+  if (grid > 148 * 4) grid = 148 * 4;
   if (grid < 1) grid = 1;
   allgather_kernel<<<(unsigned)grid, kTpThreads, 0, stream>>>(peers, state, seg, status);
   MX_CUDA(cudaGetLastError());

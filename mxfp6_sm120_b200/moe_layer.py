@@ -8,7 +8,7 @@ one CUDA graph.  The reference leaves this composition to its benchmark
 
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 
 import torch
 
@@ -17,11 +17,18 @@ from .moe_ops import qwen35_topk_quant_route_out
 from .qwen35 import (
     MoeShape,
     Qwen35GroupedWorkspace,
+    Qwen35MoeB1Workspace,
     SharedExpertWorkspace,
     _grouped_experts_out,
     qwen35_grouped_reduce_out,
+    qwen35_moe_decode_logits_out,
     shared_expert_out,
 )
+
+# Batches of at most this many tokens take the decode schedule (one single-row GEMM per
+# route, three launches); larger ones the grouped schedule.  Measured on a B200 with the
+# named configuration (hidden 2048, 256 experts, top-8, intermediate 512).
+DECODE_MAX_TOKENS = 8
 
 
 @dataclass
@@ -32,6 +39,7 @@ class MoeLayerState:
     side_stream: torch.cuda.Stream | None = None
     fork: torch.cuda.Event | None = None
     join: torch.cuda.Event | None = None
+    decode: Qwen35MoeB1Workspace | None = None   # batches of up to DECODE_MAX_TOKENS tokens
 
 
 @dataclass
@@ -72,18 +80,49 @@ class MoeLayer:
     def workspace(self, tokens: int) -> MoeLayerState:
         device = self.w1.values.device
         local = MoeShape(self.shape.hidden, self.shape.intermediate, self.local_experts, self.shape.topk)
+        output = torch.empty((tokens, self.shape.hidden), dtype=torch.bfloat16, device=device)
+        decode = None
+        if self._decode_applies(tokens):
+            decode = replace(Qwen35MoeB1Workspace.allocate(device, local, batch=tokens), output=output)
         return MoeLayerState(
             Qwen35GroupedWorkspace.allocate(tokens, device, local),
             SharedExpertWorkspace.allocate(tokens, device, self.shape),
-            torch.empty((tokens, self.shape.hidden), dtype=torch.bfloat16, device=device),
+            output,
             torch.cuda.Stream(device) if device.type == "cuda" else None,
             torch.cuda.Event() if device.type == "cuda" else None,
             torch.cuda.Event() if device.type == "cuda" else None,
+            decode,
         )
+
+    def _decode_applies(self, tokens: int) -> bool:
+        # the reduce kernel keeps one accumulator per route of a token: top-8 + shared at most,
+        # and a down projection of at most 2048 inputs
+        return (tokens <= DECODE_MAX_TOKENS and self.expert_map is None and self.shape.topk <= 8
+                and self.shape.intermediate <= 2048 and self.shape.intermediate % 128 == 0
+                and self.shape.hidden % 128 == 0 and self.shape.hidden <= 8192)
 
     def forward(self, state: MoeLayerState, hidden: torch.Tensor, router_logits: torch.Tensor,
                 shared_gate: torch.Tensor | None, with_shared: bool = True) -> torch.Tensor:
-        """Queue the layer on the current stream.  The shared expert runs on a side
+        """Queue the layer on the current stream without allocating: the decode schedule
+        for small batches, the grouped schedule otherwise."""
+        if state.decode is not None and with_shared and shared_gate is not None:
+            return self.forward_decode(state, hidden, router_logits, shared_gate)
+        return self.forward_grouped(state, hidden, router_logits, shared_gate, with_shared)
+
+    def forward_decode(self, state: MoeLayerState, hidden: torch.Tensor, router_logits: torch.Tensor,
+                       shared_gate: torch.Tensor) -> torch.Tensor:
+        """Three launches: top-k + quantization, W1 routes with SwiGLU, W2 routes + reduce;
+        the shared expert is one more route of every token."""
+        e, i, h = self.local_experts, self.shape.intermediate, self.shape.hidden
+        return qwen35_moe_decode_logits_out(
+            state.decode, hidden, router_logits, shared_gate,
+            self.w1.values.view(e, 2 * i, h * 3 // 4), self.w1.scales,
+            self.w2.values.view(e, h, i * 3 // 4), self.w2.scales, self.shared_w1, self.shared_w2,
+            renormalize=True)
+
+    def forward_grouped(self, state: MoeLayerState, hidden: torch.Tensor, router_logits: torch.Tensor,
+                        shared_gate: torch.Tensor | None, with_shared: bool = True) -> torch.Tensor:
+        """The grouped schedule.  The shared expert runs on a side
         stream between the quantization and the final reduce (the reference's
         benchmark overlaps it the same way); under capture both branches land in
         the one graph."""

@@ -299,14 +299,15 @@ def qwen35_route_mxfp8_out(
 def qwen35_topk_quant_out(
     quantized: torch.Tensor,
     logical_scales: torch.Tensor,
-    packed_scales: torch.Tensor,
+    packed_scales: torch.Tensor | None,
     topk_weights: torch.Tensor,
     topk_ids: torch.Tensor,
     hidden: torch.Tensor,
     routed_logits: torch.Tensor,
     renormalize: bool = False,
 ) -> None:
-    """Fuse softmax top-k routing with dual-layout MXFP8 quantization of ``hidden``."""
+    """Fuse softmax top-k routing with dual-layout MXFP8 quantization of ``hidden``
+    (``packed_scales`` may be ``None`` when only the logical layout is wanted)."""
     if (
         hidden.device.type != "cuda"
         or hidden.dtype != torch.bfloat16
@@ -341,7 +342,7 @@ def qwen35_topk_quant_out(
             or not tensor.is_contiguous()
         ):
             raise ValueError(f"{name} must be contiguous CUDA {dtype} {tuple(shape)}")
-    if (
+    if packed_scales is not None and (
         packed_scales.device != hidden.device
         or packed_scales.dtype != torch.uint8
         or packed_scales.numel() < packed_scale_numel(batch, width)
@@ -359,7 +360,7 @@ def qwen35_topk_quant_out(
             library().mxfp6_moe_topk_quant(
                 hidden.data_ptr(), routed_logits.data_ptr(), batch, width, experts, topk,
                 int(renormalize), _as_u8(quantized).data_ptr(), logical_scales.data_ptr(),
-                packed_scales.data_ptr(), topk_weights.data_ptr(), topk_ids.data_ptr(),
+                _ptr(packed_scales), topk_weights.data_ptr(), topk_ids.data_ptr(),
                 _stream(hidden.device),
             )
         )
@@ -734,3 +735,389 @@ def moe_reduce_tp2_out(
                    shared_gate)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(output, group=group)
+
+
+# ------------------------------------------------- decode batches: one GEMM per route
+#
+# Route r = token * lanes + lane with lanes = topk + include_shared; the expert of a
+# routed lane is ``topk_ids[token, lane]``, the lane after the last routed one is the
+# always-on shared expert (the LAST matrix of the weight stack, or a separate one).
+# These are the reference's "array" and split-K operators (python/mxfp6/ops.py:1143-1241,
+# 1553-1950); here they are generic in hidden size, intermediate size and expert count.
+
+
+def _check_route_operands(activation, logical_scales, weight, weight_scales, topk_ids):
+    if (
+        activation.device.type != "cuda"
+        or activation.dtype not in (torch.float8_e4m3fn, torch.uint8)
+        or activation.ndim != 2
+        or not activation.is_contiguous()
+    ):
+        raise ValueError("activation must be contiguous CUDA float8_e4m3fn/uint8 [M,K]")
+    _require_sm100(activation.device)
+    for tensor, name in ((logical_scales, "logical_scales"), (weight, "weight"),
+                         (weight_scales, "weight_scales")):
+        _require_cuda_uint8_contiguous(tensor, name)
+        if tensor.device != activation.device:
+            raise ValueError(f"{name} must be on {activation.device}")
+    if (
+        topk_ids.device != activation.device
+        or topk_ids.dtype not in (torch.int32, torch.int64)
+        or topk_ids.ndim != 2
+        or not topk_ids.is_contiguous()
+    ):
+        raise ValueError("topk_ids must be contiguous CUDA int32/int64 [tokens,topk]")
+    if weight.ndim != 3:
+        raise ValueError("weight must have shape [E,N,packed_K]")
+    k = int(activation.shape[1])
+    if int(weight.shape[2]) * 4 != k * 3:
+        raise ValueError("activation K does not match packed weight K")
+    if tuple(logical_scales.shape) != (int(activation.shape[0]), k // SCALE_VECTOR_SIZE):
+        raise ValueError("logical_scales must have shape [activation_rows,K/32]")
+    return k
+
+
+def _check_separate_shared(shared_weight, shared_weight_scales, weight, device):
+    if (shared_weight is None) != (shared_weight_scales is None):
+        raise ValueError("shared_weight and shared_weight_scales must be provided together")
+    if shared_weight is None:
+        return
+    for tensor, name in ((shared_weight, "shared_weight"), (shared_weight_scales, "shared_weight_scales")):
+        _require_cuda_uint8_contiguous(tensor, name)
+        if tensor.device != device:
+            raise ValueError(f"{name} must be on {device}")
+    if shared_weight.ndim != 3 or tuple(shared_weight.shape) != (1, *weight.shape[1:]):
+        raise ValueError("shared_weight must be contiguous CUDA uint8 [1,N,packed_K]")
+
+
+def array_gemm_w6a8_out(
+    output: torch.Tensor,
+    activation: torch.Tensor,
+    logical_scales: torch.Tensor,
+    weight: torch.Tensor,
+    weight_scales: torch.Tensor,
+    topk_ids: torch.Tensor,
+    include_shared: bool = False,
+) -> None:
+    """Run equal-shape route GEMMs, optionally appending a shared route."""
+    k = _check_route_operands(activation, logical_scales, weight, weight_scales, topk_ids)
+    tokens, topk = (int(v) for v in topk_ids.shape)
+    routes = tokens * (topk + int(include_shared))
+    n = int(weight.shape[1])
+    if (
+        output.device != activation.device
+        or output.dtype not in (torch.float16, torch.bfloat16)
+        or output.ndim != 2
+        or not output.is_contiguous()
+    ):
+        raise ValueError("output must be contiguous CUDA float16/bfloat16 [routes,N]")
+    if tuple(output.shape) != (routes, n):
+        raise ValueError("output must contain all routed/shared rows")
+    if int(activation.shape[0]) not in (tokens, routes):
+        raise ValueError("activation rows must equal tokens or all routed/shared rows")
+    load_library()
+    with torch.cuda.device(activation.device):
+        check(
+            library().mxfp6_array_gemm_w6a8(
+                output.data_ptr(), _DTYPE_CODE[output.dtype], _as_u8(activation).data_ptr(),
+                logical_scales.data_ptr(), int(activation.shape[0]), weight.data_ptr(),
+                weight_scales.data_ptr(), int(weight.shape[0]), topk_ids.data_ptr(),
+                int(topk_ids.dtype == torch.int64), tokens, topk, int(include_shared), n, k,
+                _stream(activation.device),
+            )
+        )
+
+
+def array_gemm_w6a8_silu_mxfp8_out(
+    output: torch.Tensor,
+    output_scales: torch.Tensor,
+    activation: torch.Tensor,
+    logical_scales: torch.Tensor,
+    weight: torch.Tensor,
+    weight_scales: torch.Tensor,
+    topk_ids: torch.Tensor,
+    include_shared: bool = False,
+    shared_weight: torch.Tensor | None = None,
+    shared_weight_scales: torch.Tensor | None = None,
+) -> None:
+    """Fuse route W6A8 gate/up GEMM, SiLU multiply, and MXFP8 quantization.
+
+    ``weight`` is ``[E, 2I, packed_K]`` (gate rows, then up rows); ``output`` is E4M3
+    ``[routes, I]`` and ``output_scales`` logical UE8M0 ``[routes, I/32]``.
+    """
+    k = _check_route_operands(activation, logical_scales, weight, weight_scales, topk_ids)
+    _check_separate_shared(shared_weight, shared_weight_scales, weight, activation.device)
+    tokens, topk = (int(v) for v in topk_ids.shape)
+    routes = tokens * (topk + int(include_shared))
+    inter = int(weight.shape[1]) // 2
+    for tensor, name in ((output, "output"), (output_scales, "output_scales")):
+        _require_cuda_uint8_contiguous(_as_u8(tensor), name)
+        if tensor.device != activation.device:
+            raise ValueError(f"{name} must be on {activation.device}")
+    if tuple(output.shape) != (routes, inter) or tuple(output_scales.shape) != (routes, inter // 32):
+        raise ValueError("output must be [routes,I] and output_scales [routes,I/32]")
+    if int(activation.shape[0]) not in (tokens, routes):
+        raise ValueError("activation rows must equal tokens or all routed/shared rows")
+    load_library()
+    with torch.cuda.device(activation.device):
+        check(
+            library().mxfp6_array_gemm_w6a8_silu_mxfp8(
+                _as_u8(output).data_ptr(), output_scales.data_ptr(), _as_u8(activation).data_ptr(),
+                logical_scales.data_ptr(), int(activation.shape[0]), weight.data_ptr(),
+                weight_scales.data_ptr(), int(weight.shape[0]), _ptr(shared_weight),
+                _ptr(shared_weight_scales), topk_ids.data_ptr(),
+                int(topk_ids.dtype == torch.int64), tokens, topk, int(include_shared), inter, k,
+                _stream(activation.device),
+            )
+        )
+
+
+def qwen35_w1_splitk_silu_mxfp8_out(
+    output: torch.Tensor,
+    output_scales: torch.Tensor,
+    partial: torch.Tensor | None,
+    activation: torch.Tensor,
+    logical_scales: torch.Tensor,
+    weight: torch.Tensor,
+    weight_scales: torch.Tensor,
+    topk_ids: torch.Tensor,
+    include_shared: bool = True,
+    shared_weight: torch.Tensor | None = None,
+    shared_weight_scales: torch.Tensor | None = None,
+) -> None:
+    """Small-batch split-K W1 with the fused SiLU / MXFP8 epilogue.
+
+    One activation row per token (``activation`` is ``[B, K]``); K is split over the CTAs
+    of a thread-block cluster and reduced through distributed shared memory, so
+    ``partial`` (the reference's global split-K scratch) is accepted and not used.
+    """
+    if not isinstance(include_shared, bool):
+        raise TypeError("include_shared must be a bool")
+    if int(activation.shape[0]) != int(topk_ids.shape[0]):
+        raise ValueError("activation must hold one row per token")
+    array_gemm_w6a8_silu_mxfp8_out(output, output_scales, activation, logical_scales, weight,
+                                   weight_scales, topk_ids, include_shared, shared_weight,
+                                   shared_weight_scales)
+
+
+def _gate_stride(shared_gate: torch.Tensor, tokens: int, device) -> int:
+    if (
+        shared_gate.device != device
+        or shared_gate.dtype not in _GATE_CODE
+        or not shared_gate.is_contiguous()
+        or (shared_gate.numel() != tokens and (shared_gate.ndim != 2 or shared_gate.shape[0] != tokens))
+    ):
+        raise ValueError("shared_gate must contain one contiguous floating value or row per token")
+    return shared_gate.numel() // tokens
+
+
+def array_gemm_w6a8_reduce_out(
+    output: torch.Tensor,
+    activation: torch.Tensor,
+    logical_scales: torch.Tensor,
+    weight: torch.Tensor,
+    weight_scales: torch.Tensor,
+    topk_ids: torch.Tensor,
+    topk_weights: torch.Tensor,
+    shared_gate: torch.Tensor,
+    shared_output: torch.Tensor | None = None,
+    shared_weight: torch.Tensor | None = None,
+    shared_weight_scales: torch.Tensor | None = None,
+    use_packed_vector_loads: bool = False,
+) -> None:
+    """Route W2 GEMMs fused with the weighted reduce and the gated shared expert.
+
+    ``activation`` is ``[tokens * 9, K]`` (eight routed rows and the shared row per token)
+    or ``[tokens * 8, K]`` when ``shared_output`` brings the shared expert's rows.
+    ``use_packed_vector_loads`` selects a load path of the reference's kernel and has no
+    counterpart here.
+    """
+    k = _check_route_operands(activation, logical_scales, weight, weight_scales, topk_ids)
+    _check_separate_shared(shared_weight, shared_weight_scales, weight, activation.device)
+    tokens, topk = (int(v) for v in topk_ids.shape)
+    if (
+        topk_weights.device != activation.device
+        or topk_weights.dtype != torch.float32
+        or not topk_weights.is_contiguous()
+        or topk_weights.shape != topk_ids.shape
+    ):
+        raise ValueError("topk_weights must be contiguous CUDA float32 [tokens,topk]")
+    if (
+        output.device != activation.device
+        or output.dtype not in (torch.float16, torch.bfloat16)
+        or output.ndim != 2
+        or not output.is_contiguous()
+        or tuple(output.shape) != (tokens, int(weight.shape[1]))
+    ):
+        raise ValueError("output must be contiguous CUDA float16/bfloat16 [tokens,N]")
+    external = shared_output is not None
+    if external and shared_weight is not None:
+        raise ValueError("separate shared weights cannot be combined with shared_output")
+    if external and (
+        shared_output.device != activation.device
+        or shared_output.dtype != output.dtype
+        or shared_output.shape != output.shape
+        or not shared_output.is_contiguous()
+    ):
+        raise ValueError(
+            "shared_output must be contiguous and match output's shape, dtype, and CUDA device")
+    lanes = topk + (0 if external else 1)
+    if int(activation.shape[0]) != tokens * lanes:
+        raise ValueError(f"activation must have shape [tokens*({topk} or {topk + 1}),K]")
+    stride = _gate_stride(shared_gate, tokens, activation.device)
+    load_library()
+    with torch.cuda.device(activation.device):
+        check(
+            library().mxfp6_array_gemm_w6a8_reduce(
+                output.data_ptr(), _DTYPE_CODE[output.dtype], _as_u8(activation).data_ptr(),
+                logical_scales.data_ptr(), weight.data_ptr(), weight_scales.data_ptr(),
+                int(weight.shape[0]), _ptr(shared_weight), _ptr(shared_weight_scales),
+                topk_ids.data_ptr(), int(topk_ids.dtype == torch.int64), topk_weights.data_ptr(),
+                shared_gate.data_ptr(), _GATE_CODE[shared_gate.dtype], stride, _ptr(shared_output),
+                0 if external else 1, tokens, topk, int(weight.shape[1]), k,
+                _stream(activation.device),
+            )
+        )
+
+
+def qwen35_w2_splitk_reduce_out(
+    output: torch.Tensor,
+    partial: torch.Tensor | None,
+    activation: torch.Tensor,
+    logical_scales: torch.Tensor,
+    weight: torch.Tensor,
+    weight_scales: torch.Tensor,
+    topk_ids: torch.Tensor,
+    topk_weights: torch.Tensor,
+    shared_gate: torch.Tensor,
+    shared_weight: torch.Tensor | None = None,
+    shared_weight_scales: torch.Tensor | None = None,
+) -> None:
+    """Small-batch W2 with the weighted reduce and the gated shared row in its epilogue.
+
+    The lanes of a token are split over the CTAs of a cluster and every lane accumulates
+    in tensor memory, so ``partial`` (the reference's split-K scratch) is accepted and not
+    used.
+    """
+    array_gemm_w6a8_reduce_out(output, activation, logical_scales, weight, weight_scales, topk_ids,
+                               topk_weights, shared_gate, None, shared_weight, shared_weight_scales)
+
+
+def moe_reduce_array_out(
+    output: torch.Tensor,
+    combined_output: torch.Tensor,
+    topk_weights: torch.Tensor,
+    shared_gate: torch.Tensor,
+) -> None:
+    """Reduce interleaved routed/shared rows emitted by the array path."""
+    if (
+        combined_output.device.type != "cuda"
+        or combined_output.dtype not in (torch.float16, torch.bfloat16)
+        or combined_output.ndim != 2
+        or not combined_output.is_contiguous()
+    ):
+        raise ValueError(
+            "combined_output must be contiguous CUDA float16/bfloat16 [tokens*(topk+1),H]")
+    if (
+        output.device != combined_output.device
+        or output.dtype != combined_output.dtype
+        or output.ndim != 2
+        or not output.is_contiguous()
+    ):
+        raise ValueError("output must be contiguous CUDA [tokens,H] with combined_output's dtype")
+    if (
+        topk_weights.device != combined_output.device
+        or topk_weights.dtype != torch.float32
+        or topk_weights.ndim != 2
+        or not topk_weights.is_contiguous()
+    ):
+        raise ValueError("topk_weights must be contiguous CUDA float32 [tokens,topk]")
+    tokens, hidden = (int(v) for v in output.shape)
+    topk = int(topk_weights.shape[1])
+    if tuple(combined_output.shape) != (tokens * (topk + 1), hidden) or int(topk_weights.shape[0]) != tokens:
+        raise ValueError("combined_output must have shape [tokens*(topk+1),H]")
+    _require_sm100(output.device)
+    stride = _gate_stride(shared_gate, tokens, output.device)
+    load_library()
+    with torch.cuda.device(output.device):
+        check(
+            library().mxfp6_moe_reduce_array(
+                output.data_ptr(), combined_output.data_ptr(), _DTYPE_CODE[output.dtype],
+                topk_weights.data_ptr(), shared_gate.data_ptr(), _GATE_CODE[shared_gate.dtype],
+                stride, tokens, topk, hidden, _stream(output.device),
+            )
+        )
+
+
+def qwen35_router_quant_out(
+    quantized: torch.Tensor,
+    logical_scales: torch.Tensor,
+    routed_logits: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    shared_gate: torch.Tensor,
+    hidden: torch.Tensor,
+    gate_weight: torch.Tensor,
+    renormalize: bool = False,
+    shared_gate_weight: torch.Tensor | None = None,
+) -> None:
+    """Router GEMV, softmax top-k and MXFP8 quantization of the hidden rows.
+
+    ``gate_weight`` holds the routed gate rows ``[E, H]`` followed by the shared expert's
+    gate row (``[E + 1, H]``) unless ``shared_gate_weight`` ``[1, H]`` brings that row.
+    Two launches here (the logits, then top-k + quantization) where the reference has one
+    cooperative kernel.
+    """
+    if (
+        hidden.device.type != "cuda"
+        or hidden.dtype != torch.bfloat16
+        or hidden.ndim != 2
+        or not hidden.is_contiguous()
+        or hidden.shape[1] % 32
+    ):
+        raise ValueError("hidden must be contiguous CUDA bfloat16 [B,H] with H divisible by 32")
+    _require_sm100(hidden.device)
+    batch, width = (int(v) for v in hidden.shape)
+    experts = int(routed_logits.shape[1])
+    gate_rows = experts if shared_gate_weight is not None else experts + 1
+    if (
+        gate_weight.device != hidden.device
+        or gate_weight.dtype != torch.bfloat16
+        or tuple(gate_weight.shape) != (gate_rows, width)
+        or not gate_weight.is_contiguous()
+    ):
+        raise ValueError(f"gate_weight must be contiguous CUDA bfloat16 [{gate_rows},{width}]")
+    if shared_gate_weight is not None and (
+        shared_gate_weight.device != hidden.device
+        or shared_gate_weight.dtype != torch.bfloat16
+        or tuple(shared_gate_weight.shape) != (1, width)
+        or not shared_gate_weight.is_contiguous()
+    ):
+        raise ValueError(f"shared_gate_weight must be contiguous CUDA bfloat16 [1,{width}]")
+    if (
+        routed_logits.device != hidden.device
+        or routed_logits.dtype != torch.bfloat16
+        or tuple(routed_logits.shape) != (batch, experts)
+        or not routed_logits.is_contiguous()
+    ):
+        raise ValueError("routed_logits must be contiguous CUDA bfloat16 [B,E]")
+    if (
+        shared_gate.device != hidden.device
+        or shared_gate.dtype != torch.bfloat16
+        or shared_gate.numel() != batch
+        or not shared_gate.is_contiguous()
+    ):
+        raise ValueError("shared_gate must be contiguous CUDA bfloat16 with B values")
+    if not isinstance(renormalize, bool):
+        raise TypeError("renormalize must be a bool")
+    load_library()
+    with torch.cuda.device(hidden.device):
+        check(
+            library().mxfp6_moe_router_logits(
+                hidden.data_ptr(), gate_weight.data_ptr(), _ptr(shared_gate_weight),
+                routed_logits.data_ptr(), shared_gate.data_ptr(), batch, width, experts, gate_rows,
+                _stream(hidden.device),
+            )
+        )
+    qwen35_topk_quant_out(quantized, logical_scales, None, topk_weights, topk_ids, hidden,
+                          routed_logits, renormalize=renormalize)

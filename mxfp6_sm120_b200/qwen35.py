@@ -3,9 +3,8 @@
 Follows the reference's ``python/mxfp6/qwen35.py`` (workspace carved out of
 caller-owned storage, one call per layer, capturable in one CUDA graph) with two
 differences: the sizes (hidden, intermediate, experts, k) are parameters with the
-reference model's values as defaults instead of module constants, and one
-persistent grouped tcgen05 kernel family serves every batch size, so the
-single-token schedule is the grouped schedule.
+reference model's values as defaults instead of module constants, and the
+decode schedule (one single-row GEMM per route) takes any small batch, not one token.
 """
 
 from __future__ import annotations
@@ -23,6 +22,9 @@ from .moe_ops import (
     qwen35_route_mxfp8_out,
     qwen35_topk_quant_out,
     qwen35_topk_quant_route_out,
+    qwen35_router_quant_out,
+    qwen35_w1_splitk_silu_mxfp8_out,
+    qwen35_w2_splitk_reduce_out,
     silu_and_mul_mxfp8_grouped_out,
 )
 from .ops import MXFP8Tensor, PackedMXFP6Tensor, gemm_w6a8, packed_scale_numel, quantize_mxfp8_logical
@@ -402,35 +404,111 @@ def shared_expert_out(
     return gemm_w6a8(act, w2, out_dtype=torch.bfloat16, out=shared.output)
 
 
-# ---- single-token schedule: same kernels, kept for API compatibility -----------------
+# ---- decode schedule: one single-row GEMM per route, three launches after the router ----
 
 
 @dataclass(frozen=True)
 class Qwen35MoeB1Workspace:
-    """Workspace of the one-token decode schedule (a batch-1 grouped workspace)."""
+    """Scratch of the decode schedule (the reference's B=1 workspace,
+    python/mxfp6/qwen35.py:73-83,247-298, for ``batch`` tokens of any layer shape).
 
-    grouped: Qwen35GroupedWorkspace
+    ``activation`` holds ``topk + 1`` rows per token: the routed experts' activated rows,
+    then the shared expert's.  ``w1_partial`` / ``w2_partial`` are the reference's split-K
+    scratch; the kernels here reduce inside a thread-block cluster, so both are empty.
+    """
+
+    quantized: torch.Tensor          # [B, H] e4m3
+    input_scales: torch.Tensor       # [B, H/32] logical UE8M0
+    routed_logits: torch.Tensor      # [B, E] bf16
+    topk_weights: torch.Tensor       # [B, topk] f32
+    topk_ids: torch.Tensor           # [B, topk] i32
+    shared_gate: torch.Tensor        # [B] bf16 (logit; the reduce applies the sigmoid)
+    w1_partial: torch.Tensor
+    activation: torch.Tensor         # [B * (topk + 1), I] e4m3
+    activation_scales: torch.Tensor  # [B * (topk + 1), I/32]
+    w2_partial: torch.Tensor
+    output: torch.Tensor             # [B, H] bf16
 
     @classmethod
-    def allocate(cls, device, shape: MoeShape = MoeShape()):
-        return cls(Qwen35GroupedWorkspace.allocate(1, device, shape))
+    def allocate(cls, device, shape: MoeShape = MoeShape(), batch: int = 1):
+        if batch < 1:
+            raise ValueError("batch must be positive")
+        h, i, e, k = shape.hidden, shape.intermediate, shape.experts, shape.topk
+        lanes = batch * (k + 1)
+        u8 = dict(dtype=torch.uint8, device=device)
+        return cls(
+            torch.empty((batch, h), dtype=torch.float8_e4m3fn, device=device),
+            torch.empty((batch, h // 32), **u8),
+            torch.empty((batch, e), dtype=torch.bfloat16, device=device),
+            torch.empty((batch, k), dtype=torch.float32, device=device),
+            torch.empty((batch, k), dtype=torch.int32, device=device),
+            torch.empty((batch,), dtype=torch.bfloat16, device=device),
+            torch.empty((0,), dtype=torch.float32, device=device),
+            torch.empty((lanes, i), dtype=torch.float8_e4m3fn, device=device),
+            torch.empty((lanes, i // 32), **u8),
+            torch.empty((0,), dtype=torch.float32, device=device),
+            torch.empty((batch, h), dtype=torch.bfloat16, device=device),
+        )
 
 
 def qwen35_moe_b1_out(
     workspace: Qwen35MoeB1Workspace,
-    output: torch.Tensor,
     hidden: torch.Tensor,
-    router_logits: torch.Tensor,
+    combined_gate: torch.Tensor,
     w1: torch.Tensor,
     w1_scales: torch.Tensor,
     w2: torch.Tensor,
     w2_scales: torch.Tensor,
-    shared_output: torch.Tensor | None = None,
-    shared_gate: torch.Tensor | None = None,
+    renormalize: bool = False,
+) -> torch.Tensor:
+    """Decode schedule from the hidden rows: router, W1 routes, W2 routes + reduce
+    (python/mxfp6/qwen35.py:384-432).
+
+    ``combined_gate`` is the routed gate rows followed by the shared expert's gate row;
+    ``w1`` ``[E + 1, 2I, 3H/4]`` and ``w2`` ``[E + 1, H, 3I/4]`` end with the shared expert.
+    """
+    qwen35_router_quant_out(
+        workspace.quantized, workspace.input_scales, workspace.routed_logits,
+        workspace.topk_weights, workspace.topk_ids, workspace.shared_gate, hidden,
+        combined_gate, renormalize=renormalize)
+    return _decode_routes_out(workspace, w1, w1_scales, w2, w2_scales, None, None)
+
+
+def qwen35_moe_decode_logits_out(
+    workspace: Qwen35MoeB1Workspace,
+    hidden: torch.Tensor,
+    router_logits: torch.Tensor,
+    shared_gate: torch.Tensor,
+    w1: torch.Tensor,
+    w1_scales: torch.Tensor,
+    w2: torch.Tensor,
+    w2_scales: torch.Tensor,
+    shared_w1: PackedMXFP6Tensor | None = None,
+    shared_w2: PackedMXFP6Tensor | None = None,
     renormalize: bool = True,
 ) -> torch.Tensor:
-    """One-token decode: the grouped schedule at batch 1."""
-    return qwen35_grouped_moe_logits_out(
-        workspace.grouped, output, hidden, router_logits, w1, w1_scales, w2, w2_scales,
-        shared_output=shared_output, renormalize=renormalize, shared_gate=shared_gate,
-    )
+    """Decode schedule from given router logits: top-k + quantization, W1 routes, W2 routes
+    + reduce, three launches in all.  The shared expert is the last matrix of ``w1`` /
+    ``w2`` or, when ``shared_w1`` / ``shared_w2`` are given, a separate pair."""
+    qwen35_topk_quant_out(workspace.quantized, workspace.input_scales, None,
+                          workspace.topk_weights, workspace.topk_ids, hidden, router_logits,
+                          renormalize=renormalize)
+    return _decode_routes_out(workspace, w1, w1_scales, w2, w2_scales, shared_w1, shared_w2,
+                              shared_gate)
+
+
+def _decode_routes_out(workspace, w1, w1_scales, w2, w2_scales, shared_w1, shared_w2,
+                       shared_gate=None):
+    sw1 = sw1s = sw2 = sw2s = None
+    if shared_w1 is not None:
+        sw1, sw1s = shared_w1.values.view(1, *w1.shape[1:]), shared_w1.scales
+        sw2, sw2s = shared_w2.values.view(1, *w2.shape[1:]), shared_w2.scales
+    qwen35_w1_splitk_silu_mxfp8_out(
+        workspace.activation, workspace.activation_scales, workspace.w1_partial,
+        workspace.quantized, workspace.input_scales, w1, w1_scales, workspace.topk_ids,
+        True, sw1, sw1s)
+    qwen35_w2_splitk_reduce_out(
+        workspace.output, workspace.w2_partial, workspace.activation,
+        workspace.activation_scales, w2, w2_scales, workspace.topk_ids, workspace.topk_weights,
+        workspace.shared_gate if shared_gate is None else shared_gate, sw2, sw2s)
+    return workspace.output

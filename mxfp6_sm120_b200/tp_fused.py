@@ -147,6 +147,28 @@ class SymmetricBlocks:
             )
         return out
 
+    # From this many bytes per rank on, the all-reduce runs in two phases (slices summed in
+    # place, then gathered): every rank then moves 2 (G - 1) / G of the tensor instead of
+    # reading all of it from every peer.
+    TWO_PHASE_MIN_BYTES = 1 << 20
+
+    def allreduce_any(self, out: torch.Tensor) -> torch.Tensor:
+        """:meth:`allreduce` for small outputs, the two-phase form for large ones."""
+        rows, hidden = (int(v) for v in out.shape)
+        if rows * hidden * 2 < self.TWO_PHASE_MIN_BYTES or rows % self.world:
+            return self.allreduce(out)
+        if out.dtype != torch.bfloat16 or not out.is_contiguous():
+            raise ValueError("out must be contiguous BF16")
+        buffer = self._take(self._next)
+        with torch.cuda.device(self.device):
+            check(
+                library().mxfp6_tp_allreduce_two_phase_bf16(
+                    self._blocks, self.world, self.rank, buffer, self.partial_bytes,
+                    out.data_ptr(), rows, hidden, _stream(self.device),
+                )
+            )
+        return out
+
     def allgather(self, buffer: int, segments) -> None:
         """``segments`` = up to four ``(offset_bytes, tensor)``: the ``tensor.nbytes / world``
         bytes at ``offset_bytes`` of every rank's partial buffer ``buffer`` are gathered into

@@ -199,3 +199,40 @@ def test_peer_that_never_signals_ends_as_status_301(mx):
     finally:
         blocks.check(lib.mxfp6_tp_set_wait_limit(before))
         blocks.free()
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_two_phase_allreduce_reduces_its_slice_in_place_and_gathers_by_rank(mx, world):
+    """Rank 0's half of the two-phase all-reduce: its slice of rows is summed over all
+    ranks (FP32, rank order) and written over its own copy, then the slices are gathered
+    rank by rank.  The other ranks' kernels do not run here, so their slices arrive as
+    they were: that pins the addressing of both phases."""
+    device = torch.device("cuda", 0)
+    rows, hidden = 64, 1024
+    blocks = _Blocks(mx, world, rows * hidden * 2, device)
+    try:
+        gen = torch.Generator(device=device).manual_seed(40 + world)
+        parts = []
+        for r in range(world):
+            p = torch.randn((rows, hidden), generator=gen, device=device).to(torch.bfloat16)
+            blocks.partial(r, 1, rows, hidden).copy_(p)
+            parts.append(p)
+        blocks.peers_have_signalled()
+        out = torch.zeros((rows, hidden), dtype=torch.bfloat16, device=device)
+        blocks.check(blocks.lib.mxfp6_tp_allreduce_two_phase_bf16(
+            blocks.array, world, 0, 1, blocks.partial_bytes, out.data_ptr(), rows, hidden,
+            _stream(device)))
+        torch.cuda.synchronize()
+        assert mx.device_status(device) == 0          # two steps on one buffer, by design
+        per = rows // world
+        assert torch.equal(out[:per], _rank_order_sum([p[:per] for p in parts]))
+        for r in range(1, world):
+            assert torch.equal(out[r * per: (r + 1) * per], parts[r][r * per: (r + 1) * per])
+        assert torch.equal(blocks.partial(0, 1, rows, hidden)[:per], out[:per])   # in place
+        assert blocks.state()[0] == 2 and blocks.state()[2] == 2                  # steps, last buffer + 1
+        # rows that the ranks cannot share evenly are refused
+        assert blocks.lib.mxfp6_tp_allreduce_two_phase_bf16(
+            blocks.array, world, 0, 0, blocks.partial_bytes, out.data_ptr(), rows - 1, hidden,
+            _stream(device)) == 1
+    finally:
+        blocks.free()
