@@ -286,7 +286,9 @@ def quantizer_rows(mx, device, stream, peaks) -> dict:
 def moe_layer_latency(mx, device, stream, peaks) -> dict:
     """Latency of one routed-MoE layer (hidden 2048, 256 experts, top-8, intermediate 512,
     gated shared expert), one CUDA graph per token batch.  ``us_warm`` = back-to-back
-    replays (the reference's method); ``us_cold`` = L2 flushed between replays."""
+    replays of a graph holding one layer (the reference's method); ``us_warm_stacked`` = per
+    layer when the graph holds twenty calls, as a decoder's graph does; ``us_cold`` = L2
+    flushed between replays.  ``schedule`` names the path the layer object took."""
     from mxfp6_sm120_b200.moe_layer import MoeLayer
 
     shape = mx.MoeShape()
@@ -323,11 +325,27 @@ def moe_layer_latency(mx, device, stream, peaks) -> dict:
             stream.synchronize()
             cold.append(start.elapsed_time(stop) * 1e3)
         cold.sort()
-        used = int(torch.unique(state.workspace.topk_ids).numel())
+        stacked = None
+        if batch <= 96:
+            deep = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(deep, stream=stream):
+                for _ in range(20):
+                    layer.forward(state, hidden, logits, gate)
+            for _ in range(2):
+                deep.replay()
+            start.record(stream)
+            for _ in range(5):
+                deep.replay()
+            stop.record(stream)
+            stream.synchronize()
+            stacked = round(start.elapsed_time(stop) * 1e3 / 100, 1)
+        decode = state.decode is not None
+        used = int(torch.unique((state.decode if decode else state.workspace).topk_ids).numel())
         byts = (used + 1) * 2457600 + batch * shape.hidden * 4 + batch * shape.experts * 2
         flops = 9.0 * batch * 6291456
         cold_us = cold[len(cold) // 2]
-        rows.append({"tokens": batch, "us_warm": round(warm, 1), "us_cold": round(cold_us, 1),
+        rows.append({"tokens": batch, "schedule": "decode" if decode else "grouped",
+                     "us_warm": round(warm, 1), "us_warm_stacked": stacked, "us_cold": round(cold_us, 1),
                      "experts_hit": used, "gbs_cold": round(byts / cold_us / 1e3, 0),
                      "hbm_frac_cold": round(byts / cold_us / 1e3 / float(peaks["hbm_gbs"]), 3),
                      "tflops_warm": round(flops / warm / 1e6, 1)})

@@ -203,8 +203,8 @@ int mxfp6_gemm_w6a8_static_scratch(const uint8_t* a_values_dev, const uint8_t* a
 /* Plan query: fills tile_tokens, scratch splits, stages, grid, partial bytes, counter
  * bytes, cluster split factor, 1 when the two-CTA kernel runs the problem, the kernel
  * family (0 persistent single-CTA, 1 CTA pair, 2 weight streaming) and the dynamic shared
- * memory of a CTA.  A registered override of the exact problem (mxfp6_set_w6a8_config)
- * is applied when tile_tokens and splits are both 0. */
+ * memory of a CTA.  A registered override of the exact problem with BF16 output
+ * (mxfp6_set_w6a8_config) is applied when tile_tokens and splits are both 0. */
 int mxfp6_gemm_w6a8_plan(int64_t m, int64_t n, int64_t k, int tile_tokens, int splits,
                          int64_t out_plan[10]);
 /* Dense launches of at most 64 rows run on the weight-streaming kernel (two CTAs per SM,
@@ -239,7 +239,7 @@ int mxfp6_get_split_k_mode(void);
  * 256 weight rows per tile, each CTA stages half of the activation tile); 0 keeps them
  * on the single-CTA kernel.  Default 1.  Results are bit-identical either way.  No
  * reference counterpart: the reference picks kernels in its autotuner,
- * mxfp6_sm120/autotune.py:18-60. */
+ * python/mxfp6/autotune.py:33-85 (candidate list), :552-885 (search). */
 int mxfp6_set_cta_pair_mode(int enabled);
 int mxfp6_get_cta_pair_mode(void);
 /* torch.ops.mxfp6.gemm_from_float (csrc/torch_extension.cu:1869-1925): quantize the
@@ -352,7 +352,11 @@ int mxfp6_array_gemm_w6a8_silu_mxfp8(uint8_t* output_dev, uint8_t* output_scales
  * [tokens * lanes, k] with lanes = topk + compute_shared;
  * output[t] = cast(sigmoid(gate[t]) * shared[t] + sum_l w[t, l] * cast(routed[t, l])), FP32,
  * shared term first, where the shared row is computed here (compute_shared), given
- * (shared_output_dev, [tokens, n] of the output type) or absent.  At most 9 lanes, k <= 2048. */
+ * (shared_output_dev, [tokens, n] of the output type) or absent.  At most 9 lanes, k <= 2048.
+ * routing_ready != 0: the caller vouches that topk_ids were complete before the kernel that
+ * precedes this one on the stream let its dependents start (true behind
+ * mxfp6_array_gemm_w6a8_silu_mxfp8, which waits for its own inputs first); the kernel then
+ * fetches the experts' weights before its dependency wait.  0 is always safe. */
 int mxfp6_array_gemm_w6a8_reduce(void* output_dev, int out_dtype, const uint8_t* activation_dev,
                                  const uint8_t* logical_scales_dev, const uint8_t* weight_dev,
                                  const uint8_t* weight_scales_dev, int experts,
@@ -361,7 +365,7 @@ int mxfp6_array_gemm_w6a8_reduce(void* output_dev, int out_dtype, const uint8_t*
                                  int ids_are_int64, const float* topk_weights_dev,
                                  const void* shared_gate_dev, int gate_dtype, int gate_stride,
                                  const void* shared_output_dev, int compute_shared, int64_t tokens,
-                                 int topk, int64_t n, int64_t k, void* stream);
+                                 int topk, int64_t n, int64_t k, int routing_ready, void* stream);
 /* torch.ops.mxfp6.moe_reduce_array_out (schema csrc/moe.cu:10129-10131, kernel :8237-8282):
  * combined [tokens * (topk + 1), hidden], the shared row last of each token. */
 int mxfp6_moe_reduce_array(void* output_dev, const void* combined_dev, int dtype,
@@ -385,6 +389,21 @@ int mxfp6_moe_reduce(void* out_dev, const void* routed_dev, int dtype,
                      const void* shared_dev, const void* shared_gate_dev, int gate_dtype,
                      int gate_stride, int64_t tokens, int hidden_size, int topk,
                      int64_t routed_rows, void* stream);
+/* torch.ops.mxfp6.moe_reduce_tp2_out (schema csrc/moe.cu:10124-10128, kernel :7698-7925) with
+ * the reference's argument list: the reduce above (BF16) into this rank's data buffer, then
+ * the sum over `world` ranks (2 in the reference, up to 8 here) in rank order, FP32, rounded
+ * once.  signal_ptrs_host[r] / buffer_ptrs_host[r]: rank r's signal area (>= 64 bytes, zero
+ * before the first call) and data buffer (>= tokens * hidden * 2 bytes), both valid on this
+ * device.  Every wait is bounded (status 301); a closing handshake makes the single buffer
+ * safe to rewrite when the call's last kernel has run. */
+int mxfp6_moe_reduce_tp_pointers(void* out_dev, const void* routed_dev,
+                                 const float* topk_weights_dev,
+                                 const int32_t* inverse_permutation_dev, const void* shared_dev,
+                                 const void* shared_gate_dev, int gate_dtype, int gate_stride,
+                                 int64_t tokens, int hidden_size, int topk, int64_t routed_rows,
+                                 const uint64_t* signal_ptrs_host,
+                                 const uint64_t* buffer_ptrs_host, int world, int rank,
+                                 void* stream);
 
 /* ---- split-K workspace arena ----------------------------------------------
  * torch.ops.mxfp6.begin_workspace_planning / finalize_workspace_planning /

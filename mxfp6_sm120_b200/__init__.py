@@ -102,6 +102,9 @@ from .qwen35 import (
     shared_expert_out,
 )
 
+from .checkpoint import MoeLayerCheckpoint, TensorSource, load_linear, load_moe_layer
+from . import torch_ops  # registers torch.ops.mxfp6.* (the reference's dispatcher names)
+
 from .decoder import (
     DecoderConfig,
     DecoderLayer,

@@ -41,6 +41,8 @@ int tp_block_close(void*);
 int tp_block_free(void*);
 int tp_allreduce_sum(void* const*, int, int, int, size_t, void*, int64_t, int64_t, cudaStream_t);
 int tp_reduce_scatter(void* const*, int, int, int, size_t, void*, int64_t, int64_t, cudaStream_t);
+int tp_allreduce_pointers(const uint64_t*, const uint64_t*, int, int, void*, int64_t, int64_t,
+                          cudaStream_t);
 int tp_allreduce_two_phase(void* const*, int, int, int, size_t, void*, int64_t, int64_t,
                            cudaStream_t);
 int tp_allgather(void* const*, int, int, int, size_t, int, const int64_t*, const int64_t*,
@@ -79,7 +81,7 @@ int moe_route_gemm(void*, uint8_t*, int, int, const uint8_t*, const uint8_t*, in
 int moe_route_w2_reduce(void*, int, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*,
                         int, const uint8_t*, const uint8_t*, const void*, int, const float*,
                         const void*, int, int, const void*, int, int64_t, int, int64_t, int64_t,
-                        cudaStream_t);
+                        int, cudaStream_t);
 int moe_reduce_array(void*, const void*, int, const float*, const void*, int, int, int64_t, int,
                      int64_t, cudaStream_t);
 int moe_router_logits(const void*, const void*, const void*, void*, void*, int64_t, int64_t, int,
@@ -705,6 +707,24 @@ int mxfp6_moe_reduce(void* out, const void* routed, int dtype, const float* topk
                     static_cast<cudaStream_t>(stream));
 }
 
+int mxfp6_moe_reduce_tp_pointers(void* out, const void* routed, const float* topk_weights,
+                                 const int32_t* inverse_permutation, const void* shared,
+                                 const void* shared_gate, int gate_dtype, int gate_stride,
+                                 int64_t tokens, int hidden_size, int topk, int64_t routed_rows,
+                                 const uint64_t* signal_ptrs, const uint64_t* buffer_ptrs,
+                                 int world, int rank, void* stream) {
+  MX_REQUIRE(signal_ptrs != nullptr && buffer_ptrs != nullptr && world >= 1 && world <= 8 &&
+                 rank >= 0 && rank < world,
+             "world must be in [1, 8], rank inside it, pointer lists non-null");
+  void* partial = reinterpret_cast<void*>(static_cast<uintptr_t>(buffer_ptrs[rank]));
+  if (int rc = moe_reduce(partial, routed, kBF16, topk_weights, inverse_permutation, shared,
+                          shared_gate, gate_dtype, gate_stride, tokens, hidden_size, topk,
+                          routed_rows, static_cast<cudaStream_t>(stream)))
+    return rc;
+  return tp_allreduce_pointers(signal_ptrs, buffer_ptrs, world, rank, out, tokens, hidden_size,
+                               static_cast<cudaStream_t>(stream));
+}
+
 int mxfp6_array_gemm_w6a8(void* output, int out_dtype, const uint8_t* activation,
                           const uint8_t* logical_scales, int64_t activation_rows,
                           const uint8_t* weight, const uint8_t* weight_scales, int experts,
@@ -736,11 +756,12 @@ int mxfp6_array_gemm_w6a8_reduce(void* output, int out_dtype, const uint8_t* act
                                  const void* topk_ids, int ids_are_int64, const float* topk_weights,
                                  const void* shared_gate, int gate_dtype, int gate_stride,
                                  const void* shared_output, int compute_shared, int64_t tokens,
-                                 int topk, int64_t n, int64_t k, void* stream) {
+                                 int topk, int64_t n, int64_t k, int routing_ready, void* stream) {
   return moe_route_w2_reduce(output, out_dtype, activation, logical_scales, weight, weight_scales,
                              experts, shared_weight, shared_weight_scales, topk_ids, ids_are_int64,
                              topk_weights, shared_gate, gate_dtype, gate_stride, shared_output,
-                             compute_shared, tokens, topk, n, k, static_cast<cudaStream_t>(stream));
+                             compute_shared, tokens, topk, n, k, routing_ready,
+                             static_cast<cudaStream_t>(stream));
 }
 
 int mxfp6_moe_reduce_array(void* output, const void* combined, int dtype, const float* topk_weights,

@@ -131,22 +131,27 @@ __device__ __forceinline__ void warp_softmax_topk(const __nv_bfloat16* __restric
 }
 
 // ---------------------------------------------------------------- top-k + quantize
-// One CTA per `tokens_per_cta` tokens (1 for decode batches, 8 otherwise).  All
-// threads quantize the rows; then one warp per token does the softmax top-k.
-__global__ void __launch_bounds__(256)
+// One CTA per `tokens_per_cta` tokens (1 for decode batches, 8 otherwise).  The first 256
+// threads quantize the rows; then one warp per token does the softmax top-k.  A CTA of 288
+// threads (one token per CTA) gives the top-k a warp of its own, beside the quantization.
+constexpr int kQuantThreads = 256;
+
+__global__ void __launch_bounds__(kQuantThreads + 32)
 topk_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16* __restrict__ logits,
                   uint8_t* __restrict__ quantized, uint8_t* __restrict__ logical_scales,
                   uint8_t* __restrict__ dense_scales, float* __restrict__ topk_weights,
                   int32_t* __restrict__ topk_ids, int tokens, int tokens_per_cta, int hidden_size,
                   int experts, int topk, int renormalize) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the rows may come from the kernel before
   const int first = blockIdx.x * tokens_per_cta;
   const int count = min(tokens_per_cta, tokens - first);
   const int groups = hidden_size / kScaleVec;
-  if (quantized != nullptr) {
+  const bool own_topk_warp = blockDim.x > kQuantThreads;
+  if (quantized != nullptr && threadIdx.x < kQuantThreads) {
     const int row_chunks = hidden_size / 8;
     const int chunks = count * row_chunks;
-    const int rounds = (chunks + blockDim.x - 1) / blockDim.x;
+    const int rounds = (chunks + kQuantThreads - 1) / kQuantThreads;
     // Four 16-byte loads per thread are in flight before the first one is used.
     constexpr int kUnroll = 4;
     const bool words = groups % 4 == 0 &&
@@ -156,7 +161,7 @@ topk_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16*
       uint4 raw[kUnroll];
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
-        const int c = (it0 + u) * blockDim.x + threadIdx.x;
+        const int c = (it0 + u) * kQuantThreads + threadIdx.x;
         raw[u] = make_uint4(0u, 0u, 0u, 0u);
         if (c < chunks) {
           raw[u] = __ldg(reinterpret_cast<const uint4*>(hidden) + ((int64_t)first * row_chunks + c));
@@ -164,7 +169,7 @@ topk_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16*
       }
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
-        const int c = (it0 + u) * blockDim.x + threadIdx.x;
+        const int c = (it0 + u) * kQuantThreads + threadIdx.x;
         const bool valid = c < chunks;
         const int64_t gc = (int64_t)first * row_chunks + c;  // chunk index in the whole matrix
         float v[8];
@@ -213,6 +218,13 @@ topk_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16*
   }
   if (topk_ids == nullptr) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (own_topk_warp) {
+    if (warp == kQuantThreads / 32 && count > 0) {
+      warp_softmax_topk(logits + (int64_t)first * experts, experts, topk, renormalize,
+                        topk_weights + (int64_t)first * topk, topk_ids + (int64_t)first * topk, lane);
+    }
+    return;
+  }
   for (int t = warp; t < count; t += blockDim.x >> 5) {
     const int token = first + t;
     warp_softmax_topk(logits + (int64_t)token * experts, experts, topk, renormalize,
@@ -677,11 +689,21 @@ int moe_topk_quant(const void* hidden, const void* logits, int64_t tokens, int h
   }
   const int tokens_per_cta = tokens <= 148 ? 1 : 8;
   const unsigned grid = (unsigned)((tokens + tokens_per_cta - 1) / tokens_per_cta);
-  topk_quant_kernel<<<grid, 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(hidden), static_cast<const __nv_bfloat16*>(logits),
-      quantized, logical_scales, dense_scales, topk_weights, topk_ids, (int)tokens, tokens_per_cta,
-      hidden_size, experts, topk, renormalize);
-  MX_CUDA(cudaGetLastError());
+  // One token per CTA: the top-k gets a warp of its own beside the 256 quantizing threads.
+  const bool own_topk_warp = tokens_per_cta == 1 && topk_ids != nullptr && quantized != nullptr;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(own_topk_warp ? kQuantThreads + 32 : kQuantThreads);
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = grid <= 148 ? 1 : 0;  // the kernel opens with a dependency wait
+  MX_CUDA(cudaLaunchKernelEx(&config, topk_quant_kernel, static_cast<const __nv_bfloat16*>(hidden),
+                             static_cast<const __nv_bfloat16*>(logits), quantized, logical_scales,
+                             dense_scales, topk_weights, topk_ids, (int)tokens, tokens_per_cta,
+                             hidden_size, experts, topk, renormalize));
   return kOk;
 }
 

@@ -38,6 +38,7 @@
 #include <cuda.h>
 #include <cuda_fp8.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <mutex>
 #include <unordered_map>
@@ -59,7 +60,8 @@ constexpr uint32_t kWTileTxBytes = kWTileBytes / 4 * 3;  // 16U6_ALIGN16B counts
 constexpr uint32_t kATileBytes = kRows * kTileK;
 constexpr uint32_t kAtomBytes = 512;
 constexpr int kMaxKBlocks = 64;   // K <= 8192
-constexpr int kMaxCluster = 4;
+constexpr int kMaxCluster = 4;      // K split of the route GEMM (its reduction buffer holds four ranks)
+constexpr int kMaxLaneCluster = 5;  // lane split of the reduce kernel: two lanes per CTA at most
 constexpr int kMaxLanes = 9;      // routes of one token in the reduce kernel (top-8 + shared)
 
 enum RouteMode : int { kRouteStore = 0, kRouteSwiglu = 1 };
@@ -91,6 +93,7 @@ struct RouteArgs {
   int tiles;            // n / 128
   int cluster;          // CTAs per cluster (K split, or lane split in the reduce kernel)
   int out_dtype;
+  int routing_ready;    // reduce kernel: ids were complete before the preceding kernel's dependents started
 };
 
 __device__ __forceinline__ int read_expert(const RouteArgs& a, int token, int lane) {
@@ -130,7 +133,6 @@ route_gemm_kernel(const __grid_constant__ CUtensorMap tm_w,
                   const __grid_constant__ CUtensorMap tm_shared,
                   const __grid_constant__ CUtensorMap tm_a, const RouteArgs args) {
   using C = RCfg<MODE>;
-  ptx::grid_launch_dependents();
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -193,8 +195,11 @@ route_gemm_kernel(const __grid_constant__ CUtensorMap tm_w,
   if (ck > 1) ptx::cluster_sync_all();
   bool cluster_arrived = false;
 
-  // Expert ids, activations and their scales come from the kernel before this one.
+  // Expert ids, activations and their scales come from the kernel before this one.  The
+  // kernel after this one starts only now, so that it may read that routing data before
+  // its own dependency wait (route_w2_reduce_kernel fetches its weights that early).
   ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
   const int expert = read_expert(args, token, route_lane);  // -1: no such expert, -2: separate shared
   const bool live = expert != -1;
   const CUtensorMap* wmap = expert == -2 ? &tm_shared : &tm_w;
@@ -475,36 +480,56 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
   if (cr > 1) ptx::cluster_sync_all();
   bool cluster_arrived = false;
 
-  ptx::grid_dependency_wait();
   // Every warp needs the experts of this CTA's lanes: each reads them for itself (a few words).
   auto lane_of = [&](int p) { return shared_first != 0 ? (p == 0 ? args.lanes - 1 : p - 1) : p; };
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
+    // Weights and their scales depend on the routing data only.  Where the caller vouches
+    // that this data was complete before the preceding kernel let this one start, the ring
+    // is filled with them before the dependency wait; the activation tiles follow after it.
+    auto load_weights = [&](int stage, int expert, int kb) {
+      const CUtensorMap* wmap = expert == -2 ? &tm_shared : &tm_w;
+      const uint8_t* wsc = expert == -2 ? args.shared_w_scales : args.w_scales;
+      const int w_row = (expert < 0 ? 0 : expert) * args.w_rows + tile * kTileF;
+      const uint32_t bar = full0 + 8 * stage;
+      ptx::mbar_arrive_expect_tx(bar, tx_stage);
+      ptx::tma_load_2d(ptx::smem_u32(w_tiles + (size_t)stage * kWTileBytes), wmap, kb * kTileK, w_row, bar);
+      ptx::bulk_load(ptx::smem_u32(sfa_tiles + (size_t)stage * kAtomBytes),
+                     wsc + ((int64_t)(w_row / kAtomRows) * kbn + kb) * kAtomBytes, kAtomBytes, bar);
+    };
+    int ahead = 0;  // blocks whose weights are already on their way
+    if (args.routing_ready != 0) {
+      for (int p = p0; p < p1 && ahead < C::kStages; ++p) {
+        const int expert = read_expert(args, token, lane_of(p));
+        if (expert == -1) continue;
+        for (int kb = 0; kb < kbn && ahead < C::kStages; ++kb) {
+          if (ptx::elect_one()) load_weights(ahead, expert, kb);
+          __syncwarp();
+          ++ahead;
+        }
+      }
+    }
+    ptx::grid_dependency_wait();
     int stage = 0;
     uint32_t phase = 0;
+    int block = 0;
     bool ok = true;
     for (int p = p0; ok && p < p1; ++p) {
       const int l = lane_of(p);
       const int expert = read_expert(args, token, l);
       if (expert == -1) continue;
-      const CUtensorMap* wmap = expert == -2 ? &tm_shared : &tm_w;
-      const uint8_t* wsc = expert == -2 ? args.shared_w_scales : args.w_scales;
-      const int w_row = (expert < 0 ? 0 : expert) * args.w_rows + tile * kTileF;
       const int src_row = token * args.lanes + l;
-      for (int kb = 0; ok && kb < kbn; ++kb) {
-        ok = __all_sync(0xffffffffu, bounded_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag,
-                                                  args.status, 131));
-        if (!ok) break;
+      for (int kb = 0; ok && kb < kbn; ++kb, ++block) {
+        if (block >= ahead) {
+          ok = __all_sync(0xffffffffu, bounded_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag,
+                                                    args.status, 131));
+          if (!ok) break;
+        }
         if (ptx::elect_one()) {
-          const uint32_t bar = full0 + 8 * stage;
-          ptx::mbar_arrive_expect_tx(bar, tx_stage);
-          ptx::tma_load_2d(ptx::smem_u32(w_tiles + (size_t)stage * kWTileBytes), wmap, kb * kTileK,
-                           w_row, bar);
-          ptx::bulk_load(ptx::smem_u32(sfa_tiles + (size_t)stage * kAtomBytes),
-                         wsc + ((int64_t)(w_row / kAtomRows) * kbn + kb) * kAtomBytes, kAtomBytes, bar);
+          if (block >= ahead) load_weights(stage, expert, kb);
           ptx::tma_load_2d(ptx::smem_u32(a_tiles + (size_t)stage * kATileBytes), &tm_a, kb * kTileK,
-                           src_row, bar);
+                           src_row, full0 + 8 * stage);
         }
         __syncwarp();
         if (++stage == C::kStages) {
@@ -520,6 +545,7 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
     int stage = 0;
     uint32_t phase = 0;
     uint32_t sf_set = 0;
+    ptx::grid_dependency_wait();
     bool ok = __all_sync(0xffffffffu, bounded_wait(sfb_bar, 0u, abort_flag, args.status, 132));
     for (int p = p0; ok && p < p1; ++p) {
       const int l = lane_of(p);
@@ -562,6 +588,7 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
     const int quarter = warp & 3;
+    ptx::grid_dependency_wait();
     if (warp == 2) {
       // activation scale words of this CTA's lanes: lane position q, block kb -> word at
       // (q * 16 + kb) * 16 bytes
@@ -577,9 +604,32 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(sfb_bar);
     }
-    bool ok = bounded_wait(tfull, 0u, abort_flag, args.status, 134);
+    // Weights of this CTA's lanes (0 for a lane without an expert) and the gate: fetched
+    // while the tensor cores work.
+    float weight_of[kMaxLanes];
+    bool live_lane[kMaxLanes];
+#pragma unroll
+    for (int q = 0; q < kMaxLanes; ++q) {
+      weight_of[q] = 0.0f;
+      live_lane[q] = false;
+      if (p0 + q < p1) {
+        const int l = lane_of(p0 + q);
+        live_lane[q] = read_expert(args, token, l) != -1;
+        weight_of[q] = l >= args.topk ? gate_of(args, token)
+                                      : args.topk_weights[(int64_t)token * args.topk + l];
+      }
+    }
     const int f = tile * kTileF + quarter * 32 + lane;
     const bool bf16_out = args.out_dtype == kBF16;
+    float external = 0.0f;
+    if (rank == 0 && args.shared_output != nullptr) {
+      // a shared row computed elsewhere comes first in the sum, gated
+      const int64_t at = (int64_t)token * args.n + f;
+      const float s = bf16_out ? __bfloat162float(static_cast<const __nv_bfloat16*>(args.shared_output)[at])
+                               : __half2float(static_cast<const __half*>(args.shared_output)[at]);
+      external = __fmul_rn(gate_of(args, token), s);
+    }
+    bool ok = bounded_wait(tfull, 0u, abort_flag, args.status, 134);
     // Every lane's weighted term goes to the owner (rank 0), which adds them one by one in
     // the order of the unfused reduce, so the sum does not depend on the cluster size.
     // terms[quarter][position][32]: the owner's own terms are written in place.
@@ -587,20 +637,22 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
     if (ok) {
       ptx::tc_fence_after();
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-      for (int p = p0; p < p1; ++p) {
-        const int l = lane_of(p);
-        float term = 0.0f;
-        if (read_expert(args, token, l) != -1) {
-          uint32_t r[16];
-          ptx::tmem_ld_x16(t_addr + (p - p0) * kRows, r);
-          ptx::tmem_ld_wait();
-          // The routed row as the GEMM would have stored it: rounded to the output type.
-          const float raw = __uint_as_float(r[0]);
-          const float v = bf16_out ? __bfloat162float(__float2bfloat16_rn(raw)) : __half2float(__float2half_rn(raw));
-          const float w = l >= args.topk ? gate_of(args, token) : args.topk_weights[(int64_t)token * args.topk + l];
-          term = __fmul_rn(w, v);
+#pragma unroll
+      for (int q = 0; q < kMaxLanes; ++q) {
+        if (p0 + q < p1) {
+          float term = 0.0f;
+          if (live_lane[q]) {
+            uint32_t r[16];
+            ptx::tmem_ld_x16(t_addr + q * kRows, r);
+            ptx::tmem_ld_wait();
+            // The routed row as the GEMM would have stored it: rounded to the output type.
+            const float raw = __uint_as_float(r[0]);
+            const float v = bf16_out ? __bfloat162float(__float2bfloat16_rn(raw))
+                                     : __half2float(__float2half_rn(raw));
+            term = __fmul_rn(weight_of[q], v);
+          }
+          terms[(p0 + q) * 32 + lane] = term;
         }
-        terms[p * 32 + lane] = term;
       }
     }
     if (cr > 1) {
@@ -619,14 +671,9 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
     }
     if (ok && rank == 0) {
       const int64_t at = (int64_t)token * args.n + f;
-      float acc;
+      float acc = external;
       int p = 0;
-      if (args.shared_output != nullptr) {
-        // a shared row computed elsewhere comes first in the sum, gated
-        const float s = bf16_out ? __bfloat162float(static_cast<const __nv_bfloat16*>(args.shared_output)[at])
-                                 : __half2float(static_cast<const __half*>(args.shared_output)[at]);
-        acc = __fmul_rn(gate_of(args, token), s);
-      } else {
+      if (args.shared_output == nullptr) {
         acc = terms[lane];
         p = 1;
       }
@@ -871,10 +918,15 @@ int moe_route_gemm(void* out, uint8_t* out_scales, int out_dtype, int swiglu,
   args.k_blocks = (int)(k / kTileK);
   args.tiles = (int)(n / kTileF);
   args.out_dtype = out_dtype;
-  // Split K while the launch stays inside the GPU's CTA slots (two per SM).
+  // Split K while the launch stays inside the GPU's CTA slots (two per SM); every CTA keeps
+  // at least two K blocks.  Clusters of more than two CTAs do not fill the last slots of
+  // the GPU, so such a launch stops at 240 CTAs.
   const int64_t units = routes * args.tiles;
-  int ck = 1;
-  while (ck < kMaxCluster && units * (ck * 2) <= 2 * sm_count() - 8 && args.k_blocks / (ck * 2) >= 2) ck *= 2;
+  const int64_t slots = 2 * (int64_t)sm_count() - 8;
+  const int64_t wide_slots = slots - slots / 6;
+  int ck = (int)std::min<int64_t>({(int64_t)kMaxCluster, wide_slots / units, (int64_t)args.k_blocks / 2});
+  if (ck < 2 && units * 2 <= slots && args.k_blocks >= 4) ck = 2;
+  if (ck < 1) ck = 1;
   args.cluster = ck;
   MX_REQUIRE(units * ck <= INT32_MAX, "too many routes");
   if (swiglu != 0) {
@@ -896,7 +948,7 @@ int moe_route_w2_reduce(void* out, int out_dtype, const uint8_t* activation,
                         const void* topk_ids, int ids_are_int64, const float* topk_weights,
                         const void* shared_gate, int gate_dtype, int gate_stride,
                         const void* shared_output, int compute_shared, int64_t tokens, int topk,
-                        int64_t n, int64_t k, cudaStream_t stream) {
+                        int64_t n, int64_t k, int routing_ready, cudaStream_t stream) {
   if (int rc = common_checks(activation, act_scales, weight, weight_scales, topk_ids, tokens, topk,
                              num_experts, n, k))
     return rc;
@@ -956,10 +1008,20 @@ int moe_route_w2_reduce(void* out, int out_dtype, const uint8_t* activation,
   args.k_blocks = (int)(k / kTileK);
   args.tiles = (int)(n / kTileF);
   args.out_dtype = out_dtype;
+  args.routing_ready = routing_ready != 0 ? 1 : 0;
+  // Lanes per CTA: two where the launch stays inside the GPU's CTA slots, then three, then
+  // half of them, then all (clusters of more than two CTAs stop at 240 CTAs, as above).
   const int64_t units = tokens * args.tiles;
+  const int64_t slots = 2 * (int64_t)sm_count() - 8;
+  const int64_t wide_slots = slots - slots / 6;
   int cr = 1;
-  if (units * 3 <= 2 * sm_count() - 8 && lanes >= 6) cr = 3;
-  else if (units * 2 <= 2 * sm_count() - 8 && lanes >= 4) cr = 2;
+  const int choices[3] = {(lanes + 1) / 2, (lanes + 2) / 3, 2};
+  for (int c : choices) {
+    if (c >= 2 && c <= kMaxLaneCluster && c <= lanes && units * c <= (c > 2 ? wide_slots : slots)) {
+      cr = c;
+      break;
+    }
+  }
   args.cluster = cr;
   return launch_route(route_w2_reduce_kernel, WCfg::kSmemBytes, (int)(units * cr), cr, stream, tm_w,
                       tm_shared, tm_a, args);

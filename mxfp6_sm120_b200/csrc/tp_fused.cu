@@ -687,6 +687,68 @@ int tp_allreduce_two_phase(void* const* blocks, int world, int rank, int buffer,
   return kOk;
 }
 
+namespace {
+// Handshake only: a rank that has passed it has seen every peer leave the step before, so
+// whatever that step read may be overwritten.  It records the OTHER buffer index as the last
+// one used, so that the next sum on the single caller-owned buffer is not taken for a repeat.
+__global__ void __launch_bounds__(kTpThreads)
+step_barrier_kernel(const TpPeers peers, TpState* state, int* status) {
+  __shared__ uint32_t step_shared;
+  __shared__ int ok_shared;
+  const uint32_t step = tp_handshake(peers, state, status, &step_shared, &ok_shared);
+  tp_finish(state, step, peers.buffer ^ 1);
+}
+}  // namespace
+
+// The all-reduce over caller-owned memory, as the reference's fused reducer takes it from
+// vLLM's custom all-reduce (csrc/moe.cu:7698-7925: one signal area and one data buffer per
+// rank, every rank's pointers valid on this device).  signals[r] points to at least 64
+// zero-initialised bytes (eight flags and the step state), buffers[r] to the rank's
+// [rows, k] BF16 partial; this rank's partial is complete on `stream` before the call.  One
+// buffer per rank means a closing barrier: the second launch returns only when every peer has
+// finished reading, and only then may the caller's next producer overwrite the buffer.
+int tp_allreduce_pointers(const uint64_t* signals, const uint64_t* buffers, int world, int rank,
+                          void* out, int64_t rows, int64_t k, cudaStream_t stream) {
+  MX_REQUIRE(signals != nullptr && buffers != nullptr && world >= 1 && world <= kTpMaxRanks &&
+                 rank >= 0 && rank < world,
+             "world must be in [1, %d] and rank inside it", kTpMaxRanks);
+  MX_REQUIRE(out != nullptr && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+             "out must be a 16-byte aligned device pointer");
+  MX_REQUIRE(rows > 0 && k > 0 && k % 8 == 0, "rows must be positive and k a multiple of 8");
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  int* status = device_status_word(device);
+  if (status == nullptr) return kCudaError;
+  TpPeers peers;
+  peers.world = world;
+  peers.rank = rank;
+  peers.buffer = 0;
+  peers.second_phase = 0;
+  peers.wait_cycles = g_tp_wait_cycles;
+  for (int r = 0; r < kTpMaxRanks; ++r) {
+    peers.partial[r] = nullptr;
+    peers.flags[r] = nullptr;
+  }
+  for (int r = 0; r < world; ++r) {
+    MX_REQUIRE(signals[r] != 0 && buffers[r] != 0 && (signals[r] & 3) == 0 && (buffers[r] & 15) == 0,
+               "signal and buffer pointers of rank %d must be non-null and aligned (4 / 16 bytes)", r);
+    peers.flags[r] = reinterpret_cast<uint32_t*>(static_cast<uintptr_t>(signals[r]));
+    peers.partial[r] = reinterpret_cast<const void*>(static_cast<uintptr_t>(buffers[r]));
+  }
+  auto* state = reinterpret_cast<TpState*>(reinterpret_cast<uint8_t*>(peers.flags[rank]) +
+                                           kTpMaxRanks * sizeof(uint32_t));
+  const int64_t chunks = rows * k / 8;
+  int64_t grid = (chunks + kTpThreads - 1) / kTpThreads;
+  if (grid > 148 * 4) grid = 148 * 4;
+  allreduce_sum_kernel<<<(unsigned)grid, kTpThreads, 0, stream>>>(
+      peers, state, static_cast<__nv_bfloat16*>(out), chunks, status);
+  MX_CUDA(cudaGetLastError());
+  peers.second_phase = 1;
+  step_barrier_kernel<<<1, kTpThreads, 0, stream>>>(peers, state, status);
+  MX_CUDA(cudaGetLastError());
+  return kOk;
+}
+
 size_t tp_block_header_bytes() { return kTpHeaderBytes; }
 
 }  // namespace mx

@@ -9,6 +9,8 @@ and k are read from the tensors) instead of the reference's hard-coded
 
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from ._loader import check, library, load_library
@@ -626,16 +628,9 @@ def dense_w1_silu_mxfp8_out(
 # ------------------------------------------------------------------------------- reduce
 
 
-def moe_reduce_out(
-    output: torch.Tensor,
-    routed_output: torch.Tensor,
-    topk_weights: torch.Tensor,
-    inverse_permutation: torch.Tensor,
-    shared_output: torch.Tensor | None = None,
-    shared_gate: torch.Tensor | None = None,
-    use_pdl: bool = False,
-) -> None:
-    """Reduce routed rows and optionally gate/add a shared-expert output."""
+def _check_reduce_operands(output, routed_output, topk_weights, inverse_permutation,
+                           shared_output, shared_gate) -> int:
+    """Argument checks of the reducers; returns the row length of the gate tensor."""
     if (
         routed_output.device.type != "cuda"
         or routed_output.dtype not in (torch.float16, torch.bfloat16)
@@ -690,6 +685,21 @@ def moe_reduce_out(
                 "value or row per token"
             )
         gate_stride = shared_gate.numel() // output.shape[0]
+    return gate_stride
+
+
+def moe_reduce_out(
+    output: torch.Tensor,
+    routed_output: torch.Tensor,
+    topk_weights: torch.Tensor,
+    inverse_permutation: torch.Tensor,
+    shared_output: torch.Tensor | None = None,
+    shared_gate: torch.Tensor | None = None,
+    use_pdl: bool = False,
+) -> None:
+    """Reduce routed rows and optionally gate/add a shared-expert output."""
+    gate_stride = _check_reduce_operands(output, routed_output, topk_weights, inverse_permutation,
+                                         shared_output, shared_gate)
     load_library()
     tokens, hidden = (int(v) for v in output.shape)
     with torch.cuda.device(output.device):
@@ -711,19 +721,59 @@ def moe_reduce_tp2_out(
     inverse_permutation: torch.Tensor,
     shared_output: torch.Tensor | None = None,
     shared_gate: torch.Tensor | None = None,
+    signal_ptrs: list[int] | None = None,
+    buffer_ptrs: list[int] | None = None,
+    rank: int | None = None,
+    *,
     group=None,
     peer=None,
 ) -> None:
     """Reduce, then sum the result over the tensor-parallel ranks.
 
-    The reference fuses a 2-rank peer-pointer all-reduce with unbounded spins into
-    its reducer (csrc/moe.cu:7698-7925).  Here, for any world size up to 8: with
-    ``peer`` (a ``tp_fused.SymmetricBlocks``) the reducer writes this rank's partial
-    into its symmetric block and one kernel sums all ranks' partials over peer memory
-    with bounded waits; without it an NCCL all-reduce follows the reduce kernel.
+    With ``signal_ptrs`` / ``buffer_ptrs`` / ``rank`` this is the reference's call
+    (python/mxfp6/ops.py:950-1025, kernel csrc/moe.cu:7698-7925): the pointers of every
+    rank's signal area (64 zero-initialised bytes at least) and data buffer, as a
+    custom all-reduce hands them out, for 2 ranks as in the reference or up to 8.  The
+    partial goes into this rank's buffer, one kernel sums all ranks' partials over peer
+    memory in rank order with bounded waits (the reference spins without a limit), and a
+    closing handshake makes the buffer safe to rewrite.  BF16 only, like the reference.
+
+    Without the pointer lists: with ``peer`` (a ``tp_fused.SymmetricBlocks``) the partial goes
+    into this rank's symmetric block and the same kernel sums over the blocks; without it an
+    NCCL all-reduce follows the reduce kernel.
     """
     import torch.distributed as dist
 
+    if signal_ptrs is not None or buffer_ptrs is not None or rank is not None:
+        if signal_ptrs is None or buffer_ptrs is None or rank is None:
+            raise ValueError("signal_ptrs, buffer_ptrs and rank go together")
+        world = len(signal_ptrs)
+        if world != len(buffer_ptrs) or not 1 <= world <= 8 or not 0 <= int(rank) < world:
+            raise ValueError("the fused reduce requires one signal and one buffer pointer per rank "
+                             "(at most 8) and a rank among them")
+        if output.dtype != torch.bfloat16 or routed_output.dtype != torch.bfloat16:
+            raise ValueError("routed_output and output must be contiguous CUDA bfloat16")
+        if shared_output is None or shared_gate is None:
+            raise ValueError("shared_output and shared_gate are required")
+        # the argument checks of the plain reduce, without launching it
+        _check_reduce_operands(output, routed_output, topk_weights, inverse_permutation,
+                               shared_output, shared_gate)
+        _require_sm100(output.device)
+        load_library()
+        tokens, hidden = (int(v) for v in output.shape)
+        signals = (ctypes.c_uint64 * world)(*[int(v) for v in signal_ptrs])
+        buffers = (ctypes.c_uint64 * world)(*[int(v) for v in buffer_ptrs])
+        with torch.cuda.device(output.device):
+            check(
+                library().mxfp6_moe_reduce_tp_pointers(
+                    output.data_ptr(), routed_output.data_ptr(), topk_weights.data_ptr(),
+                    inverse_permutation.data_ptr(), shared_output.data_ptr(), shared_gate.data_ptr(),
+                    _GATE_CODE[shared_gate.dtype], shared_gate.numel() // tokens, tokens, hidden,
+                    int(topk_weights.shape[1]), int(routed_output.shape[0]), signals, buffers, world,
+                    int(rank), _stream(output.device),
+                )
+            )
+        return
     if peer is not None and peer.world > 1:
         rows, hidden = (int(v) for v in output.shape)
         partial = peer.next_partial(rows, hidden)
@@ -924,13 +974,17 @@ def array_gemm_w6a8_reduce_out(
     shared_weight: torch.Tensor | None = None,
     shared_weight_scales: torch.Tensor | None = None,
     use_packed_vector_loads: bool = False,
+    routing_ready: bool = False,
 ) -> None:
     """Route W2 GEMMs fused with the weighted reduce and the gated shared expert.
 
     ``activation`` is ``[tokens * 9, K]`` (eight routed rows and the shared row per token)
     or ``[tokens * 8, K]`` when ``shared_output`` brings the shared expert's rows.
     ``use_packed_vector_loads`` selects a load path of the reference's kernel and has no
-    counterpart here.
+    counterpart here.  ``routing_ready=True`` (not in the reference) vouches that ``topk_ids``
+    were complete before the kernel preceding this one let its dependents start, as they are
+    behind ``array_gemm_w6a8_silu_mxfp8_out``; the weights are then fetched ahead of the
+    dependency wait.
     """
     k = _check_route_operands(activation, logical_scales, weight, weight_scales, topk_ids)
     _check_separate_shared(shared_weight, shared_weight_scales, weight, activation.device)
@@ -974,7 +1028,7 @@ def array_gemm_w6a8_reduce_out(
                 int(weight.shape[0]), _ptr(shared_weight), _ptr(shared_weight_scales),
                 topk_ids.data_ptr(), int(topk_ids.dtype == torch.int64), topk_weights.data_ptr(),
                 shared_gate.data_ptr(), _GATE_CODE[shared_gate.dtype], stride, _ptr(shared_output),
-                0 if external else 1, tokens, topk, int(weight.shape[1]), k,
+                0 if external else 1, tokens, topk, int(weight.shape[1]), k, int(routing_ready),
                 _stream(activation.device),
             )
         )
@@ -992,6 +1046,7 @@ def qwen35_w2_splitk_reduce_out(
     shared_gate: torch.Tensor,
     shared_weight: torch.Tensor | None = None,
     shared_weight_scales: torch.Tensor | None = None,
+    routing_ready: bool = False,
 ) -> None:
     """Small-batch W2 with the weighted reduce and the gated shared row in its epilogue.
 
@@ -1000,7 +1055,8 @@ def qwen35_w2_splitk_reduce_out(
     used.
     """
     array_gemm_w6a8_reduce_out(output, activation, logical_scales, weight, weight_scales, topk_ids,
-                               topk_weights, shared_gate, None, shared_weight, shared_weight_scales)
+                               topk_weights, shared_gate, None, shared_weight, shared_weight_scales,
+                               routing_ready=routing_ready)
 
 
 def moe_reduce_array_out(

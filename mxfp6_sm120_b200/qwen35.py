@@ -510,5 +510,6 @@ def _decode_routes_out(workspace, w1, w1_scales, w2, w2_scales, shared_w1, share
     qwen35_w2_splitk_reduce_out(
         workspace.output, workspace.w2_partial, workspace.activation,
         workspace.activation_scales, w2, w2_scales, workspace.topk_ids, workspace.topk_weights,
-        workspace.shared_gate if shared_gate is None else shared_gate, sw2, sw2s)
+        workspace.shared_gate if shared_gate is None else shared_gate, sw2, sw2s,
+        routing_ready=True)  # the ids were written before W1, which waits before it lets W2 start
     return workspace.output

@@ -12,13 +12,6 @@ pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
 
 
-@pytest.fixture(scope="module")
-def mx():
-    import mxfp6_sm120_b200 as package
-
-    return package
-
-
 def _cpu_gen(seed):
     return torch.Generator(device="cpu").manual_seed(seed)
 

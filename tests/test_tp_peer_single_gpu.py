@@ -236,3 +236,44 @@ def test_two_phase_allreduce_reduces_its_slice_in_place_and_gathers_by_rank(mx, 
             _stream(device)) == 1
     finally:
         blocks.free()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_reduce_with_the_reference_argument_list_sums_caller_owned_buffers(mx, world):
+    """``moe_reduce_tp2_out(..., signal_ptrs, buffer_ptrs, rank)`` as the reference's caller
+    makes it (python/mxfp6/ops.py:950-1025): one signal area and one data buffer per rank.
+    Rank 0 runs; the other ranks' partials and flags are in place beforehand."""
+    device = torch.device("cuda", 0)
+    tokens, hidden, topk = 6, 2048, 8
+    gen = torch.Generator(device=device).manual_seed(1300 + world)
+    routed = torch.randn((tokens * topk, hidden), generator=gen, device=device).to(torch.bfloat16)
+    shared = torch.randn((tokens, hidden), generator=gen, device=device).to(torch.bfloat16)
+    gate = torch.randn((tokens,), generator=gen, device=device).to(torch.bfloat16)
+    weights = torch.rand((tokens, topk), generator=gen, device=device)
+    inverse = torch.randperm(tokens * topk, generator=gen, device=device).to(torch.int32)
+    signals = torch.zeros((world, 16), dtype=torch.int32, device=device)
+    buffers = [torch.randn((tokens, hidden), generator=gen, device=device).to(torch.bfloat16)
+               for _ in range(world)]
+    signals[0, 1:world] = FAR_STEP   # rank 0 finds every peer far ahead of any step it reaches
+    mine = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=device)
+    mx.moe_reduce_out(mine, routed, weights, inverse, shared, gate)
+    want = _rank_order_sum([mine] + buffers[1:])
+
+    out = torch.zeros((tokens, hidden), dtype=torch.bfloat16, device=device)
+    for call in range(2):   # the single buffer is reused: the closing handshake allows it
+        mx.moe_reduce_tp2_out(out, routed, weights, inverse, shared, gate,
+                              [signals[r].data_ptr() for r in range(world)],
+                              [b.data_ptr() for b in buffers], 0)
+        torch.cuda.synchronize()
+        assert mx.device_status(device) == 0
+        assert torch.equal(out, want)
+        assert torch.equal(buffers[0], mine)              # the partial went into rank 0's buffer
+        state = signals[0, 8:11].cpu().tolist()           # done_step, finished, last_buffer
+        assert state == [2 * (call + 1), 0, 2]
+    with pytest.raises(ValueError):
+        mx.moe_reduce_tp2_out(out, routed, weights, inverse, shared, gate,
+                              [signals[0].data_ptr()], [b.data_ptr() for b in buffers], 0)
+    with pytest.raises(ValueError):
+        mx.moe_reduce_tp2_out(out, routed, weights, inverse, shared, gate,
+                              [signals[r].data_ptr() for r in range(world)],
+                              [b.data_ptr() for b in buffers], world)

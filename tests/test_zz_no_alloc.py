@@ -79,6 +79,24 @@ def test_static_scratch_gemm_matches_regular_entry_point(mx):
     free_after, _ = torch.cuda.mem_get_info()
     assert free_after == free_before
     assert torch.equal(got, want) and torch.equal(got2, want2)
+    # and it captures: both shape classes have run eagerly above, so nothing is set up lazily
+    side = torch.cuda.Stream()
+    got.fill_(float("nan"))
+    got2.fill_(float("nan"))
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            stream = torch.cuda.current_stream().cuda_stream
+            assert getattr(lib, "mxfp6_gemm_w6a8_static_scratch")(
+                act.values.data_ptr(), act.scales.data_ptr(), wgt.values.data_ptr(), wgt.scales.data_ptr(),
+                act.rows, wgt.rows, act.k, ctypes.c_float(1.0), got.data_ptr(), 1, stream) == 0
+            assert getattr(lib, "mxfp6_gemm_w6a8_static_scratch")(
+                act2.values.data_ptr(), act2.scales.data_ptr(), wgt2.values.data_ptr(), wgt2.scales.data_ptr(),
+                act2.rows, wgt2.rows, act2.k, ctypes.c_float(1.0), got2.data_ptr(), 1, stream) == 0
+        for _ in range(5):
+            graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(got, want) and torch.equal(got2, want2)
     assert mx.device_status() == 0
 
 
