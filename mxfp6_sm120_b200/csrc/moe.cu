@@ -541,7 +541,10 @@ silu_mul_quant_kernel(const T* __restrict__ input, uint8_t* __restrict__ output,
                      (reinterpret_cast<uintptr_t>(packed) & 3) == 0;
   const int warps = static_cast<int>(gridDim.x) * (blockDim.x >> 5);
   const int first = static_cast<int>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  for (int64_t row = first; row < rows; row += warps) {
+  // A grouped buffer is sized for the worst case; only the rows the offsets cover are live
+  // (an expert-parallel rank holds about 1 / world of the routes its buffer could take).
+  const int64_t live = grouped ? min((int64_t)row_begin[experts], rows) : rows;
+  for (int64_t row = first; row < live; row += warps) {
     int64_t srow = row;
     if (grouped) {
       int lo = 0, hi = experts;  // largest e with row_begin[e] <= row

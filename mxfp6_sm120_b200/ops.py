@@ -10,6 +10,7 @@ fallback: a missing library raises ``ImportError`` and a non-sm_100 GPU raises
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 
 import torch
@@ -31,6 +32,12 @@ TUNED_NK = frozenset(
 TUNED_M = frozenset((1, 2, 4, 8, 16, 24, 32, 64, 96, 512, 1024, 2048, 4096, 8192))
 
 _DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1}
+
+
+# MXFP6_AUTOTUNE=on / cache_only makes gemm() tune (or look up) a shape on its first use; read
+# once at import so that the hot path pays one global load.
+_AUTOTUNE_ON_FIRST_USE = os.environ.get("MXFP6_AUTOTUNE", "off").strip().lower() not in (
+    "", "0", "false", "no", "off")
 
 
 def _stream(device: torch.device) -> int:
@@ -913,9 +920,36 @@ def warmup_w6a8(
     torch.cuda.synchronize(b.device)
 
 
-def autotune_w6a8(*args, **kwargs):
-    """Candidate search is replaced by a static per-M table; returns ``None``."""
-    return None
+def autotune_w6a8(
+    a: torch.Tensor | MXFP8Tensor,
+    b: PackedMXFP6Tensor,
+    *,
+    out_dtype: torch.dtype = torch.float16,
+    force: bool = False,
+):
+    """Pick, install and cache the fastest explicit configuration for this problem before
+    graph capture (see :mod:`.autotune`).  Shapes of the measured table keep the default
+    plan unless ``force=True`` or ``MXFP6_AUTOTUNE_EXACT`` is set; returns the installed
+    ``W6A8Config`` or ``None``."""
+    from . import autotune
+
+    out_dtype = _validate_output_dtype(out_dtype)
+    if not isinstance(b, PackedMXFP6Tensor):
+        raise TypeError("b must be a PackedMXFP6Tensor instance")
+    if isinstance(a, torch.Tensor):
+        _validate_float_activation(a)
+        a = quantize_mxfp8(a)
+    elif not isinstance(a, MXFP8Tensor):
+        raise TypeError("a must be an FP16/BF16 Tensor or MXFP8Tensor")
+    if a.k != b.k or a.device != b.device:
+        raise ValueError("a and b must have matching K and CUDA device")
+    _validate_problem(a.rows, b.rows, a.k)
+    _require_sm100(a.device)
+    load_library()
+    if (not force and is_tuned_shape(a.rows, b.rows, a.k) and not autotune.should_tune_exact_shapes()
+            and not autotune.is_autotune_cache_only()):
+        return None
+    return autotune.ensure_w6a8_tuned(a, b, out_dtype=out_dtype, force=force)
 
 
 def gemm(
@@ -935,6 +969,8 @@ def gemm(
     if isinstance(a, torch.Tensor):
         if not isinstance(b, PackedMXFP6Tensor):
             raise TypeError("FP16/BF16 activation input requires a PackedMXFP6Tensor weight")
+        if _AUTOTUNE_ON_FIRST_USE:
+            autotune_w6a8(a, b, out_dtype=out_dtype)  # no-op once the shape has a decision
         return gemm_from_float(a, b, alpha, out_dtype=out_dtype)
     if isinstance(a, MXFP8Tensor):
         if not isinstance(b, PackedMXFP6Tensor):

@@ -275,7 +275,7 @@ def named_layer(mx):
     torch.cuda.empty_cache()
 
 
-@pytest.mark.parametrize("tokens", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("tokens", [1, 2, 3, 4, 8, 16, 24, 32])
 def test_decode_schedule_named_config_against_oracle_and_graph(mx, named_layer, tokens):
     """Hidden 2048, 256 experts + shared, top-8, intermediate 512: three launches per layer."""
     shape, (w1, w2, sw1, sw2) = named_layer
@@ -304,6 +304,8 @@ def test_decode_schedule_named_config_against_oracle_and_graph(mx, named_layer, 
 
     layer = MoeLayer(shape, w1, w2, sw1, sw2)
     state = layer.workspace(tokens)
+    assert state.decode is not None      # the layer object takes this schedule for these batches
+    assert torch.equal(layer.forward(state, hidden_d, logits_d, gate_d), out)
     grouped = layer.forward_grouped(state, hidden_d, logits_d, gate_d)
     assert _rel_fro(out, grouped) <= 5e-3
 
