@@ -103,6 +103,7 @@ from .qwen35 import (
 )
 
 from .checkpoint import MoeLayerCheckpoint, TensorSource, load_linear, load_moe_layer
+from .adapter import MxFp6LinearKernel, MxFp6MoERunner
 from . import torch_ops  # registers torch.ops.mxfp6.* (the reference's dispatcher names)
 
 from .decoder import (

@@ -123,7 +123,8 @@ class MoeLayer:
             renormalize=True)
 
     def forward_grouped(self, state: MoeLayerState, hidden: torch.Tensor, router_logits: torch.Tensor,
-                        shared_gate: torch.Tensor | None, with_shared: bool = True) -> torch.Tensor:
+                        shared_gate: torch.Tensor | None, with_shared: bool = True,
+                        renormalize: bool = True) -> torch.Tensor:
         """The grouped schedule.  The shared expert runs on a side
         stream between the quantization and the final reduce (the reference's
         benchmark overlaps it the same way); under capture both branches land in
@@ -134,7 +135,7 @@ class MoeLayer:
             ws.quantized, ws.input_scales, ws.packed_input_scales, ws.topk_weights, ws.topk_ids,
             ws.permuted, ws.grouped_input_scales, ws.expert_cursors, ws.expert_offsets,
             ws.scale_offsets, ws.inverse_permutation, hidden, router_logits,
-            source_tokens=ws.source_tokens, renormalize=True, expert_map=self.expert_map)
+            source_tokens=ws.source_tokens, renormalize=renormalize, expert_map=self.expert_map)
         shared_out = None
         overlap = with_shared and state.side_stream is not None
         if overlap:
