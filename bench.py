@@ -569,6 +569,10 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--row-sum", default="auto", choices=["auto", "nccl", "peer"],
+                        help="N > 1: sum of the prefill-sized row-parallel outputs through NCCL or "
+                             "through this library's two-phase peer-memory kernels (auto: peer from "
+                             "4 GPUs on)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--no-moe", action="store_true")
@@ -607,8 +611,12 @@ def main() -> None:
             for key in acts}
     # M-major.  Sharded, the two row-parallel projections of a batch size go first, so
     # that their sums run beside the three column-parallel GEMMs that follow.
-    shapes = NK_SHAPES if world == 1 else (
-        [s for s in NK_SHAPES if s in ROW_PARALLEL] + [s for s in NK_SHAPES if s not in ROW_PARALLEL])
+    # (row, column, row, column, column: every sum has a GEMM to run beside.)
+    shapes = NK_SHAPES
+    if world > 1:
+        rows_first = [s for s in NK_SHAPES if s in ROW_PARALLEL]
+        columns = [s for s in NK_SHAPES if s not in ROW_PARALLEL]
+        shapes = [rows_first[0], columns[0], rows_first[1]] + columns[1:]
     # Sharded, the large batches also go first: their sums are the long pole (two times 84 MB
     # at 8192 rows) and then run beside everything that follows instead of after it.
     m_order = M_VALUES if world == 1 else sorted(M_VALUES, reverse=True)
@@ -638,7 +646,7 @@ def main() -> None:
         mx.gemm_from_float(acts[key], weight, out_dtype=torch.bfloat16, out=partial)
         return peer.allreduce(outs[key])
 
-    sweep_peer = None
+    sweep_peer = big_peer = None
     if world > 1:
         from mxfp6_sm120_b200 import tp
         from mxfp6_sm120_b200.tp_fused import SymmetricBlocks
@@ -646,14 +654,42 @@ def main() -> None:
         try:  # raises on every rank alike when any rank could not map a peer's block
             sweep_peer = SymmetricBlocks(tp.PEER_ALLREDUCE_MAX_ROWS, max(n for n, _ in ROW_PARALLEL),
                                          device)
+            if args.row_sum == "peer" or (args.row_sum == "auto" and world >= 4):
+                big_peer = SymmetricBlocks(max(M_VALUES), max(n for n, _ in ROW_PARALLEL), device)
         except RuntimeError:
-            sweep_peer = None
+            sweep_peer = big_peer = None
+    last_sum = [None]
+
+    def run_shape_peer_big(key):
+        """Row-parallel shape with a prefill-sized output: partial into the large symmetric
+        block, then the two-phase peer-memory sum (every rank sums its slice of rows in place,
+        all gather the slices) on the side stream.  A partial buffer is written again two sums
+        later; the GEMM that does so waits for the sum in between, whose handshake shows that
+        every peer has finished reading that buffer."""
+        weight, _ = layers[key[1:]]
+        current = torch.cuda.current_stream(device)
+        if last_sum[0] is not None:
+            current.wait_event(last_sum[0])
+        partial = big_peer.next_partial(key[0], weight.rows)
+        mx.gemm_from_float(acts[key], weight, out_dtype=torch.bfloat16, out=partial)
+        computed = torch.cuda.Event()
+        computed.record(current)
+        reduce_stream.wait_event(computed)
+        with torch.cuda.stream(reduce_stream):
+            big_peer.allreduce_any(outs[key])
+            done = torch.cuda.Event()
+            done.record(reduce_stream)
+        last_sum[0] = done
+        return outs[key]
 
     def run_sweep():
+        last_sum[0] = None
         for key in order:
             weight, mode = layers[key[1:]]
             if sweep_peer is not None and mode == "row" and key[0] <= tp.PEER_ALLREDUCE_MAX_ROWS:
                 run_shape_peer(key, sweep_peer)
+            elif big_peer is not None and mode == "row" and key[0] % world == 0:
+                run_shape_peer_big(key)
             else:
                 run_shape(key)
         if reduce_stream is not None:
@@ -728,6 +764,8 @@ def main() -> None:
                     if sweep_peer is not None and key[0] <= tp.PEER_ALLREDUCE_MAX_ROWS:
                         sweep_peer.next_partial(key[0], layers[key[1:]][0].rows)
                         sweep_peer.allreduce(outs[key])
+                    elif big_peer is not None and key[0] % world == 0:
+                        big_peer.allreduce_any(outs[key])
                     else:
                         dist.all_reduce(outs[key])
 
@@ -869,8 +907,10 @@ def main() -> None:
         "config": {"workload": WORKLOAD, "shapes": NK_SHAPES, "m_values": M_VALUES,
                    "parallelism": "single GPU" if world == 1 else
                    f"tp{world}: K=5120 projections column-parallel, 5120x6144 and 5120x17408 "
-                   "row-parallel + all-reduce (one peer-memory kernel up to 256 rows; NCCL above, "
-                   "on a side stream beside the following shapes' GEMMs)",
+                   "row-parallel + all-reduce (one peer-memory kernel up to 256 rows; above, "
+                   + ("two-phase peer-memory kernels" if big_peer is not None else "NCCL")
+                   + " on a side stream beside the following shapes' GEMMs)",
+                   "row_sum": "peer" if big_peer is not None else "nccl",
                    "l2": "inputs larger than L2: shapes run M-major, 270 MB of packed weights "
                          "cycle through the 126 MB L2 between reuses",
                    "graph": "one CUDA graph per step"},

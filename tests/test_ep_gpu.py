@@ -43,6 +43,7 @@ def _worker(rank: int, world: int, port: int, results) -> None:
     # single-GPU result over all tokens
     state = layer.workspace(world * local_tokens)
     want = layer.forward(state, hidden, logits, gate).clone()
+    want_ids = (state.decode if state.decode is not None else state.workspace).topk_ids
     # expert parallel over the ranks
     mine = slice(rank * local_tokens, (rank + 1) * local_tokens)
     moe = ExpertParallelMoe(layer)
@@ -50,7 +51,7 @@ def _worker(rank: int, world: int, port: int, results) -> None:
     got = moe.forward(ep_state, hidden[mine].contiguous(), logits[mine].contiguous(), gate[mine].contiguous())
     torch.cuda.synchronize()
     cos = torch.nn.functional.cosine_similarity(got.float().flatten(), want[mine].float().flatten(), dim=0)
-    same_ids = torch.equal(ep_state.local.topk_ids, state.workspace.topk_ids[mine])
+    same_ids = torch.equal(ep_state.local.topk_ids, want_ids[mine])
     # the same layer with both exchanges over peer memory (one kernel each), eager and replayed
     from mxfp6_sm120_b200.tp_fused import SymmetricBlocks
 
@@ -72,7 +73,7 @@ def _worker(rank: int, world: int, port: int, results) -> None:
         stream.synchronize()
     replay_equal = bool(torch.equal(state_p.output, got_p))
     cos_p = torch.nn.functional.cosine_similarity(got_p.float().flatten(), want[mine].float().flatten(), dim=0)
-    same_ids_p = torch.equal(state_p.local.topk_ids, state.workspace.topk_ids[mine])
+    same_ids_p = torch.equal(state_p.local.topk_ids, want_ids[mine])
     results[rank] = (bool(same_ids and same_ids_p), float(min(cos, cos_p)), mx.device_status(),
                      replay_equal)
     dist.barrier()
