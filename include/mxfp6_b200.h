@@ -366,6 +366,33 @@ int mxfp6_array_gemm_w6a8_reduce(void* output_dev, int out_dtype, const uint8_t*
                                  const void* shared_gate_dev, int gate_dtype, int gate_stride,
                                  const void* shared_output_dev, int compute_shared, int64_t tokens,
                                  int topk, int64_t n, int64_t k, int routing_ready, void* stream);
+/* The decode schedule of python/mxfp6/qwen35.py:384-432 from given router logits, in two
+ * launches: W1 over the routes (top-k + shared expert per token) with the softmax top-k and
+ * the MXFP8 quantization of the hidden rows done inside every CTA (the arithmetic of
+ * mxfp6_moe_topk_quant), then W2 with the weighted reduce and the gated shared row.  hidden
+ * [tokens, hidden_size] and router_logits [tokens, logit_experts] are BF16; w1 is
+ * [experts, 2 * inter, 3 * hidden_size / 4], w2 [experts, hidden_size, 3 * inter / 4], the last
+ * matrix of both the shared expert unless the four shared_* pointers bring it; activation
+ * [tokens * (topk + 1), inter] + activation_scales [.., inter / 32] are scratch; topk_ids /
+ * topk_weights receive the selection; output [tokens, hidden_size].  _supported returns 1 when
+ * the shapes fit (topk <= 8, inter <= 2048, at most 16 blocks of 128 hidden values per CTA of
+ * the W1 launch); otherwise use the three entry points above.  _preferred returns 1 when this
+ * form is also expected to be the faster one (the front kernel it saves against the top-k every
+ * CTA of the second launch repeats; host arithmetic over the two grids). */
+int mxfp6_moe_decode_layer_supported(int64_t tokens, int topk, int logit_experts,
+                                     int64_t hidden_size, int64_t inter);
+int mxfp6_moe_decode_layer_preferred(int64_t tokens, int topk, int logit_experts,
+                                     int64_t hidden_size, int64_t inter);
+int mxfp6_moe_decode_layer(void* output_dev, int out_dtype, const void* hidden_dev,
+                           const void* router_logits_dev, const void* shared_gate_dev,
+                           int gate_dtype, int gate_stride, const uint8_t* w1_dev,
+                           const uint8_t* w1_scales_dev, const uint8_t* w2_dev,
+                           const uint8_t* w2_scales_dev, int experts, const uint8_t* shared_w1_dev,
+                           const uint8_t* shared_w1_scales_dev, const uint8_t* shared_w2_dev,
+                           const uint8_t* shared_w2_scales_dev, uint8_t* activation_dev,
+                           uint8_t* activation_scales_dev, int32_t* topk_ids_dev,
+                           float* topk_weights_dev, int64_t tokens, int topk, int logit_experts,
+                           int renormalize, int64_t hidden_size, int64_t inter, void* stream);
 /* torch.ops.mxfp6.moe_reduce_array_out (schema csrc/moe.cu:10129-10131, kernel :8237-8282):
  * combined [tokens * (topk + 1), hidden], the shared row last of each token. */
 int mxfp6_moe_reduce_array(void* output_dev, const void* combined_dev, int dtype,

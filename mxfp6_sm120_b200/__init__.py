@@ -70,6 +70,9 @@ from .moe_ops import (
     grouped_gemm_w6a8,
     grouped_gemm_w6a8_out,
     grouped_scale_rows,
+    moe_decode_layer_out,
+    moe_decode_layer_preferred,
+    moe_decode_layer_supported,
     moe_reduce_array_out,
     moe_reduce_out,
     moe_reduce_tp2_out,

@@ -130,6 +130,14 @@ SIGNATURES: dict[str, tuple] = {
          c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int64, c_int,
          c_int64, c_int64, c_int, c_void_p],
     ),
+    "mxfp6_moe_decode_layer_supported": (c_int, [c_int64, c_int, c_int, c_int64, c_int64]),
+    "mxfp6_moe_decode_layer_preferred": (c_int, [c_int64, c_int, c_int, c_int64, c_int64]),
+    "mxfp6_moe_decode_layer": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_int64, c_int, c_int, c_int, c_int64, c_int64, c_void_p],
+    ),
     "mxfp6_moe_reduce_tp_pointers": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int,

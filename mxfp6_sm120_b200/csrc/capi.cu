@@ -81,7 +81,13 @@ int moe_route_gemm(void*, uint8_t*, int, int, const uint8_t*, const uint8_t*, in
 int moe_route_w2_reduce(void*, int, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*,
                         int, const uint8_t*, const uint8_t*, const void*, int, const float*,
                         const void*, int, int, const void*, int, int64_t, int, int64_t, int64_t,
-                        int, cudaStream_t);
+                        int, const void*, int, int, cudaStream_t);
+int moe_decode_layer_supported(int64_t, int, int, int64_t, int64_t);
+int moe_decode_layer_preferred(int64_t, int, int, int64_t, int64_t);
+int moe_decode_layer(void*, int, const void*, const void*, const void*, int, int, const uint8_t*,
+                     const uint8_t*, const uint8_t*, const uint8_t*, int, const uint8_t*,
+                     const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, uint8_t*, int32_t*,
+                     float*, int64_t, int, int, int, int64_t, int64_t, cudaStream_t);
 int moe_reduce_array(void*, const void*, int, const float*, const void*, int, int, int64_t, int,
                      int64_t, cudaStream_t);
 int moe_router_logits(const void*, const void*, const void*, void*, void*, int64_t, int64_t, int,
@@ -760,8 +766,34 @@ int mxfp6_array_gemm_w6a8_reduce(void* output, int out_dtype, const uint8_t* act
   return moe_route_w2_reduce(output, out_dtype, activation, logical_scales, weight, weight_scales,
                              experts, shared_weight, shared_weight_scales, topk_ids, ids_are_int64,
                              topk_weights, shared_gate, gate_dtype, gate_stride, shared_output,
-                             compute_shared, tokens, topk, n, k, routing_ready,
+                             compute_shared, tokens, topk, n, k, routing_ready, nullptr, 0, 0,
                              static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_moe_decode_layer_supported(int64_t tokens, int topk, int logit_experts,
+                                     int64_t hidden_size, int64_t inter) {
+  return moe_decode_layer_supported(tokens, topk, logit_experts, hidden_size, inter);
+}
+
+int mxfp6_moe_decode_layer_preferred(int64_t tokens, int topk, int logit_experts,
+                                     int64_t hidden_size, int64_t inter) {
+  return moe_decode_layer_preferred(tokens, topk, logit_experts, hidden_size, inter);
+}
+
+int mxfp6_moe_decode_layer(void* output, int out_dtype, const void* hidden, const void* router_logits,
+                           const void* shared_gate, int gate_dtype, int gate_stride,
+                           const uint8_t* w1, const uint8_t* w1_scales, const uint8_t* w2,
+                           const uint8_t* w2_scales, int experts, const uint8_t* shared_w1,
+                           const uint8_t* shared_w1_scales, const uint8_t* shared_w2,
+                           const uint8_t* shared_w2_scales, uint8_t* activation,
+                           uint8_t* activation_scales, int32_t* topk_ids, float* topk_weights,
+                           int64_t tokens, int topk, int logit_experts, int renormalize,
+                           int64_t hidden_size, int64_t inter, void* stream) {
+  return moe_decode_layer(output, out_dtype, hidden, router_logits, shared_gate, gate_dtype,
+                          gate_stride, w1, w1_scales, w2, w2_scales, experts, shared_w1,
+                          shared_w1_scales, shared_w2, shared_w2_scales, activation,
+                          activation_scales, topk_ids, topk_weights, tokens, topk, logit_experts,
+                          renormalize, hidden_size, inter, static_cast<cudaStream_t>(stream));
 }
 
 int mxfp6_moe_reduce_array(void* output, const void* combined, int dtype, const float* topk_weights,

@@ -17,6 +17,8 @@
 // The launch shapes are new and generic in hidden size, expert count and k.
 #include "common.cuh"
 
+#include "topk.cuh"
+
 #include <cuda_fp8.h>
 
 namespace mx {
@@ -31,102 +33,17 @@ __device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
   return lo | (hi << 16);
 }
 
-// FP32 softmax of one token's BF16 logits and k rounds of arg-max (ties to the
-// smaller id), by one full warp; lane l owns experts l, l + 32, ...
-template <int kPerLane>
-__device__ __forceinline__ void warp_softmax_topk_n(const __nv_bfloat16* __restrict__ logits_row,
-                                                    int experts, int topk, int renormalize,
-                                                    float* __restrict__ weights_row,
-                                                    int32_t* __restrict__ ids_row, int lane) {
-  float p[kPerLane];
-  float vmax = -INFINITY;
-  const int per_lane = (experts + 31) / 32;
-#pragma unroll
-  for (int i = 0; i < kPerLane; ++i) {
-    p[i] = -INFINITY;
-    const int e = lane + 32 * i;
-    if (i < per_lane && e < experts) {
-      p[i] = __bfloat162float(logits_row[e]);
-      vmax = fmaxf(vmax, p[i]);
-    }
-  }
-#pragma unroll
-  for (int d = 16; d > 0; d >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, d));
-  float sum = 0.0f;
-#pragma unroll
-  for (int i = 0; i < kPerLane; ++i) {
-    const int e = lane + 32 * i;
-    if (i < per_lane && e < experts) {
-      p[i] = expf(p[i] - vmax);
-      sum += p[i];
-    } else {
-      p[i] = -1.0f;  // never selected
-    }
-  }
-#pragma unroll
-  for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
-  const float inv_sum = 1.0f / sum;
-#pragma unroll
-  for (int i = 0; i < kPerLane; ++i) {
-    if (p[i] >= 0.0f) {
-      float q = p[i] * inv_sum;
-      if (!isfinite(q)) q = 0.0f;
-      p[i] = q;
-    }
-  }
-  float weight_sum = 0.0f;
-  float my_weight = 0.0f;  // lane r keeps the r-th selected weight
-  int my_id = 0;
-  for (int r = 0; r < topk; ++r) {
-    float best = -2.0f;
-    int best_id = 0x7fffffff;
-#pragma unroll
-    for (int i = 0; i < kPerLane; ++i) {
-      const int e = lane + 32 * i;
-      if (p[i] > best) {  // ascending ids inside a lane: first maximum is the smallest id
-        best = p[i];
-        best_id = e;
-      }
-    }
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, d);
-      const int oi = __shfl_xor_sync(0xffffffffu, best_id, d);
-      if (ov > best || (ov == best && oi < best_id)) {
-        best = ov;
-        best_id = oi;
-      }
-    }
-    if (lane == (best_id & 31)) {
-#pragma unroll
-      for (int i = 0; i < kPerLane; ++i) {
-        if (lane + 32 * i == best_id) p[i] = -10000.0f;
-      }
-    }
-    if (lane == r) {
-      my_weight = best;
-      my_id = best_id;
-    }
-    weight_sum += best;
-  }
-  if (lane < topk) {
-    float w = my_weight;
-    if (renormalize) w = weight_sum > 0.0f ? w / weight_sum : 0.0f;
-    weights_row[lane] = w;
-    ids_row[lane] = my_id;
-  }
-}
-
-// Up to 256 experts need 8 values per lane; the general case 32.
+// Softmax top-k of one token by one warp (topk.cuh), written to the token's rows.
 __device__ __forceinline__ void warp_softmax_topk(const __nv_bfloat16* __restrict__ logits_row,
                                                   int experts, int topk, int renormalize,
                                                   float* __restrict__ weights_row,
                                                   int32_t* __restrict__ ids_row, int lane) {
-  if (experts <= 256) {
-    warp_softmax_topk_n<8>(logits_row, experts, topk, renormalize, weights_row, ids_row, lane);
-  } else {
-    warp_softmax_topk_n<kMaxExperts / 32>(logits_row, experts, topk, renormalize, weights_row,
-                                          ids_row, lane);
+  float weight;
+  int id;
+  warp_softmax_topk_any(logits_row, experts, topk, renormalize, lane, &weight, &id);
+  if (lane < topk) {
+    weights_row[lane] = weight;
+    ids_row[lane] = id;
   }
 }
 
@@ -423,8 +340,14 @@ topk_quant_route_small_kernel(const __nv_bfloat16* __restrict__ hidden,
   }
   // ---- top-k: one warp per token
   for (int token = warp; token < tokens; token += kFusedThreads / 32) {
-    warp_softmax_topk(logits + (int64_t)token * experts, experts, topk, renormalize,
-                      topk_weights + (int64_t)token * topk, topk_ids + (int64_t)token * topk, lane);
+    float weight;
+    int id;
+    warp_softmax_topk_regs<8>(logits + (int64_t)token * experts, experts, topk, renormalize, lane,
+                              &weight, &id);
+    if (lane < topk) {
+      topk_weights[(int64_t)token * topk + lane] = weight;
+      topk_ids[(int64_t)token * topk + lane] = id;
+    }
   }
   __syncthreads();  // rows, scales and ids written by this CTA are visible to all its threads
   // ---- histogram of local experts
@@ -761,7 +684,8 @@ int moe_topk_quant_route(const void* hidden, const void* logits, int64_t tokens,
                          cudaStream_t stream) {
   MX_REQUIRE(tokens > 0 && topk > 0, "tokens and topk must be positive");
   // One CTA copies every routed row, so the fusion only pays for a handful of tokens.
-  const bool small = tokens * topk <= kFusedMaxRoutes && tokens <= 8;
+  // (the single-CTA kernel keeps eight logits per lane in registers: up to 256 experts)
+  const bool small = tokens * topk <= kFusedMaxRoutes && tokens <= 8 && experts <= 256;
   if (!small) {
     if (int rc = moe_topk_quant(hidden, logits, tokens, hidden_size, experts, topk, renormalize,
                                 quantized, logical_scales, dense_scales, topk_weights, topk_ids,

@@ -33,6 +33,7 @@
 // the scale rows of tokens that do not exist.
 #include "gemm.cuh"
 #include "ptx.cuh"
+#include "topk.cuh"
 #include "wait.cuh"
 
 #include <cuda.h>
@@ -94,6 +95,13 @@ struct RouteArgs {
   int cluster;          // CTAs per cluster (K split, or lane split in the reduce kernel)
   int out_dtype;
   int routing_ready;    // reduce kernel: ids were complete before the preceding kernel's dependents started
+  // front kernel / reduce kernel with the routing done inside the CTA
+  const void* hidden;      // BF16 [tokens, K]: quantized by the front kernel itself
+  const void* logits;      // BF16 [tokens, logit_experts]: softmax top-k per CTA
+  int32_t* ids_out;        // front kernel: [tokens, topk], written once per token
+  float* weights_out;      // front kernel: [tokens, topk]
+  int logit_experts;
+  int renormalize;
 };
 
 __device__ __forceinline__ int read_expert(const RouteArgs& a, int token, int lane) {
@@ -428,8 +436,10 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
   float* red = reinterpret_cast<float*>(sfb + C::kSfbBytes);
   uint8_t* fixed = reinterpret_cast<uint8_t*>(red) + C::kRedBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(fixed);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fixed + 8 * (2 * C::kStages + 3));
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fixed + 8 * (2 * C::kStages + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* own_ids = reinterpret_cast<volatile int*>(tmem_slot + 4);        // [16]
+  volatile float* own_weights = reinterpret_cast<volatile float*>(tmem_slot + 20);  // [16]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -438,6 +448,11 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
   const uint32_t tfull = empty0 + 8 * C::kStages;
   const uint32_t sfb_bar = tfull + 8;
   const uint32_t red_full = sfb_bar + 8;
+  const uint32_t ids_bar = red_full + 8;
+  // With the logits given, every CTA selects the experts of its token itself (one warp, before
+  // the dependency wait: the logits are older than the kernel in front) instead of reading
+  // the ids and weights another kernel wrote.
+  const bool own_routing = args.logits != nullptr;
 
   const int cr = args.cluster;
   const int rank = cr > 1 ? (int)ptx::cluster_ctarank() : 0;
@@ -461,6 +476,7 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
     ptx::mbar_init(tfull, 1);
     ptx::mbar_init(sfb_bar, 1);
     ptx::mbar_init(red_full, 1);
+    ptx::mbar_init(ids_bar, 1);
     if (cr > 1 && rank == 0) {
       // terms of the other ranks' lanes: 128 bytes per lane and epilogue warp
       ptx::mbar_arrive_expect_tx(red_full, (uint32_t)(args.lanes - args.lanes / cr) * 4u * 128u);
@@ -482,6 +498,11 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
 
   // Every warp needs the experts of this CTA's lanes: each reads them for itself (a few words).
   auto lane_of = [&](int p) { return shared_first != 0 ? (p == 0 ? args.lanes - 1 : p - 1) : p; };
+  auto expert_of = [&](int l) -> int {
+    if (!own_routing) return read_expert(args, token, l);
+    if (l >= args.topk) return args.separate_shared != 0 ? -2 : args.num_experts - 1;
+    return own_ids[l];
+  };
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -499,9 +520,13 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
                      wsc + ((int64_t)(w_row / kAtomRows) * kbn + kb) * kAtomBytes, kAtomBytes, bar);
     };
     int ahead = 0;  // blocks whose weights are already on their way
-    if (args.routing_ready != 0) {
+    bool routed = true;
+    if (own_routing) {
+      routed = __all_sync(0xffffffffu, bounded_wait(ids_bar, 0u, abort_flag, args.status, 137));
+    }
+    if (routed && (args.routing_ready != 0 || own_routing)) {
       for (int p = p0; p < p1 && ahead < C::kStages; ++p) {
-        const int expert = read_expert(args, token, lane_of(p));
+        const int expert = expert_of(lane_of(p));
         if (expert == -1) continue;
         for (int kb = 0; kb < kbn && ahead < C::kStages; ++kb) {
           if (ptx::elect_one()) load_weights(ahead, expert, kb);
@@ -514,10 +539,10 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
     int stage = 0;
     uint32_t phase = 0;
     int block = 0;
-    bool ok = true;
+    bool ok = routed;
     for (int p = p0; ok && p < p1; ++p) {
       const int l = lane_of(p);
-      const int expert = read_expert(args, token, l);
+      const int expert = expert_of(l);
       if (expert == -1) continue;
       const int src_row = token * args.lanes + l;
       for (int kb = 0; ok && kb < kbn; ++kb, ++block) {
@@ -549,7 +574,7 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
     bool ok = __all_sync(0xffffffffu, bounded_wait(sfb_bar, 0u, abort_flag, args.status, 132));
     for (int p = p0; ok && p < p1; ++p) {
       const int l = lane_of(p);
-      if (read_expert(args, token, l) == -1) continue;
+      if (!own_routing && read_expert(args, token, l) == -1) continue;
       const uint32_t d_t = tmem_base + (p - p0) * kRows;
       for (int kb = 0; ok && kb < kbn; ++kb) {
         ok = __all_sync(0xffffffffu,
@@ -588,6 +613,19 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
     const int quarter = warp & 3;
+    if (own_routing && warp == 2) {
+      float weight;
+      int id;
+      warp_softmax_topk_any(static_cast<const __nv_bfloat16*>(args.logits) +
+                                (int64_t)token * args.logit_experts,
+                            args.logit_experts, args.topk, args.renormalize, lane, &weight, &id);
+      if (lane < args.topk) {
+        own_ids[lane] = id;
+        own_weights[lane] = weight;
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(ids_bar);
+    }
     ptx::grid_dependency_wait();
     if (warp == 2) {
       // activation scale words of this CTA's lanes: lane position q, block kb -> word at
@@ -608,14 +646,16 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
     // while the tensor cores work.
     float weight_of[kMaxLanes];
     bool live_lane[kMaxLanes];
+    if (own_routing) bounded_wait(ids_bar, 0u, abort_flag, args.status, 138);
 #pragma unroll
     for (int q = 0; q < kMaxLanes; ++q) {
       weight_of[q] = 0.0f;
       live_lane[q] = false;
       if (p0 + q < p1) {
         const int l = lane_of(p0 + q);
-        live_lane[q] = read_expert(args, token, l) != -1;
+        live_lane[q] = expert_of(l) != -1;
         weight_of[q] = l >= args.topk ? gate_of(args, token)
+                       : own_routing  ? own_weights[l]
                                       : args.topk_weights[(int64_t)token * args.topk + l];
       }
     }
@@ -686,6 +726,325 @@ route_w2_reduce_kernel(const __grid_constant__ CUtensorMap tm_w,
   ptx::tc_fence_before();
   __syncthreads();
   if (cr > 1) {
+    if (!cluster_arrived) ptx::cluster_arrive_relaxed();
+    ptx::cluster_wait();
+  }
+  if (*abort_flag != 0) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+
+// ------------------------------------------------------------------------------------
+// W1 of the decode schedule with its front end inside: every CTA selects the experts of its
+// token itself (softmax top-k of the token's logits by one warp) and quantizes its K slice of
+// the token's BF16 row straight into the MMA's shared-memory operand, so the layer needs no
+// top-k / quantization kernel in front and this kernel depends on nothing but the layer's
+// inputs.  One (route, 128-feature tile) per cluster, K split over the cluster, SwiGLU + MXFP8
+// epilogue as route_gemm_kernel<swiglu>; the bytes equal those of topk_quant_kernel followed
+// by that kernel (same top-k code, same quantizer arithmetic).
+//
+// The route's activation: 128 codes per K block at the start of a 1 KB slot (row 0 of a
+// 128-byte-swizzled 8-row atom; rows 1..7 and the second atom, which is the next block's slot,
+// are never-read padding of the N = 16 operand).  The ring holds ONE weight tile per stage
+// (gate and up tiles of a K block alternate), which leaves room for 17 such slots.
+struct FCfg {
+  static constexpr int kMaxBlocks = 16;                                  // K blocks per CTA
+  static constexpr uint32_t kStageBytes = kWTileBytes + kAtomBytes;       // one weight tile
+  static constexpr uint32_t kABytes = (kMaxBlocks + 1) * 1024;
+  static constexpr uint32_t kSfbBytes = kMaxBlocks * 16 + kAtomBytes;
+  static constexpr uint32_t kRedBytes = kMaxCluster * 4 * 2 * 128;
+  static constexpr size_t kBudget = 233472 / 2 - 1024;
+  static constexpr int kStages = (int)((kBudget - 2048 - kABytes - kSfbBytes - kRedBytes) / kStageBytes);
+  static_assert(kStages >= 4, "the ring needs a few stages");
+  static constexpr size_t kSmemBytes =
+      1024 + (size_t)kStages * kStageBytes + kABytes + kSfbBytes + kRedBytes + 1024;
+  static_assert(kSmemBytes <= kBudget, "two CTAs must fit one SM");
+  static constexpr int kSfSets = 4;
+  static constexpr int kSfaCol = 2 * kRows;                  // behind the two accumulators
+  static constexpr int kSfbCol = kSfaCol + kSfSets * 4;
+  static constexpr int kTmemCols = 128;
+  static_assert(kSfbCol + kSfSets * 4 <= kTmemCols, "tensor memory layout");
+};
+
+__device__ __forceinline__ uint32_t e4m3x4_codes(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+route_w1_front_kernel(const __grid_constant__ CUtensorMap tm_w,
+                      const __grid_constant__ CUtensorMap tm_shared, const RouteArgs args) {
+  using C = FCfg;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* w_tiles = smem;                                             // [S][16 KB]
+  uint8_t* a_buf = w_tiles + (size_t)C::kStages * kWTileBytes;         // [blocks + 1][1 KB]
+  uint8_t* sfa_tiles = a_buf + C::kABytes;                             // [S][512]
+  uint8_t* sfb = sfa_tiles + (size_t)C::kStages * kAtomBytes;
+  float* red = reinterpret_cast<float*>(sfb + C::kSfbBytes);
+  uint8_t* fixed = reinterpret_cast<uint8_t*>(red) + C::kRedBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(fixed);  // full[S], empty[S], tfull, act, ids, red
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fixed + 8 * (2 * C::kStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* expert_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t full0 = ptx::smem_u32(bars);
+  const uint32_t empty0 = full0 + 8 * C::kStages;
+  const uint32_t tfull = empty0 + 8 * C::kStages;
+  const uint32_t act_bar = tfull + 8;
+  const uint32_t ids_bar = act_bar + 8;
+  const uint32_t red_full = ids_bar + 8;
+
+  const int ck = args.cluster;
+  const int rank = ck > 1 ? (int)ptx::cluster_ctarank() : 0;
+  const int unit = (int)blockIdx.x / ck;
+  const int route = unit / args.tiles;
+  const int tile = unit - route * args.tiles;
+  const int token = route / args.lanes;
+  const int route_lane = route - token * args.lanes;
+  const int kb0 = (rank * args.k_blocks) / ck;
+  const int kb1 = ((rank + 1) * args.k_blocks) / ck;
+  const uint32_t tx_stage = kWTileTxBytes + kAtomBytes;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < C::kStages; ++s) {
+      ptx::mbar_init(full0 + 8 * s, 1);
+      ptx::mbar_init(empty0 + 8 * s, 1);
+    }
+    ptx::mbar_init(tfull, 1);
+    ptx::mbar_init(act_bar, 3);   // the three quantizing warps
+    ptx::mbar_init(ids_bar, 1);
+    ptx::mbar_init(red_full, 1);
+    if (ck > 1 && rank == 0) ptx::mbar_arrive_expect_tx(red_full, (uint32_t)(ck * 4 * 2 * 128));
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tm_w);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), C::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (ck > 1) ptx::cluster_sync_all();
+  bool cluster_arrived = false;
+
+  // The hidden rows and the logits come from the kernel before this one.  The kernel after
+  // this one starts only now: it may read the logits before its own dependency wait.
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
+
+  if (warp == 0) {
+    // ---------------- TMA producer: needs the expert, then streams its two tiles per block ----
+    bool ok = __all_sync(0xffffffffu, bounded_wait(ids_bar, 0u, abort_flag, args.status, 141));
+    const int expert = ok ? *expert_slot : 0;
+    const CUtensorMap* wmap = expert == -2 ? &tm_shared : &tm_w;
+    const uint8_t* wsc = expert == -2 ? args.shared_w_scales : args.w_scales;
+    const int w_row0 = (expert < 0 ? 0 : expert) * args.w_rows + tile * kTileF;
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int kb = kb0; ok && kb < kb1; ++kb) {
+      for (int t = 0; ok && t < 2; ++t) {
+        ok = __all_sync(0xffffffffu, bounded_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag,
+                                                  args.status, 142));
+        if (!ok) break;
+        if (ptx::elect_one()) {
+          const uint32_t bar = full0 + 8 * stage;
+          const int w_row = w_row0 + t * args.n;  // t = 1: the up rows, n rows further down
+          ptx::mbar_arrive_expect_tx(bar, tx_stage);
+          ptx::tma_load_2d(ptx::smem_u32(w_tiles + (size_t)stage * kWTileBytes), wmap, kb * kTileK,
+                           w_row, bar);
+          ptx::bulk_load(ptx::smem_u32(sfa_tiles + (size_t)stage * kAtomBytes),
+                         wsc + ((int64_t)(w_row / kAtomRows) * args.k_blocks + kb) * kAtomBytes,
+                         kAtomBytes, bar);
+        }
+        __syncwarp();
+        if (++stage == C::kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    constexpr uint32_t kIdesc = (4u << 7) | (0u << 10) | ((uint32_t)(kRows >> 3) << 17) | (1u << 23) |
+                                ((uint32_t)(kTileF >> 4) << 24);
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t set = 0;
+    bool ok = __all_sync(0xffffffffu, bounded_wait(act_bar, 0u, abort_flag, args.status, 143));
+    for (int kb = kb0; ok && kb < kb1; ++kb) {
+      const uint32_t sfb_t = tmem_base + C::kSfbCol + (uint32_t)((kb - kb0) % C::kSfSets) * 4;
+      for (int t = 0; ok && t < 2; ++t) {
+        ok = __all_sync(0xffffffffu,
+                        bounded_wait(full0 + 8 * stage, phase, abort_flag, args.status, 144));
+        if (!ok) break;
+        ptx::tc_fence_after();
+        if (ptx::elect_one()) {
+          const uint32_t sfa_t = tmem_base + C::kSfaCol + set * 4;
+          ptx::tc_cp_32x128b_warpx4(sfa_t, ptx::smem_desc_scale_atom(
+                                               ptx::smem_u32(sfa_tiles + (size_t)stage * kAtomBytes)));
+          if (t == 0) {
+            ptx::tc_cp_32x128b_warpx4(sfb_t, ptx::smem_desc_scale_atom(ptx::smem_u32(sfb + (kb - kb0) * 16)));
+          }
+          const uint64_t a_desc = ptx::smem_desc_sw128(ptx::smem_u32(w_tiles + (size_t)stage * kWTileBytes));
+          const uint64_t b_desc = ptx::smem_desc_sw128(ptx::smem_u32(a_buf + (size_t)(kb - kb0) * 1024));
+#pragma unroll
+          for (int ks = 0; ks < kTileK / kMmaK; ++ks) {
+            const uint32_t idesc = kIdesc | ((uint32_t)ks << 4) | ((uint32_t)ks << 29);
+            ptx::tc_mma_mxf8f6f4(tmem_base + t * kRows, a_desc + 2 * ks, b_desc + 2 * ks, idesc, sfa_t,
+                                 sfb_t, (kb > kb0 || ks > 0) ? 1u : 0u);
+          }
+          ptx::tc_commit(empty0 + 8 * stage);
+        }
+        __syncwarp();
+        set = (set + 1u) % C::kSfSets;
+        if (++stage == C::kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+    if (ok) {
+      if (ptx::elect_one()) ptx::tc_commit(tfull);
+      __syncwarp();
+    }
+  } else {
+    // ---------------- warps 2..5: front end, then the epilogue ----------------
+    const int quarter = warp & 3;
+    if (warp == 2) {
+      // routing of this CTA's token: the route's expert, and once per token the ids and weights
+      int expert = args.separate_shared != 0 ? -2 : args.num_experts - 1;  // the shared lane
+      if (route_lane < args.topk) {
+        float weight;
+        int id;
+        warp_softmax_topk_any(static_cast<const __nv_bfloat16*>(args.logits) +
+                                  (int64_t)token * args.logit_experts,
+                              args.logit_experts, args.topk, args.renormalize, lane, &weight, &id);
+        expert = __shfl_sync(0xffffffffu, id, route_lane);
+        if (route_lane == 0 && tile == 0 && rank == 0 && lane < args.topk) {
+          args.ids_out[(int64_t)token * args.topk + lane] = id;
+          args.weights_out[(int64_t)token * args.topk + lane] = weight;
+        }
+      }
+      if (lane == 0) {
+        *expert_slot = expert;
+        ptx::mbar_arrive(ids_bar);
+      }
+    } else {
+      // MXFP8 of this CTA's K slice of the token's row: 8 values per thread, 4 threads per
+      // scale group, the arithmetic of the activation quantizer (quantize.cu)
+      const int t96 = (int)threadIdx.x - 96;
+      const int chunks = (kb1 - kb0) * 16;
+      const uint4* row = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(args.hidden) +
+                                                        (int64_t)token * args.k_blocks * kTileK +
+                                                        (int64_t)kb0 * kTileK);
+      for (int c0 = 0; c0 < chunks; c0 += 96) {
+        const int c = c0 + t96;
+        const bool valid = c < chunks;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (valid) raw = __ldg(row + c);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          v[2 * i] = __uint_as_float(w[i] << 16);
+          v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
+        const float inv = ue8m0_inverse(sbits);
+        const uint32_t code = sbits >> 23;
+        uint32_t word = code;
+        word |= __shfl_down_sync(0xffffffffu, code, 4) << 8;
+        word |= __shfl_down_sync(0xffffffffu, code, 8) << 16;
+        word |= __shfl_down_sync(0xffffffffu, code, 12) << 24;
+        if (valid) {
+          *reinterpret_cast<uint2*>(a_buf + (size_t)(c >> 4) * 1024 + (c & 15) * 8) =
+              make_uint2(e4m3x4_codes(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
+                         e4m3x4_codes(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
+          if ((c & 15) == 0) *reinterpret_cast<uint32_t*>(sfb + (c >> 4) * 16) = word;
+        }
+      }
+      ptx::fence_proxy_async();  // the MMA and tcgen05.cp read these through the async proxy
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(act_bar);
+    }
+    bool ok = bounded_wait(tfull, 0u, abort_flag, args.status, 145);
+    float acc[2] = {0.0f, 0.0f};
+    if (ok) {
+      ptx::tc_fence_after();
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        uint32_t r[16];
+        ptx::tmem_ld_x16(t_addr + t * kRows, r);
+        ptx::tmem_ld_wait();
+        acc[t] = __uint_as_float(r[0]);  // column 0: the route's row
+      }
+    }
+    if (ck > 1) {
+      float* send = reinterpret_cast<float*>(w_tiles) + (quarter * 2) * 32;  // the ring is idle
+      if (ok) {
+        send[lane] = acc[0];
+        send[32 + lane] = acc[1];
+        ptx::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::bulk_copy_to_peer(ptx::mapa(ptx::smem_u32(red + ((rank * 4 + quarter) * 2) * 32), 0u),
+                                 ptx::smem_u32(send), 256u, ptx::mapa(red_full, 0u));
+        }
+      }
+      if (rank == 0 && ok) {
+        ok = bounded_wait_cluster(red_full, 0u, abort_flag, args.status, 146);
+        if (ok) {
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            float sum = 0.0f;
+            for (int src = 0; src < ck; ++src) sum += red[((src * 4 + quarter) * 2 + t) * 32 + lane];
+            acc[t] = sum;
+          }
+        }
+      }
+      ptx::cluster_arrive_relaxed();
+      cluster_arrived = true;
+    }
+    if (ok && rank == 0) {
+      const int f = tile * kTileF + quarter * 32 + lane;
+      const float g = round_bf16(acc[0]);
+      const float u = round_bf16(acc[1]);
+      const float v = round_bf16(silu_bf16_lookup(args.silu_lut, g) * u);
+      float amax = fabsf(v);
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+      const uint32_t sbits = ue8m0_scale_bits(amax, 448.0f);
+      const uint32_t code = __nv_cvt_float2_to_fp8x2(make_float2(v * ue8m0_inverse(sbits), 0.0f),
+                                                     __NV_SATFINITE, __NV_E4M3) & 0xffu;
+      static_cast<uint8_t*>(args.out)[(int64_t)route * args.n + f] = (uint8_t)code;
+      if (lane == 0) {
+        args.out_scales[(int64_t)route * (args.n / kScaleVec) + f / kScaleVec] = (uint8_t)(sbits >> 23);
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (ck > 1) {
     if (!cluster_arrived) ptx::cluster_arrive_relaxed();
     ptx::cluster_wait();
   }
@@ -843,6 +1202,23 @@ int common_checks(const uint8_t* activation, const uint8_t* act_scales, const ui
   return kOk;
 }
 
+int sm_count();
+
+// Lanes of a token per CTA of the reduce kernel: two where the launch stays inside the GPU's
+// CTA slots, then three, then half of them, then all (clusters of more than two CTAs stop at
+// 240 CTAs).  Returns the cluster size.
+int lane_cluster(int64_t units, int lanes) {
+  const int64_t slots = 2 * (int64_t)sm_count() - 8;
+  const int64_t wide_slots = slots - slots / 6;
+  const int choices[3] = {(lanes + 1) / 2, (lanes + 2) / 3, 2};
+  for (int c : choices) {
+    if (c >= 2 && c <= kMaxLaneCluster && c <= lanes && units * c <= (c > 2 ? wide_slots : slots)) {
+      return c;
+    }
+  }
+  return 1;
+}
+
 int sm_count() {
   static int count = []() {
     int device = 0, sms = 148;
@@ -948,7 +1324,8 @@ int moe_route_w2_reduce(void* out, int out_dtype, const uint8_t* activation,
                         const void* topk_ids, int ids_are_int64, const float* topk_weights,
                         const void* shared_gate, int gate_dtype, int gate_stride,
                         const void* shared_output, int compute_shared, int64_t tokens, int topk,
-                        int64_t n, int64_t k, int routing_ready, cudaStream_t stream) {
+                        int64_t n, int64_t k, int routing_ready, const void* logits,
+                        int logit_experts, int renormalize, cudaStream_t stream) {
   if (int rc = common_checks(activation, act_scales, weight, weight_scales, topk_ids, tokens, topk,
                              num_experts, n, k))
     return rc;
@@ -1009,22 +1386,178 @@ int moe_route_w2_reduce(void* out, int out_dtype, const uint8_t* activation,
   args.tiles = (int)(n / kTileF);
   args.out_dtype = out_dtype;
   args.routing_ready = routing_ready != 0 ? 1 : 0;
+  if (logits != nullptr) {
+    MX_REQUIRE(logit_experts >= topk && logit_experts <= 1024 && topk <= 16,
+               "in-kernel routing takes up to 1024 experts and top-16");
+    MX_REQUIRE(shared_weight != nullptr ? logit_experts <= num_experts : logit_experts < num_experts + (compute_shared != 0 ? 0 : 1),
+               "the logits name more experts than the weight stack holds");
+    args.logits = logits;
+    args.logit_experts = logit_experts;
+    args.renormalize = renormalize != 0 ? 1 : 0;
+  }
   // Lanes per CTA: two where the launch stays inside the GPU's CTA slots, then three, then
   // half of them, then all (clusters of more than two CTAs stop at 240 CTAs, as above).
   const int64_t units = tokens * args.tiles;
-  const int64_t slots = 2 * (int64_t)sm_count() - 8;
-  const int64_t wide_slots = slots - slots / 6;
-  int cr = 1;
-  const int choices[3] = {(lanes + 1) / 2, (lanes + 2) / 3, 2};
-  for (int c : choices) {
-    if (c >= 2 && c <= kMaxLaneCluster && c <= lanes && units * c <= (c > 2 ? wide_slots : slots)) {
-      cr = c;
-      break;
-    }
-  }
+  const int cr = lane_cluster(units, lanes);
   args.cluster = cr;
   return launch_route(route_w2_reduce_kernel, WCfg::kSmemBytes, (int)(units * cr), cr, stream, tm_w,
                       tm_shared, tm_a, args);
+}
+
+namespace {
+// K split of a W1 launch over `units` (route, tile) pairs (two CTA slots per SM; every CTA keeps
+// at least two K blocks; clusters of more than two CTAs stop at 240 CTAs).
+int w1_cluster(int64_t units, int k_blocks) {
+  const int64_t slots = 2 * (int64_t)sm_count() - 8;
+  const int64_t wide_slots = slots - slots / 6;
+  int ck = (int)std::min<int64_t>({(int64_t)kMaxCluster, wide_slots / units, (int64_t)k_blocks / 2});
+  if (ck < 2 && units * 2 <= slots && k_blocks >= 4) ck = 2;
+  return ck < 1 ? 1 : ck;
+}
+}  // namespace
+
+// Whether moe_decode_layer takes the problem: at most 9 routes per token, a down projection of
+// at most 2048 inputs, and at most 16 K blocks of the hidden size per CTA of the W1 launch.
+int moe_decode_layer_supported(int64_t tokens, int topk, int logit_experts, int64_t hidden_size,
+                               int64_t inter) {
+  if (tokens <= 0 || topk <= 0 || topk + 1 > kMaxLanes || logit_experts < topk || logit_experts > 1024)
+    return 0;
+  if (hidden_size <= 0 || hidden_size % 128 != 0 || inter <= 0 || inter % 128 != 0) return 0;
+  if (inter / 128 > WCfg::kMaxKBlocksPerLane) return 0;
+  const int k_blocks = (int)(hidden_size / kTileK);
+  const int ck = w1_cluster(tokens * (topk + 1) * (inter / kTileF), k_blocks);
+  return (k_blocks + ck - 1) / ck <= FCfg::kMaxBlocks ? 1 : 0;
+}
+
+// Whether the two-launch form is expected to beat top-k kernel + W1 + W2.  It saves the front
+// kernel (about 3 us) but every W2 CTA repeats the top-k (about 1.5 us), which is hidden only
+// while W2's CTAs sit beside W1's on the GPU or W1's tail is long: measured on the named shape
+// (hidden 2048, intermediate 512, 256 experts, top-8; two / three launches, warm, us) 16.6 / 16.5
+// at 1 token, 21.1 / 18.8 at 2 (W1 in clusters of three, W2 not resident beside it), 24.7 / 27.0
+// at 4, 38.5 / 39.2 at 8.
+int moe_decode_layer_preferred(int64_t tokens, int topk, int logit_experts, int64_t hidden_size,
+                               int64_t inter) {
+  if (moe_decode_layer_supported(tokens, topk, logit_experts, hidden_size, inter) == 0) return 0;
+  const int lanes = topk + 1;
+  const int64_t w1_units = tokens * lanes * (inter / kTileF);
+  const int ck = w1_cluster(w1_units, (int)(hidden_size / kTileK));
+  const int64_t w2_units = tokens * (hidden_size / kTileF);
+  const int64_t slots = 2 * (int64_t)sm_count() - 8;
+  const int cr = lane_cluster(w2_units, lanes);
+  return (w1_units * ck + w2_units * cr <= slots || ck <= 2) ? 1 : 0;
+}
+
+// The decode schedule of one routed-MoE layer in two launches (the reference's three-kernel
+// schedule, python/mxfp6/qwen35.py:384-432, without the kernel in front): W1 over routes with
+// top-k selection and activation quantization inside every CTA, then W2 with the weighted
+// reduce, which selects the experts again for itself while W1 runs.  hidden / logits BF16;
+// activation [tokens * (topk + 1), inter] and its logical scales are scratch between the two;
+// topk_ids / topk_weights receive the selection.
+int moe_decode_layer(void* out, int out_dtype, const void* hidden, const void* logits,
+                     const void* shared_gate, int gate_dtype, int gate_stride, const uint8_t* w1,
+                     const uint8_t* w1_scales, const uint8_t* w2, const uint8_t* w2_scales,
+                     int num_experts, const uint8_t* shared_w1, const uint8_t* shared_w1_scales,
+                     const uint8_t* shared_w2, const uint8_t* shared_w2_scales, uint8_t* activation,
+                     uint8_t* activation_scales, int32_t* topk_ids, float* topk_weights,
+                     int64_t tokens, int topk, int logit_experts, int renormalize,
+                     int64_t hidden_size, int64_t inter, cudaStream_t stream) {
+  MX_REQUIRE(out && hidden && logits && shared_gate && w1 && w1_scales && w2 && w2_scales &&
+                 activation && activation_scales && topk_ids && topk_weights,
+             "pointers must not be null");
+  MX_REQUIRE(moe_decode_layer_supported(tokens, topk, logit_experts, hidden_size, inter) != 0,
+             "the two-launch decode schedule does not take %lld tokens, top-%d, hidden %lld, "
+             "intermediate %lld", (long long)tokens, topk, (long long)hidden_size, (long long)inter);
+  MX_REQUIRE((shared_w1 == nullptr) == (shared_w1_scales == nullptr) &&
+                 (shared_w1 == nullptr) == (shared_w2 == nullptr) &&
+                 (shared_w1 == nullptr) == (shared_w2_scales == nullptr),
+             "the separate shared expert comes as four pointers or none");
+  MX_REQUIRE(shared_w1 != nullptr ? logit_experts <= num_experts : logit_experts < num_experts,
+             "the logits name more experts than the weight stack holds");
+  MX_REQUIRE((reinterpret_cast<uintptr_t>(hidden) & 15) == 0 && (reinterpret_cast<uintptr_t>(w1) & 31) == 0 &&
+                 (reinterpret_cast<uintptr_t>(w1_scales) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(activation_scales) & 3) == 0,
+             "hidden 16-byte, weights 32-byte, weight scales 16-byte, activation scales 4-byte aligned");
+  const int lanes = topk + 1;
+  const int w_rows = (int)inter * 2;
+  CUtensorMap tm_w, tm_shared;
+  if (int rc = make_tensor_map_2d(&tm_w, (int)CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B, w1,
+                                  (uint64_t)hidden_size, (uint64_t)num_experts * w_rows,
+                                  (uint64_t)hidden_size * 3 / 4, kTileF))
+    return rc;
+  tm_shared = tm_w;
+  if (shared_w1 != nullptr) {
+    MX_REQUIRE((reinterpret_cast<uintptr_t>(shared_w1) & 31) == 0, "shared weight must be 32-byte aligned");
+    if (int rc = make_tensor_map_2d(&tm_shared, (int)CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B, shared_w1,
+                                    (uint64_t)hidden_size, (uint64_t)w_rows,
+                                    (uint64_t)hidden_size * 3 / 4, kTileF))
+      return rc;
+  }
+  int device = 0;
+  MX_CUDA(cudaGetDevice(&device));
+  RouteArgs args = {};
+  args.w_scales = w1_scales;
+  args.shared_w_scales = shared_w1_scales;
+  args.out = activation;
+  args.out_scales = activation_scales;
+  args.status = device_status_word(device);
+  if (args.status == nullptr) return kCudaError;
+  args.tokens = (int)tokens;
+  args.topk = topk;
+  args.lanes = lanes;
+  args.num_experts = num_experts;
+  args.separate_shared = shared_w1 != nullptr ? 1 : 0;
+  args.n = (int)inter;
+  args.w_rows = w_rows;
+  args.k_blocks = (int)(hidden_size / kTileK);
+  args.tiles = (int)(inter / kTileF);
+  args.hidden = hidden;
+  args.logits = logits;
+  args.ids_out = topk_ids;
+  args.weights_out = topk_weights;
+  args.logit_experts = logit_experts;
+  args.renormalize = renormalize != 0 ? 1 : 0;
+  const int64_t units = tokens * lanes * args.tiles;
+  args.cluster = w1_cluster(units, args.k_blocks);
+  if (int rc = silu_table(stream, &args.silu_lut)) return rc;
+  {
+    // One attribute call per device.
+    static std::mutex mutex;
+    static unsigned long long configured = 0;
+    std::lock_guard<std::mutex> lock(mutex);
+    if (device < 64 && (configured >> device & 1ull) == 0) {
+      MX_CUDA(cudaFuncSetAttribute(route_w1_front_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)FCfg::kSmemBytes));
+      MX_CUDA(cudaFuncSetAttribute(route_w1_front_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                   cudaSharedmemCarveoutMaxShared));
+      configured |= 1ull << device;
+    }
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((unsigned)(units * args.cluster));
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = FCfg::kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  int count = 0;
+  if (args.cluster > 1) {
+    attribute[count].id = cudaLaunchAttributeClusterDimension;
+    attribute[count].val.clusterDim.x = (unsigned)args.cluster;
+    attribute[count].val.clusterDim.y = 1;
+    attribute[count].val.clusterDim.z = 1;
+    ++count;
+  }
+  if (use_pdl()) {
+    attribute[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  config.attrs = attribute;
+  config.numAttrs = count;
+  MX_CUDA(cudaLaunchKernelEx(&config, route_w1_front_kernel, tm_w, tm_shared, args));
+  return moe_route_w2_reduce(out, out_dtype, activation, activation_scales, w2, w2_scales, num_experts,
+                             shared_w2, shared_w2_scales, topk_ids, 0, topk_weights, shared_gate,
+                             gate_dtype, gate_stride, nullptr, 1, tokens, topk, hidden_size, inter, 0,
+                             logits, logit_experts, renormalize, stream);
 }
 
 // Router half of torch.ops.mxfp6.qwen35_router_quant_out (csrc/moe.cu:237-511): the BF16 gate

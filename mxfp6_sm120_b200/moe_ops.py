@@ -1177,3 +1177,119 @@ def qwen35_router_quant_out(
         )
     qwen35_topk_quant_out(quantized, logical_scales, None, topk_weights, topk_ids, hidden,
                           routed_logits, renormalize=renormalize)
+
+
+def moe_decode_layer_supported(tokens: int, topk: int, experts: int, hidden_size: int,
+                               intermediate: int) -> bool:
+    """Whether :func:`moe_decode_layer_out` takes the problem (host arithmetic, no GPU)."""
+    load_library()
+    return bool(library().mxfp6_moe_decode_layer_supported(int(tokens), int(topk), int(experts),
+                                                           int(hidden_size), int(intermediate)))
+
+
+def moe_decode_layer_preferred(tokens: int, topk: int, experts: int, hidden_size: int,
+                               intermediate: int) -> bool:
+    """Whether the two-launch form is supported AND expected to be the faster one."""
+    load_library()
+    return bool(library().mxfp6_moe_decode_layer_preferred(int(tokens), int(topk), int(experts),
+                                                           int(hidden_size), int(intermediate)))
+
+
+def moe_decode_layer_out(
+    output: torch.Tensor,
+    activation: torch.Tensor,
+    activation_scales: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    hidden: torch.Tensor,
+    router_logits: torch.Tensor,
+    shared_gate: torch.Tensor,
+    w1: torch.Tensor,
+    w1_scales: torch.Tensor,
+    w2: torch.Tensor,
+    w2_scales: torch.Tensor,
+    shared_w1: torch.Tensor | None = None,
+    shared_w1_scales: torch.Tensor | None = None,
+    shared_w2: torch.Tensor | None = None,
+    shared_w2_scales: torch.Tensor | None = None,
+    renormalize: bool = True,
+) -> None:
+    """The decode schedule in two launches: top-k selection and MXFP8 quantization of the hidden
+    rows happen inside the W1 kernel's CTAs (and the selection once more inside W2's), so no
+    front-end kernel runs and W1 depends on nothing but ``hidden`` and ``router_logits``.
+
+    Same results as ``qwen35_topk_quant_out`` -> ``qwen35_w1_splitk_silu_mxfp8_out`` ->
+    ``qwen35_w2_splitk_reduce_out`` (the reference's schedule, python/mxfp6/qwen35.py:384-432).
+    ``w1`` ``[E(+1), 2I, 3H/4]``, ``w2`` ``[E(+1), H, 3I/4]``; the shared expert is the last
+    matrix of both unless the four ``shared_*`` tensors bring it.  ``activation``
+    ``[tokens * (topk + 1), I]`` and ``activation_scales`` are scratch.
+    """
+    if (
+        hidden.device.type != "cuda"
+        or hidden.dtype != torch.bfloat16
+        or hidden.ndim != 2
+        or not hidden.is_contiguous()
+    ):
+        raise ValueError("hidden must be contiguous CUDA bfloat16 [tokens,H]")
+    _require_sm100(hidden.device)
+    tokens, width = (int(v) for v in hidden.shape)
+    if (
+        router_logits.device != hidden.device
+        or router_logits.dtype != torch.bfloat16
+        or router_logits.ndim != 2
+        or int(router_logits.shape[0]) != tokens
+        or not router_logits.is_contiguous()
+    ):
+        raise ValueError("router_logits must be contiguous CUDA bfloat16 [tokens,E]")
+    experts = int(router_logits.shape[1])
+    topk = int(topk_ids.shape[1])
+    for tensor, name in ((w1, "w1"), (w1_scales, "w1_scales"), (w2, "w2"), (w2_scales, "w2_scales")):
+        _require_cuda_uint8_contiguous(tensor, name)
+        if tensor.device != hidden.device:
+            raise ValueError(f"{name} must be on {hidden.device}")
+    if w1.ndim != 3 or w2.ndim != 3 or int(w1.shape[2]) * 4 != width * 3 or int(w2.shape[1]) != width:
+        raise ValueError("w1 must be [E,2I,3H/4] and w2 [E,H,3I/4]")
+    inter = int(w1.shape[1]) // 2
+    if int(w2.shape[2]) * 4 != inter * 3 or w1.shape[0] != w2.shape[0]:
+        raise ValueError("w1 and w2 disagree on the intermediate size or the expert count")
+    shared = (shared_w1, shared_w1_scales, shared_w2, shared_w2_scales)
+    if any(t is None for t in shared) != all(t is None for t in shared):
+        raise ValueError("the separate shared expert comes as four tensors or none")
+    if shared_w1 is not None:
+        _check_separate_shared(shared_w1, shared_w1_scales, w1, hidden.device)
+        _check_separate_shared(shared_w2, shared_w2_scales, w2, hidden.device)
+    lanes = tokens * (topk + 1)
+    if (
+        topk_ids.dtype != torch.int32
+        or topk_weights.dtype != torch.float32
+        or tuple(topk_weights.shape) != (tokens, topk)
+        or tuple(topk_ids.shape) != (tokens, topk)
+        or not topk_ids.is_contiguous()
+        or not topk_weights.is_contiguous()
+    ):
+        raise ValueError("topk_ids int32 and topk_weights float32 must be contiguous [tokens,topk]")
+    if tuple(activation.shape) != (lanes, inter) or tuple(activation_scales.shape) != (lanes, inter // 32):
+        raise ValueError("activation must be [tokens*(topk+1),I] and activation_scales [..,I/32]")
+    if (
+        output.device != hidden.device
+        or output.dtype not in (torch.float16, torch.bfloat16)
+        or tuple(output.shape) != (tokens, width)
+        or not output.is_contiguous()
+    ):
+        raise ValueError("output must be contiguous CUDA float16/bfloat16 [tokens,H]")
+    stride = _gate_stride(shared_gate, tokens, hidden.device)
+    if not isinstance(renormalize, bool):
+        raise TypeError("renormalize must be a bool")
+    load_library()
+    with torch.cuda.device(hidden.device):
+        check(
+            library().mxfp6_moe_decode_layer(
+                output.data_ptr(), _DTYPE_CODE[output.dtype], hidden.data_ptr(),
+                router_logits.data_ptr(), shared_gate.data_ptr(), _GATE_CODE[shared_gate.dtype], stride,
+                w1.data_ptr(), w1_scales.data_ptr(), w2.data_ptr(), w2_scales.data_ptr(),
+                int(w1.shape[0]), _ptr(shared_w1), _ptr(shared_w1_scales), _ptr(shared_w2),
+                _ptr(shared_w2_scales), _as_u8(activation).data_ptr(), activation_scales.data_ptr(),
+                topk_ids.data_ptr(), topk_weights.data_ptr(), tokens, topk, experts, int(renormalize),
+                width, inter, _stream(hidden.device),
+            )
+        )

@@ -17,6 +17,8 @@ from .moe_ops import (
     dense_w1_silu_mxfp8_out,
     grouped_gemm_w6a8_out,
     grouped_scale_rows,
+    moe_decode_layer_out,
+    moe_decode_layer_preferred,
     moe_reduce_out,
     qwen35_grouped_w1_silu_mxfp8_out,
     qwen35_route_mxfp8_out,
@@ -486,10 +488,27 @@ def qwen35_moe_decode_logits_out(
     shared_w1: PackedMXFP6Tensor | None = None,
     shared_w2: PackedMXFP6Tensor | None = None,
     renormalize: bool = True,
+    two_launches: bool | None = None,
 ) -> torch.Tensor:
-    """Decode schedule from given router logits: top-k + quantization, W1 routes, W2 routes
-    + reduce, three launches in all.  The shared expert is the last matrix of ``w1`` /
-    ``w2`` or, when ``shared_w1`` / ``shared_w2`` are given, a separate pair."""
+    """Decode schedule from given router logits.  Two launches where that is expected to be
+    faster (top-k and quantization inside the W1 kernel, ``moe_decode_layer_out``), else three:
+    top-k + quantization, W1 routes, W2 routes + reduce; ``two_launches`` forces either.
+    Both give the same bytes.  The shared expert is the last matrix of ``w1`` / ``w2`` or,
+    when ``shared_w1`` / ``shared_w2`` are given, a separate pair."""
+    tokens, hidden_size = (int(v) for v in hidden.shape)
+    topk = int(workspace.topk_ids.shape[1])
+    if two_launches is None:
+        two_launches = moe_decode_layer_preferred(tokens, topk, int(router_logits.shape[1]),
+                                                  hidden_size, int(w1.shape[1]) // 2)
+    if two_launches:
+        sw = (None,) * 4
+        if shared_w1 is not None:
+            sw = (shared_w1.values.view(1, *w1.shape[1:]), shared_w1.scales,
+                  shared_w2.values.view(1, *w2.shape[1:]), shared_w2.scales)
+        moe_decode_layer_out(workspace.output, workspace.activation, workspace.activation_scales,
+                             workspace.topk_weights, workspace.topk_ids, hidden, router_logits,
+                             shared_gate, w1, w1_scales, w2, w2_scales, *sw, renormalize=renormalize)
+        return workspace.output
     qwen35_topk_quant_out(workspace.quantized, workspace.input_scales, None,
                           workspace.topk_weights, workspace.topk_ids, hidden, router_logits,
                           renormalize=renormalize)

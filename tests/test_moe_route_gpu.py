@@ -295,6 +295,22 @@ def test_decode_schedule_named_config_against_oracle_and_graph(mx, named_layer, 
     out = step().clone()
     want, want_ids = _oracle_decode_layer(mx, shape, w1, w2, sw1, sw2, hidden, logits, gate, ws.topk_ids.cpu())
     assert torch.equal(ws.topk_ids.cpu(), want_ids)
+    # two launches (top-k and quantization inside the W1 kernel) and three launches give the
+    # same bytes, ids and weights; the default picks one of them by the size of the grids
+    assert mx.moe_decode_layer_supported(tokens, shape.topk, e, h, i)
+    assert mx.moe_decode_layer_preferred(tokens, shape.topk, e, h, i) == (tokens != 2)
+    ws3 = mx.Qwen35MoeB1Workspace.allocate(DEV, shape, batch=tokens)
+    three = mx.qwen35_moe_decode_logits_out(ws3, hidden_d, logits_d, gate_d, w1v, w1.scales, w2v, w2.scales,
+                                            sw1, sw2, renormalize=True, two_launches=False)
+    assert torch.equal(three, out)
+    ws2 = mx.Qwen35MoeB1Workspace.allocate(DEV, shape, batch=tokens)
+    two = mx.qwen35_moe_decode_logits_out(ws2, hidden_d, logits_d, gate_d, w1v, w1.scales, w2v, w2.scales,
+                                          sw1, sw2, renormalize=True, two_launches=True)
+    assert torch.equal(two, out)
+    assert torch.equal(ws2.topk_ids, ws.topk_ids) and torch.equal(ws2.topk_weights, ws.topk_weights)
+    assert torch.equal(ws3.topk_ids, ws.topk_ids) and torch.equal(ws3.topk_weights, ws.topk_weights)
+    assert torch.equal(ws3.activation.view(torch.uint8), ws.activation.view(torch.uint8))
+    assert torch.equal(ws3.activation_scales, ws.activation_scales)
     per_token = torch.nn.functional.cosine_similarity(out.float().cpu(), want.float(), dim=1)
     assert float(per_token.min()) >= 0.999
     assert _rel_fro(out, want) <= 2e-2
@@ -347,3 +363,14 @@ def test_b1_schedule_with_router_and_stacked_shared_expert(mx):
         assert torch.equal(ids, want_ids)
         per_token = torch.nn.functional.cosine_similarity(out.float().cpu(), want.float(), dim=1)
         assert float(per_token.min()) >= 0.999
+        # the two-launch form on the same logits, shared expert last in both stacks, no renormalisation
+        two = torch.empty_like(out)
+        act = torch.zeros_like(ws.activation)
+        act_scales = torch.zeros_like(ws.activation_scales)
+        tw, ti = torch.zeros_like(ws.topk_weights), torch.zeros_like(ws.topk_ids)
+        for renormalize in (True, False):
+            ref = mx.qwen35_moe_b1_out(ws, hidden.to(DEV), gate_w.to(DEV), w1v, w1.scales, w2v, w2.scales,
+                                       renormalize=renormalize).clone()
+            mx.moe_decode_layer_out(two, act, act_scales, tw, ti, hidden.to(DEV), ws.routed_logits,
+                                    ws.shared_gate, w1v, w1.scales, w2v, w2.scales, renormalize=renormalize)
+            assert torch.equal(two, ref) and torch.equal(ti, ws.topk_ids) and torch.equal(tw, ws.topk_weights)
