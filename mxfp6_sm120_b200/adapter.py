@@ -117,8 +117,6 @@ class MxFp6MoERunner:
     def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
         """``[tokens, H]`` BF16 in, ``[tokens, H]`` BF16 out (this rank's partial under tensor
         parallelism: the caller sums the ranks, e.g. with ``moe_reduce_tp2_out``'s collective)."""
-        from .moe_ops import qwen35_router_quant_out
-
         total = int(hidden_states.shape[0])
         if total > self.max_tokens:
             # chunks of one size share a workspace: each result is copied out before the next runs
@@ -130,18 +128,19 @@ class MxFp6MoERunner:
         logits, shared_gate = self._logits[total]
         hidden_states = hidden_states.contiguous()
         if state.decode is not None and total <= DECODE_MAX_TOKENS:
-            # router, top-k and quantization in the workspace of the decode schedule
-            ws = state.decode
-            qwen35_router_quant_out(ws.quantized, ws.input_scales, ws.routed_logits, ws.topk_weights,
-                                    ws.topk_ids, ws.shared_gate, hidden_states,
-                                    self.weights.combined_gate, renormalize=self.renormalize)
-            from .qwen35 import _decode_routes_out
+            # the router GEMV, then the decode schedule on its logits (two or three launches)
+            from .moe_ops import router_logits_out
+            from .qwen35 import qwen35_moe_decode_logits_out
 
+            ws = state.decode
+            router_logits_out(ws.routed_logits, ws.shared_gate, hidden_states, self.weights.combined_gate)
             e, i, h = self.weights.experts, self.weights.intermediate, self.weights.hidden
             lay = self.layer
-            return _decode_routes_out(ws, lay.w1.values.view(e, 2 * i, h * 3 // 4), lay.w1.scales,
-                                      lay.w2.values.view(e, h, i * 3 // 4), lay.w2.scales,
-                                      lay.shared_w1, lay.shared_w2)
+            return qwen35_moe_decode_logits_out(
+                ws, hidden_states, ws.routed_logits, ws.shared_gate,
+                lay.w1.values.view(e, 2 * i, h * 3 // 4), lay.w1.scales,
+                lay.w2.values.view(e, h, i * 3 // 4), lay.w2.scales, lay.shared_w1, lay.shared_w2,
+                renormalize=self.renormalize)
         from ._loader import check, library
         from .ops import _stream
 

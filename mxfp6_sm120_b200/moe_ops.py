@@ -1105,25 +1105,16 @@ def moe_reduce_array_out(
         )
 
 
-def qwen35_router_quant_out(
-    quantized: torch.Tensor,
-    logical_scales: torch.Tensor,
+def router_logits_out(
     routed_logits: torch.Tensor,
-    topk_weights: torch.Tensor,
-    topk_ids: torch.Tensor,
     shared_gate: torch.Tensor,
     hidden: torch.Tensor,
     gate_weight: torch.Tensor,
-    renormalize: bool = False,
     shared_gate_weight: torch.Tensor | None = None,
 ) -> None:
-    """Router GEMV, softmax top-k and MXFP8 quantization of the hidden rows.
-
-    ``gate_weight`` holds the routed gate rows ``[E, H]`` followed by the shared expert's
-    gate row (``[E + 1, H]``) unless ``shared_gate_weight`` ``[1, H]`` brings that row.
-    Two launches here (the logits, then top-k + quantization) where the reference has one
-    cooperative kernel.
-    """
+    """The router GEMV alone: ``routed_logits[b, e] = bf16(hidden[b] . gate_weight[e])`` in FP32
+    and the shared expert's gate logit into ``shared_gate[b]`` (the first half of
+    ``qwen35_router_quant_out``)."""
     if (
         hidden.device.type != "cuda"
         or hidden.dtype != torch.bfloat16
@@ -1164,8 +1155,6 @@ def qwen35_router_quant_out(
         or not shared_gate.is_contiguous()
     ):
         raise ValueError("shared_gate must be contiguous CUDA bfloat16 with B values")
-    if not isinstance(renormalize, bool):
-        raise TypeError("renormalize must be a bool")
     load_library()
     with torch.cuda.device(hidden.device):
         check(
@@ -1175,6 +1164,30 @@ def qwen35_router_quant_out(
                 _stream(hidden.device),
             )
         )
+
+
+def qwen35_router_quant_out(
+    quantized: torch.Tensor,
+    logical_scales: torch.Tensor,
+    routed_logits: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    shared_gate: torch.Tensor,
+    hidden: torch.Tensor,
+    gate_weight: torch.Tensor,
+    renormalize: bool = False,
+    shared_gate_weight: torch.Tensor | None = None,
+) -> None:
+    """Router GEMV, softmax top-k and MXFP8 quantization of the hidden rows.
+
+    ``gate_weight`` holds the routed gate rows ``[E, H]`` followed by the shared expert's
+    gate row (``[E + 1, H]``) unless ``shared_gate_weight`` ``[1, H]`` brings that row.
+    Two launches here (the logits, then top-k + quantization) where the reference has one
+    cooperative kernel.
+    """
+    if not isinstance(renormalize, bool):
+        raise TypeError("renormalize must be a bool")
+    router_logits_out(routed_logits, shared_gate, hidden, gate_weight, shared_gate_weight)
     qwen35_topk_quant_out(quantized, logical_scales, None, topk_weights, topk_ids, hidden,
                           routed_logits, renormalize=renormalize)
 

@@ -25,6 +25,7 @@ from .moe_ops import (
     qwen35_topk_quant_out,
     qwen35_topk_quant_route_out,
     qwen35_router_quant_out,
+    router_logits_out,
     qwen35_w1_splitk_silu_mxfp8_out,
     qwen35_w2_splitk_reduce_out,
     silu_and_mul_mxfp8_grouped_out,
@@ -469,6 +470,17 @@ def qwen35_moe_b1_out(
     ``combined_gate`` is the routed gate rows followed by the shared expert's gate row;
     ``w1`` ``[E + 1, 2I, 3H/4]`` and ``w2`` ``[E + 1, H, 3I/4]`` end with the shared expert.
     """
+    tokens, hidden_size = (int(v) for v in hidden.shape)
+    if moe_decode_layer_preferred(tokens, int(workspace.topk_ids.shape[1]),
+                                  int(workspace.routed_logits.shape[1]), hidden_size,
+                                  int(w1.shape[1]) // 2):
+        # router, then W1 with top-k and quantization inside, then W2: three launches
+        router_logits_out(workspace.routed_logits, workspace.shared_gate, hidden, combined_gate)
+        moe_decode_layer_out(workspace.output, workspace.activation, workspace.activation_scales,
+                             workspace.topk_weights, workspace.topk_ids, hidden,
+                             workspace.routed_logits, workspace.shared_gate, w1, w1_scales, w2,
+                             w2_scales, renormalize=renormalize)
+        return workspace.output
     qwen35_router_quant_out(
         workspace.quantized, workspace.input_scales, workspace.routed_logits,
         workspace.topk_weights, workspace.topk_ids, workspace.shared_gate, hidden,
