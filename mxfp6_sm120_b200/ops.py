@@ -233,24 +233,45 @@ def is_stream_k_enabled() -> bool:
     return library().mxfp6_get_split_k_mode() == 2
 
 
+def _refuse(failed: bool, message: str, kind: type[Exception] = ValueError) -> None:
+    """One line per argument rule: raise ``kind(message)`` when the rule is broken."""
+    if failed:
+        raise kind(message)
+
+
 def _validate_problem(m: int, n: int, k: int) -> None:
-    if m <= 0:
-        raise ValueError(f"m must be positive; got {m}")
-    if n <= 0 or n % 8:
-        raise ValueError(f"n must be a positive multiple of 8; got {n}")
-    if k <= 0 or k % 128:
-        raise ValueError(f"k must be a positive multiple of 128; got {k}")
+    _refuse(m <= 0, f"m must be positive; got {m}")
+    _refuse(n <= 0 or n % 8 != 0, f"n must be a positive multiple of 8; got {n}")
+    _refuse(k <= 0 or k % 128 != 0, f"k must be a positive multiple of 128; got {k}")
 
 
 def _validate_output_dtype(out_dtype: torch.dtype) -> torch.dtype:
-    if out_dtype not in (torch.float16, torch.bfloat16):
-        raise TypeError(f"out_dtype must be torch.float16 or torch.bfloat16; got {out_dtype}")
+    _refuse(out_dtype not in _DTYPE_CODE,
+            f"out_dtype must be torch.float16 or torch.bfloat16; got {out_dtype}", TypeError)
     return out_dtype
 
 
+class _Operand:
+    """What both operand containers share: where the bytes live and the logical extent."""
+
+    values: torch.Tensor
+    rows: int
+    k: int
+
+    @property
+    def device(self) -> torch.device:
+        return self.values.device
+
+    @property
+    def shape(self) -> tuple[int, int]:
+        return (self.rows, self.k)
+
+
 @dataclass(frozen=True)
-class PackedMXFP6Tensor:
-    """An E3M2 matrix and its UE8M0/32 scales in the packed physical layout."""
+class PackedMXFP6Tensor(_Operand):
+    """MXFP6 operand as the kernels read it: ``values`` = E3M2 codes, four per three bytes,
+    row-major ``[rows, 3k/4]`` flattened; ``scales`` = UE8M0 bytes in 128 x 4 atoms;
+    ``logical_scales`` = the same scales as ``[rows, k/32]`` when the producer kept them."""
 
     values: torch.Tensor
     scales: torch.Tensor
@@ -258,51 +279,31 @@ class PackedMXFP6Tensor:
     k: int
     logical_scales: torch.Tensor | None = None
 
-    @property
-    def device(self) -> torch.device:
-        return self.values.device
-
-    @property
-    def shape(self) -> tuple[int, int]:
-        return (self.rows, self.k)
-
 
 @dataclass(frozen=True)
-class MXFP8Tensor:
-    """A byte-aligned E4M3 matrix and UE8M0/32 scales for native W6A8."""
+class MXFP8Tensor(_Operand):
+    """MXFP8 activation: ``values`` = one E4M3 byte per element, ``[rows, k]`` flattened;
+    ``scales`` = UE8M0 bytes in 128 x 4 atoms."""
 
     values: torch.Tensor
     scales: torch.Tensor
     rows: int
     k: int
 
-    @property
-    def device(self) -> torch.device:
-        return self.values.device
-
-    @property
-    def shape(self) -> tuple[int, int]:
-        return (self.rows, self.k)
-
     def dequantized_values(self) -> torch.Tensor:
-        """Return the E4M3 payload viewed as a float8 matrix (without scales)."""
+        """The codes as a ``[rows, k]`` ``float8_e4m3fn`` matrix (scales not applied)."""
         return self.values.view(self.rows, self.k).view(torch.float8_e4m3fn)
 
 
 def _validate_float_activation(input: torch.Tensor) -> tuple[int, int]:
-    if input.device.type != "cuda":
-        raise ValueError(f"input must be a CUDA tensor; got {input.device}")
-    if input.dtype not in (torch.float16, torch.bfloat16):
-        raise TypeError(
-            f"input must have dtype torch.float16 or torch.bfloat16; got {input.dtype}"
-        )
-    if input.ndim != 2:
-        raise ValueError(f"input must have shape [M,K]; got {tuple(input.shape)}")
-    if not input.is_contiguous():
-        raise ValueError("input must be contiguous")
-    rows, k = (int(value) for value in input.shape)
-    if rows <= 0 or k <= 0 or k % SCALE_VECTOR_SIZE:
-        raise ValueError("M must be positive and K a positive multiple of 32")
+    _refuse(input.device.type != "cuda", f"input must be a CUDA tensor; got {input.device}")
+    _refuse(input.dtype not in _DTYPE_CODE,
+            f"input must have dtype torch.float16 or torch.bfloat16; got {input.dtype}", TypeError)
+    _refuse(input.ndim != 2, f"input must have shape [M,K]; got {tuple(input.shape)}")
+    _refuse(not input.is_contiguous(), "input must be contiguous")
+    rows, k = map(int, input.shape)
+    _refuse(min(rows, k) <= 0 or k % SCALE_VECTOR_SIZE != 0,
+            "M must be positive and K a positive multiple of 32")
     return rows, k
 
 
@@ -366,14 +367,14 @@ def pad_fp6(packed: torch.Tensor) -> torch.Tensor:
 
 
 def to_mma_k64_weight(weight: torch.Tensor) -> torch.Tensor:
-    """Transpose packed ``[E,N,64]`` weights (kept for API compatibility)."""
+    """Per expert, the ``[N, 64]`` code matrix transposed and packed again (the layout one of
+    the reference's SM120 kernels reads; no kernel here needs it, the op is kept for callers)."""
     _require_cuda_uint8_contiguous(weight, "weight")
-    if weight.ndim != 3 or weight.shape[2] != 48:
-        raise ValueError("weight must contain packed [E,N,64] FP6 values")
-    experts, rows, _ = weight.shape
-    codes = unpack_fp6(weight, experts * rows, 64)
-    transposed = codes.view(experts, rows, 64).transpose(1, 2).contiguous()
-    return pack_fp6(transposed.flatten(0, 1)).view_as(weight)
+    _refuse(weight.ndim != 3 or weight.shape[2] != 48, "weight must contain packed [E,N,64] FP6 values")
+    experts, rows = int(weight.shape[0]), int(weight.shape[1])
+    per_expert = unpack_fp6(weight, experts * rows, 64).view(experts, rows, 64)
+    swapped = per_expert.permute(0, 2, 1).contiguous().view(experts * 64, rows)
+    return pack_fp6(swapped).view_as(weight)
 
 
 def expand_fp6_to_fp8(packed: torch.Tensor, rows: int, k: int) -> torch.Tensor:
@@ -442,19 +443,12 @@ def pack_grouped_scales(
     scale offsets keep every expert on a 128-row scale-atom boundary.
     """
     _require_cuda_uint8_contiguous(logical, "logical scales")
-    if logical.ndim != 2 or logical.shape[0] <= 0 or logical.shape[1] <= 0:
-        raise ValueError("logical scales must have shape [M, K / 32]")
-    if (
-        expert_offsets.device != logical.device
-        or expert_offsets.dtype != torch.int64
-        or expert_offsets.ndim != 1
-        or expert_offsets.numel() < 2
-        or not expert_offsets.is_contiguous()
-    ):
-        raise ValueError(
-            "expert_offsets must be a contiguous CUDA int64 tensor with E+1 entries"
-        )
-    rows, groups = (int(v) for v in logical.shape)
+    _refuse(logical.ndim != 2 or 0 in logical.shape, "logical scales must have shape [M, K / 32]")
+    offsets_ok = (expert_offsets.device == logical.device and expert_offsets.dtype == torch.int64
+                  and expert_offsets.ndim == 1 and expert_offsets.numel() >= 2
+                  and expert_offsets.is_contiguous())
+    _refuse(not offsets_ok, "expert_offsets must be a contiguous CUDA int64 tensor with E+1 entries")
+    rows, groups = map(int, logical.shape)
     experts = expert_offsets.numel() - 1
     # Upper bound of padded rows: every expert may add up to 127 rows of padding.
     padded_rows = (rows + 127) // 128 * 128 + 128 * min(experts, rows)
@@ -486,38 +480,25 @@ def pack_grouped_scales(
 
 
 def pack_operand(codes: torch.Tensor, logical_scales: torch.Tensor) -> PackedMXFP6Tensor:
-    """Pack a logical ``[rows, k]`` E3M2 operand and its UE8M0 scales."""
-    _require_cuda_uint8_contiguous(codes, "codes")
-    _require_cuda_uint8_contiguous(logical_scales, "logical_scales")
-    if codes.ndim != 2:
-        raise ValueError("codes must have shape [rows, k]")
-    rows, k = (int(value) for value in codes.shape)
-    expected_scale_shape = (rows, k // SCALE_VECTOR_SIZE)
-    if k % SCALE_VECTOR_SIZE or tuple(logical_scales.shape) != expected_scale_shape:
-        raise ValueError(
-            f"logical_scales must have shape {expected_scale_shape}; "
-            f"got {tuple(logical_scales.shape)}"
-        )
-    if codes.device != logical_scales.device:
-        raise ValueError("codes and logical_scales must be on the same device")
-    return PackedMXFP6Tensor(
-        pack_fp6(codes),
-        pack_scales(logical_scales),
-        rows,
-        k,
-        logical_scales,
-    )
+    """``[rows, k]`` E3M2 codes + ``[rows, k/32]`` UE8M0 scales -> the packed operand (the
+    logical scales stay attached, so ``unpack_operand`` gives them back without a kernel)."""
+    for tensor, name in ((codes, "codes"), (logical_scales, "logical_scales")):
+        _require_cuda_uint8_contiguous(tensor, name)
+    _refuse(codes.ndim != 2, "codes must have shape [rows, k]")
+    rows, k = map(int, codes.shape)
+    want = (rows, k // SCALE_VECTOR_SIZE)
+    _refuse(k % SCALE_VECTOR_SIZE != 0 or tuple(logical_scales.shape) != want,
+            f"logical_scales must have shape {want}; got {tuple(logical_scales.shape)}")
+    _refuse(codes.device != logical_scales.device, "codes and logical_scales must be on the same device")
+    return PackedMXFP6Tensor(pack_fp6(codes), pack_scales(logical_scales), rows, k, logical_scales)
 
 
 def unpack_operand(operand: PackedMXFP6Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-    """Return logical E3M2 codes and logical UE8M0 scales for an operand."""
-    logical_scales = operand.logical_scales
-    if logical_scales is None:
-        logical_scales = unpack_scales(operand.scales, operand.rows, operand.k)
-    return (
-        unpack_fp6(operand.values, operand.rows, operand.k),
-        logical_scales,
-    )
+    """The inverse of :func:`pack_operand`: ``(codes [rows, k], logical scales [rows, k/32])``."""
+    scales = operand.logical_scales
+    if scales is None:
+        scales = unpack_scales(operand.scales, operand.rows, operand.k)
+    return unpack_fp6(operand.values, operand.rows, operand.k), scales
 
 
 # ----------------------------------------------------------------------- quantizers
@@ -721,22 +702,14 @@ def gemm_w6a8(
 ) -> torch.Tensor:
     """Compute native ``MXFP8(A) @ MXFP6(B).T`` on SM100."""
     out_dtype = _validate_output_dtype(out_dtype)
-    if not isinstance(a, MXFP8Tensor):
-        raise TypeError("a must be an MXFP8Tensor instance")
-    if not isinstance(b, PackedMXFP6Tensor):
-        raise TypeError("b must be a PackedMXFP6Tensor instance")
-    if a.k != b.k:
-        raise ValueError(f"a.k and b.k must match; got {a.k} and {b.k}")
-    if a.device != b.device:
-        raise ValueError("a and b must be on the same CUDA device")
+    _refuse(not isinstance(a, MXFP8Tensor), "a must be an MXFP8Tensor instance", TypeError)
+    _refuse(not isinstance(b, PackedMXFP6Tensor), "b must be a PackedMXFP6Tensor instance", TypeError)
+    _refuse(a.k != b.k, f"a.k and b.k must match; got {a.k} and {b.k}")
+    _refuse(a.device != b.device, "a and b must be on the same CUDA device")
     _validate_problem(a.rows, b.rows, a.k)
-    for tensor, name in (
-        (a.values, "a.values"),
-        (a.scales, "a.scales"),
-        (b.values, "b.values"),
-        (b.scales, "b.scales"),
-    ):
-        _require_cuda_uint8_contiguous(tensor, name)
+    for operand, label in ((a, "a"), (b, "b")):
+        _require_cuda_uint8_contiguous(operand.values, f"{label}.values")
+        _require_cuda_uint8_contiguous(operand.scales, f"{label}.scales")
     _require_sm100(a.device)
     load_library()
     if out is None:

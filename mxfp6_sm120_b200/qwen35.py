@@ -9,6 +9,7 @@ decode schedule (one single-row GEMM per route) takes any small batch, not one t
 
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass
 
 import torch
@@ -105,6 +106,8 @@ def qwen35_grouped_workspace_shapes(
 
 
 class _ByteArena:
+    """Carves typed, aligned views out of one caller-owned allocation, front to back."""
+
     def __init__(self, storage: torch.Tensor, offset: int = 0) -> None:
         if not storage.is_contiguous():
             raise ValueError("workspace storage must be contiguous")
@@ -112,18 +115,14 @@ class _ByteArena:
         self.offset = offset
 
     def take(self, shape: tuple[int, ...], dtype: torch.dtype, alignment: int) -> torch.Tensor:
-        elements = 1
-        for dimension in shape:
-            elements *= dimension
-        size = elements * torch.empty((), dtype=dtype).element_size()
-        base = self.storage.data_ptr()
-        self.offset = _align_up(base + self.offset, alignment) - base
-        end = self.offset + size
-        if end > self.storage.numel():
+        nbytes = math.prod(shape) * dtype.itemsize
+        # alignment is a property of the ADDRESS, not of the offset into the allocation
+        address = self.storage.data_ptr() + self.offset
+        begin = self.offset + (-address) % alignment
+        if begin + nbytes > self.storage.numel():
             raise ValueError("grouped MoE workspace is too small")
-        result = self.storage[self.offset : end].view(dtype).view(shape)
-        self.offset = end
-        return result
+        self.offset = begin + nbytes
+        return self.storage[begin : self.offset].view(dtype).view(shape)
 
 
 @dataclass(frozen=True)
