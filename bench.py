@@ -569,10 +569,10 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--row-sum", default="auto", choices=["auto", "nccl", "peer"],
-                        help="N > 1: sum of the prefill-sized row-parallel outputs through NCCL or "
-                             "through this library's two-phase peer-memory kernels (auto: peer from "
-                             "4 GPUs on)")
+    parser.add_argument("--row-sum", default="nccl", choices=["nccl", "nccl_pair", "peer"],
+                        help="N > 1: sum of the prefill-sized row-parallel outputs: one NCCL "
+                             "all-reduce per projection, one per batch size over both projections' "
+                             "outputs, or this library's two-phase peer-memory kernels")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--no-moe", action="store_true")
@@ -609,6 +609,18 @@ def main() -> None:
     layers, acts = build_sweep(mx, device, rank, world)
     outs = {key: torch.empty((key[0], layers[key[1:]][0].rows), dtype=torch.bfloat16, device=device)
             for key in acts}
+    # nccl_pair: the two row-parallel outputs of a batch size sit in one buffer and are summed
+    # by one all-reduce (half as many collectives, twice the message)
+    row_pairs = {}
+    if world > 1 and args.row_sum == "nccl_pair":
+        row_shapes = [s for s in NK_SHAPES if s in ROW_PARALLEL]
+        for m in M_VALUES:
+            width = layers[row_shapes[0]][0].rows
+            assert all(layers[s][0].rows == width for s in row_shapes)
+            both = torch.empty((len(row_shapes), m, width), dtype=torch.bfloat16, device=device)
+            for index, shape in enumerate(row_shapes):
+                outs[(m, *shape)] = both[index]
+            row_pairs[m] = (both, (m, *row_shapes[-1]))
     # M-major.  Sharded, the two row-parallel projections of a batch size go first, so
     # that their sums run beside the three column-parallel GEMMs that follow.
     # (row, column, row, column, column: every sum has a GEMM to run beside.)
@@ -631,11 +643,14 @@ def main() -> None:
         out = mx.gemm_from_float(acts[key] if a is None else a, weight, out_dtype=torch.bfloat16,
                                  out=outs[key])
         if mode == "row" and world > 1:
+            pair = row_pairs.get(key[0])
+            if pair is not None and key != pair[1]:
+                return out          # summed together with the batch size's other projection
             computed = torch.cuda.Event()
             computed.record(torch.cuda.current_stream(device))
             reduce_stream.wait_event(computed)
             with torch.cuda.stream(reduce_stream):
-                dist.all_reduce(out)
+                dist.all_reduce(out if pair is None else pair[0])
         return out
 
     def run_shape_peer(key, peer):
@@ -654,7 +669,7 @@ def main() -> None:
         try:  # raises on every rank alike when any rank could not map a peer's block
             sweep_peer = SymmetricBlocks(tp.PEER_ALLREDUCE_MAX_ROWS, max(n for n, _ in ROW_PARALLEL),
                                          device)
-            if args.row_sum == "peer" or (args.row_sum == "auto" and world >= 4):
+            if args.row_sum == "peer":
                 big_peer = SymmetricBlocks(max(M_VALUES), max(n for n, _ in ROW_PARALLEL), device)
         except RuntimeError:
             sweep_peer = big_peer = None
@@ -766,6 +781,9 @@ def main() -> None:
                         sweep_peer.allreduce(outs[key])
                     elif big_peer is not None and key[0] % world == 0:
                         big_peer.allreduce_any(outs[key])
+                    elif key[0] in row_pairs:
+                        if key == row_pairs[key[0]][1]:
+                            dist.all_reduce(row_pairs[key[0]][0])
                     else:
                         dist.all_reduce(outs[key])
 
@@ -910,7 +928,7 @@ def main() -> None:
                    "row-parallel + all-reduce (one peer-memory kernel up to 256 rows; above, "
                    + ("two-phase peer-memory kernels" if big_peer is not None else "NCCL")
                    + " on a side stream beside the following shapes' GEMMs)",
-                   "row_sum": "peer" if big_peer is not None else "nccl",
+                   "row_sum": args.row_sum,
                    "l2": "inputs larger than L2: shapes run M-major, 270 MB of packed weights "
                          "cycle through the 126 MB L2 between reuses",
                    "graph": "one CUDA graph per step"},
