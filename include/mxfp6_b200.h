@@ -374,7 +374,10 @@ int mxfp6_array_gemm_w6a8_reduce(void* output_dev, int out_dtype, const uint8_t*
  * [experts, 2 * inter, 3 * hidden_size / 4], w2 [experts, hidden_size, 3 * inter / 4], the last
  * matrix of both the shared expert unless the four shared_* pointers bring it; activation
  * [tokens * (topk + 1), inter] + activation_scales [.., inter / 32] are scratch; topk_ids /
- * topk_weights receive the selection; output [tokens, hidden_size].  _supported returns 1 when
+ * topk_weights receive the selection; output [tokens, hidden_size].  w2_own_routing != 0: the
+ * second launch repeats the selection for itself before its dependency wait and fetches
+ * weights meanwhile; 0: it reads topk_ids / topk_weights once the first has completed (same
+ * bytes either way).  _supported returns 1 when
  * the shapes fit (topk <= 8, inter <= 2048, at most 16 blocks of 128 hidden values per CTA of
  * the W1 launch); otherwise use the three entry points above.  _preferred returns 1 when this
  * form is also expected to be the faster one (the front kernel it saves against the top-k every
@@ -392,7 +395,8 @@ int mxfp6_moe_decode_layer(void* output_dev, int out_dtype, const void* hidden_d
                            const uint8_t* shared_w2_scales_dev, uint8_t* activation_dev,
                            uint8_t* activation_scales_dev, int32_t* topk_ids_dev,
                            float* topk_weights_dev, int64_t tokens, int topk, int logit_experts,
-                           int renormalize, int64_t hidden_size, int64_t inter, void* stream);
+                           int renormalize, int64_t hidden_size, int64_t inter, int w2_own_routing,
+                           void* stream);
 /* torch.ops.mxfp6.moe_reduce_array_out (schema csrc/moe.cu:10129-10131, kernel :8237-8282):
  * combined [tokens * (topk + 1), hidden], the shared row last of each token. */
 int mxfp6_moe_reduce_array(void* output_dev, const void* combined_dev, int dtype,

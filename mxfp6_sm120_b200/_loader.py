@@ -136,7 +136,7 @@ SIGNATURES: dict[str, tuple] = {
         c_int,
         [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
          c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-         c_void_p, c_int64, c_int, c_int, c_int, c_int64, c_int64, c_void_p],
+         c_void_p, c_int64, c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p],
     ),
     "mxfp6_moe_reduce_tp_pointers": (
         c_int,

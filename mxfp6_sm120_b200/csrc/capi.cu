@@ -87,7 +87,7 @@ int moe_decode_layer_preferred(int64_t, int, int, int64_t, int64_t);
 int moe_decode_layer(void*, int, const void*, const void*, const void*, int, int, const uint8_t*,
                      const uint8_t*, const uint8_t*, const uint8_t*, int, const uint8_t*,
                      const uint8_t*, const uint8_t*, const uint8_t*, uint8_t*, uint8_t*, int32_t*,
-                     float*, int64_t, int, int, int, int64_t, int64_t, cudaStream_t);
+                     float*, int64_t, int, int, int, int64_t, int64_t, int, cudaStream_t);
 int moe_reduce_array(void*, const void*, int, const float*, const void*, int, int, int64_t, int,
                      int64_t, cudaStream_t);
 int moe_router_logits(const void*, const void*, const void*, void*, void*, int64_t, int64_t, int,
@@ -788,12 +788,13 @@ int mxfp6_moe_decode_layer(void* output, int out_dtype, const void* hidden, cons
                            const uint8_t* shared_w2_scales, uint8_t* activation,
                            uint8_t* activation_scales, int32_t* topk_ids, float* topk_weights,
                            int64_t tokens, int topk, int logit_experts, int renormalize,
-                           int64_t hidden_size, int64_t inter, void* stream) {
+                           int64_t hidden_size, int64_t inter, int w2_own_routing, void* stream) {
   return moe_decode_layer(output, out_dtype, hidden, router_logits, shared_gate, gate_dtype,
                           gate_stride, w1, w1_scales, w2, w2_scales, experts, shared_w1,
                           shared_w1_scales, shared_w2, shared_w2_scales, activation,
                           activation_scales, topk_ids, topk_weights, tokens, topk, logit_experts,
-                          renormalize, hidden_size, inter, static_cast<cudaStream_t>(stream));
+                          renormalize, hidden_size, inter, w2_own_routing,
+                          static_cast<cudaStream_t>(stream));
 }
 
 int mxfp6_moe_reduce_array(void* output, const void* combined, int dtype, const float* topk_weights,

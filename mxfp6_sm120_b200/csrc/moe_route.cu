@@ -1460,7 +1460,7 @@ int moe_decode_layer(void* out, int out_dtype, const void* hidden, const void* l
                      const uint8_t* shared_w2, const uint8_t* shared_w2_scales, uint8_t* activation,
                      uint8_t* activation_scales, int32_t* topk_ids, float* topk_weights,
                      int64_t tokens, int topk, int logit_experts, int renormalize,
-                     int64_t hidden_size, int64_t inter, cudaStream_t stream) {
+                     int64_t hidden_size, int64_t inter, int w2_own_routing, cudaStream_t stream) {
   MX_REQUIRE(out && hidden && logits && shared_gate && w1 && w1_scales && w2 && w2_scales &&
                  activation && activation_scales && topk_ids && topk_weights,
              "pointers must not be null");
@@ -1554,10 +1554,12 @@ int moe_decode_layer(void* out, int out_dtype, const void* hidden, const void* l
   config.attrs = attribute;
   config.numAttrs = count;
   MX_CUDA(cudaLaunchKernelEx(&config, route_w1_front_kernel, tm_w, tm_shared, args));
+  // W2 either repeats the selection for itself before its dependency wait (and fills its ring
+  // with weights meanwhile), or reads the ids and weights W1 wrote once W1 has completed.
   return moe_route_w2_reduce(out, out_dtype, activation, activation_scales, w2, w2_scales, num_experts,
                              shared_w2, shared_w2_scales, topk_ids, 0, topk_weights, shared_gate,
                              gate_dtype, gate_stride, nullptr, 1, tokens, topk, hidden_size, inter, 0,
-                             logits, logit_experts, renormalize, stream);
+                             w2_own_routing != 0 ? logits : nullptr, logit_experts, renormalize, stream);
 }
 
 // Router half of torch.ops.mxfp6.qwen35_router_quant_out (csrc/moe.cu:237-511): the BF16 gate

@@ -1226,6 +1226,7 @@ def moe_decode_layer_out(
     shared_w2: torch.Tensor | None = None,
     shared_w2_scales: torch.Tensor | None = None,
     renormalize: bool = True,
+    w2_own_routing: bool = True,
 ) -> None:
     """The decode schedule in two launches: top-k selection and MXFP8 quantization of the hidden
     rows happen inside the W1 kernel's CTAs (and the selection once more inside W2's), so no
@@ -1235,7 +1236,8 @@ def moe_decode_layer_out(
     ``qwen35_w2_splitk_reduce_out`` (the reference's schedule, python/mxfp6/qwen35.py:384-432).
     ``w1`` ``[E(+1), 2I, 3H/4]``, ``w2`` ``[E(+1), H, 3I/4]``; the shared expert is the last
     matrix of both unless the four ``shared_*`` tensors bring it.  ``activation``
-    ``[tokens * (topk + 1), I]`` and ``activation_scales`` are scratch.
+    ``[tokens * (topk + 1), I]`` and ``activation_scales`` are scratch.  ``w2_own_routing=False``
+    makes W2 read the ids and weights W1 wrote instead of selecting again (same bytes).
     """
     if (
         hidden.device.type != "cuda"
@@ -1303,6 +1305,6 @@ def moe_decode_layer_out(
                 int(w1.shape[0]), _ptr(shared_w1), _ptr(shared_w1_scales), _ptr(shared_w2),
                 _ptr(shared_w2_scales), _as_u8(activation).data_ptr(), activation_scales.data_ptr(),
                 topk_ids.data_ptr(), topk_weights.data_ptr(), tokens, topk, experts, int(renormalize),
-                width, inter, _stream(hidden.device),
+                width, inter, int(bool(w2_own_routing)), _stream(hidden.device),
             )
         )
