@@ -21,6 +21,8 @@
 
 #include <cuda_fp8.h>
 
+#include <cstdlib>
+
 namespace mx {
 namespace {
 
@@ -613,7 +615,13 @@ int moe_topk_quant(const void* hidden, const void* logits, int64_t tokens, int h
     MX_REQUIRE(experts > 0 && experts <= kMaxExperts, "experts must be in [1, %d]", kMaxExperts);
     MX_REQUIRE(topk > 0 && topk <= kMaxTopk && topk <= experts, "topk must be in [1, %d]", kMaxTopk);
   }
-  const int tokens_per_cta = tokens <= 148 ? 1 : 8;
+  // One token per CTA lets the top-k run in a warp of its own beside the quantization;
+  // MXFP6_B200_TOPK_ROWS=8 restores eight tokens per CTA for batches above 148 tokens.
+  static const int wide_rows = []() {
+    const char* env = std::getenv("MXFP6_B200_TOPK_ROWS");
+    return env != nullptr && env[0] == '8' ? 8 : 1;
+  }();
+  const int tokens_per_cta = tokens <= 148 ? 1 : wide_rows;
   const unsigned grid = (unsigned)((tokens + tokens_per_cta - 1) / tokens_per_cta);
   // One token per CTA: the top-k gets a warp of its own beside the 256 quantizing threads.
   const bool own_topk_warp = tokens_per_cta == 1 && topk_ids != nullptr && quantized != nullptr;
