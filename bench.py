@@ -569,10 +569,12 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--row-sum", default="nccl", choices=["nccl", "nccl_pair", "peer"],
+    parser.add_argument("--row-sum", default="nccl_pair",
+                        choices=["nccl", "nccl_pair", "nccl_merged", "peer"],
                         help="N > 1: sum of the prefill-sized row-parallel outputs: one NCCL "
                              "all-reduce per projection, one per batch size over both projections' "
-                             "outputs, or this library's two-phase peer-memory kernels")
+                             "outputs, two over all prefill batches, or this library's two-phase "
+                             "peer-memory kernels")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--no-moe", action="store_true")
@@ -609,30 +611,44 @@ def main() -> None:
     layers, acts = build_sweep(mx, device, rank, world)
     outs = {key: torch.empty((key[0], layers[key[1:]][0].rows), dtype=torch.bfloat16, device=device)
             for key in acts}
-    # nccl_pair: the two row-parallel outputs of a batch size sit in one buffer and are summed
-    # by one all-reduce (half as many collectives, twice the message)
-    row_pairs = {}
-    if world > 1 and args.row_sum == "nccl_pair":
-        row_shapes = [s for s in NK_SHAPES if s in ROW_PARALLEL]
-        for m in M_VALUES:
-            width = layers[row_shapes[0]][0].rows
-            assert all(layers[s][0].rows == width for s in row_shapes)
-            both = torch.empty((len(row_shapes), m, width), dtype=torch.bfloat16, device=device)
-            for index, shape in enumerate(row_shapes):
-                outs[(m, *shape)] = both[index]
-            row_pairs[m] = (both, (m, *row_shapes[-1]))
-    # M-major.  Sharded, the two row-parallel projections of a batch size go first, so
-    # that their sums run beside the three column-parallel GEMMs that follow.
-    # (row, column, row, column, column: every sum has a GEMM to run beside.)
-    shapes = NK_SHAPES
-    if world > 1:
-        rows_first = [s for s in NK_SHAPES if s in ROW_PARALLEL]
-        columns = [s for s in NK_SHAPES if s not in ROW_PARALLEL]
-        shapes = [rows_first[0], columns[0], rows_first[1]] + columns[1:]
-    # Sharded, the large batches also go first: their sums are the long pole (two times 84 MB
-    # at 8192 rows) and then run beside everything that follows instead of after it.
+    # Sharded: which row-parallel outputs one all-reduce sums.  nccl = one per projection;
+    # nccl_pair = both projections of a batch size in one buffer; nccl_merged = the prefill
+    # batches in two buffers (8192 rows; 4096 down to 512 rows), whose GEMMs all run first so
+    # that two large all-reduces run beside every column-parallel GEMM of the step.
     m_order = M_VALUES if world == 1 else sorted(M_VALUES, reverse=True)
-    order = [(m, n, k) for m in m_order for (n, k) in shapes]
+    rows_first = [s for s in NK_SHAPES if s in ROW_PARALLEL]
+    columns = [s for s in NK_SHAPES if s not in ROW_PARALLEL]
+    sum_groups = []
+    if world > 1 and args.row_sum == "nccl_pair":
+        sum_groups = [[m] for m in m_order]
+    elif world > 1 and args.row_sum == "nccl_merged":
+        large = [m for m in m_order if m > 256]
+        sum_groups = [large[:1], large[1:]]
+    row_pairs = {}
+    for group in sum_groups:
+        width = layers[rows_first[0]][0].rows
+        assert all(layers[s][0].rows == width for s in rows_first)
+        flat = torch.empty((sum(group) * len(rows_first), width), dtype=torch.bfloat16, device=device)
+        begin = 0
+        for m in group:
+            for shape in rows_first:
+                outs[(m, *shape)] = flat[begin: begin + m]
+                begin += m
+        for m in group:
+            row_pairs[m] = (flat, (group[-1], *rows_first[-1]))   # summed after the group's last GEMM
+    # M-major.  Sharded, the large batches go first (their sums are the long pole) and row and
+    # column shapes alternate (row, column, row, column, column: every sum has a GEMM to run
+    # beside); with merged sums every prefill-sized row-parallel GEMM comes before the others.
+    if world == 1:
+        order = [(m, n, k) for m in m_order for (n, k) in NK_SHAPES]
+    else:
+        mixed = [rows_first[0], columns[0], rows_first[1]] + columns[1:]
+        if args.row_sum == "nccl_merged":
+            large = [m for m in m_order if m > 256]
+            order = ([(m, *s) for m in large for s in rows_first] + [(m, *s) for m in large for s in columns]
+                     + [(m, *s) for m in m_order if m <= 256 for s in mixed])
+        else:
+            order = [(m, *s) for m in m_order for s in mixed]
 
     # Prefill-sized row-parallel sums (NCCL, bandwidth bound) run on a side stream beside the
     # GEMMs of the following shapes; the sweep's shapes do not depend on one another.
