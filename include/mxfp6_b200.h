@@ -380,8 +380,7 @@ int mxfp6_array_gemm_w6a8_reduce(void* output_dev, int out_dtype, const uint8_t*
  * bytes either way).  _supported returns 1 when
  * the shapes fit (topk <= 8, inter <= 2048, at most 16 blocks of 128 hidden values per CTA of
  * the W1 launch); otherwise use the three entry points above.  _preferred returns 1 when this
- * form is also expected to be the faster one (the front kernel it saves against the top-k every
- * CTA of the second launch repeats; host arithmetic over the two grids). */
+ * form is also expected to be the faster one (measured: wherever it is supported). */
 int mxfp6_moe_decode_layer_supported(int64_t tokens, int topk, int logit_experts,
                                      int64_t hidden_size, int64_t inter);
 int mxfp6_moe_decode_layer_preferred(int64_t tokens, int topk, int logit_experts,

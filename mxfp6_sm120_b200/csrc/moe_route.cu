@@ -1429,22 +1429,15 @@ int moe_decode_layer_supported(int64_t tokens, int topk, int logit_experts, int6
   return (k_blocks + ck - 1) / ck <= FCfg::kMaxBlocks ? 1 : 0;
 }
 
-// Whether the two-launch form is expected to beat top-k kernel + W1 + W2.  It saves the front
-// kernel (about 3 us) but every W2 CTA repeats the top-k (about 1.5 us), which is hidden only
-// while W2's CTAs sit beside W1's on the GPU or W1's tail is long: measured on the named shape
-// (hidden 2048, intermediate 512, 256 experts, top-8; two / three launches, warm, us) 16.6 / 16.5
-// at 1 token, 21.1 / 18.8 at 2 (W1 in clusters of three, W2 not resident beside it), 24.7 / 27.0
-// at 4, 38.5 / 39.2 at 8.
+// Whether the two-launch form is expected to beat top-k kernel + W1 + W2: wherever it is
+// supported.  Measured on the named shape (hidden 2048, intermediate 512, 256 experts, top-8;
+// warm, us per layer; three launches / two with W2 selecting again / two with W2 reading the
+// ids W1 wrote): 16.5 / 16.6 / 16.5 at 1 token, 19.0 / 20.9 / 18.5 at 2, 26.5 / 26.1 / 24.7 at 4,
+// 39.0 / 38.2 / 37.1 at 8, 61.0 / 60.3 / 59.4 at 16, 110.8 / 112.3 / 110.6 at 32.  W2 repeating the
+// selection pays only while its CTAs sit beside W1's (1 token); reading the ids is never worse.
 int moe_decode_layer_preferred(int64_t tokens, int topk, int logit_experts, int64_t hidden_size,
                                int64_t inter) {
-  if (moe_decode_layer_supported(tokens, topk, logit_experts, hidden_size, inter) == 0) return 0;
-  const int lanes = topk + 1;
-  const int64_t w1_units = tokens * lanes * (inter / kTileF);
-  const int ck = w1_cluster(w1_units, (int)(hidden_size / kTileK));
-  const int64_t w2_units = tokens * (hidden_size / kTileF);
-  const int64_t slots = 2 * (int64_t)sm_count() - 8;
-  const int cr = lane_cluster(w2_units, lanes);
-  return (w1_units * ck + w2_units * cr <= slots || ck <= 2) ? 1 : 0;
+  return moe_decode_layer_supported(tokens, topk, logit_experts, hidden_size, inter);
 }
 
 // The decode schedule of one routed-MoE layer in two launches (the reference's three-kernel

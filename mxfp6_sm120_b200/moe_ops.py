@@ -1226,18 +1226,20 @@ def moe_decode_layer_out(
     shared_w2: torch.Tensor | None = None,
     shared_w2_scales: torch.Tensor | None = None,
     renormalize: bool = True,
-    w2_own_routing: bool = True,
+    w2_own_routing: bool = False,
 ) -> None:
     """The decode schedule in two launches: top-k selection and MXFP8 quantization of the hidden
-    rows happen inside the W1 kernel's CTAs (and the selection once more inside W2's), so no
-    front-end kernel runs and W1 depends on nothing but ``hidden`` and ``router_logits``.
+    rows happen inside the W1 kernel's CTAs, so no front-end kernel runs and W1 depends on
+    nothing but ``hidden`` and ``router_logits``.
 
     Same results as ``qwen35_topk_quant_out`` -> ``qwen35_w1_splitk_silu_mxfp8_out`` ->
     ``qwen35_w2_splitk_reduce_out`` (the reference's schedule, python/mxfp6/qwen35.py:384-432).
     ``w1`` ``[E(+1), 2I, 3H/4]``, ``w2`` ``[E(+1), H, 3I/4]``; the shared expert is the last
     matrix of both unless the four ``shared_*`` tensors bring it.  ``activation``
-    ``[tokens * (topk + 1), I]`` and ``activation_scales`` are scratch.  ``w2_own_routing=False``
-    makes W2 read the ids and weights W1 wrote instead of selecting again (same bytes).
+    ``[tokens * (topk + 1), I]`` and ``activation_scales`` are scratch.  W2 reads the ids and
+    weights W1 wrote; ``w2_own_routing=True`` makes it select again for itself before its
+    dependency wait and fetch weights meanwhile (same bytes; it pays only while W2's CTAs fit
+    on the GPU beside W1's).
     """
     if (
         hidden.device.type != "cuda"

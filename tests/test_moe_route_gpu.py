@@ -298,7 +298,7 @@ def test_decode_schedule_named_config_against_oracle_and_graph(mx, named_layer, 
     # two launches (top-k and quantization inside the W1 kernel) and three launches give the
     # same bytes, ids and weights; the default picks one of them by the size of the grids
     assert mx.moe_decode_layer_supported(tokens, shape.topk, e, h, i)
-    assert mx.moe_decode_layer_preferred(tokens, shape.topk, e, h, i) == (tokens != 2)
+    assert mx.moe_decode_layer_preferred(tokens, shape.topk, e, h, i)
     ws3 = mx.Qwen35MoeB1Workspace.allocate(DEV, shape, batch=tokens)
     three = mx.qwen35_moe_decode_logits_out(ws3, hidden_d, logits_d, gate_d, w1v, w1.scales, w2v, w2.scales,
                                             sw1, sw2, renormalize=True, two_launches=False)
@@ -308,6 +308,13 @@ def test_decode_schedule_named_config_against_oracle_and_graph(mx, named_layer, 
                                           sw1, sw2, renormalize=True, two_launches=True)
     assert torch.equal(two, out)
     assert torch.equal(ws2.topk_ids, ws.topk_ids) and torch.equal(ws2.topk_weights, ws.topk_weights)
+    # and with W2 selecting the experts again for itself instead of reading W1's ids
+    own = torch.empty_like(out)
+    mx.moe_decode_layer_out(own, ws2.activation, ws2.activation_scales, ws2.topk_weights, ws2.topk_ids,
+                            hidden_d, logits_d, gate_d, w1v, w1.scales, w2v, w2.scales,
+                            sw1.values.view(1, 2 * i, -1), sw1.scales, sw2.values.view(1, h, -1), sw2.scales,
+                            renormalize=True, w2_own_routing=True)
+    assert torch.equal(own, out)
     assert torch.equal(ws3.topk_ids, ws.topk_ids) and torch.equal(ws3.topk_weights, ws.topk_weights)
     assert torch.equal(ws3.activation.view(torch.uint8), ws.activation.view(torch.uint8))
     assert torch.equal(ws3.activation_scales, ws.activation_scales)

@@ -121,12 +121,11 @@ def test_explicit_configurations_are_described_and_validated():
 def test_decode_layer_schedule_choice_is_host_arithmetic():
     """Which decode schedule a routed-MoE batch takes is decided on the host from the two grids
     (148 SMs assumed): two launches need at most 16 blocks of 128 hidden values per W1 CTA and
-    pay when W1 runs without a wide cluster or W2 fits beside it."""
+    are taken wherever they fit."""
     named = dict(topk=8, experts=256, hidden_size=2048, intermediate=512)
     for tokens in (1, 2, 3, 4, 8, 16, 32, 64):
         assert mx.moe_decode_layer_supported(tokens, **named)
-    assert [mx.moe_decode_layer_preferred(t, **named) for t in (1, 2, 3, 4, 8, 32)] == [
-        True, False, True, True, True, True]
+    assert all(mx.moe_decode_layer_preferred(t, **named) for t in (1, 2, 3, 4, 8, 32))
     # hidden 5120: 40 K blocks, so only launches that split K over a cluster fit the 16 slots
     assert mx.moe_decode_layer_supported(1, 8, 256, 5120, 512)
     assert not mx.moe_decode_layer_supported(8, 8, 256, 5120, 512)
