@@ -71,6 +71,16 @@ class TensorSource:
             self._open[file] = safe_open(file, framework="pt", device="cpu")
         return self._open[file]
 
+    def close(self) -> None:
+        """Drop the open file handles (tensors already returned stay valid)."""
+        self._open.clear()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()
+
     def __contains__(self, name: str) -> bool:
         return name in (self._memory if self._memory is not None else self._files)
 
