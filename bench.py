@@ -569,12 +569,14 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--row-sum", default="nccl_pair",
-                        choices=["nccl", "nccl_pair", "nccl_merged", "peer"],
+    parser.add_argument("--row-sum", default="auto",
+                        choices=["auto", "nccl", "nccl_pair", "nccl_merged", "peer"],
                         help="N > 1: sum of the prefill-sized row-parallel outputs: one NCCL "
                              "all-reduce per projection, one per batch size over both projections' "
                              "outputs, two over all prefill batches, or this library's two-phase "
-                             "peer-memory kernels")
+                             "peer-memory kernels.  auto = nccl_merged at 8 GPUs, nccl_pair below "
+                             "(measured TFLOP/s at 8 GPUs: nccl 4835, nccl_pair 5054, nccl_merged "
+                             "5268, peer 4287; at 2 GPUs: 3070, 3168, 3006, 3037)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--no-moe", action="store_true")
@@ -607,6 +609,8 @@ def main() -> None:
     parity = None
     if world > 1:
         parity = parity_check_sharded(mx, device, world, rank)
+    if args.row_sum == "auto":
+        args.row_sum = "nccl_merged" if world >= 8 else "nccl_pair"
 
     layers, acts = build_sweep(mx, device, rank, world)
     outs = {key: torch.empty((key[0], layers[key[1:]][0].rows), dtype=torch.bfloat16, device=device)
