@@ -28,7 +28,7 @@ from .qwen35 import (
 # Batches of at most this many tokens take the decode schedule (one single-row GEMM per
 # route, three launches); larger ones the grouped schedule.  Measured on a B200 with the
 # named configuration (hidden 2048, 256 experts, top-8, intermediate 512), warm, decode
-# against grouped: 16.5 / 35 us at 1 token, 37.5 / 66 at 8, 58 / 82 at 16, 107 / 115 at 32;
+# against grouped: 16.5 / 35 us at 1 token, 36.9 / 66 at 8, 59 / 82 at 16, 111 / 115 at 32;
 # beyond that the grouped schedule reads every expert once and wins.
 DECODE_MAX_TOKENS = 32
 
