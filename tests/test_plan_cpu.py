@@ -30,14 +30,18 @@ def test_named_sweep_plans(m, n, k):
         else:
             assert plan["cluster_k"] == 1 and plan["grid"] == n_tiles <= 288
     elif m <= 96:
-        # one row tile of exactly the batch's width class, weights streamed once
-        assert plan["kernel"] == "persistent" and plan["cta_pair"] == 0 and tile >= m
-        if 2 * n_tiles <= 148:
+        # 65..96 rows: two 64-row tiles per feature tile while the weights (read twice then)
+        # fit the L2, else one 96-row tile; 64 rows of the widest matrix: one 64-row tile
+        two_tiles = m > 64 and n * k * 3 // 4 <= 32 << 20
+        assert plan["kernel"] == "persistent" and plan["cta_pair"] == 0
+        assert tile == (64 if (two_tiles or m <= 64) else 96)
+        tiles = n_tiles * -(-m // tile)
+        if 2 * tiles <= 148:
             # too few tiles for the GPU: clusters split K, and every cluster fits the GPU
             assert 2 <= plan["cluster_k"] <= 8
-            assert plan["grid"] == n_tiles * plan["cluster_k"] <= 148
+            assert plan["grid"] == tiles * plan["cluster_k"] <= 148
         else:
-            assert plan["cluster_k"] == 1 and plan["grid"] == min(n_tiles, 148)
+            assert plan["cluster_k"] == 1 and plan["grid"] == min(tiles, 148)
     else:
         # prefill batches run on CTA pairs: 256 weight rows per tile, an even grid
         assert plan["cta_pair"] == 1 and plan["kernel"] == "cta_pair" and tile in (128, 192, 256)

@@ -35,8 +35,11 @@ def _expected_plan(m: int, n: int, k: int) -> dict:
         return {"kernel": "stream", "tile_tokens": 16 if m <= 16 else 32 if m <= 32 else 64,
                 "cluster_k": max(ck, 1), "cta_pair": 0, "splits": 1}
     if m <= 96:
-        ck = min(8, (148 - 16) // n_tiles, k // 128) if 2 * n_tiles <= 148 else 1
-        return {"kernel": "persistent", "tile_tokens": 64 if m <= 64 else 96,
+        # 65..96 rows: two 64-row tiles while the weights fit the L2, else one 96-row tile
+        tile = 64 if (m <= 64 or n * k * 3 // 4 <= 32 << 20) else 96
+        tiles = n_tiles * -(-m // tile)
+        ck = min(8, (148 - 16) // tiles, k // 128) if 2 * tiles <= 148 else 1
+        return {"kernel": "persistent", "tile_tokens": tile,
                 "cluster_k": ck if ck >= 2 else 1, "cta_pair": 0, "splits": 1}
     return {"kernel": "cta_pair", "cluster_k": 1, "cta_pair": 1, "splits": 1}
 

@@ -106,12 +106,12 @@ def test_static_scratch_rejects_oversized_problems(mx):
     lib = library()
     mx.set_split_k_mode("workspace")
     try:
-        plan = mx.gemm_w6a8_plan(96, 7168, 5120)
+        plan = mx.gemm_w6a8_plan(96, 5120, 17408)
     finally:
         mx.set_split_k_mode("cluster")
     assert plan["partial_bytes"] > 4 << 20  # needs more than the 4 MiB built in
-    act, wgt = _operands(mx, 96, 7168, 5120, seed=7)
-    out = torch.empty((96, 7168), dtype=torch.bfloat16, device=DEV)
+    act, wgt = _operands(mx, 96, 5120, 17408, seed=7)
+    out = torch.empty((96, 5120), dtype=torch.bfloat16, device=DEV)
     assert _call(lib, "mxfp6_gemm_w6a8_static_scratch", act, wgt, out) == 1
     message = lib.mxfp6_b200_last_error().decode()
     assert "built-in array" in message and str(plan["partial_bytes"]) in message
