@@ -570,13 +570,14 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--row-sum", default="auto",
-                        choices=["auto", "nccl", "nccl_pair", "nccl_merged", "peer"],
+                        choices=["auto", "nccl", "nccl_pair", "nccl_merged", "nccl_early", "peer"],
                         help="N > 1: sum of the prefill-sized row-parallel outputs: one NCCL "
                              "all-reduce per projection, one per batch size over both projections' "
                              "outputs, two over all prefill batches, or this library's two-phase "
-                             "peer-memory kernels.  auto = nccl_merged at 8 GPUs, nccl_pair below "
+                             "peer-memory kernels.  auto = nccl_early at 8 GPUs, nccl_pair below "
                              "(measured TFLOP/s at 8 GPUs: nccl 4835, nccl_pair 5054, nccl_merged "
-                             "5268, peer 4287; at 2 GPUs: 3070, 3168, 3006, 3037)")
+                             "5268, peer 4287; at 2 GPUs: 3070, 3168, 3006, 3037; nccl_early is "
+                             "nccl_merged with its first sum one GEMM earlier)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--no-moe", action="store_true")
@@ -610,7 +611,7 @@ def main() -> None:
     if world > 1:
         parity = parity_check_sharded(mx, device, world, rank)
     if args.row_sum == "auto":
-        args.row_sum = "nccl_merged" if world >= 8 else "nccl_pair"
+        args.row_sum = "nccl_early" if world >= 8 else "nccl_pair"
 
     layers, acts = build_sweep(mx, device, rank, world)
     outs = {key: torch.empty((key[0], layers[key[1:]][0].rows), dtype=torch.bfloat16, device=device)
@@ -618,28 +619,31 @@ def main() -> None:
     # Sharded: which row-parallel outputs one all-reduce sums.  nccl = one per projection;
     # nccl_pair = both projections of a batch size in one buffer; nccl_merged = the prefill
     # batches in two buffers (8192 rows; 4096 down to 512 rows), whose GEMMs all run first so
-    # that two large all-reduces run beside every column-parallel GEMM of the step.
+    # that two large all-reduces run beside every column-parallel GEMM of the step;
+    # nccl_early = the same two all-reduces, the first one over the first GEMM's output alone
+    # so that the sums start one GEMM into the step.
     m_order = M_VALUES if world == 1 else sorted(M_VALUES, reverse=True)
     rows_first = [s for s in NK_SHAPES if s in ROW_PARALLEL]
     columns = [s for s in NK_SHAPES if s not in ROW_PARALLEL]
+    merged_order = ("nccl_merged", "nccl_early")
+    large_rows = [(m, *s) for m in m_order if m > 256 for s in rows_first]
     sum_groups = []
     if world > 1 and args.row_sum == "nccl_pair":
-        sum_groups = [[m] for m in m_order]
+        sum_groups = [[(m, *s) for s in rows_first] for m in m_order]
     elif world > 1 and args.row_sum == "nccl_merged":
-        large = [m for m in m_order if m > 256]
-        sum_groups = [large[:1], large[1:]]
+        sum_groups = [large_rows[: len(rows_first)], large_rows[len(rows_first):]]
+    elif world > 1 and args.row_sum == "nccl_early":
+        sum_groups = [large_rows[:1], large_rows[1:]]
     row_pairs = {}
     for group in sum_groups:
         width = layers[rows_first[0]][0].rows
-        assert all(layers[s][0].rows == width for s in rows_first)
-        flat = torch.empty((sum(group) * len(rows_first), width), dtype=torch.bfloat16, device=device)
+        assert all(layers[key[1:]][0].rows == width for key in group)
+        flat = torch.empty((sum(key[0] for key in group), width), dtype=torch.bfloat16, device=device)
         begin = 0
-        for m in group:
-            for shape in rows_first:
-                outs[(m, *shape)] = flat[begin: begin + m]
-                begin += m
-        for m in group:
-            row_pairs[m] = (flat, (group[-1], *rows_first[-1]))   # summed after the group's last GEMM
+        for key in group:
+            outs[key] = flat[begin: begin + key[0]]
+            begin += key[0]
+            row_pairs[key] = (flat, group[-1])   # summed after the group's last GEMM
     # M-major.  Sharded, the large batches go first (their sums are the long pole) and row and
     # column shapes alternate (row, column, row, column, column: every sum has a GEMM to run
     # beside); with merged sums every prefill-sized row-parallel GEMM comes before the others.
@@ -647,9 +651,9 @@ def main() -> None:
         order = [(m, n, k) for m in m_order for (n, k) in NK_SHAPES]
     else:
         mixed = [rows_first[0], columns[0], rows_first[1]] + columns[1:]
-        if args.row_sum == "nccl_merged":
+        if args.row_sum in merged_order:
             large = [m for m in m_order if m > 256]
-            order = ([(m, *s) for m in large for s in rows_first] + [(m, *s) for m in large for s in columns]
+            order = (large_rows + [(m, *s) for m in large for s in columns]
                      + [(m, *s) for m in m_order if m <= 256 for s in mixed])
         else:
             order = [(m, *s) for m in m_order for s in mixed]
@@ -663,9 +667,9 @@ def main() -> None:
         out = mx.gemm_from_float(acts[key] if a is None else a, weight, out_dtype=torch.bfloat16,
                                  out=outs[key])
         if mode == "row" and world > 1:
-            pair = row_pairs.get(key[0])
+            pair = row_pairs.get(key)
             if pair is not None and key != pair[1]:
-                return out          # summed together with the batch size's other projection
+                return out          # summed together with the other outputs of its group
             computed = torch.cuda.Event()
             computed.record(torch.cuda.current_stream(device))
             reduce_stream.wait_event(computed)
@@ -801,9 +805,9 @@ def main() -> None:
                         sweep_peer.allreduce(outs[key])
                     elif big_peer is not None and key[0] % world == 0:
                         big_peer.allreduce_any(outs[key])
-                    elif key[0] in row_pairs:
-                        if key == row_pairs[key[0]][1]:
-                            dist.all_reduce(row_pairs[key[0]][0])
+                    elif key in row_pairs:
+                        if key == row_pairs[key][1]:
+                            dist.all_reduce(row_pairs[key][0])
                     else:
                         dist.all_reduce(outs[key])
 
