@@ -742,6 +742,24 @@ def main() -> None:
         mx.finalize_workspace_planning(device)
         run_sweep()
         stream.synchronize()
+        if world > 1 and parity is not None:
+            # The step's own summed outputs (grouped buffers, side stream) against the same
+            # GEMM summed by a plain all-reduce of its own: largest and smallest prefill
+            # batch of both row-parallel projections, and one decode batch (peer kernel).
+            worst = 0.0
+            for m in (max(M_VALUES), min(v for v in M_VALUES if v > 256), 16):
+                for shape in rows_first:
+                    key = (m, *shape)
+                    want = mx.gemm_from_float(acts[key], layers[shape][0], out_dtype=torch.bfloat16)
+                    dist.all_reduce(want)
+                    worst = max(worst, _rel(outs[key], want))
+            over_ranks = torch.tensor([worst], device=device)
+            dist.all_reduce(over_ranks, op=dist.ReduceOp.MAX)
+            worst = float(over_ranks.item())
+            parity["cases"]["sweep_row_sums"] = round(worst, 6)
+            parity["max_rel"] = max(parity["max_rel"], worst)
+            parity["ok"] = bool(parity["ok"] and worst <= 1e-2)
+            parity["limits"] += "; sweep_row_sums (the timed step's own summed outputs against GEMM + plain all-reduce) 1e-2"
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             run_sweep()
