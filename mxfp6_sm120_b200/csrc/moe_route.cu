@@ -6,7 +6,7 @@
 // lane after the last routed one): route_w6a8_kernel / route_w6a8_silu_mxfp8_kernel /
 // route_w6a8_reduce_kernel and the cooperative qwen35_w1_splitk / qwen35_w2_splitk kernels
 // (csrc/moe.cu:1306-1481, 1882-2286, 2689-2960, 2977-3270, 3272-3629; host entry points
-// :6713-7393).  Here that is two tcgen05 kernels built like the weight-streaming GEMM
+// :6713-7393).  Here that is three tcgen05 kernels built like the weight-streaming GEMM
 // (gemm_stream.cu): under half an SM's shared memory per CTA, programmatic launch, bounded
 // waits, cluster push reductions through distributed shared memory.
 //
@@ -22,6 +22,11 @@
 //       in lane order (csrc/moe.cu:3228-3265, 7972-7988): the bytes equal those of the
 //       store kernel followed by moe_reduce_array_kernel, and no routed output reaches
 //       global memory.
+//
+//   route_w1_front_kernel                the W1 (SwiGLU) kernel of the decode schedule with the
+//       layer's front end inside: every CTA runs the softmax top-k of its token and quantizes
+//       its K slice of the token's BF16 row into the shared-memory operand, so the schedule is
+//       two launches (moe_decode_layer) and depends on nothing but the layer's inputs.
 //
 // A route's activation is one row.  It is MMA operand B with N = 16 (row 0 real, rows 1..15
 // whatever follows it in memory or zero fill: their accumulator columns are never read).
