@@ -1102,32 +1102,46 @@ router_logits_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat
                      __nv_bfloat16* __restrict__ shared_gate, int batch, int k, int routed) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  __shared__ float warp_sums[8];
+  constexpr int kTokens = 8;  // tokens per pass over the gate row
+  __shared__ float warp_sums[kTokens][8];
   const int e = blockIdx.x;
   const __nv_bfloat16* row = e < routed ? gate + (int64_t)e * k
                                         : (shared_gate_row != nullptr ? shared_gate_row : gate + (int64_t)e * k);
-  for (int b = 0; b < batch; ++b) {
-    float acc = 0.0f;
+  // Per token the sum runs in one fixed order (a thread's strided elements, a shuffle tree, the
+  // warps in turn), whatever the batch size: a token's logits do not depend on its neighbours.
+  for (int b0 = 0; b0 < batch; b0 += kTokens) {
+    float acc[kTokens];
+#pragma unroll
+    for (int t = 0; t < kTokens; ++t) acc[t] = 0.0f;
     for (int i = threadIdx.x * 8; i < k; i += blockDim.x * 8) {
       const uint4 w = __ldg(reinterpret_cast<const uint4*>(row + i));
-      const uint4 x = __ldg(reinterpret_cast<const uint4*>(hidden + (int64_t)b * k + i));
       const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&w);
-      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 wf = __bfloat1622float2(wp[j]);
-        const float2 xf = __bfloat1622float2(xp[j]);
-        acc = fmaf(wf.x, xf.x, acc);
-        acc = fmaf(wf.y, xf.y, acc);
+      for (int t = 0; t < kTokens; ++t) {
+        if (b0 + t < batch) {
+          const uint4 x = __ldg(reinterpret_cast<const uint4*>(hidden + (int64_t)(b0 + t) * k + i));
+          const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 wf = __bfloat1622float2(wp[j]);
+            const float2 xf = __bfloat1622float2(xp[j]);
+            acc[t] = fmaf(wf.x, xf.x, acc[t]);
+            acc[t] = fmaf(wf.y, xf.y, acc[t]);
+          }
+        }
       }
     }
 #pragma unroll
-    for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
-    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = acc;
+    for (int t = 0; t < kTokens; ++t) {
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], d);
+      if ((threadIdx.x & 31) == 0) warp_sums[t][threadIdx.x >> 5] = acc[t];
+    }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < kTokens && b0 + (int)threadIdx.x < batch) {
+      const int b = b0 + (int)threadIdx.x;
       float total = 0.0f;
-      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) total += warp_sums[w];
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) total += warp_sums[threadIdx.x][w];
       if (e < routed) logits[(int64_t)b * routed + e] = __float2bfloat16_rn(total);
       else shared_gate[b] = __float2bfloat16_rn(total);
     }
