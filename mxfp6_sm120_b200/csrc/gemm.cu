@@ -1057,16 +1057,18 @@ int plan_w6a8(const GemmProblem& p, GemmPlan* plan) {
     } else if (rows <= 16) tn = 16;
     else if (rows <= 32) tn = 32;
     else if (rows <= 64) tn = 64;
-    else if (rows <= 96) {
-      // 65..96 rows: two 64-row tiles per feature tile (twice the tiles, double-buffered
-      // accumulators, no or a smaller cluster reduce) beat one 96-row tile while the weights,
-      // which are then read twice, stay in L2.  Measured at 96 rows: 12.0 against 15.2 us at
-      // 7168 x 5120, 9.2 against 13.5 us at 2048 x 5120, 13.3 against 13.7 us at 5120 x 6144;
+    else if (rows <= 128) {
+      // 65..128 rows: two 64-row tiles per feature tile (twice the tiles, double-buffered
+      // accumulators, no or a smaller cluster reduce) beat one 96- or 128-row tile while the
+      // weights, which are then read twice, stay in L2.  Measured at 96 rows: 12.0 against
+      // 15.2 us at 7168 x 5120, 9.2 against 13.5 us at 2048 x 5120, 13.3 against 13.7 us at
+      // 5120 x 6144; at 128 rows: 12.1 against 14.3, 10.5 against 14.1, 13.5 against 16.4 us.
       // 5120 x 17408 (67 MB of weights) and 34816 x 5120 (134 MB) keep the single tile.
       const int64_t weight_bytes = (int64_t)p.n * p.k / 4 * 3;
-      tn = (p.mode == kGemmStore && p.cluster_k <= 1 && p.splits <= 1 && weight_bytes <= (32ll << 20)) ? 64
-                                                                                                     : 96;
-    } else if (rows <= 128) tn = 128;
+      const bool two_tiles = p.mode == kGemmStore && p.cluster_k <= 1 && p.splits <= 1 &&
+                             weight_bytes <= (32ll << 20);
+      tn = two_tiles ? 64 : (rows <= 96 ? 96 : 128);
+    }
     else if (rows % 256 == 0 && p.k >= 12288) tn = 256;
     else tn = 192;
   }

@@ -24,7 +24,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 GEMM_REL_FRO = 1.0e-3
 NK = [(7168, 5120), (5120, 6144), (34816, 5120), (5120, 17408), (2048, 5120)]
-M_VALUES = [1, 8, 32, 64, 96, 512]
+M_VALUES = [1, 8, 32, 64, 96, 128, 512]
 
 
 def _expected_plan(m: int, n: int, k: int) -> dict:
@@ -34,11 +34,12 @@ def _expected_plan(m: int, n: int, k: int) -> dict:
         ck = min(8, 240 // n_tiles, k // 128) if split else 1
         return {"kernel": "stream", "tile_tokens": 16 if m <= 16 else 32 if m <= 32 else 64,
                 "cluster_k": max(ck, 1), "cta_pair": 0, "splits": 1}
-    if m <= 96:
-        # 65..96 rows: two 64-row tiles while the weights fit the L2, else one 96-row tile
-        tile = 64 if (m <= 64 or n * k * 3 // 4 <= 32 << 20) else 96
+    if m <= 128:
+        # 65..128 rows: two 64-row tiles while the weights fit the L2, else one 96- or 128-row
+        # tile (the 128-row tile has no cluster split)
+        tile = 64 if (m <= 64 or n * k * 3 // 4 <= 32 << 20) else 96 if m <= 96 else 128
         tiles = n_tiles * -(-m // tile)
-        ck = min(8, (148 - 16) // tiles, k // 128) if 2 * tiles <= 148 else 1
+        ck = min(8, (148 - 16) // tiles, k // 128) if (2 * tiles <= 148 and tile <= 96) else 1
         return {"kernel": "persistent", "tile_tokens": tile,
                 "cluster_k": ck if ck >= 2 else 1, "cta_pair": 0, "splits": 1}
     return {"kernel": "cta_pair", "cluster_k": 1, "cta_pair": 1, "splits": 1}
@@ -82,7 +83,7 @@ def test_default_plan_matches_oracle_on_sampled_columns(mx, weights, m, n, k):
 
     inner = torch.randint(130, n - 130, (6,), generator=torch.Generator().manual_seed(n + m))
     cols = torch.cat([torch.arange(0, 130), inner, torch.arange(n - 130, n)]).to(DEV)
-    rows = torch.arange(m) if m <= 96 else torch.tensor([0, 1, 127, 128, 191, 192, 255, 256, m - 1])
+    rows = torch.arange(m) if m <= 128 else torch.tensor([0, 1, 127, 128, 191, 192, 255, 256, m - 1])
     w_codes = mx.unpack_fp6(wgt.values, n, k)[cols].cpu().numpy()
     w_scales = mx.unpack_scales(wgt.scales, n, k)[cols].cpu().numpy()
     want = o.gemm_w6a8(a_codes[rows.numpy()], a_scales[rows.numpy()], w_codes, w_scales,
