@@ -563,6 +563,38 @@ def parity_check_sharded(mx, device, world: int, rank: int) -> dict:
             "limits": "row-parallel 1e-2, column-parallel 1e-3 (rel-Frobenius), layer 1 - cos 1e-3"}
 
 
+def plan_row_sums(row_sum: str, world: int):
+    """Host logic of the sharded sweep: the order of the (M, N, K) launches of a step and which
+    row-parallel outputs one NCCL all-reduce sums (``groups``: lists of launch keys whose
+    outputs share one buffer; the sum is issued after the LAST key of a group has run).
+
+    One GPU: M-major in the listed order, nothing to sum.  Sharded: large batches first (their
+    sums are the long pole) and row / column shapes alternating (row, column, row, column,
+    column: every sum has a GEMM to run beside); with merged sums every prefill-sized
+    row-parallel GEMM comes before all the others."""
+    if world == 1:
+        return [], [(m, n, k) for m in M_VALUES for (n, k) in NK_SHAPES]
+    m_order = sorted(M_VALUES, reverse=True)
+    rows_first = [s for s in NK_SHAPES if s in ROW_PARALLEL]
+    columns = [s for s in NK_SHAPES if s not in ROW_PARALLEL]
+    mixed = [rows_first[0], columns[0], rows_first[1]] + columns[1:]
+    large = [m for m in m_order if m > 256]
+    large_rows = [(m, *s) for m in large for s in rows_first]
+    groups = []
+    if row_sum == "nccl_pair":
+        groups = [[(m, *s) for s in rows_first] for m in m_order]
+    elif row_sum == "nccl_merged":
+        groups = [large_rows[: len(rows_first)], large_rows[len(rows_first):]]
+    elif row_sum == "nccl_early":
+        groups = [large_rows[:1], large_rows[1:]]
+    if row_sum in ("nccl_merged", "nccl_early"):
+        order = (large_rows + [(m, *s) for m in large for s in columns]
+                 + [(m, *s) for m in m_order if m <= 256 for s in mixed])
+    else:
+        order = [(m, *s) for m in m_order for s in mixed]
+    return groups, order
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -622,18 +654,8 @@ def main() -> None:
     # that two large all-reduces run beside every column-parallel GEMM of the step;
     # nccl_early = the same two all-reduces, the first one over the first GEMM's output alone
     # so that the sums start one GEMM into the step.
-    m_order = M_VALUES if world == 1 else sorted(M_VALUES, reverse=True)
     rows_first = [s for s in NK_SHAPES if s in ROW_PARALLEL]
-    columns = [s for s in NK_SHAPES if s not in ROW_PARALLEL]
-    merged_order = ("nccl_merged", "nccl_early")
-    large_rows = [(m, *s) for m in m_order if m > 256 for s in rows_first]
-    sum_groups = []
-    if world > 1 and args.row_sum == "nccl_pair":
-        sum_groups = [[(m, *s) for s in rows_first] for m in m_order]
-    elif world > 1 and args.row_sum == "nccl_merged":
-        sum_groups = [large_rows[: len(rows_first)], large_rows[len(rows_first):]]
-    elif world > 1 and args.row_sum == "nccl_early":
-        sum_groups = [large_rows[:1], large_rows[1:]]
+    sum_groups, order = plan_row_sums(args.row_sum, world)
     row_pairs = {}
     for group in sum_groups:
         width = layers[rows_first[0]][0].rows
@@ -644,20 +666,6 @@ def main() -> None:
             outs[key] = flat[begin: begin + key[0]]
             begin += key[0]
             row_pairs[key] = (flat, group[-1])   # summed after the group's last GEMM
-    # M-major.  Sharded, the large batches go first (their sums are the long pole) and row and
-    # column shapes alternate (row, column, row, column, column: every sum has a GEMM to run
-    # beside); with merged sums every prefill-sized row-parallel GEMM comes before the others.
-    if world == 1:
-        order = [(m, n, k) for m in m_order for (n, k) in NK_SHAPES]
-    else:
-        mixed = [rows_first[0], columns[0], rows_first[1]] + columns[1:]
-        if args.row_sum in merged_order:
-            large = [m for m in m_order if m > 256]
-            order = (large_rows + [(m, *s) for m in large for s in columns]
-                     + [(m, *s) for m in m_order if m <= 256 for s in mixed])
-        else:
-            order = [(m, *s) for m in m_order for s in mixed]
-
     # Prefill-sized row-parallel sums (NCCL, bandwidth bound) run on a side stream beside the
     # GEMMs of the following shapes; the sweep's shapes do not depend on one another.
     reduce_stream = torch.cuda.Stream(device) if world > 1 else None
