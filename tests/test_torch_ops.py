@@ -93,3 +93,26 @@ def test_format_and_moe_operators_through_the_dispatcher():
     mx.moe_reduce_array_out(want_reduced, want, weights, gate)
     assert torch.equal(reduced, want_reduced)
     assert mx.device_status() == 0
+
+
+def test_every_implementation_binds_the_arguments_of_its_schema():
+    """The dispatcher calls an implementation with ALL schema arguments, positionally (defaults
+    filled in).  Most operators are exercised on the GPU through the package functions, not
+    through the dispatcher, so the binding of each one is checked here without a GPU."""
+    import inspect
+
+    from mxfp6_sm120_b200 import torch_ops
+
+    for name, implementation in torch_ops._IMPLEMENTATIONS.items():
+        schema = getattr(torch.ops.mxfp6, name).default._schema
+        count = len(schema.arguments)
+        signature = inspect.signature(implementation)
+        try:
+            signature.bind(*([None] * count))
+        except TypeError as error:  # too many or too few positional parameters
+            raise AssertionError(f"{name}: implementation does not take {count} arguments: {error}")
+        # and it must not need more than the schema provides
+        required = [p for p in signature.parameters.values()
+                    if p.default is inspect.Parameter.empty
+                    and p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD)]
+        assert len(required) <= count, name
