@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define MXFP6_B200_ABI_VERSION 4
+#define MXFP6_B200_ABI_VERSION 5
 
 #define MXFP6_DTYPE_F16 0
 #define MXFP6_DTYPE_BF16 1
@@ -276,6 +276,21 @@ int mxfp6_moe_route(const uint8_t* activation_dev, const uint8_t* logical_scales
                     int local_experts, int64_t* expert_offsets_dev, int64_t* scale_offsets_dev,
                     int32_t* cursors_dev, uint8_t* permuted_dev, uint8_t* grouped_scales_dev,
                     int32_t* inverse_permutation_dev, int32_t* source_tokens_dev, void* stream);
+/* The same with the reference's include_shared flag (csrc/moe.cu:4449-4631, the shared_rows
+ * of its histogram and gather kernels): when set, local_experts counts one TRAILING shared
+ * expert that no id selects (ids and expert_map values must lie below local_experts - 1, others
+ * are dropped); its group holds one row per token, token t at row
+ * expert_offsets[local_experts - 1] + t, after all routed rows.  permuted then has
+ * T*k + T rows, the scale buffer one more padded group, and inverse_permutation still T*k
+ * entries (the shared rows are addressed through the offset, not through it). */
+int mxfp6_moe_route_shared(const uint8_t* activation_dev, const uint8_t* logical_scales_dev,
+                           const void* topk_ids_dev, int ids_are_int64, int64_t tokens, int topk,
+                           int hidden_size, const int32_t* expert_map_dev, int expert_map_size,
+                           int local_experts, int include_shared, int64_t* expert_offsets_dev,
+                           int64_t* scale_offsets_dev, int32_t* cursors_dev,
+                           uint8_t* permuted_dev, uint8_t* grouped_scales_dev,
+                           int32_t* inverse_permutation_dev, int32_t* source_tokens_dev,
+                           void* stream);
 /* torch.ops.mxfp6.qwen35_topk_quant_route_out (csrc/moe.cu:620-962, host :9716-10008):
  * mxfp6_moe_topk_quant followed by mxfp6_moe_route.  Batches of at most 8 tokens
  * (and tokens * topk <= 1024) run as ONE single-CTA kernel; larger ones as three. */

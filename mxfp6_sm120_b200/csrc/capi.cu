@@ -65,7 +65,7 @@ int pack_grouped_scales(const uint8_t*, const int64_t*, const int64_t*, int, int
 int moe_topk_quant(const void*, const void*, int64_t, int, int, int, int, uint8_t*, uint8_t*,
                    uint8_t*, float*, int32_t*, cudaStream_t);
 int moe_route(const uint8_t*, const uint8_t*, const void*, int, int64_t, int, int, const int32_t*,
-              int, int, int64_t*, int64_t*, int32_t*, uint8_t*, uint8_t*, int32_t*, int32_t*,
+              int, int, int, int64_t*, int64_t*, int32_t*, uint8_t*, uint8_t*, int32_t*, int32_t*,
               cudaStream_t);
 int moe_topk_quant_route(const void*, const void*, int64_t, int, int, int, int, uint8_t*, uint8_t*,
                          uint8_t*, float*, int32_t*, const int32_t*, int, int, int64_t*, int64_t*,
@@ -674,9 +674,22 @@ int mxfp6_moe_route(const uint8_t* activation, const uint8_t* logical_scales, co
                     uint8_t* permuted, uint8_t* grouped_scales, int32_t* inverse_permutation,
                     int32_t* source_tokens, void* stream) {
   return moe_route(activation, logical_scales, topk_ids, ids_are_int64, tokens, topk, hidden_size,
-                   expert_map, expert_map_size, local_experts, expert_offsets, scale_offsets,
+                   expert_map, expert_map_size, local_experts, 0, expert_offsets, scale_offsets,
                    cursors, permuted, grouped_scales, inverse_permutation, source_tokens,
                    static_cast<cudaStream_t>(stream));
+}
+
+int mxfp6_moe_route_shared(const uint8_t* activation, const uint8_t* logical_scales,
+                           const void* topk_ids, int ids_are_int64, int64_t tokens, int topk,
+                           int hidden_size, const int32_t* expert_map, int expert_map_size,
+                           int local_experts, int include_shared, int64_t* expert_offsets,
+                           int64_t* scale_offsets, int32_t* cursors, uint8_t* permuted,
+                           uint8_t* grouped_scales, int32_t* inverse_permutation,
+                           int32_t* source_tokens, void* stream) {
+  return moe_route(activation, logical_scales, topk_ids, ids_are_int64, tokens, topk, hidden_size,
+                   expert_map, expert_map_size, local_experts, include_shared ? 1 : 0,
+                   expert_offsets, scale_offsets, cursors, permuted, grouped_scales,
+                   inverse_permutation, source_tokens, static_cast<cudaStream_t>(stream));
 }
 
 int mxfp6_moe_topk_quant_route(const void* hidden, const void* logits, int64_t tokens,

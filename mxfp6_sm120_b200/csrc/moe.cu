@@ -163,23 +163,28 @@ __device__ __forceinline__ int local_expert(int64_t global, const int32_t* exper
   return (local >= 0 && local < local_experts) ? local : -1;
 }
 
-// Single CTA: histogram of the routed expert ids, exclusive prefix sums.
+// Single CTA: histogram of the routed expert ids, exclusive prefix sums.  With shared_rows > 0
+// the last of the local_experts groups is the always-hit shared expert: no id selects it and
+// it holds shared_rows rows (one per token), as in the reference's histogram
+// (csrc/moe.cu:4486-4571).
 template <class Id>
 __global__ void __launch_bounds__(1024)
 route_count_kernel(const Id* __restrict__ topk_ids, int64_t routes,
                    const int32_t* __restrict__ expert_map, int map_size, int local_experts,
-                   int64_t* __restrict__ expert_offsets, int64_t* __restrict__ scale_offsets,
-                   int32_t* __restrict__ cursors) {
+                   int shared_rows, int64_t* __restrict__ expert_offsets,
+                   int64_t* __restrict__ scale_offsets, int32_t* __restrict__ cursors) {
   __shared__ int counts[kMaxExperts];
   __shared__ int warp_sums[2][32];
   const int tid = threadIdx.x;
   for (int e = tid; e < kMaxExperts; e += blockDim.x) counts[e] = 0;
   __syncthreads();
+  const int routed_experts = local_experts - (shared_rows > 0 ? 1 : 0);
   for (int64_t i = tid; i < routes; i += blockDim.x) {
     const int e = local_expert(static_cast<int64_t>(topk_ids[i]), expert_map, map_size,
-                               local_experts);
+                               routed_experts);
     if (e >= 0) atomicAdd(&counts[e], 1);
   }
+  if (shared_rows > 0 && tid == 0) counts[local_experts - 1] = shared_rows;  // no id reaches it
   __syncthreads();
   // Block-wide inclusive scans (one expert per thread) of counts and padded counts.
   const int c = tid < local_experts ? counts[tid] : 0;
@@ -228,14 +233,16 @@ route_count_kernel(const Id* __restrict__ topk_ids, int64_t routes,
   }
 }
 
-// One warp per route: claim a row of its expert, copy the MXFP8 row and its scales.
+// One warp per route: claim a row of its expert, copy the MXFP8 row and its scales.  Warps
+// routes .. routes + shared_rows - 1 fill the trailing shared group: token t is its row t, and
+// the inverse permutation (routed routes only) has no entry for it.
 template <class Id>
 __global__ void __launch_bounds__(256)
 route_scatter_kernel(const uint8_t* __restrict__ activation,
                      const uint8_t* __restrict__ logical_scales, const Id* __restrict__ topk_ids,
                      int64_t routes, int topk, int hidden_size,
                      const int32_t* __restrict__ expert_map, int map_size, int local_experts,
-                     const int64_t* __restrict__ expert_offsets,
+                     int shared_rows, const int64_t* __restrict__ expert_offsets,
                      const int64_t* __restrict__ scale_offsets, int32_t* __restrict__ cursors,
                      uint8_t* __restrict__ permuted, uint8_t* __restrict__ grouped_scales,
                      int32_t* __restrict__ inverse_permutation,
@@ -244,18 +251,27 @@ route_scatter_kernel(const uint8_t* __restrict__ activation,
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int64_t route = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (route >= routes) return;
-  const int e = local_expert(static_cast<int64_t>(topk_ids[route]), expert_map, map_size,
-                             local_experts);
-  if (e < 0) {
-    if (lane == 0) inverse_permutation[route] = -1;  // dropped: the reducer skips it
-    return;
+  if (route >= routes + shared_rows) return;
+  const bool shared = route >= routes;
+  int e, local = 0;
+  int64_t token;
+  if (shared) {
+    e = local_experts - 1;
+    token = route - routes;
+    local = static_cast<int>(token);
+    if (lane == 0) atomicAdd(&cursors[e], 1);  // the cursors end as the group sizes
+  } else {
+    e = local_expert(static_cast<int64_t>(topk_ids[route]), expert_map, map_size,
+                     local_experts - (shared_rows > 0 ? 1 : 0));
+    if (e < 0) {
+      if (lane == 0) inverse_permutation[route] = -1;  // dropped: the reducer skips it
+      return;
+    }
+    if (lane == 0) local = atomicAdd(&cursors[e], 1);
+    local = __shfl_sync(0xffffffffu, local, 0);
+    token = route / topk;
   }
-  int local = 0;
-  if (lane == 0) local = atomicAdd(&cursors[e], 1);
-  local = __shfl_sync(0xffffffffu, local, 0);
   const int64_t row = expert_offsets[e] + local;
-  const int64_t token = route / topk;
   if (permuted != nullptr) {
     const uint4* src = reinterpret_cast<const uint4*>(activation + token * hidden_size);
     uint4* dst = reinterpret_cast<uint4*>(permuted + row * hidden_size);
@@ -289,7 +305,7 @@ route_scatter_kernel(const uint8_t* __restrict__ activation,
     }
   }
   if (lane == 0) {
-    inverse_permutation[route] = static_cast<int32_t>(row);
+    if (!shared) inverse_permutation[route] = static_cast<int32_t>(row);
     if (source_tokens != nullptr) source_tokens[row] = static_cast<int32_t>(token);
   }
 }
@@ -662,12 +678,14 @@ int moe_topk_quant(const void* hidden, const void* logits, int64_t tokens, int h
 
 int moe_route(const uint8_t* activation, const uint8_t* logical_scales, const void* topk_ids,
               int ids_are_int64, int64_t tokens, int topk, int hidden_size,
-              const int32_t* expert_map, int map_size, int local_experts,
+              const int32_t* expert_map, int map_size, int local_experts, int include_shared,
               int64_t* expert_offsets, int64_t* scale_offsets, int32_t* cursors,
               uint8_t* permuted, uint8_t* grouped_scales, int32_t* inverse_permutation,
               int32_t* source_tokens, cudaStream_t stream) {
   MX_REQUIRE(tokens > 0 && topk > 0, "tokens and topk must be positive");
-  MX_REQUIRE(local_experts > 0 && local_experts <= kMaxExperts, "local_experts must be in [1, %d]",
+  MX_REQUIRE(local_experts > (include_shared ? 1 : 0) && local_experts <= kMaxExperts,
+             "local_experts must be in [1, %d] and count one trailing shared expert when "
+             "include_shared is set",
              kMaxExperts);
   MX_REQUIRE(hidden_size > 0 && hidden_size % kScaleVec == 0 && hidden_size % 16 == 0,
              "hidden size must be a multiple of 32");
@@ -677,25 +695,27 @@ int moe_route(const uint8_t* activation, const uint8_t* logical_scales, const vo
   MX_REQUIRE(permuted == nullptr || (activation != nullptr && aligned16(activation) && aligned16(permuted)),
              "activation / permuted rows must be 16-byte aligned");
   const int64_t routes = tokens * topk;
-  const unsigned scatter_grid = (unsigned)((routes + 7) / 8);
+  MX_REQUIRE(routes + tokens <= INT32_MAX, "routed and shared rows must fit int32");
+  const int shared_rows = include_shared ? static_cast<int>(tokens) : 0;
+  const unsigned scatter_grid = (unsigned)((routes + shared_rows + 7) / 8);
   if (ids_are_int64) {
     const int64_t* ids = static_cast<const int64_t*>(topk_ids);
     route_count_kernel<int64_t><<<1, 1024, 0, stream>>>(ids, routes, expert_map, map_size,
-                                                        local_experts, expert_offsets,
+                                                        local_experts, shared_rows, expert_offsets,
                                                         scale_offsets, cursors);
     route_scatter_kernel<int64_t><<<scatter_grid, 256, 0, stream>>>(
         activation, logical_scales, ids, routes, topk, hidden_size, expert_map, map_size,
-        local_experts, expert_offsets, scale_offsets, cursors, permuted, grouped_scales,
-        inverse_permutation, source_tokens);
+        local_experts, shared_rows, expert_offsets, scale_offsets, cursors, permuted,
+        grouped_scales, inverse_permutation, source_tokens);
   } else {
     const int32_t* ids = static_cast<const int32_t*>(topk_ids);
     route_count_kernel<int32_t><<<1, 1024, 0, stream>>>(ids, routes, expert_map, map_size,
-                                                        local_experts, expert_offsets,
+                                                        local_experts, shared_rows, expert_offsets,
                                                         scale_offsets, cursors);
     route_scatter_kernel<int32_t><<<scatter_grid, 256, 0, stream>>>(
         activation, logical_scales, ids, routes, topk, hidden_size, expert_map, map_size,
-        local_experts, expert_offsets, scale_offsets, cursors, permuted, grouped_scales,
-        inverse_permutation, source_tokens);
+        local_experts, shared_rows, expert_offsets, scale_offsets, cursors, permuted,
+        grouped_scales, inverse_permutation, source_tokens);
   }
   MX_CUDA(cudaGetLastError());
   return kOk;
@@ -719,8 +739,8 @@ int moe_topk_quant_route(const void* hidden, const void* logits, int64_t tokens,
                                 stream))
       return rc;
     return moe_route(quantized, logical_scales, topk_ids, 0, tokens, topk, hidden_size, expert_map,
-                     map_size, local_experts, expert_offsets, scale_offsets, cursors, permuted,
-                     grouped_scales, inverse_permutation, source_tokens, stream);
+                     map_size, local_experts, /*include_shared=*/0, expert_offsets, scale_offsets,
+                     cursors, permuted, grouped_scales, inverse_permutation, source_tokens, stream);
   }
   MX_REQUIRE(hidden && logits && quantized && logical_scales && topk_weights && topk_ids &&
                  expert_offsets && scale_offsets && permuted && grouped_scales &&

@@ -172,15 +172,16 @@ def silu_and_mul_mxfp8_grouped_out(
 
 
 def _route_raw(activation, logical_scales, topk_ids, expert_map, local_experts, permuted,
-               grouped_scales, cursors, expert_offsets, scale_offsets, inverse, source_tokens):
+               grouped_scales, cursors, expert_offsets, scale_offsets, inverse, source_tokens,
+               include_shared=False):
     tokens, hidden = (int(v) for v in activation.shape)
     with torch.cuda.device(activation.device):
         check(
-            library().mxfp6_moe_route(
+            library().mxfp6_moe_route_shared(
                 _as_u8(activation).data_ptr(), logical_scales.data_ptr(), topk_ids.data_ptr(),
                 int(topk_ids.dtype == torch.int64), tokens, int(topk_ids.shape[1]), hidden,
                 _ptr(expert_map), 0 if expert_map is None else expert_map.numel(), local_experts,
-                expert_offsets.data_ptr(), scale_offsets.data_ptr(), cursors.data_ptr(),
+                int(bool(include_shared)), expert_offsets.data_ptr(), scale_offsets.data_ptr(), cursors.data_ptr(),
                 None if permuted is None else _as_u8(permuted).data_ptr(),
                 grouped_scales.data_ptr(), inverse.data_ptr(), _ptr(source_tokens),
                 _stream(activation.device),
@@ -230,24 +231,32 @@ def route_mxfp8_out(
 
     Returns ``(grouped_scales, expert_offsets, scale_offsets, inverse_permutation)``.
     ``expert_map`` (global id -> local id or -1) drops routes of experts that live
-    on other ranks; their ``inverse_permutation`` entries are -1.
+    on other ranks; their ``inverse_permutation`` entries are -1.  With ``include_shared``
+    ``local_experts`` counts one trailing shared expert: its group holds every token once, in
+    token order, after the routed rows (``permuted_activation`` then has ``M*topk + M`` rows;
+    ``inverse_permutation`` keeps ``M*topk`` entries), as in the reference
+    (python/mxfp6/ops.py:694-774, csrc/moe.cu:4449-4631).
     """
     _check_route_inputs(activation, logical_scales, topk_ids)
-    if include_shared:
-        raise ValueError("include_shared is not supported: run the shared expert as a dense GEMM")
+    include_shared = bool(include_shared)
     routes = activation.shape[0] * topk_ids.shape[1]
+    total_rows = routes + (activation.shape[0] if include_shared else 0)
     if (
         permuted_activation.device != activation.device
         or permuted_activation.dtype != activation.dtype
-        or tuple(permuted_activation.shape) != (routes, activation.shape[1])
+        or tuple(permuted_activation.shape) != (total_rows, activation.shape[1])
         or not permuted_activation.is_contiguous()
     ):
         raise ValueError(
-            f"permuted_activation must be contiguous {(routes, activation.shape[1])} "
+            f"permuted_activation must be contiguous {(total_rows, activation.shape[1])} "
             "with the activation dtype and device"
         )
-    if not 1 <= local_experts <= 1024:
-        raise ValueError("local_experts must be in [1, 1024]")
+    minimum_experts = 2 if include_shared else 1
+    if not minimum_experts <= local_experts <= 1024:
+        raise ValueError(
+            f"local_experts must be in [{minimum_experts}, 1024] and include one trailing "
+            "shared expert when include_shared is true"
+        )
     if expert_map is not None and (
         expert_map.device != activation.device
         or expert_map.dtype != torch.int32
@@ -260,7 +269,8 @@ def route_mxfp8_out(
     device = activation.device
     groups = (activation.shape[1] // SCALE_VECTOR_SIZE + 3) // 4 * 4
     grouped_scales = torch.full(
-        (grouped_scale_rows(routes, local_experts) * groups,), 0x7F, dtype=torch.uint8, device=device
+        (grouped_scale_rows(total_rows, local_experts) * groups,), 0x7F, dtype=torch.uint8,
+        device=device,
     )
     expert_offsets = torch.empty(local_experts + 1, dtype=torch.int64, device=device)
     scale_offsets = torch.empty(local_experts + 1, dtype=torch.int64, device=device)
@@ -268,7 +278,7 @@ def route_mxfp8_out(
     inverse = torch.empty(routes, dtype=torch.int32, device=device)
     _route_raw(activation, logical_scales, topk_ids, expert_map, local_experts,
                permuted_activation, grouped_scales, cursors, expert_offsets, scale_offsets,
-               inverse, None)
+               inverse, None, include_shared)
     return grouped_scales, expert_offsets, scale_offsets, inverse
 
 
@@ -286,16 +296,43 @@ def qwen35_route_mxfp8_out(
     source_tokens: torch.Tensor | None = None,
     expert_map: torch.Tensor | None = None,
 ) -> None:
-    """Route MXFP8 rows into preallocated grouped buffers (allocation-free)."""
+    """Route MXFP8 rows into preallocated grouped buffers (allocation-free).
+
+    ``expert_offsets`` / ``scale_offsets`` have one entry per local expert plus one; with
+    ``include_shared`` the last expert is the shared one (python/mxfp6/ops.py:776-870), so the
+    buffers are sized for ``M*topk + M`` rows and one more padded scale group.
+    """
     _check_route_inputs(activation, logical_scales, topk_ids)
-    if include_shared:
-        raise ValueError("include_shared is not supported: run the shared expert as a dense GEMM")
+    include_shared = bool(include_shared)
+    local_experts = expert_offsets.numel() - 1
+    tokens, hidden = (int(v) for v in activation.shape)
+    routes = tokens * int(topk_ids.shape[1])
+    total_rows = routes + (tokens if include_shared else 0)
+    if local_experts < (2 if include_shared else 1):
+        raise ValueError("expert_offsets must hold one entry per local expert plus one, the "
+                         "trailing shared expert included when include_shared is true")
+    # capacities, not exact shapes: a workspace may hold larger buffers than one call needs
+    groups = (hidden // SCALE_VECTOR_SIZE + 3) // 4 * 4
+    active_experts = min(routes, local_experts - int(include_shared)) + int(include_shared)
+    for tensor, dtype, need, name in (
+        (expert_cursors, torch.int32, local_experts, "expert_cursors"),
+        (scale_offsets, torch.int64, local_experts + 1, "scale_offsets"),
+        (inverse_permutation, torch.int32, routes, "inverse_permutation"),
+        (packed_scales, torch.uint8, (total_rows + active_experts * 127) * groups, "packed_scales"),
+    ) + (() if source_tokens is None else ((source_tokens, torch.int32, total_rows, "source_tokens"),)) + (
+        () if permuted_activation is None
+        else ((permuted_activation, activation.dtype, total_rows * hidden, "permuted_activation"),)
+    ):
+        same_type = tensor.dtype == dtype or (
+            name == "permuted_activation" and tensor.dtype in (torch.uint8, torch.float8_e4m3fn))
+        if (tensor.device != activation.device or not same_type
+                or tensor.numel() < need or not tensor.is_contiguous()):
+            raise ValueError(f"{name} must be contiguous CUDA {dtype} with at least {need} values")
     _require_sm100(activation.device)
     load_library()
-    local_experts = expert_offsets.numel() - 1
     _route_raw(activation, logical_scales, topk_ids, expert_map, local_experts,
                permuted_activation, packed_scales, expert_cursors, expert_offsets, scale_offsets,
-               inverse_permutation, source_tokens)
+               inverse_permutation, source_tokens, include_shared)
 
 
 def qwen35_topk_quant_out(

@@ -94,6 +94,91 @@ def test_routing_invariants_and_expert_map(mx):
     assert bool((loc_inv.cpu()[~dropped] >= 0).all())
 
 
+@pytest.mark.parametrize("tokens,topk,hidden,routed_experts", [(5, 3, 128, 4), (70, 8, 512, 24)])
+def test_shared_group_routing_and_reduce(mx, tokens, topk, hidden, routed_experts):
+    """``include_shared``: one trailing always-hit group, token t at its row t, and the
+    reduction that takes the shared rows from the tail of the routed output (the case of the
+    reference's tests/test_ops.py:1309-1381, plus a batch that spans several scale atoms)."""
+    gen = _cpu_gen(17)
+    act = torch.randint(0, 0x78, (tokens, hidden), generator=gen, dtype=torch.uint8)
+    scales = torch.randint(120, 130, (tokens, hidden // 32), generator=gen, dtype=torch.uint8)
+    ids = torch.stack([torch.randperm(routed_experts, generator=gen)[:topk]
+                       for _ in range(tokens)]).to(torch.int32)
+    routes = tokens * topk
+    experts = routed_experts + 1
+    permuted = torch.zeros((routes + tokens, hidden), dtype=torch.uint8, device=DEV)
+    grouped, offsets, soff, inverse = mx.route_mxfp8_out(
+        act.to(DEV), scales.to(DEV), ids.to(DEV), None, experts, permuted, include_shared=True)
+    counts = torch.bincount(ids.flatten().long(), minlength=routed_experts).tolist() + [tokens]
+    want_offsets = [0, *np.cumsum(counts).tolist()]
+    assert offsets.cpu().tolist() == want_offsets
+    assert soff.cpu().tolist() == o.grouped_scale_offsets(np.asarray(want_offsets)).tolist()
+    shared_start = int(offsets[routed_experts])
+    assert shared_start == routes and int(offsets[-1]) == routes + tokens
+    rows = permuted.cpu()
+    assert torch.equal(rows[shared_start:], act)  # token order
+    inv = inverse.cpu().long()
+    assert tuple(inv.shape) == (routes,) and sorted(inv.tolist()) == list(range(routes))
+    flat = ids.flatten().long()
+    for route in range(routes):
+        e, row = int(flat[route]), int(inv[route])
+        assert want_offsets[e] <= row < want_offsets[e + 1]
+        assert torch.equal(rows[row], act[route // topk])
+    # the scales of all rows, shared ones included, in the grouped packed layout
+    logical_permuted = torch.empty((routes + tokens, hidden // 32), dtype=torch.uint8)
+    logical_permuted[inv] = scales.repeat_interleave(topk, dim=0)
+    logical_permuted[shared_start:] = scales
+    want, _ = o.pack_grouped_scales(logical_permuted.numpy(), np.asarray(want_offsets))
+    got = grouped.cpu().numpy()[: want.size]
+    written = want != 0x7F
+    assert np.array_equal(got[written], want[written])
+
+    # the preallocated form writes the same offsets and rows, and the row -> token list
+    cursors = torch.empty(experts, dtype=torch.int32, device=DEV)
+    offsets2 = torch.empty(experts + 1, dtype=torch.int64, device=DEV)
+    soff2 = torch.empty(experts + 1, dtype=torch.int64, device=DEV)
+    inverse2 = torch.empty(routes, dtype=torch.int32, device=DEV)
+    permuted2 = torch.zeros_like(permuted)
+    packed2 = torch.full_like(grouped, 0x7F)
+    source_tokens = torch.full((routes + tokens,), -7, dtype=torch.int32, device=DEV)
+    mx.qwen35_route_mxfp8_out(act.to(DEV), scales.to(DEV), ids.to(DEV), permuted2, packed2, cursors,
+                              offsets2, soff2, inverse2, include_shared=True,
+                              source_tokens=source_tokens)
+    assert offsets2.cpu().tolist() == want_offsets and soff2.cpu().tolist() == soff.cpu().tolist()
+    assert cursors.cpu().tolist() == counts
+    src = source_tokens.cpu().long()
+    assert src[shared_start:].tolist() == list(range(tokens))
+    assert torch.equal(permuted2.cpu(), act[src])
+    inv2 = inverse2.cpu().long()
+    assert torch.equal(src[inv2], torch.arange(routes) // topk)
+
+    # the final reduction with the shared rows taken from the tail of the routed output
+    routed_output = torch.randn((routes + tokens, hidden), generator=gen).to(torch.bfloat16)
+    weights = torch.rand((tokens, topk), generator=gen)
+    weights /= weights.sum(dim=1, keepdim=True)
+    gate = torch.randn((tokens, 1), generator=gen).to(torch.bfloat16)
+    out = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=DEV)
+    routed_dev = routed_output.to(DEV)
+    mx.moe_reduce_out(out, routed_dev, weights.to(DEV), inverse,
+                      routed_dev[shared_start: shared_start + tokens], gate.to(DEV))
+    want_out = o.moe_reduce(routed_output, weights, inverse.cpu(), routed_output[shared_start:], gate)
+    assert _rel_fro(out, want_out) <= 1e-3  # FP32 fused multiply-adds against the oracle's separate ones
+    assert float((out.float().cpu() - want_out.float()).abs().max()) <= 2.0**-7 * float(want_out.float().abs().max())
+    # reading the shared rows in place equals reading a separate copy of them, bit for bit
+    out_copy = torch.empty_like(out)
+    mx.moe_reduce_out(out_copy, routed_dev, weights.to(DEV), inverse,
+                      routed_dev[shared_start: shared_start + tokens].clone(), gate.to(DEV))
+    assert torch.equal(out, out_copy)
+
+    # without the flag the trailing expert is an ordinary one, and the flag needs two experts
+    with pytest.raises(ValueError):
+        mx.route_mxfp8_out(act.to(DEV), scales.to(DEV), ids.to(DEV), None, 1, permuted,
+                           include_shared=True)
+    with pytest.raises(ValueError):
+        mx.route_mxfp8_out(act.to(DEV), scales.to(DEV), ids.to(DEV), None, experts,
+                           permuted[:routes], include_shared=True)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_silu_and_mul_variants_bit_exact(mx, dtype):
     rows, inter = 37, 256
