@@ -358,6 +358,44 @@ def test_moe_layer_small_shape(mx, tokens):
     assert _rel_fro(out, want) <= 2e-2
 
 
+@pytest.mark.parametrize("tokens", [3, 40, 300])
+def test_shared_expert_as_trailing_group_matches_the_layer(mx, tokens):
+    """The reference's other way to run the shared expert: as group E of the grouped GEMMs
+    (benchmarks/benchmark_qwen35_moe_layer.py:700-760) - ``include_shared`` routing, W1 and W2
+    over E+1 weight matrices, and the reduction reading the shared rows from the tail of the
+    routed output.  Same layer, so it must agree with the dense shared-expert path and the oracle."""
+    shape = mx.MoeShape(hidden=512, intermediate=256, experts=32, topk=4)
+    case = _layer_case(mx, tokens, shape)
+    w1, w2, sw1, sw2, hidden, logits, gate = case
+    out, ws, _ = _run_layer(mx, shape, *case)
+    e, i, h, k = shape.experts, shape.intermediate, shape.hidden, shape.topk
+    w1_all = torch.cat([w1.values.reshape(-1), sw1.values.reshape(-1)]).view(e + 1, 2 * i, h * 3 // 4)
+    w1s_all = torch.cat([w1.scales.reshape(-1), sw1.scales.reshape(-1)]).view(e + 1, -1)
+    w2_all = torch.cat([w2.values.reshape(-1), sw2.values.reshape(-1)]).view(e + 1, h, i * 3 // 4)
+    w2s_all = torch.cat([w2.scales.reshape(-1), sw2.scales.reshape(-1)]).view(e + 1, -1)
+    routes = tokens * k
+    rows = routes + tokens
+    permuted = torch.empty((rows, h), dtype=torch.uint8, device=DEV)
+    grouped, offsets, soff, inverse = mx.route_mxfp8_out(
+        ws.quantized, ws.input_scales, ws.topk_ids, None, e + 1, permuted, include_shared=True)
+    assert int(offsets[e]) == routes and int(offsets[e + 1]) == rows
+    activated = torch.empty((rows, i), dtype=torch.uint8, device=DEV)
+    activated_scales = torch.full((int(soff[-1]) * ((i // 32 + 3) // 4 * 4),), 0x7F,
+                                  dtype=torch.uint8, device=DEV)
+    mx.qwen35_grouped_w1_silu_mxfp8_out(activated, activated_scales, permuted, grouped, w1_all,
+                                        w1s_all, offsets, soff)
+    routed_output = torch.empty((rows, h), dtype=torch.bfloat16, device=DEV)
+    mx.grouped_gemm_w6a8_out(routed_output, activated, activated_scales, w2_all, w2s_all, offsets, soff)
+    got = torch.empty_like(out)
+    mx.moe_reduce_out(got, routed_output, ws.topk_weights, inverse, routed_output[routes:],
+                      gate.to(DEV))
+    assert _rel_fro(got, out) <= 5e-3  # the dense path may split K; the grouped one does not
+    want, _ = _oracle_layer(mx, shape, *case, ids=ws.topk_ids.cpu())
+    cos = torch.nn.functional.cosine_similarity(got.float().cpu().flatten(), want.float().flatten(), dim=0)
+    assert float(cos) >= 0.999
+    assert _rel_fro(got, want) <= 2e-2
+
+
 @pytest.mark.parametrize("tokens", [1, 2, 4, 8, 16, 24, 32, 64, 96])
 def test_moe_layer_named_config_and_graph_replay(mx, tokens):
     """Hidden 2048, 256 experts, top-8, intermediate 512, shared expert with sigmoid gate:
