@@ -358,6 +358,49 @@ def test_moe_layer_small_shape(mx, tokens):
     assert _rel_fro(out, want) <= 2e-2
 
 
+@pytest.mark.parametrize("tokens", [5, 40])
+def test_preallocated_routing_on_workspace_buffers(mx, tokens):
+    """``qwen35_route_mxfp8_out`` on the buffers a workspace allocates: with the caller's ids
+    (``qwen35_grouped_moe_out``) and with an expert map over a workspace sized for the local
+    experts only, the way the expert-parallel layer calls it."""
+    shape = mx.MoeShape(hidden=512, intermediate=256, experts=32, topk=4)
+    case = _layer_case(mx, tokens, shape)
+    w1, w2, sw1, sw2, hidden, logits, gate = case
+    _, ws0, _ = _run_layer(mx, shape, *case)
+    e, i, h, k = shape.experts, shape.intermediate, shape.hidden, shape.topk
+    want = torch.empty((tokens, h), dtype=torch.bfloat16, device=DEV)
+    mx.moe_reduce_out(want, ws0.routed_output, ws0.topk_weights, ws0.inverse_permutation)
+    ws1 = mx.Qwen35GroupedWorkspace.allocate(tokens, DEV, shape)
+    got = torch.empty_like(want)
+    mx.qwen35_grouped_moe_out(ws1, got, hidden.to(DEV), w1.values.view(e, 2 * i, h * 3 // 4), w1.scales,
+                              w2.values.view(e, h, i * 3 // 4), w2.scales, ws0.topk_weights,
+                              ws0.topk_ids)
+    assert torch.equal(got, want)  # a row's result does not depend on where it sits in its group
+
+    local = 8
+    expert_map = torch.full((e,), -1, dtype=torch.int32)
+    expert_map[8:16] = torch.arange(local, dtype=torch.int32)
+    ws2 = mx.Qwen35GroupedWorkspace.allocate(tokens, DEV, mx.MoeShape(h, i, local, k))
+    mx.qwen35_route_mxfp8_out(ws0.quantized, ws0.input_scales, ws0.topk_ids, ws2.permuted,
+                              ws2.grouped_input_scales, ws2.expert_cursors, ws2.expert_offsets,
+                              ws2.scale_offsets, ws2.inverse_permutation,
+                              source_tokens=ws2.source_tokens, expert_map=expert_map.to(DEV))
+    flat = ws0.topk_ids.cpu().flatten().long()
+    counts = torch.bincount(flat, minlength=e)[8:16]
+    assert ws2.expert_offsets.cpu().tolist() == [0, *torch.cumsum(counts, 0).tolist()]
+    inv = ws2.inverse_permutation.cpu()
+    is_local = (flat >= 8) & (flat < 16)
+    assert bool((inv[~is_local] == -1).all()) and bool((inv[is_local] >= 0).all())
+    kept = inv[is_local].long()
+    assert torch.equal(ws2.source_tokens.cpu()[kept].long(), torch.nonzero(is_local).flatten() // k)
+    assert torch.equal(ws2.permuted.cpu()[kept], ws0.quantized.cpu()[torch.nonzero(is_local).flatten() // k])
+    # a scale buffer that is too small is refused on the host, before any launch
+    with pytest.raises(ValueError):
+        mx.qwen35_route_mxfp8_out(ws0.quantized, ws0.input_scales, ws0.topk_ids, ws2.permuted,
+                                  ws2.grouped_input_scales[:64], ws2.expert_cursors,
+                                  ws2.expert_offsets, ws2.scale_offsets, ws2.inverse_permutation)
+
+
 @pytest.mark.parametrize("tokens", [3, 40, 300])
 def test_shared_expert_as_trailing_group_matches_the_layer(mx, tokens):
     """The reference's other way to run the shared expert: as group E of the grouped GEMMs
